@@ -1,0 +1,481 @@
+"""Model packer: builds the operator graph of a served model and writes it, with
+its weights, as one binary "pack" file that the job adapters load from
+``$LLIS_MODELS_DIR`` at ``full_init`` time.
+
+This is the counterpart of the reference's offline compile step
+(sosp23_artifact/setup/onnx2tvm.py:14-29 turns an ONNX file into
+``<model>-cuda_llis-pack.so``, which jobs/tvm_mnist/tvm_mnist.cpp:24-33 loads).
+There is no code generation here: the pack is a flat table of operators that the
+C++ graph executor maps onto hand-written sm_100a kernels.
+
+Pack layout (little endian):
+  header   64 B : magic "PB2PACK\\0", u32 version, n_tensors, n_ops,
+                  input_tensor, output_tensor, precision (0 fp32, 1 bf16),
+                  u64 weight_floats, char name[24]
+  tensors  n_tensors x 16 B : u32 C, H, W, reserved        (batch is always 1)
+  ops      n_ops x 96 B     : 24 x u32, see OP_FIELDS
+  names    n_ops x 64 B     : NUL padded layer names
+  weights  weight_floats x f32: conv weights OIHW, dense [out][in], biases [out]
+
+Boundary layouts are the reference's: NCHW fp32 input, fp32 output vector.  A
+concatenation is expressed by several producers writing channel slices
+(``out_c_off``) of one tensor.  Weights are He-normal N(0, 2/fan_in) from a
+seeded generator; batch-norm layers are folded into the preceding convolution
+(w' = w * gamma / sqrt(var + eps), b' = beta - mean * gamma / sqrt(var + eps)
+with the freshly initialised statistics gamma=1, beta=0, mean=0, var=1).
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+
+MAGIC = b"PB2PACK\0"
+VERSION = 1
+NONE = 0xFFFFFFFF
+
+OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX = 1, 2, 3, 4, 5, 6, 7
+ACT_NONE, ACT_RELU, ACT_RELU6 = 0, 1, 2
+FLAG_COUNT_INCLUDE_PAD = 1
+
+OP_FIELDS = ("type", "in0", "in1", "out", "rsv0", "out_c_off", "cin", "cout", "r", "s",
+             "stride_h", "stride_w", "pad_h", "pad_w", "groups", "act", "flags", "rsv1",
+             "w_off_lo", "w_off_hi", "b_off_lo", "b_off_hi", "rsv2", "rsv3")
+
+
+@dataclass
+class Op:
+    type: int
+    in0: int
+    out: int
+    in1: int = NONE
+    out_c_off: int = 0
+    cin: int = 0
+    cout: int = 0
+    r: int = 1
+    s: int = 1
+    stride_h: int = 1
+    stride_w: int = 1
+    pad_h: int = 0
+    pad_w: int = 0
+    groups: int = 1
+    act: int = ACT_NONE
+    flags: int = 0
+    w_off: int = 0
+    b_off: int = 0
+    name: str = ""
+
+    def record(self) -> bytes:
+        return struct.pack(
+            "<24I", self.type, self.in0, self.in1, self.out, 0, self.out_c_off, self.cin,
+            self.cout, self.r, self.s, self.stride_h, self.stride_w, self.pad_h, self.pad_w,
+            self.groups, self.act, self.flags, 0, self.w_off & 0xFFFFFFFF, self.w_off >> 32,
+            self.b_off & 0xFFFFFFFF, self.b_off >> 32, 0, 0)
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+@dataclass
+class Graph:
+    """Operator graph under construction.  Tensors are (C, H, W) at batch 1."""
+    name: str
+    in_shape: tuple
+    seed: int = 1234
+    precision: int = 1
+    bias_std: float = 0.0           # biases are 0 as in the benchmark configs; tests set > 0
+    round_weights_bf16: bool = False
+    tensors: list = field(default_factory=list)
+    ops: list = field(default_factory=list)
+    weights: list = field(default_factory=list)
+    n_floats: int = 0
+    output: int = 0
+
+    def __post_init__(self):
+        self.rng = np.random.default_rng(self.seed)
+        self.input = self.tensor(*self.in_shape)
+        self.output = self.input
+
+    # -- tensors and weights -------------------------------------------------
+    def tensor(self, c, h, w) -> int:
+        self.tensors.append((int(c), int(h), int(w)))
+        return len(self.tensors) - 1
+
+    def shape(self, t):
+        return self.tensors[t]
+
+    def _push(self, arr) -> int:
+        arr = np.ascontiguousarray(arr, dtype=np.float32).ravel()
+        off = self.n_floats
+        self.weights.append(arr)
+        self.n_floats += arr.size
+        return off
+
+    def _he(self, shape, fan_in, scale=1.0):
+        w = self.rng.standard_normal(shape, dtype=np.float32) * np.float32(np.sqrt(2.0 / fan_in))
+        w = (w * np.float32(scale)).astype(np.float32)
+        if self.round_weights_bf16:
+            u = w.view(np.uint32).astype(np.uint64)
+            u = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+            w = u.view(np.float32)
+        return w
+
+    def _bias(self, n):
+        if self.bias_std > 0:
+            return (self.rng.standard_normal(n, dtype=np.float32) * np.float32(self.bias_std))
+        return np.zeros(n, dtype=np.float32)
+
+    # -- operators -----------------------------------------------------------
+    def conv(self, x, cout, k, stride=1, pad=0, groups=1, act=ACT_RELU, residual=None,
+             out=None, out_c_off=0, bn_eps=None, name=""):
+        c, h, w = self.shape(x)
+        r, s = _pair(k)
+        sh, sw = _pair(stride)
+        ph, pw = _pair(pad)
+        p = (h + 2 * ph - r) // sh + 1
+        q = (w + 2 * pw - s) // sw + 1
+        if out is None:
+            out = self.tensor(cout, p, q)
+        else:
+            assert self.shape(out)[1:] == (p, q), (name, self.shape(out), p, q)
+        fan_in = (c // groups) * r * s
+        scale = 1.0 if bn_eps is None else 1.0 / np.sqrt(1.0 + bn_eps)
+        w_off = self._push(self._he((cout, c // groups, r, s), fan_in, scale))
+        b_off = self._push(self._bias(cout))
+        self.ops.append(Op(OP_CONV, x, out, NONE if residual is None else residual, out_c_off,
+                           c, cout, r, s, sh, sw, ph, pw, groups, act, 0, w_off, b_off, name))
+        self.output = out
+        return out
+
+    def dense(self, x, n_out, act=ACT_NONE, name=""):
+        c, h, w = self.shape(x)
+        n_in = c * h * w
+        out = self.tensor(n_out, 1, 1)
+        w_off = self._push(self._he((n_out, n_in), n_in))
+        b_off = self._push(self._bias(n_out))
+        self.ops.append(Op(OP_DENSE, x, out, cin=n_in, cout=n_out, act=act, w_off=w_off,
+                           b_off=b_off, name=name))
+        self.output = out
+        return out
+
+    def _pool(self, typ, x, k, stride, pad, out, out_c_off, flags, name):
+        c, h, w = self.shape(x)
+        r, s = _pair(k)
+        sh, sw = _pair(stride)
+        ph, pw = _pair(pad)
+        p = (h + 2 * ph - r) // sh + 1
+        q = (w + 2 * pw - s) // sw + 1
+        if out is None:
+            out = self.tensor(c, p, q)
+        self.ops.append(Op(typ, x, out, out_c_off=out_c_off, cin=c, cout=c, r=r, s=s,
+                           stride_h=sh, stride_w=sw, pad_h=ph, pad_w=pw, flags=flags, name=name))
+        self.output = out
+        return out
+
+    def maxpool(self, x, k, stride, pad=0, out=None, out_c_off=0, name=""):
+        return self._pool(OP_MAXPOOL, x, k, stride, pad, out, out_c_off, 0, name)
+
+    def avgpool(self, x, k, stride, pad=0, count_include_pad=True, out=None, out_c_off=0, name=""):
+        return self._pool(OP_AVGPOOL, x, k, stride, pad, out, out_c_off,
+                          FLAG_COUNT_INCLUDE_PAD if count_include_pad else 0, name)
+
+    def gap(self, x, name=""):
+        c, h, w = self.shape(x)
+        out = self.tensor(c, 1, 1)
+        self.ops.append(Op(OP_GAP, x, out, cin=c, cout=c, r=h, s=w, name=name))
+        self.output = out
+        return out
+
+    def add(self, a, b, act=ACT_NONE, name=""):
+        c, h, w = self.shape(a)
+        assert self.shape(b) == (c, h, w)
+        out = self.tensor(c, h, w)
+        self.ops.append(Op(OP_ADD, a, out, in1=b, cin=c, cout=c, act=act, name=name))
+        self.output = out
+        return out
+
+    def softmax(self, x, name=""):
+        c, h, w = self.shape(x)
+        out = self.tensor(c, h, w)
+        self.ops.append(Op(OP_SOFTMAX, x, out, cin=c * h * w, cout=c * h * w, name=name))
+        self.output = out
+        return out
+
+    # -- accounting ------------------------------------------------------------
+    def macs(self) -> int:
+        total = 0
+        for op in self.ops:
+            if op.type == OP_CONV:
+                _, p, q = self.shape(op.out)
+                total += op.cout * p * q * (op.cin // op.groups) * op.r * op.s
+            elif op.type == OP_DENSE:
+                total += op.cin * op.cout
+        return total
+
+    def layer_table(self):
+        """Per-op algorithmic work: (name, type, flops, bytes at fp32/bf16 element size e)."""
+        rows = []
+        for op in self.ops:
+            ci, hi, wi = self.shape(op.in0)
+            co, p, q = self.shape(op.out)
+            if op.type == OP_CONV:
+                flops = 2 * op.cout * p * q * (op.cin // op.groups) * op.r * op.s
+                elems = ci * hi * wi + op.cout * (op.cin // op.groups) * op.r * op.s + op.cout + op.cout * p * q
+                if op.in1 != NONE:
+                    elems += op.cout * p * q
+            elif op.type == OP_DENSE:
+                flops = 2 * op.cin * op.cout
+                elems = op.cin + op.cin * op.cout + 2 * op.cout
+            else:
+                flops = 0
+                elems = ci * hi * wi + op.cout * p * q
+                if op.type == OP_ADD:
+                    elems += ci * hi * wi
+            rows.append((op.name, op.type, flops, elems))
+        return rows
+
+    # -- serialisation ---------------------------------------------------------
+    def to_bytes(self) -> bytes:
+        hdr = struct.pack("<8s6IQ24s", MAGIC, VERSION, len(self.tensors), len(self.ops),
+                          self.input, self.output, self.precision, self.n_floats,
+                          self.name.encode()[:23])
+        assert len(hdr) == 64
+        parts = [hdr]
+        parts += [struct.pack("<4I", c, h, w, 0) for (c, h, w) in self.tensors]
+        parts += [op.record() for op in self.ops]
+        parts += [struct.pack("<64s", op.name.encode()[:63]) for op in self.ops]
+        blob = np.concatenate(self.weights) if self.weights else np.zeros(0, np.float32)
+        parts.append(blob.astype("<f4").tobytes())
+        return b"".join(parts)
+
+    def save(self, path):
+        with open(path, "wb") as f:
+            f.write(self.to_bytes())
+        return path
+
+
+# ---------------------------------------------------------------------------
+# Model zoo: the topologies named by the benchmark configurations.
+# ---------------------------------------------------------------------------
+
+def mnist_cnn(seed=1234, precision=0, **kw) -> Graph:
+    """ONNX-zoo mnist-8 topology (I/O sizes in jobs/tvm_mnist/tvm_mnist.cpp:12-18)."""
+    g = Graph("mnist", (1, 28, 28), seed, precision, **kw)
+    x = g.conv(g.input, 8, 5, 1, 2, name="conv1")
+    x = g.maxpool(x, 2, 2, name="pool1")
+    x = g.conv(x, 16, 5, 1, 2, name="conv2")
+    x = g.maxpool(x, 3, 3, name="pool2")
+    g.dense(x, 10, name="fc")
+    return g
+
+
+def _basic_block(g, x, planes, stride, name):
+    eps = 1e-5
+    cin = g.shape(x)[0]
+    idt = x
+    if stride != 1 or cin != planes:
+        idt = g.conv(x, planes, 1, stride, 0, act=ACT_NONE, bn_eps=eps, name=name + ".downsample.0")
+    y = g.conv(x, planes, 3, stride, 1, bn_eps=eps, name=name + ".conv1")
+    return g.conv(y, planes, 3, 1, 1, act=ACT_RELU, residual=idt, bn_eps=eps, name=name + ".conv2")
+
+
+def _bottleneck(g, x, planes, stride, name):
+    eps = 1e-5
+    cin = g.shape(x)[0]
+    idt = x
+    if stride != 1 or cin != planes * 4:
+        idt = g.conv(x, planes * 4, 1, stride, 0, act=ACT_NONE, bn_eps=eps, name=name + ".downsample.0")
+    y = g.conv(x, planes, 1, 1, 0, bn_eps=eps, name=name + ".conv1")
+    y = g.conv(y, planes, 3, stride, 1, bn_eps=eps, name=name + ".conv2")
+    return g.conv(y, planes * 4, 1, 1, 0, act=ACT_RELU, residual=idt, bn_eps=eps, name=name + ".conv3")
+
+
+def _resnet(name, block, layers, seed, precision, num_classes, **kw) -> Graph:
+    g = Graph(name, (3, 224, 224), seed, precision, **kw)
+    x = g.conv(g.input, 64, 7, 2, 3, bn_eps=1e-5, name="conv1")
+    x = g.maxpool(x, 3, 2, 1, name="maxpool")
+    planes = 64
+    for li, n in enumerate(layers):
+        for bi in range(n):
+            stride = 2 if (li > 0 and bi == 0) else 1
+            x = block(g, x, planes, stride, f"layer{li + 1}.{bi}")
+        planes *= 2
+    x = g.gap(x, name="avgpool")
+    g.dense(x, num_classes, name="fc")
+    return g
+
+
+def resnet18(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
+    """ResNet-18 v1 (basic blocks 2-2-2-2), batch-norm folded."""
+    return _resnet("resnet18", _basic_block, [2, 2, 2, 2], seed, precision, num_classes, **kw)
+
+
+def resnet50(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
+    """ResNet-50 v1.5 bottlenecks 3-4-6-3 (stride on the 3x3), batch-norm folded."""
+    return _resnet("resnet50", _bottleneck, [3, 4, 6, 3], seed, precision, num_classes, **kw)
+
+
+def mobilenet_v2(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
+    """MobileNetV2 width 1.0: inverted residuals with depthwise 3x3 + ReLU6."""
+    eps = 1e-5
+    g = Graph("mobilenet", (3, 224, 224), seed, precision, **kw)
+    x = g.conv(g.input, 32, 3, 2, 1, act=ACT_RELU6, bn_eps=eps, name="features.0.0")
+    cfg = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2),
+           (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]
+    idx = 1
+    for t, c, n, s in cfg:
+        for i in range(n):
+            stride = s if i == 0 else 1
+            cin = g.shape(x)[0]
+            hidden = cin * t
+            base = f"features.{idx}.conv"
+            y = x
+            j = 0
+            if t != 1:
+                y = g.conv(y, hidden, 1, 1, 0, act=ACT_RELU6, bn_eps=eps, name=f"{base}.{j}.0")
+                j += 1
+            y = g.conv(y, hidden, 3, stride, 1, groups=hidden, act=ACT_RELU6, bn_eps=eps,
+                       name=f"{base}.{j}.0")
+            j += 1
+            use_res = stride == 1 and cin == c
+            x = g.conv(y, c, 1, 1, 0, act=ACT_NONE, residual=x if use_res else None, bn_eps=eps,
+                       name=f"{base}.{j}")
+            idx += 1
+    x = g.conv(x, 1280, 1, 1, 0, act=ACT_RELU6, bn_eps=eps, name=f"features.{idx}.0")
+    x = g.gap(x, name="avgpool")
+    g.dense(x, num_classes, name="classifier.1")
+    return g
+
+
+def inception_v3(seed=1234, precision=1, num_classes=1000, size=299, **kw) -> Graph:
+    """Inception-v3 (A/B/C/D/E blocks), no auxiliary head, batch-norm (eps 1e-3) folded.
+    Every branch writes its channel slice of the block's output tensor directly."""
+    eps = 1e-3
+    g = Graph("inception_v3", (3, size, size), seed, precision, **kw)
+
+    def bc(x, cout, k, stride=1, pad=0, name="", out=None, off=0):
+        return g.conv(x, cout, k, stride, pad, bn_eps=eps, name=name + ".conv", out=out, out_c_off=off)
+
+    x = bc(g.input, 32, 3, 2, 0, "Conv2d_1a_3x3")
+    x = bc(x, 32, 3, 1, 0, "Conv2d_2a_3x3")
+    x = bc(x, 64, 3, 1, 1, "Conv2d_2b_3x3")
+    x = g.maxpool(x, 3, 2, name="maxpool1")
+    x = bc(x, 80, 1, 1, 0, "Conv2d_3b_1x1")
+    x = bc(x, 192, 3, 1, 0, "Conv2d_4a_3x3")
+    x = g.maxpool(x, 3, 2, name="maxpool2")
+
+    def block_a(x, pool_features, n):
+        _, h, w = g.shape(x)
+        out = g.tensor(64 + 64 + 96 + pool_features, h, w)
+        bc(x, 64, 1, name=n + ".branch1x1", out=out, off=0)
+        y = bc(x, 48, 1, name=n + ".branch5x5_1")
+        bc(y, 64, 5, 1, 2, n + ".branch5x5_2", out=out, off=64)
+        y = bc(x, 64, 1, name=n + ".branch3x3dbl_1")
+        y = bc(y, 96, 3, 1, 1, n + ".branch3x3dbl_2")
+        bc(y, 96, 3, 1, 1, n + ".branch3x3dbl_3", out=out, off=128)
+        y = g.avgpool(x, 3, 1, 1, True, name=n + ".avgpool")
+        bc(y, pool_features, 1, name=n + ".branch_pool", out=out, off=224)
+        return out
+
+    def block_b(x, n):
+        c, h, w = g.shape(x)
+        p = (h - 3) // 2 + 1
+        out = g.tensor(384 + 96 + c, p, p)
+        bc(x, 384, 3, 2, 0, n + ".branch3x3", out=out, off=0)
+        y = bc(x, 64, 1, name=n + ".branch3x3dbl_1")
+        y = bc(y, 96, 3, 1, 1, n + ".branch3x3dbl_2")
+        bc(y, 96, 3, 2, 0, n + ".branch3x3dbl_3", out=out, off=384)
+        g.maxpool(x, 3, 2, out=out, out_c_off=480, name=n + ".maxpool")
+        return out
+
+    def block_c(x, c7, n):
+        _, h, w = g.shape(x)
+        out = g.tensor(768, h, w)
+        bc(x, 192, 1, name=n + ".branch1x1", out=out, off=0)
+        y = bc(x, c7, 1, name=n + ".branch7x7_1")
+        y = bc(y, c7, (1, 7), 1, (0, 3), n + ".branch7x7_2")
+        bc(y, 192, (7, 1), 1, (3, 0), n + ".branch7x7_3", out=out, off=192)
+        y = bc(x, c7, 1, name=n + ".branch7x7dbl_1")
+        y = bc(y, c7, (7, 1), 1, (3, 0), n + ".branch7x7dbl_2")
+        y = bc(y, c7, (1, 7), 1, (0, 3), n + ".branch7x7dbl_3")
+        y = bc(y, c7, (7, 1), 1, (3, 0), n + ".branch7x7dbl_4")
+        bc(y, 192, (1, 7), 1, (0, 3), n + ".branch7x7dbl_5", out=out, off=384)
+        y = g.avgpool(x, 3, 1, 1, True, name=n + ".avgpool")
+        bc(y, 192, 1, name=n + ".branch_pool", out=out, off=576)
+        return out
+
+    def block_d(x, n):
+        c, h, w = g.shape(x)
+        p = (h - 3) // 2 + 1
+        out = g.tensor(320 + 192 + c, p, p)
+        y = bc(x, 192, 1, name=n + ".branch3x3_1")
+        bc(y, 320, 3, 2, 0, n + ".branch3x3_2", out=out, off=0)
+        y = bc(x, 192, 1, name=n + ".branch7x7x3_1")
+        y = bc(y, 192, (1, 7), 1, (0, 3), n + ".branch7x7x3_2")
+        y = bc(y, 192, (7, 1), 1, (3, 0), n + ".branch7x7x3_3")
+        bc(y, 192, 3, 2, 0, n + ".branch7x7x3_4", out=out, off=320)
+        g.maxpool(x, 3, 2, out=out, out_c_off=512, name=n + ".maxpool")
+        return out
+
+    def block_e(x, n):
+        _, h, w = g.shape(x)
+        out = g.tensor(2048, h, w)
+        bc(x, 320, 1, name=n + ".branch1x1", out=out, off=0)
+        y = bc(x, 384, 1, name=n + ".branch3x3_1")
+        bc(y, 384, (1, 3), 1, (0, 1), n + ".branch3x3_2a", out=out, off=320)
+        bc(y, 384, (3, 1), 1, (1, 0), n + ".branch3x3_2b", out=out, off=704)
+        y = bc(x, 448, 1, name=n + ".branch3x3dbl_1")
+        y = bc(y, 384, 3, 1, 1, n + ".branch3x3dbl_2")
+        bc(y, 384, (1, 3), 1, (0, 1), n + ".branch3x3dbl_3a", out=out, off=1088)
+        bc(y, 384, (3, 1), 1, (1, 0), n + ".branch3x3dbl_3b", out=out, off=1472)
+        y = g.avgpool(x, 3, 1, 1, True, name=n + ".avgpool")
+        bc(y, 192, 1, name=n + ".branch_pool", out=out, off=1856)
+        return out
+
+    x = block_a(x, 32, "Mixed_5b")
+    x = block_a(x, 64, "Mixed_5c")
+    x = block_a(x, 64, "Mixed_5d")
+    x = block_b(x, "Mixed_6a")
+    x = block_c(x, 128, "Mixed_6b")
+    x = block_c(x, 160, "Mixed_6c")
+    x = block_c(x, 160, "Mixed_6d")
+    x = block_c(x, 192, "Mixed_6e")
+    x = block_d(x, "Mixed_7a")
+    x = block_e(x, "Mixed_7b")
+    x = block_e(x, "Mixed_7c")
+    x = g.gap(x, name="avgpool")
+    g.dense(x, num_classes, name="fc")
+    return g
+
+
+MODELS = {
+    "mnist": mnist_cnn,
+    "resnet18": resnet18,
+    "resnet50": resnet50,
+    "mobilenet": mobilenet_v2,
+    "inception_v3": inception_v3,
+}
+
+
+def pack_file_name(model: str) -> str:
+    """File the job adapter for `model` opens under $LLIS_MODELS_DIR."""
+    return f"{model}-b200-pack.bin"
+
+
+def write_all(models_dir, models=None, seed=1234, **kw):
+    import os
+    os.makedirs(models_dir, exist_ok=True)
+    out = {}
+    for m in (models or MODELS):
+        g = MODELS[m](seed=seed, **kw)
+        out[m] = g.save(os.path.join(models_dir, pack_file_name(m)))
+    return out
+
+
+if __name__ == "__main__":
+    import sys
+    d = sys.argv[1] if len(sys.argv) > 1 else "models"
+    for m, p in write_all(d, sys.argv[2:] or None).items():
+        print(m, p)

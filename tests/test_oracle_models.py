@@ -1,0 +1,91 @@
+"""Pins the model packs + oracle executor against torchvision's definitions of the
+same topologies (CPU fp32), loading the pack's weights into the torch modules."""
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+import torchvision
+
+from oracle import graph as og
+from paella_b200 import packer
+
+
+def _load_into_torch(model, g, bn_eps):
+    pack = og.Pack(g.to_bytes())
+    mods = dict(model.named_modules())
+    scale = np.sqrt(1.0 + bn_eps)
+    for rec, name in zip(pack.ops, pack.names):
+        typ, cin, cout, r, s, groups = rec[0], rec[6], rec[7], rec[8], rec[9], rec[14]
+        woff, boff = rec[18] | (rec[19] << 32), rec[20] | (rec[21] << 32)
+        if typ == og.OP_CONV:
+            m = mods[name]
+            assert isinstance(m, nn.Conv2d), name
+            w = pack.weights[woff: woff + cout * (cin // groups) * r * s].reshape(cout, cin // groups, r, s)
+            with torch.no_grad():
+                m.weight.copy_(torch.from_numpy(w * np.float32(scale)))
+                assert m.bias is None
+        elif typ == og.OP_DENSE:
+            m = mods[name]
+            assert isinstance(m, nn.Linear), name
+            with torch.no_grad():
+                m.weight.copy_(torch.from_numpy(pack.weights[woff: woff + cout * cin].reshape(cout, cin)))
+                m.bias.copy_(torch.from_numpy(pack.weights[boff: boff + cout]))
+    for m in model.modules():   # freshly initialised batch-norm statistics
+        if isinstance(m, nn.BatchNorm2d):
+            nn.init.ones_(m.weight); nn.init.zeros_(m.bias)
+            m.running_mean.zero_(); m.running_var.fill_(1.0)
+    return pack
+
+
+CASES = [
+    ("resnet18", lambda: torchvision.models.resnet18(weights=None), 1e-5, 224),
+    ("resnet50", lambda: torchvision.models.resnet50(weights=None), 1e-5, 224),
+    ("mobilenet", lambda: torchvision.models.mobilenet_v2(weights=None), 1e-5, 224),
+    ("inception_v3", lambda: torchvision.models.inception_v3(weights=None, aux_logits=False,
+                                                              transform_input=False, init_weights=False), 1e-3, 299),
+]
+
+
+@pytest.mark.parametrize("name,ctor,eps,size", CASES, ids=[c[0] for c in CASES])
+def test_pack_matches_torchvision(oracle_lib, name, ctor, eps, size):
+    g = packer.MODELS[name](seed=1234)
+    model = ctor().eval()
+    pack = _load_into_torch(model, g, eps)
+    x = np.random.default_rng(5).standard_normal((3, size, size), dtype=np.float32)
+    with torch.no_grad():
+        ref = model(torch.from_numpy(x)[None])[0].numpy()
+    got = og.run(pack, x)
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() <= 2e-4 * scale
+    assert int(got.argmax()) == int(ref.argmax())
+
+
+def test_mnist_pack_matches_torch(oracle_lib):
+    g = packer.mnist_cnn(seed=1234, bias_std=0.1)
+    pack = og.Pack(g.to_bytes())
+    W = pack.weights
+    m = nn.Sequential(nn.Conv2d(1, 8, 5, 1, 2), nn.ReLU(), nn.MaxPool2d(2, 2), nn.Conv2d(8, 16, 5, 1, 2), nn.ReLU(),
+                      nn.MaxPool2d(3, 3), nn.Flatten(0), nn.Linear(256, 10))
+    convs = [m[0], m[3], m[7]]
+    k = 0
+    for rec in pack.ops:
+        if rec[0] in (og.OP_CONV, og.OP_DENSE):
+            woff, boff = rec[18], rec[20]
+            with torch.no_grad():
+                convs[k].weight.copy_(torch.from_numpy(W[woff: woff + convs[k].weight.numel()].reshape(convs[k].weight.shape)))
+                convs[k].bias.copy_(torch.from_numpy(W[boff: boff + convs[k].bias.numel()]))
+            k += 1
+    x = np.random.default_rng(0).random((1, 28, 28), dtype=np.float32)
+    with torch.no_grad():
+        ref = m(torch.from_numpy(x)).numpy()
+    got = og.run(pack, x)
+    np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_algorithmic_work_matches_published_counts():
+    """MAC totals per request quoted for the benchmark configurations."""
+    assert packer.mnist_cnn().macs() == 156800 + 627200 + 2560
+    assert abs(packer.resnet18().macs() / 1e9 - 1.814) < 0.002
+    assert abs(packer.inception_v3().macs() / 1e9 - 5.713) < 0.003
+    assert abs(packer.resnet50().macs() / 1e9 - 4.089) < 0.003
+    assert abs(packer.mobilenet_v2().macs() / 1e9 - 0.3006) < 0.001

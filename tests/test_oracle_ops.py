@@ -1,0 +1,89 @@
+"""Pins the CPU oracle's operators against PyTorch CPU fp32 (an independent
+implementation of the same ONNX/Relay operator semantics)."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import graph as og
+
+RNG = np.random.default_rng(7)
+
+
+def _t(a):
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+CONV_CASES = [
+    # C, H, W, K, R, S, sh, sw, ph, pw, groups
+    (1, 28, 28, 8, 5, 5, 1, 1, 2, 2, 1),
+    (8, 14, 14, 16, 5, 5, 1, 1, 2, 2, 1),
+    (3, 33, 31, 16, 7, 7, 2, 2, 3, 3, 1),
+    (16, 17, 17, 24, 1, 7, 1, 1, 0, 3, 1),
+    (16, 17, 17, 24, 7, 1, 1, 1, 3, 0, 1),
+    (12, 19, 19, 20, 3, 3, 2, 2, 0, 0, 1),
+    (32, 15, 15, 32, 3, 3, 2, 2, 1, 1, 32),
+    (32, 9, 9, 32, 3, 3, 1, 1, 1, 1, 32),
+    (24, 7, 7, 40, 1, 1, 2, 2, 0, 0, 1),
+    (5, 1, 1, 3, 1, 1, 1, 1, 0, 0, 1),
+    (8, 6, 6, 8, 3, 3, 1, 1, 1, 1, 2),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_conv2d_matches_torch(oracle_lib, case, act):
+    C, H, W, K, R, S, sh, sw, ph, pw, g = case
+    x = RNG.standard_normal((C, H, W), dtype=np.float32)
+    w = RNG.standard_normal((K, C // g, R, S), dtype=np.float32)
+    b = RNG.standard_normal(K, dtype=np.float32)
+    ref = F.conv2d(_t(x)[None], _t(w), _t(b), (sh, sw), (ph, pw), 1, g)[0]
+    res = RNG.standard_normal(tuple(ref.shape), dtype=np.float32)
+    ref = ref + _t(res)
+    if act == 1:
+        ref = F.relu(ref)
+    elif act == 2:
+        ref = F.relu6(ref)
+    got = og.conv2d(x, w, b, (sh, sw), (ph, pw), g, act, res)
+    np.testing.assert_allclose(got, ref.numpy(), rtol=1e-4, atol=1e-4)
+
+
+def test_conv2d_writes_channel_slice(oracle_lib):
+    x = RNG.standard_normal((4, 9, 9), dtype=np.float32)
+    w = RNG.standard_normal((6, 4, 3, 3), dtype=np.float32)
+    out = np.full((10, 9, 9), 7.0, np.float32)
+    og.conv2d(x, w, None, (1, 1), (1, 1), 1, 0, None, out, 3)
+    ref = F.conv2d(_t(x)[None], _t(w), None, 1, 1)[0].numpy()
+    np.testing.assert_allclose(out[3:9], ref, rtol=1e-4, atol=1e-4)
+    assert (out[:3] == 7.0).all() and (out[9:] == 7.0).all()
+
+
+@pytest.mark.parametrize("k,s,p,hw", [(2, 2, 0, 28), (3, 3, 0, 14), (3, 2, 1, 112), (3, 2, 0, 35), (3, 1, 1, 17)])
+def test_pools_match_torch(oracle_lib, k, s, p, hw):
+    x = RNG.standard_normal((5, hw, hw), dtype=np.float32)
+    got = og.maxpool(x, (k, k), (s, s), (p, p))
+    ref = F.max_pool2d(_t(x)[None], k, s, p)[0].numpy()
+    np.testing.assert_array_equal(got, ref)
+    for cip in (True, False):
+        got = og.avgpool(x, (k, k), (s, s), (p, p), cip)
+        ref = F.avg_pool2d(_t(x)[None], k, s, p, count_include_pad=cip)[0].numpy()
+        np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_dense_gap_add_softmax(oracle_lib):
+    x = RNG.standard_normal(300, dtype=np.float32)
+    w = RNG.standard_normal((17, 300), dtype=np.float32)
+    b = RNG.standard_normal(17, dtype=np.float32)
+    np.testing.assert_allclose(og.dense(x, w, b), F.linear(_t(x), _t(w), _t(b)).numpy(), rtol=1e-4, atol=1e-4)
+    t = RNG.standard_normal((6, 7, 7), dtype=np.float32)
+    np.testing.assert_allclose(og.gap(t), t.mean(axis=(1, 2)), rtol=1e-5, atol=1e-6)
+    u = RNG.standard_normal((6, 7, 7), dtype=np.float32)
+    np.testing.assert_array_equal(og.add(t, u, 1), np.maximum(t + u, 0))
+    np.testing.assert_allclose(og.softmax(x), F.softmax(_t(x), 0).numpy(), rtol=1e-5, atol=1e-7)
+
+
+def test_round_bf16_matches_torch(oracle_lib):
+    x = RNG.standard_normal(10000, dtype=np.float32) * 100
+    x[:4] = [0.0, -0.0, np.inf, 1.0000001]
+    ref = _t(x).to(torch.bfloat16).to(torch.float32).numpy()
+    np.testing.assert_array_equal(og.round_bf16(x), ref)
