@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Serving benchmark: mixed MNIST + Inception-v3 (9:1 by request count), requests/s and p50/p99.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A "step" is one batch of --batch requests per GPU (default 200: ~180 MNIST + ~20 Inception-v3)
+pushed through the serving path: plugin -> scheduler -> one kernel at a time per job, released
+by ring notifications.  W un-timed warm-up steps are fully drained, then exactly K steps are
+timed between a device synchronise on both sides (CUDA events, max over GPUs/ranks).
+
+  value : req/s with request inputs already resident in HBM (copy stages skipped)
+  e2e   : the same through host buffers: pinned H2D copy of every input and D2H copy of every
+          result inside the timed region
+  roofline     : the tcgen05 implicit-GEMM convolution over the Inception-v3 layers, timed here
+                 with CUDA events (L2 flushed before every launch)
+  cpu_baseline : the CPU oracle (fp32, OpenMP) on a bounded sample of the same mix
+
+Under torchrun (WORLD_SIZE > 1) every rank drives the GPU LOCAL_RANK with its own scheduler and
+pools; there is no data-path collective.  Ranks meet at a gloo barrier before the timed region
+and reduce (max time, sum requests) after it.  Without torchrun, --gpus N runs N replicas as
+threads of this process.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MIX = [("tvm_mnist", "mnist", 0.9), ("tvm_inception_v3", "inception_v3", 0.1)]
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.lines = None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self, gpu_ids):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9 or not f[0].isdigit() or int(f[0]) not in gpu_ids:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def write_packs(models_dir):
+    from paella_b200 import packer
+    graphs = {}
+    for _, model, _ in MIX:
+        g = packer.MODELS[model](seed=1234)
+        g.save(os.path.join(models_dir, packer.pack_file_name(model)))
+        graphs[model] = g
+    return graphs
+
+
+def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1):
+    cfg = capi.LoadgenConfig()
+    L.pb_loadgen_config_default(C.byref(cfg))
+    cfg.num_gpus = len(devices)
+    for i, d in enumerate(devices):
+        cfg.devices[i] = d
+    cfg.num_types = len(MIX)
+    for i, (job, _, prop) in enumerate(MIX):
+        cfg.plugin_paths[i] = capi.plugin_path(job).encode()
+        cfg.proportions[i] = prop
+        cfg.max_outstanding[i] = caps[i]
+    cfg.concurrency = concurrency
+    cfg.mean_interarrival_us = iat_us
+    cfg.num_jobs = batch * steps
+    cfg.warmup_jobs = batch * warmup
+    cfg.seed = seed
+    cfg.device_resident = 1 if resident else 0
+    cfg.server.num_streams = 500
+    res = capi.LoadgenResult()
+    capi.check(L.pb_loadgen_run(C.byref(cfg), C.byref(res)), "pb_loadgen_run")
+    if res.errors:
+        raise RuntimeError(f"{res.errors} requests reported an error")
+    return res
+
+
+def roofline_leg(L, capi, models_dir, iters=20):
+    """Times every stage of Inception-v3 alone; returns the tensor-core convolution aggregate and a
+    per-kind table (time share of one request)."""
+    from paella_b200 import packer
+    hbm, tf, how = measured_peaks()
+    model, inst = C.c_void_p(), C.c_void_p()
+    path = os.path.join(models_dir, packer.pack_file_name("inception_v3"))
+    capi.check(L.pb_model_load(path.encode(), 0, 1, C.byref(model)), "pb_model_load")
+    capi.check(L.pb_instance_create(model, C.byref(inst)), "pb_instance_create")
+    li, us = capi.LaunchInfo(), C.c_double()
+    per_kind = {}
+    layers = []
+    for s in range(L.pb_model_num_stages(model)):
+        L.pb_model_stage_info(model, s, C.byref(li))
+        capi.check(L.pb_instance_time_stage(inst, s, iters, 192 << 20, C.byref(us)), "pb_instance_time_stage")
+        k = capi.STAGE_NAMES[li.kind]
+        d = per_kind.setdefault(k, {"launches": 0, "us": 0.0, "flops": 0, "bytes": 0})
+        d["launches"] += 1; d["us"] += us.value; d["flops"] += li.flops; d["bytes"] += li.bytes
+        layers.append((L.pb_model_stage_name(model, s).decode(), k, us.value, li.flops, li.bytes, li.num_blocks))
+    L.pb_instance_destroy(inst)
+    L.pb_model_destroy(model)
+    conv = per_kind.get("conv_umma", {"launches": 0, "us": 1.0, "flops": 0, "bytes": 0})
+    achieved = conv["flops"] / (conv["us"] * 1e-6) / 1e12 if conv["launches"] else 0.0
+    total_us = sum(d["us"] for d in per_kind.values())
+    roof = {"bound": "tensor", "kernel": "conv_umma_kernel (tcgen05 implicit GEMM), all Inception-v3 conv layers, batch 1",
+            "achieved": round(achieved, 3), "peak": tf, "unit": "TFLOP/s", "frac": round(achieved / tf, 5), "of": how,
+            "traffic": None, "launches": conv["launches"], "avg_launch_us": round(conv["us"] / max(conv["launches"], 1), 3),
+            "hbm_gbs_same_kernel": round(conv["bytes"] / (conv["us"] * 1e-6) / 1e9, 1),
+            "time_share_of_request": round(conv["us"] / total_us, 4) if total_us else None}
+    table = {k: {"launches": d["launches"], "us": round(d["us"], 2), "share": round(d["us"] / total_us, 4),
+                 "gbs": round(d["bytes"] / (d["us"] * 1e-6) / 1e9, 1), "tflops": round(d["flops"] / (d["us"] * 1e-6) / 1e12, 3)}
+             for k, d in per_kind.items()}
+    return roof, table, layers
+
+
+def cpu_sample(graphs, n_mnist=9, n_inception=1, repeats=1):
+    """Oracle (CPU fp32, OpenMP over all cores) on a bounded sample of the mix; returns req/s."""
+    import numpy as np
+    from oracle import graph as og
+    og.build()
+    packs = {m: og.Pack(g.to_bytes()) for m, g in graphs.items()}
+    rng = np.random.default_rng(0)
+    xm = rng.random((1, 28, 28), dtype=np.float32)
+    xi = rng.standard_normal((3, 299, 299), dtype=np.float32)
+    og.run(packs["mnist"], xm)
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(repeats):
+        for _ in range(n_mnist):
+            og.run(packs["mnist"], xm); n += 1
+        for _ in range(n_inception):
+            og.run(packs["inception_v3"], xi); n += 1
+    dt = time.perf_counter() - t0
+    return n / dt, dt, n
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=200, help="requests per GPU per step")
+    ap.add_argument("--concurrency", type=int, default=24, help="closed-loop clients per GPU")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-roofline", action="store_true")
+    ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": "mixed MNIST-CNN : Inception-v3@299 = 9:1 by request count, batch 1, random He-normal weights "
+                          "(BASELINE configs[2]); closed loop",
+              "batch_per_step_per_gpu": args.batch, "clients_per_gpu": args.concurrency,
+              "instances_per_gpu": {"mnist": args.concurrency, "inception_v3": max(4, args.concurrency // 3)},
+              "scheduler": "full3", "precision": {"mnist": "fp32", "inception_v3": "bf16 x bf16 -> fp32 (tcgen05)"},
+              "replicas": "one scheduler+pools per GPU, requests dealt round-robin, no collective",
+              "l2": "not flushed between requests: the working set per GPU (47.6 MB of bf16 weights + 19 MB of activations "
+                    "per in-flight Inception instance x instances) exceeds the 126 MB L2; the roofline leg flushes L2 "
+                    "before every launch"}
+
+    # ----------------------------------------------------------------- reference arm: CPU
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        with tempfile.TemporaryDirectory() as d:
+            graphs = write_packs(d)
+        times, n_per = [], 10
+        for _ in range(args.warmup):
+            cpu_sample(graphs)
+        for _ in range(args.steps):
+            rps, dt, n_per = cpu_sample(graphs, repeats=3)
+            times.append(dt)
+        total = sum(times)
+        value = n_per * len(times) / total
+        cores = os.cpu_count()
+        line = {"impl": "reference", "metric": "requests/s, mixed MNIST + Inception-v3 (9:1)", "value": round(value, 3),
+                "unit": "req/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(1000 * total / len(times), 2), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": round(value, 3), "unit": "req/s", "cores": cores, "kind": "port",
+                                 "sample": "each step = 3 x (9 MNIST + 1 Inception-v3) requests run back to back by the CPU "
+                                           "oracle (fp32 C operators, OpenMP over all host cores); the reference's own "
+                                           "TVM CPU build is unavailable on this box"},
+                "e2e": {"value": round(value, 3), "unit": "req/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    # ----------------------------------------------------------------- our arm: GPU
+    import paella_b200 as pb
+    from paella_b200 import capi
+    L = pb.load()
+    if L.pb_device_count() < 1:
+        raise SystemExit("bench.py needs a CUDA device (paella_b200 has no CPU path)")
+    tmp = tempfile.TemporaryDirectory()
+    os.environ["LLIS_MODELS_DIR"] = tmp.name
+    graphs = write_packs(tmp.name)
+    caps = [args.concurrency, max(4, args.concurrency // 3)]
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        devices = [local_rank]
+        n_gpus = world
+    else:
+        devices = list(range(args.gpus))
+        n_gpus = args.gpus
+
+    sampler = ClockSampler()
+
+    def timed(resident):
+        if dist:
+            dist.barrier()
+        r = run_load(L, capi, devices, args.batch, args.steps, args.warmup, resident, args.concurrency, caps)
+        n = float(r.all.count)
+        ms = r.elapsed_event_ms
+        if dist:
+            import torch
+            t = torch.tensor([ms], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            c = torch.tensor([n, float(r.kernels_launched), float(r.h2d_bytes), float(r.d2h_bytes)], dtype=torch.float64)
+            dist.all_reduce(c, op=dist.ReduceOp.SUM)
+            ms, n = float(t[0]), float(c[0])
+            return r, n, ms, float(c[1]), float(c[2]), float(c[3])
+        return r, n, ms, float(r.kernels_launched), float(r.h2d_bytes), float(r.d2h_bytes)
+
+    if rank == 0:
+        sampler.start()
+    r_dev, n_dev, ms_dev, k_dev, _, _ = timed(resident=True)
+    r_e2e, n_e2e, ms_e2e, k_e2e, h2d, d2h = timed(resident=False)
+    clocks = sampler.stop(set(range(n_gpus))) if rank == 0 else None
+
+    if rank != 0:
+        dist.barrier()
+        return
+
+    value = n_dev / (ms_dev * 1e-3)
+    e2e = n_e2e / (ms_e2e * 1e-3)
+    # kernels of ours inside the timed region: compute stages + the one-block copy-done markers (2 per request)
+    gpu_launches = int(k_dev + 2 * n_dev)
+
+    def lat(r):
+        return {"all": r.all.as_dict(), "mnist": r.per_type[0].as_dict(), "inception_v3": r.per_type[1].as_dict()}
+
+    line = {"metric": "requests/s, mixed MNIST + Inception-v3 (9:1), p50/p99 reported", "value": round(value, 2), "unit": "req/s",
+            "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config, "clocks": clocks, "gpu_launches": gpu_launches,
+            "e2e": {"value": round(e2e, 2), "unit": "req/s", "h2d_bytes_per_step": int(h2d / args.steps),
+                    "d2h_bytes_per_step": int(d2h / args.steps), "ms_per_step": round(ms_e2e / args.steps, 3),
+                    "latency_us": lat(r_e2e)},
+            "latency_us": lat(r_dev),
+            "timing": "CUDA events on each GPU around the measured requests (device idle on both sides), max over GPUs",
+            "records_consumed": int(r_dev.records_consumed), "decisions": int(r_dev.decisions)}
+
+    if n_gpus == 1 and not args.no_roofline:
+        roof, table, layers = roofline_leg(L, capi, tmp.name)
+        line["roofline"] = roof
+        line["kernel_table_inception_v3"] = table
+        if args.layers:
+            with open(args.layers, "w") as f:
+                f.write("stage\tkind\tus\tflops\tbytes\tblocks\tTFLOP/s\tGB/s\n")
+                for (nm, k, us, fl, by, nb) in layers:
+                    f.write(f"{nm}\t{k}\t{us:.2f}\t{fl}\t{by}\t{nb}\t{fl / us / 1e6:.3f}\t{by / us / 1e3:.1f}\n")
+        rps, dt, n = cpu_sample(graphs, repeats=12)
+        line["cpu_baseline"] = {"value": round(rps, 3), "unit": "req/s", "cores": os.cpu_count(), "kind": "port",
+                                "sample": f"{n} requests (9:1 MNIST : Inception-v3) by the CPU oracle, fp32, OpenMP on all "
+                                          f"host cores, {dt:.1f} s"}
+    print(json.dumps(line))
+    if dist:
+        dist.barrier()
+
+
+if __name__ == "__main__":
+    main()

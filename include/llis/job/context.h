@@ -1,0 +1,31 @@
+// Per-server-thread context a plugin can query while the server calls into it.
+//
+// Same role and accessor names as the reference's include/llis/job/context.h:10-53
+// (process-global statics there).  Here the slots are thread-local: one server
+// (scheduler + pools) runs per GPU, each on its own thread of one process, and every
+// plugin call happens on the thread of the server that owns the job.
+#pragma once
+
+#include <llis/ipc/shm_primitive_channel.h>
+#include <llis/job/job.h>
+
+namespace llis {
+namespace job {
+
+class Context {
+  public:
+    static Job* get_current_job();
+    static void set_current_job(Job* job);
+    static ipc::Gpu2SchedChannel* get_gpu2sched_channel();
+    static void set_gpu2sched_channel(ipc::Gpu2SchedChannel* ch);
+    // CUDA device of the calling server thread (the reference hard-wires device 0).
+    static int get_device();
+    static void set_device(int device);
+    // True when requests' inputs are already resident in device memory and results stay
+    // there: model jobs then skip their host<->device copies (benchmark mode).
+    static bool device_resident();
+    static void set_device_resident(bool v);
+};
+
+}  // namespace job
+}  // namespace llis

@@ -1,0 +1,71 @@
+// Scheduler interface and the services a scheduler needs from its server.
+//
+// Scheduler mirrors the reference's include/llis/server/scheduler.h:18-31
+// (handle_new_job + try_handle_block_start_finish); SchedulerHost gathers the Server
+// methods the reference's schedulers call (include/llis/server/server.h:24-71:
+// update_job_stage_length, has/set_job_stage_resource, get_job_remaining_rl,
+// get_job_stage_lengths/resources, notify_job_starts/ends, release_job_instance), plus
+// the clock and the pools, so the same scheduler object runs against a live GPU or
+// against a recorded trace.
+#pragma once
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include <llis/job/instrument_info.h>
+#include <llis/job/job.h>
+#include <llis/server/sm_resources.h>
+
+namespace llis {
+namespace server {
+
+class SchedulerHost {
+  public:
+    virtual ~SchedulerHost() = default;
+    virtual double now_us() = 0;
+    // Called right after run_next() of a copy stage: must make a kMemDone record for the
+    // job appear once the copy has completed (live server: a one-block marker kernel
+    // queued behind the copy on the job's stream).
+    virtual void after_mem_stage(job::Job* job) = 0;
+    virtual void update_job_stage_length(job::Job* job, unsigned stage, double len_us) = 0;
+    virtual bool has_job_stage_resource(job::Job* job, unsigned stage) = 0;
+    virtual void set_job_stage_resource(job::Job* job, unsigned stage, float res) = 0;
+    virtual double get_job_remaining_rl(job::Job* job, unsigned from_stage) = 0;
+    virtual const std::vector<double>& get_job_stage_lengths(job::Job* job) = 0;
+    virtual const std::vector<float>& get_job_stage_resources(job::Job* job) = 0;
+    virtual void notify_job_starts(job::Job* job) = 0;
+    virtual void notify_job_ends(job::Job* job) = 0;
+    virtual void release_job_instance(job::Job* job) = 0;
+    // Observation hook: one call per dispatched stage (decision log for replay parity).
+    virtual void on_dispatch(job::Job* job, bool is_mem, bool unfit, unsigned stream_slot, unsigned notifier_slot) {
+        (void)job; (void)is_mem; (void)unfit; (void)stream_slot; (void)notifier_slot;
+    }
+};
+
+struct SchedulerConfig {
+    unsigned num_streams = 500;
+    unsigned extra_kernels = 2;       // over-subscribed ("unfit") kernels allowed in flight
+    double unfairness_threshold = 1e6;
+    unsigned sched_sleep = 0;
+    SmTotals totals;
+};
+
+class Scheduler {
+  public:
+    virtual ~Scheduler() = default;
+    virtual void handle_new_job(job::Job* job) = 0;
+    // Consumes one notification record (block start, block end or copy done).
+    virtual void handle_record(const job::InstrumentInfo& info) = 0;
+    virtual unsigned num_jobs() const = 0;
+    virtual uint64_t num_decisions() const = 0;
+    virtual const char* name() const = 0;
+
+    // Stream / notifier pools are handed over by the server (slot i <-> element i).
+    virtual void set_pools(const std::vector<cudaStream_t>& streams, const std::vector<job::FinishedBlockNotifier*>& notifiers) = 0;
+
+    static std::unique_ptr<Scheduler> create(const std::string& name, const SchedulerConfig& cfg, SchedulerHost* host);
+};
+
+}  // namespace server
+}  // namespace llis

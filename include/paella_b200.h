@@ -1,0 +1,311 @@
+/*
+ * paella_b200 C ABI.
+ *
+ * Everything the host side (the C++ scheduler/server, the job plugins, and the
+ * Python tests and benchmark through ctypes) needs from the CUDA library goes
+ * through these functions: plain pointers and sizes, no C++ or torch types.
+ * Streams are passed as `void*` holding a `cudaStream_t`; device buffers as
+ * `void*` device addresses.  Every function returns PB_OK (0) or a negative
+ * pb_status, and never aborts the process.  pb_last_error() returns a
+ * thread-local description of the most recent failure.
+ *
+ * File references name the interface of the reference implementation that each
+ * group replaces (paths inside the eniac/paella tree).
+ */
+#ifndef PAELLA_B200_H
+#define PAELLA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PB_API __attribute__((visibility("default")))
+
+typedef enum pb_status {
+    PB_OK = 0,
+    PB_ERR_CUDA = -1,          /* a CUDA runtime/driver call failed */
+    PB_ERR_INVALID = -2,       /* bad argument / unsupported shape */
+    PB_ERR_RING_OVERFLOW = -3, /* device writer lapped the host reader */
+    PB_ERR_IO = -4,            /* pack file missing or malformed */
+    PB_ERR_TIMEOUT = -5,       /* a bounded wait ran out */
+    PB_ERR_NO_DEVICE = -6,     /* no CUDA device / library built without one */
+    PB_ERR_DEVICE_FLAG = -7    /* a kernel raised its error flag (bounded wait expired on device) */
+} pb_status;
+
+PB_API const char* pb_last_error(void);
+PB_API const char* pb_version(void);
+PB_API int pb_device_count(void);
+
+/* Launch geometry and per-block resources of one kernel launch: what a job stage
+ * declares to the scheduler (include/llis/job/job.h:62-135 in the reference). */
+typedef struct pb_launch_info {
+    uint32_t num_blocks;
+    uint32_t threads_per_block;
+    uint32_t smem_per_block;     /* static + dynamic bytes */
+    uint32_t regs_per_thread;
+    uint32_t tmem_cols_per_block;
+    uint32_t kind;               /* pb_stage_kind */
+    uint64_t flops;              /* algorithmic 2*MAC */
+    uint64_t bytes;              /* algorithmic bytes: inputs + weights + outputs once */
+} pb_launch_info;
+
+/* ------------------------------------------------------------------------ *
+ * GPU -> host notification ring and notifiers.
+ * Replaces ShmPrimitiveChannelGpu<uint64_t> (include/llis/ipc/shm_primitive_channel.h:11-68,
+ * include/llis/ipc/shm_primitive_channel_impl.h:18-64, src/ipc/shm_primitive_channel.cu:49-131)
+ * and FinishedBlockNotifier::create_array/free_array (src/job/finished_block_notifier.cu:21-48).
+ * ------------------------------------------------------------------------ */
+typedef struct pb_ring pb_ring;
+
+/* capacity is rounded up to a power of two (reference default: 1 024 000 records). */
+PB_API int pb_ring_create(int device, uint64_t capacity, pb_ring** out);
+PB_API void pb_ring_destroy(pb_ring* ring);
+PB_API uint64_t pb_ring_capacity(const pb_ring* ring);
+/* Non-blocking read of up to `max` records (8 bytes each, layout of
+ * llis::job::InstrumentInfo).  Returns the number read (>= 0) or PB_ERR_RING_OVERFLOW. */
+PB_API int pb_ring_poll(pb_ring* ring, uint64_t* records, int max);
+PB_API uint64_t pb_ring_records_read(const pb_ring* ring);
+/* Fills a llis::ipc::Gpu2SchedChannelDev (24 bytes) for embedding in device objects. */
+PB_API int pb_ring_device_view(const pb_ring* ring, void* view_out, size_t view_size);
+/* n notifiers (device memory) bound to the ring; element size = pb_notifier_size(). */
+PB_API int pb_notifier_create_array(pb_ring* ring, uint32_t n, void** dev_array_out);
+PB_API void pb_notifier_free_array(void* dev_array);
+PB_API size_t pb_notifier_size(void);
+
+/* Microbenchmark kernel of the reference's tests/ipc/shm_channel/latency/shmpc_latency_gpu.cu:7-32:
+ * a grid of `num_blocks` x `threads` that only emits start/end notifications.
+ * aggregated != 0 uses the notifier (1 record / 16 blocks), else one record per block
+ * with the SM id (include/llis/job/instrument.h:9-63). */
+PB_API int pb_launch_notify_probe(void* stream, uint32_t num_blocks, uint32_t threads, uint32_t job_id,
+                                  void* notifier, int aggregated);
+/* One-block kernel that writes a kMemDone record for `job_id`: follows an async copy
+ * stage in stream order (replaces cudaLaunchHostFunc + the mem2sched CPU ring,
+ * src/server/scheduler_full3.cpp:429-431,465-468). */
+PB_API int pb_launch_mem_done(void* stream, uint32_t job_id, void* notifier_or_ring_view);
+/* Ring latency probe: like the notify probe, but the record's job_id field carries the
+ * low 32 bits of %globaltimer (ns) at the time of the write. */
+PB_API int pb_launch_latency_probe(void* stream, uint32_t num_blocks, void* notifier);
+/* Reads %globaltimer on the device and the host monotonic clock around it:
+ * out[0] = host ns before, out[1] = device globaltimer ns, out[2] = host ns after. */
+PB_API int pb_clock_calibrate(int device, uint64_t out[3]);
+
+/* ------------------------------------------------------------------------ *
+ * Synthetic jobs of the scheduler stress configuration.
+ * vec_add:  jobs/vec_add_coroutine/vec_add_coroutine.cu:8-20  (out[i] += in[i])
+ * spin:     jobs/dummy_short/dummy_short.cu:8-27 and jobs/dummy_long (occupy SMs for a known time);
+ *           each block spins on %globaltimer until `spin_ns` elapsed (bounded, never waits on the host).
+ * ------------------------------------------------------------------------ */
+PB_API int pb_vec_add_info(uint64_t n, pb_launch_info* out);
+PB_API int pb_vec_add_launch(float* out_dev, const float* in_dev, uint64_t n, void* stream, uint32_t job_id,
+                             void* notifier);
+PB_API int pb_spin_info(uint32_t num_blocks, pb_launch_info* out);
+PB_API int pb_spin_launch(uint32_t num_blocks, uint64_t spin_ns, uint32_t* sink_dev, void* stream, uint32_t job_id,
+                          void* notifier);
+
+/* ------------------------------------------------------------------------ *
+ * Inference operators (the kernels the reference's TVM job adapters launch:
+ * jobs/tvm_<model>/tvm_<model>.cpp:24-47 -> generated conv / dense / pool /
+ * depthwise / elementwise kernels).  Device tensors are channels-last
+ * [H][W][Cs] with Cs = channel count rounded up to a 16-byte vector; dtype 0 = fp32,
+ * 1 = bf16.  Each launcher enqueues exactly one kernel on `stream`; every block of it
+ * reports start/end on `notifier` (may be NULL) for `job_id`.
+ * ------------------------------------------------------------------------ */
+typedef enum pb_stage_kind {
+    PB_STAGE_INPUT = 0,      /* NCHW fp32 -> channels-last dtype */
+    PB_STAGE_CONV_SIMT = 1,
+    PB_STAGE_CONV_UMMA = 2,  /* tcgen05 implicit GEMM */
+    PB_STAGE_DWCONV = 3,
+    PB_STAGE_DENSE = 4,
+    PB_STAGE_MAXPOOL = 5,
+    PB_STAGE_AVGPOOL = 6,
+    PB_STAGE_GAP = 7,
+    PB_STAGE_ADD = 8,
+    PB_STAGE_SOFTMAX = 9,
+    PB_STAGE_MNIST_FUSED = 10
+} pb_stage_kind;
+
+typedef struct pb_op_params {
+    int32_t dtype;            /* 0 fp32, 1 bf16 (activations and weights) */
+    int32_t C, H, W, Cs;      /* input: channels, height, width, channel stride */
+    int32_t K, P, Q, Ks;      /* output: channels written, height, width, channel stride of the output tensor */
+    int32_t out_c_off;        /* first output channel written (concatenation slice) */
+    int32_t R, S, stride_h, stride_w, pad_h, pad_w, groups;
+    int32_t act;              /* 0 none, 1 relu, 2 relu6 */
+    int32_t flags;            /* bit0 count_include_pad (avg pool); bit1 output is fp32 */
+    int32_t res_Cs;           /* channel stride of the residual tensor (0 = none) */
+    const void* x;            /* input activations */
+    const void* w;            /* weights in the layout pb_op_weight_layout reports */
+    const float* bias;        /* fp32 [K] or NULL */
+    const void* residual;     /* same dtype as x, [P][Q][res_Cs], or NULL */
+    void* y;                  /* output tensor base (slice offset applied by the kernel) */
+} pb_op_params;
+
+/* Geometry/resources the launch of `kind` with `p` will use. */
+PB_API int pb_op_info(int kind, const pb_op_params* p, pb_launch_info* out);
+PB_API int pb_op_launch(int kind, const pb_op_params* p, void* stream, uint32_t job_id, void* notifier);
+/* Converts OIHW fp32 host weights into the device layout `kind` expects.  Returns the byte
+ * size needed when dst_host is NULL, else fills dst_host (host memory) and returns the size. */
+PB_API int64_t pb_op_pack_weights(int kind, const pb_op_params* p, const float* w_oihw, void* dst_host);
+/* 1 if the tcgen05 implicit-GEMM kernel supports this convolution. */
+PB_API int pb_conv_umma_supported(const pb_op_params* p);
+/* Device-side error flag raised by bounded waits inside kernels (0 = none). */
+PB_API int pb_device_error_flag(int device, uint32_t* flag_out, int reset);
+
+/* ------------------------------------------------------------------------ *
+ * Model packs and instances: the graph executor behind the model job adapters
+ * (replaces tvm::runtime::Module::LoadFromFile + "run"/"get_input"/"get_output",
+ * jobs/tvm_mnist/tvm_mnist.cpp:24-33).
+ * ------------------------------------------------------------------------ */
+typedef struct pb_model pb_model;
+typedef struct pb_instance pb_instance;
+
+/* precision: -1 = the pack's own hint, 0 = fp32 SIMT kernels, 1 = bf16 (tcgen05 where supported). */
+PB_API int pb_model_load(const char* pack_path, int device, int precision, pb_model** out);
+PB_API void pb_model_destroy(pb_model* m);
+PB_API size_t pb_model_input_bytes(const pb_model* m);   /* NCHW fp32 */
+PB_API size_t pb_model_output_bytes(const pb_model* m);  /* fp32 vector */
+PB_API int pb_model_num_stages(const pb_model* m);       /* compute stages (kernels) per request */
+PB_API int pb_model_stage_info(const pb_model* m, int stage, pb_launch_info* out);
+PB_API const char* pb_model_stage_name(const pb_model* m, int stage);
+PB_API int pb_instance_create(pb_model* m, pb_instance** out);
+PB_API void pb_instance_destroy(pb_instance* inst);
+PB_API void* pb_instance_input_dev(pb_instance* inst);   /* device staging buffer, NCHW fp32 */
+PB_API void* pb_instance_output_dev(pb_instance* inst);  /* device fp32 output */
+PB_API int pb_instance_launch_stage(pb_instance* inst, int stage, void* stream, uint32_t job_id, void* notifier);
+/* Convenience for tests: H2D, every stage, D2H on one stream, then synchronise. */
+PB_API int pb_instance_run_sync(pb_instance* inst, const float* input_host, float* output_host);
+/* Copies tensor `t` of the pack (as NCHW fp32) to host; for layer-by-layer parity tests. */
+PB_API int pb_instance_read_tensor(pb_instance* inst, int tensor, float* dst_host, size_t dst_floats);
+/* Times stage `stage` alone: `iters` launches on a private stream between CUDA events, with an
+ * L2 flush (a write of flush_bytes) before each; returns mean microseconds in *us_out. */
+PB_API int pb_instance_time_stage(pb_instance* inst, int stage, int iters, size_t flush_bytes, double* us_out);
+
+/* ------------------------------------------------------------------------ *
+ * Server: scheduler + job registry + in-process client endpoint.
+ * Replaces llis_server's main loop and scheduler (src/server/server.cpp:29-35,43-80,
+ * src/server/scheduler_full3.cpp, src/server/registered_job.cpp:26-137,
+ * src/server/sm_resources.cpp).  One server per GPU; all calls on one thread.
+ * ------------------------------------------------------------------------ */
+typedef struct pb_server pb_server;
+
+typedef struct pb_server_config {
+    int32_t device;
+    uint32_t num_streams;        /* --num_streams, default 500 */
+    uint32_t extra_kernels;      /* --extra_kernels, default 2 */
+    float unfairness_threshold;  /* --unfair, default 1e6 */
+    uint32_t sched_sleep;        /* --sched_sleep, default 0 */
+    uint64_t ring_capacity;      /* 0 = 1<<20 */
+    const char* scheduler;       /* "full3" (default), "fifo", "fifo2" */
+    int32_t device_resident;     /* 1: model jobs skip their host<->device copies (inputs already in HBM) */
+} pb_server_config;
+
+PB_API void pb_server_config_default(pb_server_config* cfg);
+PB_API int pb_server_create(const pb_server_config* cfg, pb_server** out);
+PB_API void pb_server_destroy(pb_server* s);
+/* REGISTER_JOB: dlopen the plugin and call init_job (src/server/registered_job.cpp:26-59). */
+PB_API int pb_server_register_job(pb_server* s, const char* plugin_path, uint32_t* job_ref_id_out);
+/* Pinned I/O slot size the plugin asks for (include/llis/job/job.h:54-60). */
+PB_API int pb_server_job_io_bytes(pb_server* s, uint32_t job_ref_id, size_t* in_bytes, size_t* out_bytes,
+                                  size_t* slot_bytes);
+/* LAUNCH_JOB: io_ptr is a pinned host slot (input at 0, output at align8(input size));
+ * cookie comes back from pb_server_poll_done when the job ends. */
+PB_API int pb_server_launch(pb_server* s, uint32_t job_ref_id, void* io_ptr, uint64_t cookie);
+/* One iteration of the serve loop: at most `max_records` ring records, then return. */
+PB_API int pb_server_step(pb_server* s, int max_records);
+/* Completed jobs since the last call: fills cookies/errors, returns the count. */
+PB_API int pb_server_poll_done(pb_server* s, uint64_t* cookies, int32_t* errors, int max);
+PB_API uint64_t pb_server_num_decisions(const pb_server* s);
+PB_API uint32_t pb_server_jobs_in_flight(const pb_server* s);
+
+/* ------------------------------------------------------------------------ *
+ * Load generator + request router over one server per GPU
+ * (workload semantics of app/client.cpp:123-212,393-495).
+ * ------------------------------------------------------------------------ */
+#define PB_MAX_JOB_TYPES 8
+#define PB_MAX_GPUS 8
+
+typedef struct pb_loadgen_config {
+    int32_t num_gpus;
+    int32_t devices[PB_MAX_GPUS];
+    int32_t num_types;
+    const char* plugin_paths[PB_MAX_JOB_TYPES];
+    float proportions[PB_MAX_JOB_TYPES];          /* request mix, sums to 1 */
+    uint32_t max_outstanding[PB_MAX_JOB_TYPES];   /* per type and per GPU (instances in its pool) */
+    uint32_t concurrency;          /* total outstanding cap per GPU */
+    double mean_interarrival_us;   /* per GPU stream of arrivals; <= 0 = closed loop at `concurrency` */
+    double lognormal_sigma;        /* 0 = exponential (Poisson) arrivals */
+    uint32_t num_jobs;             /* measured requests per GPU */
+    uint32_t warmup_jobs;          /* un-measured requests per GPU issued first */
+    uint32_t seed;
+    int32_t device_resident;       /* 1: inputs already in HBM, copy stages skipped */
+    pb_server_config server;
+} pb_loadgen_config;
+
+typedef struct pb_latency_stats {
+    uint64_t count;
+    double mean_us, p50_us, p90_us, p95_us, p99_us, max_us, sd_us;
+} pb_latency_stats;
+
+typedef struct pb_loadgen_result {
+    double elapsed_us;               /* host clock: last completion - first arrival of the measured requests, over all GPUs */
+    double elapsed_event_ms;         /* max over GPUs of the CUDA-event time around the measured phase */
+    double throughput_rps;           /* total measured jobs / elapsed */
+    pb_latency_stats all;
+    pb_latency_stats per_type[PB_MAX_JOB_TYPES];
+    double per_gpu_rps[PB_MAX_GPUS];
+    uint64_t kernels_launched;       /* compute stages dispatched in the measured window */
+    uint64_t records_consumed;
+    uint64_t decisions;
+    uint64_t h2d_bytes, d2h_bytes;
+    int32_t errors;
+} pb_loadgen_result;
+
+PB_API void pb_loadgen_config_default(pb_loadgen_config* cfg);
+PB_API int pb_loadgen_run(const pb_loadgen_config* cfg, pb_loadgen_result* out);
+
+/* ------------------------------------------------------------------------ *
+ * Scheduler replay (no GPU needed): feeds a recorded event trace to the product
+ * scheduler with fake streams/notifiers and returns its decision log, to be
+ * compared bit-for-bit with the oracle's restatement of
+ * src/server/scheduler_full3.cpp:123-459 and include/llis/server/scheduler_full3.h:26-208.
+ * ------------------------------------------------------------------------ */
+typedef struct pb_replay_type {
+    uint32_t num_stages;
+    const uint8_t* stage_is_mem;        /* [num_stages] */
+    const uint8_t* stage_pre_notify;    /* [num_stages] */
+    const uint32_t* stage_blocks;       /* [num_stages] */
+    const uint32_t* stage_threads;
+    const uint32_t* stage_smem;
+    const uint32_t* stage_regs;
+} pb_replay_type;
+
+typedef struct pb_replay_event {
+    uint32_t kind;      /* 0 NEW_JOB(type = a), 1 BLOCK_START(job_id = a, num = b), 2 BLOCK_END, 3 MEM_FINISH(job_id = a) */
+    uint32_t a, b;
+    double time_us;
+} pb_replay_event;
+
+typedef struct pb_replay_decision {
+    uint32_t event_index;   /* event being handled when the dispatch happened */
+    uint32_t job_id, type, stage;
+    uint32_t is_mem, unfit, stream_slot, notifier_slot;
+    double priority;
+} pb_replay_decision;
+
+typedef struct pb_replay_config {
+    uint32_t num_streams, extra_kernels;
+    double unfairness_threshold;
+    int32_t total_regs, total_smem, total_threads, total_blocks;  /* whole-GPU aggregate (sm_resources.cpp:17-34) */
+} pb_replay_config;
+
+PB_API int pb_sched_replay(const pb_replay_config* cfg, const pb_replay_type* types, uint32_t num_types,
+                           const pb_replay_event* events, uint32_t num_events, pb_replay_decision* decisions,
+                           uint32_t max_decisions, uint32_t* num_decisions_out, uint32_t* num_finished_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAELLA_B200_H */

@@ -1,0 +1,489 @@
+// Model packs and instances: the graph executor behind the model job adapters.
+//
+// A pack (written by paella_b200/packer.py) is a flat operator table plus fp32 weights
+// in boundary layouts (NCHW / OIHW).  Loading a pack turns it into a list of STAGES, one
+// kernel launch each, with weights repacked for the kernel chosen per layer:
+//   tcgen05 implicit GEMM for dense convolutions in bf16, the vectorised depthwise / pool /
+//   dense / add / softmax kernels, direct convolution as the fp32 path.
+// An instance owns the activation buffers of one in-flight request.
+//
+// Replaces what the reference gets from tvm::runtime (Module::LoadFromFile, "run",
+// "get_input", "get_output": jobs/tvm_mnist/tvm_mnist.cpp:24-33); one stage here is one of
+// the kernels its graph executor launches between two scheduler yields.
+#include <cuda_bf16.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "ops.h"
+#include "pb_common.h"
+
+namespace {
+
+constexpr uint32_t kNone = 0xFFFFFFFFu;
+enum { OP_CONV = 1, OP_DENSE = 2, OP_MAXPOOL = 3, OP_AVGPOOL = 4, OP_GAP = 5, OP_ADD = 6, OP_SOFTMAX = 7 };
+
+struct PackOp {
+    uint32_t type, in0, in1, out, rsv0, out_c_off, cin, cout, r, s, stride_h, stride_w, pad_h, pad_w, groups, act, flags,
+        rsv1, w_off_lo, w_off_hi, b_off_lo, b_off_hi, rsv2, rsv3;
+};
+static_assert(sizeof(PackOp) == 96, "pack op record is 96 bytes");
+
+struct TensorInfo {
+    int C, H, W, Cs;
+    size_t offset;   // in the activation arena (bytes); unused for the fp32 output tensor
+    size_t bytes;
+};
+
+struct Stage {
+    int kind;
+    pb_op_params p;           // pointers hold arena OFFSETS (+1) until an instance resolves them
+    size_t x_off, y_off, res_off;
+    bool x_is_input, y_is_output, has_res;
+    void* w_dev = nullptr;
+    float* bias_dev = nullptr;
+    pb::ConvUmmaPlan* plan = nullptr;
+    pb_launch_info info;
+    std::string name;
+    int out_tensor;
+};
+
+}  // namespace
+
+struct pb_model {
+    int device = 0;
+    int dtype = 1;
+    std::string name;
+    std::vector<TensorInfo> tensors;
+    std::vector<Stage> stages;
+    int t_in = 0, t_out = 0;
+    size_t arena_bytes = 0;
+    size_t in_floats = 0, out_floats = 0;
+    bool mnist_fused = false;
+    // fused MNIST weights (device)
+    float *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr, *wd = nullptr, *bd = nullptr;
+    std::vector<void*> allocs;
+};
+
+struct pb_instance {
+    pb_model* m = nullptr;
+    char* arena = nullptr;
+    float* in_dev = nullptr;
+    float* out_dev = nullptr;
+    std::vector<pb_op_params> params;   // per stage, pointers resolved
+};
+
+namespace {
+
+int upload(pb_model* m, const void* host, size_t bytes, void** dev_out) {
+    void* d = nullptr;
+    PB_CUDA(cudaMalloc(&d, bytes > 0 ? bytes : 16));
+    m->allocs.push_back(d);
+    if (bytes > 0) PB_CUDA(cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice));
+    *dev_out = d;
+    return PB_OK;
+}
+
+bool env_flag(const char* name, bool dflt) {
+    const char* v = getenv(name);
+    if (!v || !*v) return dflt;
+    return !(v[0] == '0' || v[0] == 'n' || v[0] == 'N' || v[0] == 'f' || v[0] == 'F');
+}
+
+bool is_mnist_topology(const std::vector<PackOp>& ops, const std::vector<TensorInfo>& t, int t_in) {
+    if (ops.size() != 5) return false;
+    const PackOp& c1 = ops[0]; const PackOp& p1 = ops[1]; const PackOp& c2 = ops[2]; const PackOp& p2 = ops[3]; const PackOp& fc = ops[4];
+    if (t[t_in].C != 1 || t[t_in].H != 28 || t[t_in].W != 28) return false;
+    auto conv5 = [](const PackOp& o, uint32_t ci, uint32_t co) {
+        return o.type == OP_CONV && o.cin == ci && o.cout == co && o.r == 5 && o.s == 5 && o.stride_h == 1 && o.stride_w == 1 &&
+               o.pad_h == 2 && o.pad_w == 2 && o.groups == 1 && o.act == 1 && o.in1 == kNone && o.out_c_off == 0;
+    };
+    auto pool = [](const PackOp& o, uint32_t k) {
+        return o.type == OP_MAXPOOL && o.r == k && o.s == k && o.stride_h == k && o.stride_w == k && o.pad_h == 0 && o.pad_w == 0 &&
+               o.out_c_off == 0;
+    };
+    return conv5(c1, 1, 8) && pool(p1, 2) && conv5(c2, 8, 16) && pool(p2, 3) && fc.type == OP_DENSE && fc.cin == 256 &&
+           fc.cout == 10 && fc.act == 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pb_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
+    PB_REQUIRE(p && out, "pb_op_info: NULL argument");
+    if (kind == PB_STAGE_CONV_UMMA) return pb::conv_umma_info(p, out);
+    if (kind == PB_STAGE_MNIST_FUSED) return pb::mnist_fused_info(out);
+    return pb::simple_op_info(kind, p, out);
+}
+
+int pb_op_launch(int kind, const pb_op_params* p, void* stream, uint32_t job_id, void* notifier) {
+    PB_REQUIRE(p != nullptr, "pb_op_launch: NULL params");
+    if (kind == PB_STAGE_CONV_UMMA) return pb::conv_umma_launch(p, (cudaStream_t)stream, job_id, notifier);
+    return pb::simple_op_launch(kind, p, (cudaStream_t)stream, job_id, notifier);
+}
+
+int64_t pb_op_pack_weights(int kind, const pb_op_params* p, const float* w_oihw, void* dst_host) {
+    if (!p || !w_oihw) { pb::set_error("pb_op_pack_weights: NULL argument"); return PB_ERR_INVALID; }
+    if (kind == PB_STAGE_CONV_UMMA) return pb::conv_umma_pack_weights(p, w_oihw, dst_host);
+    return pb::simple_pack_weights(kind, p, w_oihw, dst_host);
+}
+
+int pb_conv_umma_supported(const pb_op_params* p) { return p && pb::conv_umma_supported(p) ? 1 : 0; }
+
+int pb_model_load(const char* pack_path, int device, int precision, pb_model** out) {
+    PB_REQUIRE(pack_path && out, "pb_model_load: NULL argument");
+    FILE* f = fopen(pack_path, "rb");
+    if (!f) { pb::set_error("cannot open model pack %s", pack_path); return PB_ERR_IO; }
+    fseek(f, 0, SEEK_END);
+    const long fsize = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    std::vector<uint8_t> data((size_t)(fsize > 0 ? fsize : 0));
+    const size_t got = fsize > 0 ? fread(data.data(), 1, data.size(), f) : 0;
+    fclose(f);
+    if (got != data.size() || data.size() < 64 || memcmp(data.data(), "PB2PACK\0", 8) != 0) {
+        pb::set_error("%s is not a model pack", pack_path);
+        return PB_ERR_IO;
+    }
+    uint32_t hdr[6];
+    memcpy(hdr, data.data() + 8, sizeof(hdr));
+    uint64_t n_floats;
+    memcpy(&n_floats, data.data() + 32, 8);
+    const uint32_t version = hdr[0], nt = hdr[1], no = hdr[2], t_in = hdr[3], t_out = hdr[4], hint = hdr[5];
+    const size_t need = 64 + (size_t)nt * 16 + (size_t)no * (96 + 64) + (size_t)n_floats * 4;
+    if (version != 1 || need != data.size() || t_in >= nt || t_out >= nt) {
+        pb::set_error("%s: malformed pack (version %u, %zu bytes, expected %zu)", pack_path, version, data.size(), need);
+        return PB_ERR_IO;
+    }
+    PB_CUDA(cudaSetDevice(device));
+
+    pb_model* m = new pb_model();
+    m->device = device;
+    m->dtype = precision < 0 ? (int)hint : precision;
+    m->name = std::string((const char*)data.data() + 40, strnlen((const char*)data.data() + 40, 24));
+    m->t_in = (int)t_in;
+    m->t_out = (int)t_out;
+    const int vec = m->dtype == 0 ? 4 : 8;
+    const size_t es = m->dtype == 0 ? 4 : 2;
+
+    const uint8_t* pt = data.data() + 64;
+    for (uint32_t i = 0; i < nt; ++i) {
+        uint32_t rec[4];
+        memcpy(rec, pt + 16 * i, 16);
+        TensorInfo ti;
+        ti.C = (int)rec[0]; ti.H = (int)rec[1]; ti.W = (int)rec[2];
+        ti.Cs = pb::round_up(ti.C, vec);
+        ti.bytes = pb::round_up((size_t)ti.H * ti.W * ti.Cs * es, (size_t)256);
+        ti.offset = m->arena_bytes;
+        if ((int)i != m->t_out) m->arena_bytes += ti.bytes;
+        m->tensors.push_back(ti);
+    }
+    std::vector<PackOp> ops(no);
+    memcpy(ops.data(), pt + 16 * (size_t)nt, (size_t)no * 96);
+    const uint8_t* pn = pt + 16 * (size_t)nt + 96 * (size_t)no;
+    const float* W = reinterpret_cast<const float*>(pn + 64 * (size_t)no);
+    m->in_floats = (size_t)m->tensors[t_in].C * m->tensors[t_in].H * m->tensors[t_in].W;
+    m->out_floats = (size_t)m->tensors[t_out].C * m->tensors[t_out].H * m->tensors[t_out].W;
+
+#define PB_FAIL_LOAD(rc_)            \
+    do {                             \
+        int rc2_ = (rc_);            \
+        if (rc2_ != PB_OK) {         \
+            pb_model_destroy(m);     \
+            return rc2_;             \
+        }                            \
+    } while (0)
+
+    // ---- MNIST in one kernel (fp32 only) ----
+    if (m->dtype == 0 && env_flag("PB_FUSE_MNIST", true) && is_mnist_topology(ops, m->tensors, m->t_in)) {
+        m->mnist_fused = true;
+        auto woff = [](const PackOp& o) { return ((uint64_t)o.w_off_hi << 32) | o.w_off_lo; };
+        auto boff = [](const PackOp& o) { return ((uint64_t)o.b_off_hi << 32) | o.b_off_lo; };
+        std::vector<float> w1(200), w2(3200), wd(2560);
+        const float* s1 = W + woff(ops[0]);   // [8][1][5][5]
+        for (int k = 0; k < 8; ++k) for (int t = 0; t < 25; ++t) w1[t * 8 + k] = s1[k * 25 + t];
+        const float* s2 = W + woff(ops[2]);   // [16][8][5][5]
+        for (int k = 0; k < 16; ++k) for (int c = 0; c < 8; ++c) for (int t = 0; t < 25; ++t) w2[(t * 8 + c) * 16 + k] = s2[(k * 8 + c) * 25 + t];
+        const float* sd = W + woff(ops[4]);   // [10][16*4*4] in (c, h, w) order -> (h, w, c)
+        for (int o = 0; o < 10; ++o) for (int c = 0; c < 16; ++c) for (int hw = 0; hw < 16; ++hw) wd[o * 256 + hw * 16 + c] = sd[o * 256 + c * 16 + hw];
+        PB_FAIL_LOAD(upload(m, w1.data(), 800, (void**)&m->w1));
+        PB_FAIL_LOAD(upload(m, W + boff(ops[0]), 32, (void**)&m->b1));
+        PB_FAIL_LOAD(upload(m, w2.data(), 12800, (void**)&m->w2));
+        PB_FAIL_LOAD(upload(m, W + boff(ops[2]), 64, (void**)&m->b2));
+        PB_FAIL_LOAD(upload(m, wd.data(), 10240, (void**)&m->wd));
+        PB_FAIL_LOAD(upload(m, W + boff(ops[4]), 40, (void**)&m->bd));
+        Stage st{};
+        st.kind = PB_STAGE_MNIST_FUSED;
+        st.name = "mnist_fused";
+        st.x_is_input = true; st.y_is_output = true; st.has_res = false;
+        st.out_tensor = m->t_out;
+        memset(&st.p, 0, sizeof(st.p));
+        pb::mnist_fused_info(&st.info);
+        m->stages.push_back(st);
+        *out = m;
+        return PB_OK;
+    }
+
+    // ---- stage 0: NCHW fp32 -> channels-last ----
+    {
+        Stage st{};
+        st.kind = PB_STAGE_INPUT;
+        st.name = "input_layout";
+        const TensorInfo& ti = m->tensors[t_in];
+        memset(&st.p, 0, sizeof(st.p));
+        st.p.dtype = m->dtype; st.p.C = ti.C; st.p.H = ti.H; st.p.W = ti.W; st.p.Cs = ti.C;
+        st.p.K = ti.C; st.p.P = ti.H; st.p.Q = ti.W; st.p.Ks = ti.Cs;
+        st.x_is_input = true; st.y_is_output = false; st.has_res = false;
+        st.y_off = ti.offset;
+        st.out_tensor = (int)t_in;
+        PB_FAIL_LOAD(pb::simple_op_info(st.kind, &st.p, &st.info));
+        m->stages.push_back(st);
+    }
+
+    const bool use_umma = m->dtype == 1 && !env_flag("PB_DISABLE_UMMA", false);
+    for (uint32_t i = 0; i < no; ++i) {
+        const PackOp& o = ops[i];
+        if (o.in0 >= nt || o.out >= nt || (o.in1 != kNone && o.in1 >= nt)) {
+            pb::set_error("%s: op %u references a missing tensor", pack_path, i);
+            PB_FAIL_LOAD(PB_ERR_IO);
+        }
+        const TensorInfo& tx = m->tensors[o.in0];
+        const TensorInfo& ty = m->tensors[o.out];
+        const uint64_t w_off = ((uint64_t)o.w_off_hi << 32) | o.w_off_lo;
+        const uint64_t b_off = ((uint64_t)o.b_off_hi << 32) | o.b_off_lo;
+        Stage st{};
+        st.name = std::string((const char*)pn + 64 * i, strnlen((const char*)pn + 64 * i, 64));
+        st.out_tensor = (int)o.out;
+        pb_op_params& p = st.p;
+        memset(&p, 0, sizeof(p));
+        p.dtype = m->dtype;
+        p.C = tx.C; p.H = tx.H; p.W = tx.W; p.Cs = tx.Cs;
+        p.K = (int)o.cout; p.P = ty.H; p.Q = ty.W; p.Ks = ty.Cs;
+        p.out_c_off = (int)o.out_c_off;
+        p.R = (int)o.r; p.S = (int)o.s; p.stride_h = (int)o.stride_h; p.stride_w = (int)o.stride_w;
+        p.pad_h = (int)o.pad_h; p.pad_w = (int)o.pad_w; p.groups = (int)(o.groups ? o.groups : 1);
+        p.act = (int)o.act; p.flags = (int)(o.flags & 1);
+        st.x_is_input = false;
+        st.x_off = tx.offset;
+        st.y_is_output = (int)o.out == m->t_out;
+        st.y_off = ty.offset;
+        st.has_res = o.in1 != kNone;
+        if (st.has_res) { st.res_off = m->tensors[o.in1].offset; p.res_Cs = m->tensors[o.in1].Cs; p.residual = (const void*)1; }
+        if (st.y_is_output) p.flags |= 2;
+
+        std::vector<uint8_t> packed;
+        switch (o.type) {
+            case OP_CONV: {
+                if (st.y_is_output) { pb::set_error("a convolution cannot write the fp32 model output"); PB_FAIL_LOAD(PB_ERR_INVALID); }
+                const bool dw = p.groups > 1 && p.groups == p.C && p.K == p.C;
+                if (dw) st.kind = PB_STAGE_DWCONV;
+                else if (use_umma && pb::conv_umma_supported(&p)) st.kind = PB_STAGE_CONV_UMMA;
+                else st.kind = PB_STAGE_CONV_SIMT;
+                // UMMA sees the padded channel stride as its input-channel count; SIMT uses the real one.
+                const int64_t nbytes = pb_op_pack_weights(st.kind, &p, W + w_off, nullptr);
+                if (nbytes < 0) PB_FAIL_LOAD((int)nbytes);
+                packed.resize((size_t)nbytes);
+                pb_op_pack_weights(st.kind, &p, W + w_off, packed.data());
+                PB_FAIL_LOAD(upload(m, packed.data(), packed.size(), &st.w_dev));
+                PB_FAIL_LOAD(upload(m, W + b_off, (size_t)p.K * 4, (void**)&st.bias_dev));
+                break;
+            }
+            case OP_DENSE: {
+                st.kind = PB_STAGE_DENSE;
+                // input is [H][W][Cs] on the device; boundary weights are [K][C*H*W] in (c, h, w) order
+                const int n_dev = tx.H * tx.W * tx.Cs;
+                packed.assign((size_t)p.K * n_dev * (m->dtype == 0 ? 4 : 2), 0);
+                const float* src = W + w_off;
+                for (int k = 0; k < p.K; ++k)
+                    for (int c = 0; c < tx.C; ++c)
+                        for (int hw = 0; hw < tx.H * tx.W; ++hw)
+                            pb::store_elem(packed.data(), (size_t)k * n_dev + (size_t)hw * tx.Cs + c,
+                                           src[(size_t)k * o.cin + (size_t)c * tx.H * tx.W + hw], m->dtype);
+                p.C = n_dev; p.H = 1; p.W = 1; p.Cs = n_dev;
+                PB_FAIL_LOAD(upload(m, packed.data(), packed.size(), &st.w_dev));
+                PB_FAIL_LOAD(upload(m, W + b_off, (size_t)p.K * 4, (void**)&st.bias_dev));
+                break;
+            }
+            case OP_MAXPOOL: st.kind = PB_STAGE_MAXPOOL; p.K = tx.C; break;
+            case OP_AVGPOOL: st.kind = PB_STAGE_AVGPOOL; p.K = tx.C; break;
+            case OP_GAP: st.kind = PB_STAGE_GAP; p.K = tx.C; break;
+            case OP_ADD: st.kind = PB_STAGE_ADD; break;
+            case OP_SOFTMAX: st.kind = PB_STAGE_SOFTMAX; p.C = tx.C * tx.H * tx.W; break;
+            default:
+                pb::set_error("%s: unknown operator type %u", pack_path, o.type);
+                PB_FAIL_LOAD(PB_ERR_IO);
+        }
+        if (st.y_is_output && !(st.kind == PB_STAGE_DENSE || st.kind == PB_STAGE_GAP || st.kind == PB_STAGE_SOFTMAX)) {
+            pb::set_error("stage kind %d cannot write the fp32 model output", st.kind);
+            PB_FAIL_LOAD(PB_ERR_INVALID);
+        }
+        p.w = st.w_dev;
+        p.bias = st.bias_dev;
+        PB_FAIL_LOAD(pb_op_info(st.kind, &p, &st.info));
+        if (st.kind == PB_STAGE_CONV_UMMA) PB_FAIL_LOAD(pb::conv_umma_plan_create(&p, st.w_dev, &st.plan));
+        m->stages.push_back(st);
+    }
+#undef PB_FAIL_LOAD
+    *out = m;
+    return PB_OK;
+}
+
+void pb_model_destroy(pb_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    for (auto& st : m->stages) if (st.plan) pb::conv_umma_plan_destroy(st.plan);
+    for (void* d : m->allocs) cudaFree(d);
+    delete m;
+}
+
+size_t pb_model_input_bytes(const pb_model* m) { return m ? m->in_floats * 4 : 0; }
+size_t pb_model_output_bytes(const pb_model* m) { return m ? m->out_floats * 4 : 0; }
+int pb_model_num_stages(const pb_model* m) { return m ? (int)m->stages.size() : 0; }
+
+int pb_model_stage_info(const pb_model* m, int stage, pb_launch_info* out) {
+    PB_REQUIRE(m && out && stage >= 0 && stage < (int)m->stages.size(), "pb_model_stage_info: bad stage %d", stage);
+    *out = m->stages[stage].info;
+    return PB_OK;
+}
+
+const char* pb_model_stage_name(const pb_model* m, int stage) {
+    if (!m || stage < 0 || stage >= (int)m->stages.size()) return "";
+    return m->stages[stage].name.c_str();
+}
+
+int pb_instance_create(pb_model* m, pb_instance** out) {
+    PB_REQUIRE(m && out, "pb_instance_create: NULL argument");
+    PB_CUDA(cudaSetDevice(m->device));
+    pb_instance* in = new pb_instance();
+    in->m = m;
+    cudaError_t e = cudaMalloc((void**)&in->arena, m->arena_bytes + 256);
+    if (e == cudaSuccess) e = cudaMemset(in->arena, 0, m->arena_bytes + 256);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&in->in_dev, pb::round_up(m->in_floats * 4, (size_t)256));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&in->out_dev, pb::round_up(m->out_floats * 4, (size_t)256));
+    if (e == cudaSuccess) e = cudaMemset(in->out_dev, 0, pb::round_up(m->out_floats * 4, (size_t)256));
+    if (e != cudaSuccess) {
+        pb_instance_destroy(in);
+        return pb::cuda_fail(e, "instance buffers", __FILE__, __LINE__);
+    }
+    in->params.resize(m->stages.size());
+    for (size_t i = 0; i < m->stages.size(); ++i) {
+        const Stage& st = m->stages[i];
+        pb_op_params p = st.p;
+        p.x = st.x_is_input ? (const void*)in->in_dev : (const void*)(in->arena + st.x_off);
+        p.y = st.y_is_output ? (void*)in->out_dev : (void*)(in->arena + st.y_off);
+        p.residual = st.has_res ? (const void*)(in->arena + st.res_off) : nullptr;
+        in->params[i] = p;
+    }
+    *out = in;
+    return PB_OK;
+}
+
+void pb_instance_destroy(pb_instance* in) {
+    if (!in) return;
+    if (in->m) cudaSetDevice(in->m->device);
+    if (in->arena) cudaFree(in->arena);
+    if (in->in_dev) cudaFree(in->in_dev);
+    if (in->out_dev) cudaFree(in->out_dev);
+    delete in;
+}
+
+void* pb_instance_input_dev(pb_instance* in) { return in ? in->in_dev : nullptr; }
+void* pb_instance_output_dev(pb_instance* in) { return in ? in->out_dev : nullptr; }
+
+int pb_instance_launch_stage(pb_instance* in, int stage, void* stream, uint32_t job_id, void* notifier) {
+    PB_REQUIRE(in && stage >= 0 && stage < (int)in->params.size(), "pb_instance_launch_stage: bad stage %d", stage);
+    const Stage& st = in->m->stages[stage];
+    const pb_op_params* p = &in->params[stage];
+    switch (st.kind) {
+        case PB_STAGE_MNIST_FUSED: {
+            const pb_model* m = in->m;
+            return pb::mnist_fused_launch(in->in_dev, m->w1, m->b1, m->w2, m->b2, m->wd, m->bd, in->out_dev, (cudaStream_t)stream,
+                                          job_id, notifier);
+        }
+        case PB_STAGE_CONV_UMMA:
+            return pb::conv_umma_launch_planned(st.plan, p, (cudaStream_t)stream, job_id, notifier);
+        default:
+            return pb::simple_op_launch(st.kind, p, (cudaStream_t)stream, job_id, notifier);
+    }
+}
+
+int pb_instance_run_sync(pb_instance* in, const float* input_host, float* output_host) {
+    PB_REQUIRE(in && input_host && output_host, "pb_instance_run_sync: NULL argument");
+    pb_model* m = in->m;
+    PB_CUDA(cudaSetDevice(m->device));
+    cudaStream_t st;
+    PB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    int rc = PB_OK;
+    cudaError_t e = cudaMemcpyAsync(in->in_dev, input_host, m->in_floats * 4, cudaMemcpyHostToDevice, st);
+    for (int i = 0; e == cudaSuccess && rc == PB_OK && i < (int)m->stages.size(); ++i) rc = pb_instance_launch_stage(in, i, st, 0, nullptr);
+    if (e == cudaSuccess && rc == PB_OK) e = cudaMemcpyAsync(output_host, in->out_dev, m->out_floats * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && rc == PB_OK) e = cudaStreamSynchronize(st);
+    cudaStreamDestroy(st);
+    if (rc != PB_OK) return rc;
+    if (e != cudaSuccess) return pb::cuda_fail(e, "pb_instance_run_sync", __FILE__, __LINE__);
+    return PB_OK;
+}
+
+int pb_instance_read_tensor(pb_instance* in, int tensor, float* dst, size_t dst_floats) {
+    PB_REQUIRE(in && dst && tensor >= 0 && tensor < (int)in->m->tensors.size(), "pb_instance_read_tensor: bad tensor %d", tensor);
+    pb_model* m = in->m;
+    const TensorInfo& t = m->tensors[tensor];
+    const size_t n = (size_t)t.C * t.H * t.W;
+    PB_REQUIRE(dst_floats >= n, "pb_instance_read_tensor: destination too small");
+    PB_CUDA(cudaSetDevice(m->device));
+    PB_CUDA(cudaDeviceSynchronize());
+    if (tensor == m->t_out) {
+        PB_CUDA(cudaMemcpy(dst, in->out_dev, n * 4, cudaMemcpyDeviceToHost));
+        return PB_OK;
+    }
+    if (m->mnist_fused) { pb::set_error("intermediate tensors do not exist in the fused MNIST kernel"); return PB_ERR_INVALID; }
+    const size_t es = m->dtype == 0 ? 4 : 2;
+    std::vector<uint8_t> raw((size_t)t.H * t.W * t.Cs * es);
+    PB_CUDA(cudaMemcpy(raw.data(), in->arena + t.offset, raw.size(), cudaMemcpyDeviceToHost));
+    for (int c = 0; c < t.C; ++c)
+        for (int hw = 0; hw < t.H * t.W; ++hw) {
+            const size_t s = (size_t)hw * t.Cs + c;
+            float v;
+            if (m->dtype == 0) v = reinterpret_cast<const float*>(raw.data())[s];
+            else { uint32_t u = (uint32_t)reinterpret_cast<const uint16_t*>(raw.data())[s] << 16; memcpy(&v, &u, 4); }
+            dst[(size_t)c * t.H * t.W + hw] = v;
+        }
+    return PB_OK;
+}
+
+int pb_instance_time_stage(pb_instance* in, int stage, int iters, size_t flush_bytes, double* us_out) {
+    PB_REQUIRE(in && us_out && iters > 0 && stage >= 0 && stage < (int)in->params.size(), "pb_instance_time_stage: bad arguments");
+    PB_CUDA(cudaSetDevice(in->m->device));
+    cudaStream_t st;
+    PB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    void* flush = nullptr;
+    if (flush_bytes) PB_CUDA(cudaMalloc(&flush, flush_bytes));
+    cudaEvent_t e0, e1;
+    PB_CUDA(cudaEventCreate(&e0));
+    PB_CUDA(cudaEventCreate(&e1));
+    int rc = PB_OK;
+    double total_ms = 0;
+    for (int i = 0; i < 3 && rc == PB_OK; ++i) rc = pb_instance_launch_stage(in, stage, st, 0, nullptr);   // warm-up
+    for (int i = 0; i < iters && rc == PB_OK; ++i) {
+        if (flush) cudaMemsetAsync(flush, i & 0xff, flush_bytes, st);
+        cudaEventRecord(e0, st);
+        rc = pb_instance_launch_stage(in, stage, st, 0, nullptr);
+        cudaEventRecord(e1, st);
+        if (cudaEventSynchronize(e1) != cudaSuccess) { rc = PB_ERR_CUDA; pb::set_error("timing run failed: %s", cudaGetErrorString(cudaGetLastError())); break; }
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        total_ms += ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (flush) cudaFree(flush);
+    cudaStreamDestroy(st);
+    if (rc != PB_OK) return rc;
+    *us_out = total_ms * 1000.0 / iters;
+    return PB_OK;
+}
+
+}  // extern "C"

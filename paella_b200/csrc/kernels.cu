@@ -1,0 +1,650 @@
+// Inference operators other than the tensor-core convolution: channels-last
+// ([H][W][Cs]) kernels for layout conversion, direct (SIMT) convolution, depthwise
+// convolution, pooling, dense, add and softmax.  These are the memory-bound members
+// of the kernel family the reference's TVM adapters launch
+// (jobs/tvm_<model>/tvm_<model>.cpp:24-47); every kernel reports block start/end on
+// the job's notifier exactly once per block.
+//
+// Access pattern: the channel dimension is innermost and padded to a 16-byte vector
+// (4 fp32 / 8 bf16), so one thread moves one 128-bit vector and a warp reads a
+// contiguous 512-byte span whenever Cs >= 32 vectors.
+#include <cuda_bf16.h>
+#include <llis/job/finished_block_notifier.h>
+
+#include <cstring>
+
+#include "ops.h"
+#include "pb_common.h"
+
+using llis::job::FinishedBlockNotifier;
+
+namespace pb {
+
+// ---- 128-bit vectors of activations ---------------------------------------
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    float v[4];
+    __device__ __forceinline__ static Vec load(const float* p) {
+        Vec r; const float4 t = *reinterpret_cast<const float4*>(p);
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; return r;
+    }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    float v[8];
+    __device__ __forceinline__ static Vec load(const __nv_bfloat16* p) {
+        Vec r; const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            r.v[2 * i] = __uint_as_float(u[i] << 16);
+            r.v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+        return r;
+    }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+        uint32_t u[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            u[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(u[0], u[1], u[2], u[3]);
+    }
+};
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float act_fn(float v, int act) {
+    if (act == 1) return fmaxf(v, 0.f);
+    if (act == 2) return fminf(fmaxf(v, 0.f), 6.f);
+    return v;
+}
+
+#define PB_NOTIFY_START() if (nf) nf->start(job_id)
+#define PB_NOTIFY_END() if (nf) nf->end(job_id)
+
+// ---- NCHW fp32 -> channels-last T ------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) input_transform_kernel(const float* __restrict__ x, T* __restrict__ y, int C, int HW,
+                                                              int Cs, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    const int pix = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix < HW) {
+        for (int c0 = 0; c0 < Cs; c0 += Vec<T>::N) {
+            Vec<T> o;
+#pragma unroll
+            for (int j = 0; j < Vec<T>::N; ++j) o.v[j] = (c0 + j < C) ? x[(size_t)(c0 + j) * HW + pix] : 0.f;
+            o.store(y + (size_t)pix * Cs + c0);
+        }
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- direct convolution ------------------------------------------------------
+// One thread per (output pixel, output channel).  Weights [R][S][C/groups][K]: a warp
+// reads consecutive k (coalesced) and shares the input value (broadcast).
+template <typename T>
+__global__ void __launch_bounds__(256) conv_simt_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    const T* __restrict__ x = static_cast<const T*>(a.x);
+    const T* __restrict__ w = static_cast<const T*>(a.w);
+    const int total = a.P * a.Q * a.K;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) {
+        const int k = idx % a.K;
+        const int pix = idx / a.K;
+        const int q = pix % a.Q, p = pix / a.Q;
+        const int cg = a.C / a.groups;
+        const int g = k / (a.K / a.groups);
+        float acc = 0.f;
+        for (int r = 0; r < a.R; ++r) {
+            const int ih = p * a.stride_h + r - a.pad_h;
+            if (ih < 0 || ih >= a.H) continue;
+            for (int s = 0; s < a.S; ++s) {
+                const int iw = q * a.stride_w + s - a.pad_w;
+                if (iw < 0 || iw >= a.W) continue;
+                const T* xp = x + ((size_t)ih * a.W + iw) * a.Cs + g * cg;
+                const T* wp = w + ((size_t)(r * a.S + s) * cg) * a.K + k;
+                for (int c = 0; c < cg; ++c) acc = fmaf(to_f<T>(xp[c]), to_f<T>(wp[(size_t)c * a.K]), acc);
+            }
+        }
+        if (a.bias) acc += a.bias[k];
+        if (a.residual) acc += to_f<T>(static_cast<const T*>(a.residual)[(size_t)pix * a.res_Cs + k]);
+        static_cast<T*>(a.y)[(size_t)pix * a.Ks + a.out_c_off + k] = from_f<T>(act_fn(acc, a.act));
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- depthwise convolution -----------------------------------------------------
+// One thread per (output pixel, channel vector); weights [R][S][Cs].
+template <typename T>
+__global__ void __launch_bounds__(256) dwconv_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    constexpr int N = Vec<T>::N;
+    const int cv = a.Cs / N;
+    const int total = a.P * a.Q * cv;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) {
+        const int c0 = (idx % cv) * N;
+        const int pix = idx / cv;
+        const int q = pix % a.Q, p = pix / a.Q;
+        const T* __restrict__ x = static_cast<const T*>(a.x);
+        const T* __restrict__ w = static_cast<const T*>(a.w);
+        float acc[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = 0.f;
+        for (int r = 0; r < a.R; ++r) {
+            const int ih = p * a.stride_h + r - a.pad_h;
+            if (ih < 0 || ih >= a.H) continue;
+            for (int s = 0; s < a.S; ++s) {
+                const int iw = q * a.stride_w + s - a.pad_w;
+                if (iw < 0 || iw >= a.W) continue;
+                const Vec<T> xv = Vec<T>::load(x + ((size_t)ih * a.W + iw) * a.Cs + c0);
+                const Vec<T> wv = Vec<T>::load(w + (size_t)(r * a.S + s) * a.Cs + c0);
+#pragma unroll
+                for (int j = 0; j < N; ++j) acc[j] = fmaf(xv.v[j], wv.v[j], acc[j]);
+            }
+        }
+        Vec<T> o;
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            float v = acc[j] + ((a.bias && c0 + j < a.K) ? a.bias[c0 + j] : 0.f);
+            o.v[j] = (c0 + j < a.K) ? act_fn(v, a.act) : 0.f;
+        }
+        o.store(static_cast<T*>(a.y) + (size_t)pix * a.Ks + a.out_c_off + c0);
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- pooling -------------------------------------------------------------------
+template <typename T, bool kMax>
+__global__ void __launch_bounds__(256) pool_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    constexpr int N = Vec<T>::N;
+    const int cv = a.Cs / N;
+    const int total = a.P * a.Q * cv;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) {
+        const int c0 = (idx % cv) * N;
+        const int pix = idx / cv;
+        const int q = pix % a.Q, p = pix / a.Q;
+        const T* __restrict__ x = static_cast<const T*>(a.x);
+        float acc[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = kMax ? -INFINITY : 0.f;
+        int cnt = 0;
+        for (int r = 0; r < a.R; ++r) {
+            const int ih = p * a.stride_h + r - a.pad_h;
+            if (ih < 0 || ih >= a.H) continue;
+            for (int s = 0; s < a.S; ++s) {
+                const int iw = q * a.stride_w + s - a.pad_w;
+                if (iw < 0 || iw >= a.W) continue;
+                const Vec<T> xv = Vec<T>::load(x + ((size_t)ih * a.W + iw) * a.Cs + c0);
+#pragma unroll
+                for (int j = 0; j < N; ++j) acc[j] = kMax ? fmaxf(acc[j], xv.v[j]) : acc[j] + xv.v[j];
+                ++cnt;
+            }
+        }
+        Vec<T> o;
+        const float div = (a.flags & 1) ? (float)(a.R * a.S) : (float)(cnt > 0 ? cnt : 1);
+#pragma unroll
+        for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.C) ? (kMax ? acc[j] : acc[j] / div) : 0.f;
+        o.store(static_cast<T*>(a.y) + (size_t)pix * a.Ks + a.out_c_off + c0);
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- global average pool: [HW][Cs] -> [Cs] ---------------------------------------
+// Block = 32 channel vectors x 8 pixel groups; shared-memory reduction over the groups.
+template <typename T>
+__global__ void __launch_bounds__(256) gap_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    constexpr int N = Vec<T>::N;
+    __shared__ float red[8][32][N + 1];
+    const int cv = a.Cs / N;
+    const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int v = blockIdx.x * 32 + lane;
+    const int HW = a.H * a.W;
+    float acc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = 0.f;
+    if (v < cv) {
+        const T* __restrict__ x = static_cast<const T*>(a.x);
+        for (int pix = grp; pix < HW; pix += 8) {
+            const Vec<T> xv = Vec<T>::load(x + (size_t)pix * a.Cs + v * N);
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[j] += xv.v[j];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) red[grp][lane][j] = acc[j];
+    __syncthreads();
+    if (grp == 0 && v < cv) {
+        const float inv = 1.f / (float)HW;
+        float o[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            float s = 0.f;
+#pragma unroll
+            for (int gI = 0; gI < 8; ++gI) s += red[gI][lane][j];
+            o[j] = s * inv;
+        }
+        if (a.flags & 2) {
+            float* y = static_cast<float*>(a.y);
+#pragma unroll
+            for (int j = 0; j < N; ++j) if (v * N + j < a.C) y[v * N + j] = o[j];
+        } else {
+            Vec<T> ov;
+#pragma unroll
+            for (int j = 0; j < N; ++j) ov.v[j] = (v * N + j < a.C) ? o[j] : 0.f;
+            ov.store(static_cast<T*>(a.y) + v * N);
+        }
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- dense: y[k] = act(w[k,:] . x + b[k]); one warp per output row -----------------
+// x has n_in = a.C elements (already in the device's flattened channels-last order, padded
+// entries zero); w is [K][C] with C a multiple of the vector width.
+template <typename T>
+__global__ void __launch_bounds__(256) dense_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    constexpr int N = Vec<T>::N;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp < a.K) {
+        const T* __restrict__ x = static_cast<const T*>(a.x);
+        const T* __restrict__ w = static_cast<const T*>(a.w) + (size_t)warp * a.C;
+        float acc = 0.f;
+        for (int i = lane * N; i < a.C; i += 32 * N) {
+            const Vec<T> xv = Vec<T>::load(x + i);
+            const Vec<T> wv = Vec<T>::load(w + i);
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc = fmaf(xv.v[j], wv.v[j], acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            const float v = act_fn(acc + (a.bias ? a.bias[warp] : 0.f), a.act);
+            if (a.flags & 2) static_cast<float*>(a.y)[warp] = v;
+            else static_cast<T*>(a.y)[warp] = from_f<T>(v);
+        }
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- elementwise add (+activation) over [HW][Cs] ----------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) add_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    constexpr int N = Vec<T>::N;
+    const size_t nv = (size_t)a.H * a.W * a.Cs / N;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < nv) {
+        const Vec<T> u = Vec<T>::load(static_cast<const T*>(a.x) + i * N);
+        const Vec<T> v = Vec<T>::load(static_cast<const T*>(a.residual) + i * N);
+        Vec<T> o;
+#pragma unroll
+        for (int j = 0; j < N; ++j) o.v[j] = act_fn(u.v[j] + v.v[j], a.act);
+        o.store(static_cast<T*>(a.y) + i * N);
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- softmax over a.C values, one block --------------------------------------------
+template <typename T, bool kInF32>
+__global__ void __launch_bounds__(256) softmax_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    __shared__ float red[8];
+    __shared__ float bc;
+    const int n = a.C;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    auto ld = [&](int i) { return kInF32 ? static_cast<const float*>(a.x)[i] : to_f<T>(static_cast<const T*>(a.x)[i]); };
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, ld(i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[wid] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) { float t = red[0]; for (int i = 1; i < 8; ++i) t = fmaxf(t, red[i]); bc = t; }
+    __syncthreads();
+    m = bc;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += __expf(ld(i) - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncthreads();
+    if (lane == 0) red[wid] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) { float t = 0.f; for (int i = 0; i < 8; ++i) t += red[i]; bc = t; }
+    __syncthreads();
+    const float inv = 1.f / bc;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = __expf(ld(i) - m) * inv;
+        if (a.flags & 2) static_cast<float*>(a.y)[i] = v;
+        else static_cast<T*>(a.y)[i] = from_f<T>(v);
+    }
+    PB_NOTIFY_END();
+}
+
+// ---- whole MNIST-CNN in one launch ---------------------------------------------------
+// conv5x5(1->8)+ReLU, maxpool2, conv5x5(8->16)+ReLU, maxpool3, dense 256->10 for one
+// 28x28 image, fp32, activations in shared memory.  One block of 256 threads: the network
+// is 1.57 MFLOP and 24 KB of weights, so the request is launch-latency bound and one
+// kernel (one start and one end record) replaces six.
+// Weights: w1 [5][5][1][8], w2 [5][5][8][16], wd [10][4*4*16] (h, w, c order), biases fp32.
+struct MnistArgs {
+    const float* x;     // [28][28]
+    const float* w1; const float* b1;
+    const float* w2; const float* b2;
+    const float* wd; const float* bd;
+    float* y;           // [10]
+};
+
+__global__ void __launch_bounds__(256) mnist_fused_kernel(MnistArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    __shared__ float s_in[32][33];          // 28x28 image with a 2-pixel zero border
+    __shared__ float s_w1[25 * 8];
+    __shared__ float s_p1[18][18][8];       // pool1 output 14x14x8 with a 2-pixel zero border
+    __shared__ float s_w2[25 * 8 * 16];
+    __shared__ float s_c2[14 * 14][17];     // conv2 output (padded row to dodge bank conflicts)
+    __shared__ float s_p2[256];
+    const int t = threadIdx.x;
+    for (int i = t; i < 32 * 33; i += 256) (&s_in[0][0])[i] = 0.f;
+    for (int i = t; i < 18 * 18 * 8; i += 256) (&s_p1[0][0][0])[i] = 0.f;
+    for (int i = t; i < 200; i += 256) s_w1[i] = a.w1[i];
+    for (int i = t; i < 3200; i += 256) s_w2[i] = a.w2[i];
+    __syncthreads();
+    for (int i = t; i < 784; i += 256) s_in[i / 28 + 2][i % 28 + 2] = a.x[i];
+    __syncthreads();
+    // conv1 + ReLU + 2x2 max pool: one thread per (pooled pixel, channel): 14*14*8 = 1568
+    for (int i = t; i < 1568; i += 256) {
+        const int k = i & 7, pp = i >> 3;
+        const int py = pp / 14, px = pp % 14;
+        float best = 0.f;  // ReLU output is >= 0
+        const float b = a.b1[k];
+        for (int dy = 0; dy < 2; ++dy)
+            for (int dx = 0; dx < 2; ++dx) {
+                float acc = b;
+                const int oy = 2 * py + dy, ox = 2 * px + dx;
+#pragma unroll
+                for (int r = 0; r < 5; ++r)
+#pragma unroll
+                    for (int s = 0; s < 5; ++s) acc = fmaf(s_in[oy + r][ox + s], s_w1[(r * 5 + s) * 8 + k], acc);
+                best = fmaxf(best, acc);
+            }
+        s_p1[py + 2][px + 2][k] = best;
+    }
+    __syncthreads();
+    // conv2 + ReLU: one thread per (pixel, channel): 196*16 = 3136
+    for (int i = t; i < 3136; i += 256) {
+        const int k = i & 15, pp = i >> 4;
+        const int oy = pp / 14, ox = pp % 14;
+        float acc = a.b2[k];
+        for (int r = 0; r < 5; ++r)
+            for (int s = 0; s < 5; ++s) {
+                const float* ip = &s_p1[oy + r][ox + s][0];
+                const float* wp = &s_w2[((r * 5 + s) * 8) * 16 + k];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) acc = fmaf(ip[c], wp[c * 16], acc);
+            }
+        s_c2[pp][k] = fmaxf(acc, 0.f);
+    }
+    __syncthreads();
+    // 3x3/3 max pool (floor: 14 -> 4), output order (h, w, c)
+    {
+        const int k = t & 15, pp = t >> 4;
+        const int py = pp >> 2, px = pp & 3;
+        float best = -INFINITY;
+        for (int dy = 0; dy < 3; ++dy)
+            for (int dx = 0; dx < 3; ++dx) best = fmaxf(best, s_c2[(3 * py + dy) * 14 + 3 * px + dx][k]);
+        s_p2[t] = best;
+    }
+    __syncthreads();
+    // dense 256 -> 10: warps 0..7 take rows w, w+8
+    {
+        const int lane = t & 31, wid = t >> 5;
+        for (int o = wid; o < 10; o += 8) {
+            float acc = 0.f;
+            for (int i = lane; i < 256; i += 32) acc = fmaf(s_p2[i], a.wd[o * 256 + i], acc);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (lane == 0) a.y[o] = acc + a.bd[o];
+        }
+    }
+    PB_NOTIFY_END();
+}
+
+// ---------------------------------------------------------------------------------
+// Host: geometry, resources, weight layouts, dispatch
+// ---------------------------------------------------------------------------------
+static OpArgs to_args(const pb_op_params* p) {
+    OpArgs a;
+    a.C = p->C; a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.K = p->K; a.P = p->P; a.Q = p->Q; a.Ks = p->Ks;
+    a.out_c_off = p->out_c_off; a.R = p->R; a.S = p->S; a.stride_h = p->stride_h; a.stride_w = p->stride_w;
+    a.pad_h = p->pad_h; a.pad_w = p->pad_w; a.groups = p->groups > 0 ? p->groups : 1; a.act = p->act; a.flags = p->flags;
+    a.res_Cs = p->res_Cs; a.x = p->x; a.w = p->w; a.bias = p->bias; a.residual = p->residual; a.y = p->y;
+    return a;
+}
+
+static int vec_n(int dtype) { return dtype == 0 ? 4 : 8; }
+static size_t elem_size(int dtype) { return dtype == 0 ? 4 : 2; }
+
+template <typename F>
+static uint32_t regs_of(F fn) {
+    cudaFuncAttributes at;
+    if (cudaFuncGetAttributes(&at, (const void*)fn) != cudaSuccess) { cudaGetLastError(); return 32; }
+    return (uint32_t)at.numRegs;
+}
+template <typename F>
+static uint32_t static_smem_of(F fn) {
+    cudaFuncAttributes at;
+    if (cudaFuncGetAttributes(&at, (const void*)fn) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return (uint32_t)at.sharedSizeBytes;
+}
+
+// Threads of work -> blocks of 256.
+static uint32_t blocks_for(size_t work) { return (uint32_t)((work + 255) / 256 > 0 ? (work + 255) / 256 : 1); }
+
+int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
+    memset(out, 0, sizeof(*out));
+    out->kind = (uint32_t)kind;
+    out->threads_per_block = 256;
+    const int N = vec_n(p->dtype);
+    const size_t es = elem_size(p->dtype);
+    const bool f32 = p->dtype == 0;
+    const size_t in_elems = (size_t)p->C * p->H * p->W;
+    const size_t out_elems = (size_t)p->K * p->P * p->Q;
+    switch (kind) {
+        case PB_STAGE_INPUT:
+            out->num_blocks = blocks_for((size_t)p->H * p->W);
+            out->regs_per_thread = f32 ? regs_of(input_transform_kernel<float>) : regs_of(input_transform_kernel<__nv_bfloat16>);
+            out->bytes = in_elems * 4 + in_elems * es;
+            break;
+        case PB_STAGE_CONV_SIMT:
+            out->num_blocks = blocks_for((size_t)p->P * p->Q * p->K);
+            out->regs_per_thread = f32 ? regs_of(conv_simt_kernel<float>) : regs_of(conv_simt_kernel<__nv_bfloat16>);
+            out->flops = 2ull * out_elems * (p->C / (p->groups > 0 ? p->groups : 1)) * p->R * p->S;
+            out->bytes = es * (in_elems + (size_t)p->K * (p->C / (p->groups > 0 ? p->groups : 1)) * p->R * p->S + out_elems +
+                               (p->residual ? out_elems : 0)) + 4ull * p->K;
+            break;
+        case PB_STAGE_DWCONV:
+            out->num_blocks = blocks_for((size_t)p->P * p->Q * (p->Cs / N));
+            out->regs_per_thread = f32 ? regs_of(dwconv_kernel<float>) : regs_of(dwconv_kernel<__nv_bfloat16>);
+            out->flops = 2ull * out_elems * p->R * p->S;
+            out->bytes = es * (in_elems + (size_t)p->K * p->R * p->S + out_elems) + 4ull * p->K;
+            break;
+        case PB_STAGE_MAXPOOL:
+        case PB_STAGE_AVGPOOL:
+            out->num_blocks = blocks_for((size_t)p->P * p->Q * (p->Cs / N));
+            if (kind == PB_STAGE_MAXPOOL)
+                out->regs_per_thread = f32 ? regs_of(pool_kernel<float, true>) : regs_of(pool_kernel<__nv_bfloat16, true>);
+            else
+                out->regs_per_thread = f32 ? regs_of(pool_kernel<float, false>) : regs_of(pool_kernel<__nv_bfloat16, false>);
+            out->bytes = es * (in_elems + out_elems);
+            break;
+        case PB_STAGE_GAP:
+            out->num_blocks = (uint32_t)pb::ceil_div(p->Cs / N, 32);
+            out->regs_per_thread = f32 ? regs_of(gap_kernel<float>) : regs_of(gap_kernel<__nv_bfloat16>);
+            out->smem_per_block = f32 ? static_smem_of(gap_kernel<float>) : static_smem_of(gap_kernel<__nv_bfloat16>);
+            out->bytes = es * in_elems + ((p->flags & 2) ? 4 : es) * (size_t)p->C;
+            break;
+        case PB_STAGE_DENSE:
+            out->num_blocks = (uint32_t)pb::ceil_div(p->K, 8);
+            out->regs_per_thread = f32 ? regs_of(dense_kernel<float>) : regs_of(dense_kernel<__nv_bfloat16>);
+            out->flops = 2ull * p->C * p->K;
+            out->bytes = es * ((size_t)p->C + (size_t)p->C * p->K) + 4ull * p->K + ((p->flags & 2) ? 4 : es) * (size_t)p->K;
+            break;
+        case PB_STAGE_ADD:
+            out->num_blocks = blocks_for((size_t)p->H * p->W * p->Cs / N);
+            out->regs_per_thread = f32 ? regs_of(add_kernel<float>) : regs_of(add_kernel<__nv_bfloat16>);
+            out->bytes = es * 3 * in_elems;
+            break;
+        case PB_STAGE_SOFTMAX:
+            out->num_blocks = 1;
+            out->regs_per_thread = regs_of(softmax_kernel<float, true>);
+            out->smem_per_block = static_smem_of(softmax_kernel<float, true>);
+            out->bytes = 8ull * p->C;
+            break;
+        default:
+            set_error("pb_op_info: unknown stage kind %d", kind);
+            return PB_ERR_INVALID;
+    }
+    return PB_OK;
+}
+
+int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier) {
+    FinishedBlockNotifier* nf = static_cast<FinishedBlockNotifier*>(notifier);
+    pb_launch_info li;
+    int rc = simple_op_info(kind, p, &li);
+    if (rc != PB_OK) return rc;
+    const OpArgs a = to_args(p);
+    const bool f32 = p->dtype == 0;
+    const int N = vec_n(p->dtype);
+    PB_REQUIRE(p->Cs % N == 0, "channel stride %d is not a multiple of the %d-element vector", p->Cs, N);
+    const dim3 grid(li.num_blocks), block(256);
+#define PB_DISPATCH(kern_f32, kern_bf16, ...)                                           \
+    do {                                                                                \
+        if (f32) kern_f32<<<grid, block, 0, st>>>(__VA_ARGS__);                         \
+        else kern_bf16<<<grid, block, 0, st>>>(__VA_ARGS__);                            \
+    } while (0)
+    switch (kind) {
+        case PB_STAGE_INPUT:
+            if (f32) input_transform_kernel<float><<<grid, block, 0, st>>>((const float*)p->x, (float*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
+            else input_transform_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const float*)p->x, (__nv_bfloat16*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
+            break;
+        case PB_STAGE_CONV_SIMT:
+            PB_REQUIRE(a.C % a.groups == 0 && a.K % a.groups == 0, "conv: groups must divide channels");
+            PB_DISPATCH(conv_simt_kernel<float>, conv_simt_kernel<__nv_bfloat16>, a, job_id, nf);
+            break;
+        case PB_STAGE_DWCONV:
+            PB_REQUIRE(a.groups == a.C && a.K == a.C, "dwconv: needs groups == C == K");
+            PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "dwconv: output slice must be vector aligned");
+            PB_DISPATCH(dwconv_kernel<float>, dwconv_kernel<__nv_bfloat16>, a, job_id, nf);
+            break;
+        case PB_STAGE_MAXPOOL:
+            PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "pool: output slice must be vector aligned");
+            PB_DISPATCH((pool_kernel<float, true>), (pool_kernel<__nv_bfloat16, true>), a, job_id, nf);
+            break;
+        case PB_STAGE_AVGPOOL:
+            PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "pool: output slice must be vector aligned");
+            PB_DISPATCH((pool_kernel<float, false>), (pool_kernel<__nv_bfloat16, false>), a, job_id, nf);
+            break;
+        case PB_STAGE_GAP:
+            PB_DISPATCH(gap_kernel<float>, gap_kernel<__nv_bfloat16>, a, job_id, nf);
+            break;
+        case PB_STAGE_DENSE:
+            PB_REQUIRE(a.C % N == 0, "dense: input length %d is not a multiple of %d", a.C, N);
+            PB_DISPATCH(dense_kernel<float>, dense_kernel<__nv_bfloat16>, a, job_id, nf);
+            break;
+        case PB_STAGE_ADD:
+            PB_REQUIRE(a.residual != nullptr, "add: second operand missing");
+            PB_DISPATCH(add_kernel<float>, add_kernel<__nv_bfloat16>, a, job_id, nf);
+            break;
+        case PB_STAGE_SOFTMAX:
+            // flags bit2: the input is fp32 regardless of dtype
+            if (f32 || (p->flags & 4)) softmax_kernel<float, true><<<1, block, 0, st>>>(a, job_id, nf);
+            else softmax_kernel<__nv_bfloat16, false><<<1, block, 0, st>>>(a, job_id, nf);
+            break;
+        default:
+            set_error("pb_op_launch: unknown stage kind %d", kind);
+            return PB_ERR_INVALID;
+    }
+#undef PB_DISPATCH
+    return launch_check("operator kernel");
+}
+
+// Weight layouts (host side).  Source: OIHW fp32.
+//  conv_simt: [R][S][C/groups][K]      dwconv: [R][S][Cs]      dense: see graph loader
+static uint16_t f32_to_bf16_bits(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+void store_elem(void* dst, size_t i, float v, int dtype) {
+    if (dtype == 0) static_cast<float*>(dst)[i] = v;
+    else static_cast<uint16_t*>(dst)[i] = f32_to_bf16_bits(v);
+}
+
+int64_t simple_pack_weights(int kind, const pb_op_params* p, const float* w, void* dst) {
+    const size_t es = elem_size(p->dtype);
+    const int groups = p->groups > 0 ? p->groups : 1;
+    if (kind == PB_STAGE_CONV_SIMT) {
+        const int cg = p->C / groups;
+        const size_t n = (size_t)p->R * p->S * cg * p->K;
+        if (dst) {
+            for (int k = 0; k < p->K; ++k)
+                for (int c = 0; c < cg; ++c)
+                    for (int r = 0; r < p->R; ++r)
+                        for (int s = 0; s < p->S; ++s)
+                            store_elem(dst, ((size_t)(r * p->S + s) * cg + c) * p->K + k,
+                                       w[(((size_t)k * cg + c) * p->R + r) * p->S + s], p->dtype);
+        }
+        return (int64_t)(n * es);
+    }
+    if (kind == PB_STAGE_DWCONV) {
+        const size_t n = (size_t)p->R * p->S * p->Cs;
+        if (dst) {
+            memset(dst, 0, n * es);
+            for (int c = 0; c < p->C; ++c)
+                for (int r = 0; r < p->R; ++r)
+                    for (int s = 0; s < p->S; ++s)
+                        store_elem(dst, (size_t)(r * p->S + s) * p->Cs + c, w[((size_t)c * p->R + r) * p->S + s], p->dtype);
+        }
+        return (int64_t)(n * es);
+    }
+    set_error("pb_op_pack_weights: stage kind %d has no packed weights here", kind);
+    return PB_ERR_INVALID;
+}
+
+int mnist_fused_info(pb_launch_info* out) {
+    memset(out, 0, sizeof(*out));
+    out->kind = PB_STAGE_MNIST_FUSED;
+    out->num_blocks = 1;
+    out->threads_per_block = 256;
+    out->regs_per_thread = regs_of(mnist_fused_kernel);
+    out->smem_per_block = static_smem_of(mnist_fused_kernel);
+    out->flops = 2ull * (156800 + 627200 + 2560);
+    out->bytes = 4ull * (784 + 200 + 8 + 3200 + 16 + 2560 + 10 + 10);
+    return PB_OK;
+}
+
+int mnist_fused_launch(const float* x, const float* w1, const float* b1, const float* w2, const float* b2,
+                       const float* wd, const float* bd, float* y, cudaStream_t st, uint32_t job_id, void* notifier) {
+    MnistArgs a{x, w1, b1, w2, b2, wd, bd, y};
+    mnist_fused_kernel<<<1, 256, 0, st>>>(a, job_id, static_cast<FinishedBlockNotifier*>(notifier));
+    return launch_check("mnist_fused");
+}
+
+}  // namespace pb

@@ -1,0 +1,48 @@
+// Internal operator interface shared by the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "paella_b200.h"
+
+namespace pb {
+
+// Kernel-side copy of pb_op_params (passed by value as a kernel argument).
+struct OpArgs {
+    int C, H, W, Cs;
+    int K, P, Q, Ks;
+    int out_c_off;
+    int R, S, stride_h, stride_w, pad_h, pad_w, groups;
+    int act, flags, res_Cs;
+    const void* x;
+    const void* w;
+    const float* bias;
+    const void* residual;
+    void* y;
+};
+
+// kernels.cu
+int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out);
+int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
+int64_t simple_pack_weights(int kind, const pb_op_params* p, const float* w_oihw, void* dst_host);
+void store_elem(void* dst, size_t i, float v, int dtype);
+int mnist_fused_info(pb_launch_info* out);
+int mnist_fused_launch(const float* x, const float* w1, const float* b1, const float* w2, const float* b2,
+                       const float* wd, const float* bd, float* y, cudaStream_t st, uint32_t job_id, void* notifier);
+
+// conv_umma.cu: tcgen05 implicit-GEMM convolution (bf16 operands, fp32 accumulation in TMEM)
+bool conv_umma_supported(const pb_op_params* p);
+int conv_umma_info(const pb_op_params* p, pb_launch_info* out);
+int conv_umma_launch(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
+int64_t conv_umma_pack_weights(const pb_op_params* p, const float* w_oihw, void* dst_host);
+// Per-layer state the tensor-core path needs beyond pb_op_params (the TMA descriptor of the
+// packed weights).  Created once per layer at model load; `w_dev` is the packed weight buffer.
+struct ConvUmmaPlan;
+int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan** out);
+void conv_umma_plan_destroy(ConvUmmaPlan* plan);
+int conv_umma_launch_planned(const ConvUmmaPlan* plan, const pb_op_params* p, cudaStream_t st, uint32_t job_id,
+                             void* notifier);
+
+}  // namespace pb

@@ -1,0 +1,216 @@
+// The kernel-granularity scheduler ("full3"): SRPT-like priority = minus the remaining
+// sum of stage_length x stage_resource, a deficit-counter fairness override between job
+// types, a whole-GPU occupancy check with a bounded number of over-subscribed kernels.
+//
+// Decision-for-decision equivalent to the reference's SchedulerFull3
+// (src/server/scheduler_full3.cpp:123-459): handle_block_start :123-144,
+// handle_block_finish :146-222, handle_mem_finish :224-270, handle_new_job :272-313,
+// schedule_job :315-452, calculate_priority :454-459.  Pools are LIFO as there
+// (:391-397,206-207,262), ids are recycled LIFO (:280-287).
+//
+// What changed for this machine: copy-stage completions arrive as kMemDone records in the
+// same ring as block notifications instead of a driver callback thread and a second ring;
+// the occupancy totals are those of the device in use (148 SMs on B200) and include tensor
+// memory; time comes from the host interface so a trace replays exactly.
+#include <llis/server/job_queue.h>
+#include <llis/server/scheduler.h>
+
+#include <cstdio>
+
+namespace llis {
+namespace server {
+
+namespace {
+
+class SchedulerFull3 final : public Scheduler {
+  public:
+    SchedulerFull3(const SchedulerConfig& cfg, SchedulerHost* host)
+        : host_(host), cfg_(cfg), job_queue_(cfg.unfairness_threshold), gpu_resources_(cfg.totals),
+          max_num_outstanding_kernels_(cfg.extra_kernels) {}
+
+    const char* name() const override { return "full3"; }
+    unsigned num_jobs() const override { return num_jobs_; }
+    uint64_t num_decisions() const override { return num_decisions_; }
+
+    void set_pools(const std::vector<cudaStream_t>& streams, const std::vector<job::FinishedBlockNotifier*>& notifiers) override {
+        all_streams_ = streams;
+        all_notifiers_ = notifiers;
+        free_streams_.clear();
+        free_notifiers_.clear();
+        for (unsigned i = 0; i < streams.size(); ++i) free_streams_.push_back(i);
+        for (unsigned i = 0; i < notifiers.size(); ++i) free_notifiers_.push_back(i);
+        job_stream_slot_.clear();
+        job_notifier_slot_.clear();
+    }
+
+    void handle_new_job(job::Job* job) override {
+        if (!job->has_next()) {
+            host_->release_job_instance(job);
+            return;
+        }
+        JobId id;
+        if (unused_job_id_.empty()) {
+            id = (JobId)jobs_.size();
+            jobs_.push_back(job);
+            job_stream_slot_.push_back(0);
+            job_notifier_slot_.push_back(0);
+        } else {
+            id = unused_job_id_.back();
+            unused_job_id_.pop_back();
+            jobs_[id] = job;
+        }
+        job->set_id(id);
+        const unsigned next = (unsigned)(job->get_cur_stage() + 1);
+        if (!host_->has_job_stage_resource(job, next)) host_->set_job_stage_resource(job, next, 1);
+        job->set_stage_lengths_resources(host_->get_job_remaining_rl(job, 0), host_->get_job_stage_lengths(job),
+                                         host_->get_job_stage_resources(job));
+        job->set_priority(calculate_priority(job));
+        job_queue_.push(job);
+        ++num_jobs_;
+        schedule_job();
+    }
+
+    void handle_record(const job::InstrumentInfo& info) override {
+        if (info.job_id >= jobs_.size() || jobs_[info.job_id] == nullptr) {
+            ++num_stray_records_;
+            return;
+        }
+        if (info.is_start == job::InstrumentInfo::kStart) handle_block_start(info);
+        else if (info.is_start == job::InstrumentInfo::kEnd) handle_block_finish(info);
+        else handle_mem_finish(info);
+    }
+
+  private:
+    void handle_block_start(const job::InstrumentInfo& info) {
+        job::Job* job = jobs_[info.job_id];
+        if (!job->mark_block_start(info.num)) {
+            if (job->is_unfit()) {
+                job->unset_unfit();
+                --num_outstanding_kernels_;
+                schedule_job();
+            }
+        }
+    }
+
+    // Common tail of a finished stage: learn its length, re-queue or finish the job.
+    void stage_finished(job::Job* job) {
+        const double length = host_->now_us() - job->get_stage_start_time_us();
+        host_->update_job_stage_length(job, (unsigned)job->get_cur_stage(), length);
+        if (job->has_next()) {
+            const unsigned next = (unsigned)(job->get_cur_stage() + 1);
+            if (!host_->has_job_stage_resource(job, next)) host_->set_job_stage_resource(job, next, 1);
+            job->set_priority(calculate_priority(job));
+            job_queue_.push(job);
+        } else {
+            host_->notify_job_ends(job);
+            --num_jobs_;
+        }
+    }
+
+    void handle_block_finish(const job::InstrumentInfo& info) {
+        job::Job* job = jobs_[info.job_id];
+        job->mark_block_finish(info.num);
+        const bool stage_done = !job->is_running();
+        if (stage_done) {
+            stage_finished(job);
+            if (job->is_unfit()) {   // start records may still be in flight when the last end arrives
+                job->unset_unfit();
+                --num_outstanding_kernels_;
+            }
+            free_streams_.push_back(job_stream_slot_[info.job_id]);
+            free_notifiers_.push_back(job_notifier_slot_[info.job_id]);
+        }
+        gpu_resources_.release(job, info.num);
+        if (stage_done && !job->has_next()) retire(job);
+        schedule_job();
+    }
+
+    void handle_mem_finish(const job::InstrumentInfo& info) {
+        job::Job* job = jobs_[info.job_id];
+        job->unset_running();
+        stage_finished(job);
+        free_streams_.push_back(job_stream_slot_[info.job_id]);
+        if (!job->has_next()) retire(job);
+        schedule_job();
+    }
+
+    void retire(job::Job* job) {
+        const JobId id = job->get_id();
+        unused_job_id_.push_back(id);
+        jobs_[id] = nullptr;
+        host_->release_job_instance(job);
+    }
+
+    void schedule_job() {
+        if (free_streams_.empty() || job_queue_.empty()) return;
+        do {
+            job::Job* job = job_queue_.top();
+            if (cfg_.sched_sleep > 0) {
+                for (volatile unsigned i = 0; i < cfg_.sched_sleep; ++i) {}
+            }
+            const bool is_mem = job->is_mem();
+            bool unfit = false;
+            if (!is_mem && !gpu_resources_.job_fits(job)) {
+                if (num_outstanding_kernels_ >= (int)max_num_outstanding_kernels_) break;
+                ++num_outstanding_kernels_;
+                job->set_unfit();
+                unfit = true;
+            }
+            job_queue_.pop();
+            if (!job->has_started()) job->set_started();
+
+            const unsigned sslot = free_streams_.back();
+            free_streams_.pop_back();
+            job_stream_slot_[job->get_id()] = sslot;
+            job->set_running(all_streams_[sslot], host_->now_us());
+            unsigned nslot = 0;
+            if (!is_mem) {
+                nslot = free_notifiers_.back();
+                free_notifiers_.pop_back();
+                job_notifier_slot_[job->get_id()] = nslot;
+                job->set_finished_block_notifier(all_notifiers_[nslot]);
+                gpu_resources_.acquire(job, (int)job->get_cur_num_blocks());
+            }
+            if (job->is_pre_notify()) host_->notify_job_starts(job);
+            ++num_decisions_;
+            host_->on_dispatch(job, is_mem, unfit, sslot, nslot);
+
+            job->run_next();
+            if (is_mem) host_->after_mem_stage(job);
+            if (free_streams_.empty()) break;
+        } while (!job_queue_.empty());
+    }
+
+    // Priority = -(remaining length x resource); the stage about to be queued is then
+    // taken out of the remainder (scheduler_full3.cpp:454-459).
+    static double calculate_priority(job::Job* job) {
+        const double rl = job->get_cur_rl();
+        job->dec_cur_rl();
+        return -rl;
+    }
+
+    SchedulerHost* host_;
+    SchedulerConfig cfg_;
+    JobQueue job_queue_;
+    SmResources gpu_resources_;
+    std::vector<cudaStream_t> all_streams_;
+    std::vector<job::FinishedBlockNotifier*> all_notifiers_;
+    std::vector<unsigned> free_streams_, free_notifiers_;
+    std::vector<unsigned> job_stream_slot_, job_notifier_slot_;   // by JobId
+    std::vector<job::Job*> jobs_;                                 // by JobId
+    std::vector<JobId> unused_job_id_;
+    unsigned num_jobs_ = 0;
+    uint64_t num_decisions_ = 0;
+    uint64_t num_stray_records_ = 0;
+    int num_outstanding_kernels_ = 0;
+    unsigned max_num_outstanding_kernels_ = 2;
+};
+
+}  // namespace
+
+std::unique_ptr<Scheduler> make_scheduler_full3(const SchedulerConfig& cfg, SchedulerHost* host) {
+    return std::unique_ptr<Scheduler>(new SchedulerFull3(cfg, host));
+}
+
+}  // namespace server
+}  // namespace llis

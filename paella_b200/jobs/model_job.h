@@ -1,0 +1,122 @@
+// Job adapter for a packed model: H2D copy stage, one stage per kernel of the model,
+// D2H copy stage with pre-notify.  Same stage protocol as the reference's TVM adapters
+// (jobs/tvm_mnist/tvm_mnist.cpp:35-47): init() leaves the job before its first (copy)
+// stage; each run_next() enqueues exactly one operation on the job's stream and declares
+// the resources of the next stage.  Written as a stage-index state machine instead of a
+// boost coroutine; the server only sees the llis::job::Job interface.
+//
+// Differences from the reference adapters: the D2H stage copies the OUTPUT tensor (there
+// it copies from the input buffer, tvm_mnist.cpp:46); the device comes from the server
+// thread's context instead of being hard-wired to 0; CUDA failures set the job's error
+// flag instead of being ignored.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <llis/job/context.h>
+#include <llis/job/job.h>
+
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "paella_b200.h"
+
+namespace pbjobs {
+
+class ModelJob : public llis::job::Job {
+  public:
+    ModelJob(const char* model_name, size_t in_floats, size_t out_floats)
+        : name_(model_name), in_bytes_(in_floats * sizeof(float)), out_bytes_(out_floats * sizeof(float)) {}
+
+    size_t get_input_size() override { return in_bytes_; }
+    size_t get_output_size() override { return out_bytes_; }
+    size_t get_param_size() override { return 4; }
+
+    void full_init(void* io_ptr) override {
+        const int device = llis::job::Context::get_device();
+        const char* dir = std::getenv("LLIS_MODELS_DIR");
+        const std::string path = std::string(dir ? dir : ".") + "/" + name_ + "-b200-pack.bin";
+        pb_model* model = shared_model(device, path);
+        if (!model) { set_error(PB_ERR_IO); return; }
+        if (pb_model_input_bytes(model) != in_bytes_ || pb_model_output_bytes(model) != out_bytes_) { set_error(PB_ERR_INVALID); return; }
+        if (pb_instance_create(model, &inst_) != PB_OK) { set_error(PB_ERR_CUDA); return; }
+        const int n = pb_model_num_stages(model);
+        decls_.resize((size_t)n);
+        for (int i = 0; i < n; ++i) {
+            pb_launch_info li;
+            pb_model_stage_info(model, i, &li);
+            llis::job::StageDecl& d = decls_[(size_t)i];
+            d.num_blocks = li.num_blocks;
+            d.num_threads_per_block = li.threads_per_block;
+            d.smem_size_per_block = li.smem_per_block;
+            d.num_registers_per_thread = li.regs_per_thread;
+            d.tmem_cols_per_block = li.tmem_cols_per_block;
+        }
+        init(io_ptr);
+    }
+
+    void init(void* io_ptr) override {
+        io_ptr_ = static_cast<char*>(io_ptr);
+        next_ = 0;
+        resident_ = llis::job::Context::device_resident();
+        set_is_mem();   // stage 0: host -> device copy of the input
+    }
+
+    void run_next() override {
+        const int n = (int)decls_.size();
+        cudaStream_t st = get_cuda_stream();
+        if (next_ == 0) {
+            if (!resident_ && inst_) check(cudaMemcpyAsync(pb_instance_input_dev(inst_), io_ptr_, in_bytes_, cudaMemcpyHostToDevice, st));
+        } else if (next_ <= n) {
+            if (inst_ && pb_instance_launch_stage(inst_, next_ - 1, st, get_id(), get_finished_block_notifier()) != PB_OK) set_error(PB_ERR_CUDA);
+        } else {
+            if (!resident_ && inst_) check(cudaMemcpyAsync(io_ptr_ + get_output_offset(), pb_instance_output_dev(inst_), out_bytes_, cudaMemcpyDeviceToHost, st));
+        }
+        ++next_;
+        // declare the stage that follows
+        if (next_ <= n) {
+            unset_is_mem();
+            set_next_stage(decls_[(size_t)(next_ - 1)]);
+        } else if (next_ == n + 1) {
+            set_is_mem();
+            set_pre_notify();
+        }
+    }
+
+    bool has_next() const override { return next_ < (int)decls_.size() + 2; }
+
+  private:
+    void check(cudaError_t e) { if (e != cudaSuccess) set_error(PB_ERR_CUDA); }
+
+    static pb_model* shared_model(int device, const std::string& path) {
+        static std::mutex mu;
+        static std::map<std::pair<int, std::string>, pb_model*> cache;
+        std::lock_guard<std::mutex> lk(mu);
+        auto key = std::make_pair(device, path);
+        auto it = cache.find(key);
+        if (it != cache.end()) return it->second;
+        pb_model* m = nullptr;
+        int precision = -1;
+        if (const char* p = std::getenv("PB_PRECISION")) precision = std::atoi(p);
+        if (pb_model_load(path.c_str(), device, precision, &m) != PB_OK) return nullptr;
+        cache[key] = m;
+        return m;
+    }
+
+    std::string name_;
+    size_t in_bytes_, out_bytes_;
+    pb_instance* inst_ = nullptr;
+    std::vector<llis::job::StageDecl> decls_;
+    char* io_ptr_ = nullptr;
+    int next_ = 0;
+    bool resident_ = false;
+};
+
+}  // namespace pbjobs
+
+#define PB_DEFINE_MODEL_JOB(NAME, IN_FLOATS, OUT_FLOATS)                                             \
+    extern "C" __attribute__((visibility("default"))) llis::job::Job* init_job() {                  \
+        return new pbjobs::ModelJob(NAME, IN_FLOATS, OUT_FLOATS);                                    \
+    }

@@ -1,0 +1,166 @@
+"""Whole models through the graph executor (C ABI) vs the oracle and the committed golden logits.
+Tolerances: fp32 path 1e-5 of the largest |logit|; bf16 tensor-core path 1e-2 of the largest
+|logit| against the FP32 oracle with identical argmax (the seeds' top-1 margins are 0.7% - 28%)."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from oracle import graph as og
+from paella_b200 import capi, packer
+from tests import gpu_util as gu
+from tests.golden.make_golden import make_input
+
+pytestmark = pytest.mark.gpu
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden_logits.npz"))
+
+
+class Model:
+    def __init__(self, path, precision):
+        self.L = capi.load()
+        self.m, self.i = C.c_void_p(), C.c_void_p()
+        capi.check(self.L.pb_model_load(path.encode(), 0, precision, C.byref(self.m)), "pb_model_load")
+        capi.check(self.L.pb_instance_create(self.m, C.byref(self.i)), "pb_instance_create")
+
+    def run(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.zeros(self.L.pb_model_output_bytes(self.m) // 4, np.float32)
+        capi.check(self.L.pb_instance_run_sync(self.i, x.ctypes.data, y.ctypes.data), "run")
+        assert gu.error_flag() == 0
+        return y
+
+    def kinds(self):
+        li = capi.LaunchInfo()
+        out = []
+        for s in range(self.L.pb_model_num_stages(self.m)):
+            self.L.pb_model_stage_info(self.m, s, C.byref(li))
+            out.append(li.kind)
+        return out
+
+    def tensor(self, t, shape):
+        buf = np.zeros(int(np.prod(shape)), np.float32)
+        capi.check(self.L.pb_instance_read_tensor(self.i, t, buf.ctypes.data, buf.size), "read_tensor")
+        return buf.reshape(shape)
+
+    def close(self):
+        self.L.pb_instance_destroy(self.i)
+        self.L.pb_model_destroy(self.m)
+
+
+@pytest.mark.parametrize("fused", ["1", "0"])
+def test_mnist_fp32(models_dir, monkeypatch, fused):
+    monkeypatch.setenv("PB_FUSE_MNIST", fused)
+    g = packer.mnist_cnn(seed=1234)
+    m = Model(os.path.join(models_dir, packer.pack_file_name("mnist")), 0)
+    assert (capi.STAGE_MNIST_FUSED in m.kinds()) == (fused == "1")
+    pack = og.Pack(g.to_bytes())
+    for seed in range(5):
+        x = np.random.default_rng(seed).random((1, 28, 28), dtype=np.float32)
+        y, ref = m.run(x), og.run(pack, x)
+        assert float(np.abs(y - ref).max()) <= 1e-5 * float(np.abs(ref).max())
+        assert int(y.argmax()) == int(ref.argmax())
+    y = m.run(make_input("mnist"))
+    assert float(np.abs(y - GOLDEN["mnist"]).max()) <= 1e-5 * float(np.abs(GOLDEN["mnist"]).max())
+    m.close()
+
+
+def test_mnist_with_biases_both_paths(tmp_path, monkeypatch):
+    g = packer.mnist_cnn(seed=7, bias_std=0.2)
+    path = g.save(str(tmp_path / "m.bin"))
+    ref = og.run(og.Pack(g.to_bytes()), make_input("mnist"))
+    for fused in ("1", "0"):
+        monkeypatch.setenv("PB_FUSE_MNIST", fused)
+        m = Model(path, 0)
+        y = m.run(make_input("mnist"))
+        assert float(np.abs(y - ref).max()) <= 1e-5 * float(np.abs(ref).max())
+        m.close()
+
+
+def test_small_net_layer_by_layer_bf16(tmp_path):
+    """Every intermediate tensor of a small bf16 network against the bf16-emulating oracle."""
+    g = packer.Graph("small", (3, 40, 40), seed=21, precision=1, bias_std=0.05)
+    t = g.conv(g.input, 32, 3, 2, 1, name="stem")
+    r = g.conv(t, 64, 1, 1, 0, name="expand")
+    d = g.conv(r, 64, 3, 1, 1, groups=64, act=packer.ACT_RELU6, name="dw")
+    t2 = g.conv(d, 64, 3, 1, 1, residual=r, name="res")
+    cat = g.tensor(64 + 32 + 64, 10, 10)
+    g.conv(t2, 64, 3, 2, 1, out=cat, out_c_off=0, name="b0")
+    g.conv(t2, 32, (1, 7), (2, 2), (0, 3), out=cat, out_c_off=64, name="b1")
+    g.maxpool(t2, 3, 2, 1, out=cat, out_c_off=96, name="b2")
+    a = g.avgpool(cat, 3, 1, 1, True, name="avg")
+    s = g.add(a, cat, act=packer.ACT_RELU, name="add")
+    p = g.gap(s, name="gap")
+    dn = g.dense(p, 24, name="fc")
+    g.softmax(dn, name="sm")
+    path = g.save(str(tmp_path / "small.bin"))
+    m = Model(path, 1)
+    assert capi.STAGE_CONV_UMMA in m.kinds() and capi.STAGE_DWCONV in m.kinds()
+    x = np.random.default_rng(3).standard_normal((3, 40, 40), dtype=np.float32)
+    y = m.run(x)
+    ref, bufs = og.run(og.Pack(g.to_bytes()), x, emulate_bf16=True, keep_all=True)
+    for t_id, shape in enumerate(g.tensors):
+        if t_id == g.output:
+            continue
+        got = m.tensor(t_id, shape)
+        want = og.round_bf16(bufs[t_id]) if t_id != g.input else og.round_bf16(x)
+        scale = max(float(np.abs(want).max()), 1e-6)
+        tol = np.abs(want) * 2.0 ** -6 + 4e-3 * scale
+        assert (np.abs(got - want) <= tol).all(), f"tensor {t_id} {shape}: worst {float(np.abs(got - want).max())} scale {scale}"
+    np.testing.assert_allclose(y, ref, rtol=3e-2, atol=1e-4)
+    m.close()
+
+
+@pytest.mark.parametrize("model", ["resnet18", "inception_v3", "resnet50"])
+def test_imagenet_models_bf16_vs_fp32_oracle(models_dir, model):
+    m = Model(os.path.join(models_dir, packer.pack_file_name(model)), 1)
+    kinds = m.kinds()
+    assert kinds.count(capi.STAGE_CONV_UMMA) >= 20 and capi.STAGE_CONV_SIMT not in kinds
+    y = m.run(make_input(model))
+    ref = GOLDEN[model]                       # fp32 oracle logits
+    rel = float(np.abs(y - ref).max() / np.abs(ref).max())
+    assert rel <= 1e-2, rel
+    assert int(y.argmax()) == int(ref.argmax())
+    m.close()
+
+
+def test_resnet18_fp32_path(models_dir):
+    """The fp32 (direct convolution) path of the same pack: 1e-4 of the largest logit (long fp32 sums
+    in a different order than the oracle)."""
+    m = Model(os.path.join(models_dir, packer.pack_file_name("resnet18")), 0)
+    y = m.run(make_input("resnet18"))
+    ref = GOLDEN["resnet18"]
+    assert float(np.abs(y - ref).max()) <= 1e-4 * float(np.abs(ref).max())
+    assert int(y.argmax()) == int(ref.argmax())
+    m.close()
+
+
+def test_mobilenet_v2(models_dir):
+    """Depthwise + ReLU6 network.  bf16 storage loses more here (narrow linear bottlenecks): the bf16
+    path is held to the bf16-emulating oracle, the fp32 path to the fp32 oracle."""
+    ref = GOLDEN["mobilenet"]
+    m = Model(os.path.join(models_dir, packer.pack_file_name("mobilenet")), 0)
+    y = m.run(make_input("mobilenet"))
+    assert float(np.abs(y - ref).max()) <= 1e-4 * float(np.abs(ref).max())
+    m.close()
+    m = Model(os.path.join(models_dir, packer.pack_file_name("mobilenet")), 1)
+    assert capi.STAGE_DWCONV in m.kinds()
+    y = m.run(make_input("mobilenet"))
+    emu = og.run(og.Pack(packer.mobilenet_v2(seed=1234).to_bytes()), make_input("mobilenet"), emulate_bf16=True)
+    assert float(np.abs(y - emu).max()) <= 1e-2 * float(np.abs(emu).max())
+    assert int(y.argmax()) == int(ref.argmax())
+    m.close()
+
+
+def test_same_input_same_output_and_instances_are_independent(models_dir):
+    m = Model(os.path.join(models_dir, packer.pack_file_name("resnet18")), 1)
+    i2 = C.c_void_p()
+    capi.check(m.L.pb_instance_create(m.m, C.byref(i2)), "second instance")
+    x1, x2 = make_input("resnet18"), np.random.default_rng(9).standard_normal((3, 224, 224), dtype=np.float32)
+    y1 = m.run(x1)
+    y = np.zeros(1000, np.float32)
+    capi.check(m.L.pb_instance_run_sync(i2, x2.ctypes.data, y.ctypes.data), "run")
+    assert not np.array_equal(y, y1)
+    np.testing.assert_array_equal(m.run(x1), y1)      # deterministic, not disturbed by the other instance
+    m.L.pb_instance_destroy(i2)
+    m.close()

@@ -1,0 +1,231 @@
+"""Operator kernels vs the CPU oracle, through pb_op_launch.  fp32 kernels: 1e-5 relative to the
+largest output; bf16 kernels are compared with the oracle run on bf16-rounded inputs and weights
+(fp32 accumulation on both sides), so the only differences are summation order and the final
+bf16 rounding of the output: 2^-7 relative per element plus a small absolute term."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import graph as og
+from paella_b200 import capi
+from tests import gpu_util as gu
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(11)
+
+
+def _params(dtype, x_shape, K, P, Q, Ks, R=1, S=1, sh=1, sw=1, ph=0, pw=0, groups=1, act=0, flags=0, out_c_off=0, Cs=None):
+    p = capi.OpParams()
+    p.dtype = dtype
+    p.C, p.H, p.W = x_shape
+    p.Cs = Cs if Cs is not None else gu.round_up(p.C, gu.vec(dtype))
+    p.K, p.P, p.Q, p.Ks = K, P, Q, Ks
+    p.out_c_off = out_c_off
+    p.R, p.S, p.stride_h, p.stride_w, p.pad_h, p.pad_w, p.groups = R, S, sh, sw, ph, pw, groups
+    p.act, p.flags = act, flags
+    return p
+
+
+def _assert_close(got, ref, dtype):
+    scale = max(float(np.abs(ref).max()), 1e-6)
+    if dtype == 0:
+        assert float(np.abs(got - ref).max()) <= 1e-5 * scale
+    else:
+        tol = np.abs(ref) * 2.0 ** -7 + 2e-3 * scale
+        bad = np.abs(got - ref) > tol
+        assert not bad.any(), f"{int(bad.sum())} of {bad.size} elements off; worst {float(np.abs(got - ref).max())} (scale {scale})"
+
+
+def _run_conv(kind, dtype, C_, H, W, K, R, S, sh, sw, ph, pw, groups=1, act=1, residual=False, out_total=None, off=0, bias=True):
+    import torch
+    L = capi.load()
+    x = RNG.standard_normal((C_, H, W), dtype=np.float32)
+    w = (RNG.standard_normal((K, C_ // groups, R, S), dtype=np.float32) * np.float32(np.sqrt(2.0 / (C_ // groups * R * S))))
+    b = RNG.standard_normal(K, dtype=np.float32) * np.float32(0.1) if bias else np.zeros(K, np.float32)
+    P = (H + 2 * ph - R) // sh + 1
+    Q = (W + 2 * pw - S) // sw + 1
+    res = RNG.standard_normal((K, P, Q), dtype=np.float32) if residual else None
+    if dtype == 1:
+        x, w = og.round_bf16(x), og.round_bf16(w)
+        res = og.round_bf16(res) if residual else None
+    out_total = out_total or K
+    xd, cs = gu.to_device_cl(x, dtype)
+    yd, ks = gu.empty_cl(P, Q, out_total, dtype, fill=7.0)
+    p = _params(dtype, (C_, H, W), K, P, Q, ks, R, S, sh, sw, ph, pw, groups, act, 0, off, cs)
+    if residual:
+        rd, rcs = gu.to_device_cl(res, dtype)
+        p.residual, p.res_Cs = rd.data_ptr(), rcs
+    wd = gu.pack_weights(kind, p, w)
+    bd = torch.from_numpy(b).cuda()
+    p.x, p.w, p.bias, p.y = xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), yd.data_ptr()
+    li = capi.LaunchInfo()
+    capi.check(L.pb_op_info(kind, C.byref(p), C.byref(li)), "pb_op_info")
+    assert li.flops == 2 * K * P * Q * (C_ // groups) * R * S
+    capi.check(L.pb_op_launch(kind, C.byref(p), None, 0, None), "pb_op_launch")
+    gu.sync()
+    assert gu.error_flag() == 0
+    got_all = gu.from_device_cl(yd, out_total)
+    ref = og.conv2d(x, w, b, (sh, sw), (ph, pw), groups, act, res)
+    _assert_close(got_all[off:off + K], ref, dtype)
+    if out_total > K:   # channels outside the slice are untouched
+        mask = np.ones(out_total, bool)
+        mask[off:off + K] = False
+        assert (got_all[mask] == 7.0).all()
+
+
+SIMT_CASES = [
+    (1, 28, 28, 8, 5, 5, 1, 1, 2, 2), (8, 14, 14, 16, 5, 5, 1, 1, 2, 2), (3, 33, 31, 16, 7, 7, 2, 2, 3, 3),
+    (16, 17, 17, 24, 1, 7, 1, 1, 0, 3), (12, 9, 9, 20, 3, 3, 2, 2, 0, 0), (5, 1, 1, 3, 1, 1, 1, 1, 0, 0),
+]
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("case", SIMT_CASES)
+def test_conv_simt(case, dtype):
+    _run_conv(capi.STAGE_CONV_SIMT, dtype, *case, act=1, residual=(case[3] % 8 == 0))
+
+
+def test_conv_simt_grouped_and_slice():
+    _run_conv(capi.STAGE_CONV_SIMT, 0, 8, 6, 6, 8, 3, 3, 1, 1, 1, 1, groups=2, act=2)
+    _run_conv(capi.STAGE_CONV_SIMT, 0, 4, 9, 9, 8, 3, 3, 1, 1, 1, 1, out_total=24, off=8)
+
+
+UMMA_CASES = [
+    # C, H, W, K, R, S, sh, sw, ph, pw        what it exercises
+    (64, 16, 16, 64, 1, 1, 1, 1, 0, 0),       # one k-block, two row tiles
+    (64, 8, 8, 32, 1, 1, 1, 1, 0, 0),         # half-empty row tile (64 of 128 rows)
+    (128, 12, 12, 128, 3, 3, 1, 1, 1, 1),     # 18 k-blocks: pipeline wraps 4 stages several times
+    (8, 37, 37, 32, 3, 3, 2, 2, 0, 0),        # 3 real channels padded to 8 happen here as C=8: taps share a k-block
+    (16, 21, 21, 48, 5, 5, 1, 1, 2, 2),       # C < 64, 25 taps, k tail zero-filled
+    (128, 17, 17, 192, 1, 7, 1, 1, 0, 3),     # asymmetric filter; two column tiles of 96
+    (128, 17, 17, 160, 7, 1, 1, 1, 3, 0),     # 160 -> two tiles of 80
+    (192, 9, 9, 320, 3, 3, 2, 2, 0, 0),       # 320 -> three tiles of 112 (336 padded), stride 2, single row tile of 16 rows
+    (256, 14, 14, 512, 1, 1, 2, 2, 0, 0),     # strided 1x1 (down-sampling shortcut)
+    (96, 7, 7, 24, 1, 1, 1, 1, 0, 0),         # K = 24: half of the second 16-column chunk is masked
+    (32, 56, 56, 64, 3, 3, 1, 1, 1, 1),       # 25 row tiles
+    (2048, 4, 4, 1008, 1, 1, 1, 1, 0, 0),     # long reduction (32 k-blocks), 8 column tiles
+]
+
+
+@pytest.mark.parametrize("case", UMMA_CASES)
+def test_conv_umma(case):
+    L = capi.load()
+    C_, H, W, K = case[:4]
+    _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=False)
+
+
+def test_conv_umma_epilogue_variants():
+    # residual add + relu, relu6, no activation, no bias, write into a channel slice of a wider tensor
+    _run_conv(capi.STAGE_CONV_UMMA, 1, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, act=1, residual=True)
+    _run_conv(capi.STAGE_CONV_UMMA, 1, 64, 14, 14, 96, 1, 1, 1, 1, 0, 0, act=2)
+    _run_conv(capi.STAGE_CONV_UMMA, 1, 64, 14, 14, 16, 1, 1, 1, 1, 0, 0, act=0, residual=True, bias=False)
+    _run_conv(capi.STAGE_CONV_UMMA, 1, 64, 10, 10, 64, 3, 3, 1, 1, 1, 1, act=1, out_total=288, off=64)
+    _run_conv(capi.STAGE_CONV_UMMA, 1, 48, 10, 10, 64, 5, 5, 1, 1, 2, 2, act=1, out_total=256, off=192)
+
+
+def test_conv_umma_rejects_what_it_cannot_do():
+    p = _params(1, (30, 8, 8), 30, 8, 8, 32, Cs=32)
+    assert capi.load().pb_conv_umma_supported(C.byref(p)) == 0    # K not a multiple of 8
+    p = _params(0, (64, 8, 8), 64, 8, 8, 64)
+    assert capi.load().pb_conv_umma_supported(C.byref(p)) == 0    # fp32
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("case", [(32, 15, 15, 3, 3, 2, 2, 1, 1), (32, 9, 9, 3, 3, 1, 1, 1, 1), (144, 28, 28, 3, 3, 2, 2, 1, 1),
+                                  (20, 7, 7, 3, 3, 1, 1, 1, 1)])
+def test_dwconv(case, dtype):
+    C_, H, W, R, S, sh, sw, ph, pw = case
+    _run_conv(capi.STAGE_DWCONV, dtype, C_, H, W, C_, R, S, sh, sw, ph, pw, groups=C_, act=2)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("k,s,p,hw,c", [(2, 2, 0, 28, 8), (3, 3, 0, 14, 16), (3, 2, 1, 112, 64), (3, 2, 0, 35, 288), (3, 1, 1, 17, 768), (3, 2, 0, 9, 5)])
+def test_pools(dtype, k, s, p, hw, c):
+    L = capi.load()
+    x = RNG.standard_normal((c, hw, hw), dtype=np.float32)
+    if dtype == 1:
+        x = og.round_bf16(x)
+    P = (hw + 2 * p - k) // s + 1
+    for kind, ref in ((capi.STAGE_MAXPOOL, og.maxpool(x, (k, k), (s, s), (p, p))),
+                      (capi.STAGE_AVGPOOL, og.avgpool(x, (k, k), (s, s), (p, p), True))):
+        xd, cs = gu.to_device_cl(x, dtype)
+        yd, ks = gu.empty_cl(P, P, c + 16, dtype, fill=3.0)
+        off = 8 if (c % 8 == 0) else 0
+        prm = _params(dtype, (c, hw, hw), c, P, P, ks, k, k, s, s, p, p, flags=1, out_c_off=off, Cs=cs)
+        prm.x, prm.y = xd.data_ptr(), yd.data_ptr()
+        capi.check(L.pb_op_launch(kind, C.byref(prm), None, 0, None), "pool")
+        gu.sync()
+        got = gu.from_device_cl(yd, c + 16)[off:off + c]
+        if kind == capi.STAGE_MAXPOOL:
+            np.testing.assert_array_equal(got, ref)     # max of representable values: exact in both dtypes
+        else:
+            _assert_close(got, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_gap_dense_add_softmax(dtype):
+    import torch
+    L = capi.load()
+    rb = og.round_bf16 if dtype == 1 else (lambda a: a)
+    # global average pool, written as the fp32 output
+    x = rb(RNG.standard_normal((2048, 8, 8), dtype=np.float32))
+    xd, cs = gu.to_device_cl(x, dtype)
+    yd = torch.zeros(2048, dtype=torch.float32, device="cuda")
+    p = _params(dtype, (2048, 8, 8), 2048, 1, 1, 2048, flags=2, Cs=cs)
+    p.x, p.y = xd.data_ptr(), yd.data_ptr()
+    capi.check(L.pb_op_launch(capi.STAGE_GAP, C.byref(p), None, 0, None), "gap")
+    gu.sync()
+    np.testing.assert_allclose(yd.cpu().numpy(), og.gap(x), rtol=1e-5, atol=1e-5)
+    # dense on a flat vector
+    n_in, n_out = 2048, 1000
+    v = rb(RNG.standard_normal(n_in, dtype=np.float32))
+    w = rb(RNG.standard_normal((n_out, n_in), dtype=np.float32) * np.float32(0.03))
+    b = RNG.standard_normal(n_out, dtype=np.float32)
+    vd = torch.from_numpy(v).cuda().to(torch.float32 if dtype == 0 else torch.bfloat16)
+    wd = torch.from_numpy(w).cuda().to(torch.float32 if dtype == 0 else torch.bfloat16).contiguous()
+    bd = torch.from_numpy(b).cuda()
+    od = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    p = _params(dtype, (n_in, 1, 1), n_out, 1, 1, n_out, flags=2, Cs=n_in)
+    p.x, p.w, p.bias, p.y = vd.data_ptr(), wd.data_ptr(), bd.data_ptr(), od.data_ptr()
+    capi.check(L.pb_op_launch(capi.STAGE_DENSE, C.byref(p), None, 0, None), "dense")
+    gu.sync()
+    ref = og.dense(v, w, b)
+    assert float(np.abs(od.cpu().numpy() - ref).max()) <= 2e-5 * float(np.abs(ref).max())
+    # add + relu
+    a1 = rb(RNG.standard_normal((64, 7, 7), dtype=np.float32))
+    a2 = rb(RNG.standard_normal((64, 7, 7), dtype=np.float32))
+    d1, cs = gu.to_device_cl(a1, dtype)
+    d2, _ = gu.to_device_cl(a2, dtype)
+    do, ks = gu.empty_cl(7, 7, 64, dtype)
+    p = _params(dtype, (64, 7, 7), 64, 7, 7, ks, act=1, Cs=cs)
+    p.x, p.residual, p.res_Cs, p.y = d1.data_ptr(), d2.data_ptr(), cs, do.data_ptr()
+    capi.check(L.pb_op_launch(capi.STAGE_ADD, C.byref(p), None, 0, None), "add")
+    gu.sync()
+    _assert_close(gu.from_device_cl(do, 64), og.add(a1, a2, 1), dtype)
+    # softmax over 1000 logits to the fp32 output
+    lg = rb(RNG.standard_normal(1000, dtype=np.float32) * 3)
+    ld = torch.from_numpy(lg).cuda().to(torch.float32 if dtype == 0 else torch.bfloat16)
+    so = torch.zeros(1000, dtype=torch.float32, device="cuda")
+    p = _params(dtype, (1000, 1, 1), 1000, 1, 1, 1000, flags=2, Cs=1000)
+    p.x, p.y = ld.data_ptr(), so.data_ptr()
+    capi.check(L.pb_op_launch(capi.STAGE_SOFTMAX, C.byref(p), None, 0, None), "softmax")
+    gu.sync()
+    np.testing.assert_allclose(so.cpu().numpy(), og.softmax(lg), rtol=2e-4, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_input_layout_conversion(dtype):
+    import torch
+    L = capi.load()
+    x = RNG.standard_normal((3, 31, 29), dtype=np.float32)
+    xd = torch.from_numpy(x).cuda()
+    yd, ks = gu.empty_cl(31, 29, 3, dtype, fill=9.0)
+    p = _params(dtype, (3, 31, 29), 3, 31, 29, ks, Cs=3)
+    p.x, p.y = xd.data_ptr(), yd.data_ptr()
+    capi.check(L.pb_op_launch(capi.STAGE_INPUT, C.byref(p), None, 0, None), "input")
+    gu.sync()
+    full = yd.float().cpu().numpy()
+    ref = og.round_bf16(x) if dtype == 1 else x
+    np.testing.assert_array_equal(np.transpose(full[:, :, :3], (2, 0, 1)), ref)
+    assert (full[:, :, 3:] == 0).all()
