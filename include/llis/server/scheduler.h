@@ -64,7 +64,43 @@ class Scheduler {
     // Stream / notifier pools are handed over by the server (slot i <-> element i).
     virtual void set_pools(const std::vector<cudaStream_t>& streams, const std::vector<job::FinishedBlockNotifier*>& notifiers) = 0;
 
+    // Records the scheduler made up itself: when a plugin's run_next() fails (error flag set, nothing
+    // was enqueued) no notification will ever come from the GPU, so the scheduler queues the records
+    // that close the stage and the server feeds them back through handle_record().  The job then
+    // runs (and fails) through its remaining stages and ends with its error reported to the client.
+    bool take_synthetic(std::vector<job::InstrumentInfo>* out) {
+        if (synthetic_.empty()) return false;
+        out->swap(synthetic_);
+        synthetic_.clear();
+        return true;
+    }
+
     static std::unique_ptr<Scheduler> create(const std::string& name, const SchedulerConfig& cfg, SchedulerHost* host);
+
+  protected:
+    // Closes the stage a failed run_next() left open (see take_synthetic).
+    void close_failed_stage(job::Job* job, bool is_mem) {
+        job::InstrumentInfo r{};
+        r.job_id = job->get_id();
+        r.status = 1;
+        if (is_mem) {
+            r.is_start = job::InstrumentInfo::kMemDone;
+            r.num = 1;
+            synthetic_.push_back(r);
+            return;
+        }
+        for (int kind = 0; kind < 2; ++kind) {
+            unsigned left = job->get_cur_num_blocks();
+            while (left > 0) {
+                const unsigned n = left > 255 ? 255 : left;
+                r.is_start = kind == 0 ? job::InstrumentInfo::kStart : job::InstrumentInfo::kEnd;
+                r.num = (uint8_t)n;
+                synthetic_.push_back(r);
+                left -= n;
+            }
+        }
+    }
+    std::vector<job::InstrumentInfo> synthetic_;
 };
 
 }  // namespace server

@@ -529,7 +529,8 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
     const OpArgs a = to_args(p);
     const bool f32 = p->dtype == 0;
     const int N = vec_n(p->dtype);
-    PB_REQUIRE(p->Cs % N == 0, "channel stride %d is not a multiple of the %d-element vector", p->Cs, N);
+    if (kind == PB_STAGE_INPUT) PB_REQUIRE(p->Ks % N == 0, "output channel stride %d is not a multiple of the %d-element vector", p->Ks, N);
+    else PB_REQUIRE(p->Cs % N == 0, "channel stride %d is not a multiple of the %d-element vector", p->Cs, N);
     const dim3 grid(li.num_blocks), block(256);
 #define PB_DISPATCH(kern_f32, kern_bf16, ...)                                           \
     do {                                                                                \

@@ -141,7 +141,8 @@ class SchedulerFifo final : public PoolsBase {
                 ++num_decisions_;
                 host_->on_dispatch(job, is_mem, false, ss, ns);
                 job->run_next();
-                if (is_mem) host_->after_mem_stage(job);
+                if (job->has_error()) close_failed_stage(job, is_mem);
+                else if (is_mem) host_->after_mem_stage(job);
             }
         }
     }
@@ -206,7 +207,8 @@ class SchedulerFifo2 final : public PoolsBase {
             ++num_decisions_;
             host_->on_dispatch(job, is_mem, false, ss, ns);
             job->run_next();
-            if (is_mem) host_->after_mem_stage(job);
+            if (job->has_error()) close_failed_stage(job, is_mem);
+            else if (is_mem) host_->after_mem_stage(job);
         }
     }
     std::priority_queue<Job*, std::vector<Job*>, Later> heap_;

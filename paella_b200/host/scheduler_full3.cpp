@@ -176,7 +176,8 @@ class SchedulerFull3 final : public Scheduler {
             host_->on_dispatch(job, is_mem, unfit, sslot, nslot);
 
             job->run_next();
-            if (is_mem) host_->after_mem_stage(job);
+            if (job->has_error()) close_failed_stage(job, is_mem);
+            else if (is_mem) host_->after_mem_stage(job);
             if (free_streams_.empty()) break;
         } while (!job_queue_.empty());
     }

@@ -109,6 +109,9 @@ void pb_server::after_mem_stage(Job* job) {
 int pb_server::step(int max_records) {
     uint64_t recs[64];
     int handled = 0;
+    std::vector<InstrumentInfo> made_up;
+    while (scheduler->take_synthetic(&made_up))
+        for (const InstrumentInfo& r : made_up) scheduler->handle_record(r);
     while (handled < max_records) {
         const int want = max_records - handled < 64 ? max_records - handled : 64;
         const int n = pb_ring_poll(channel.handle(), recs, want);

@@ -103,8 +103,8 @@ def test_mixed_models_and_synthetic_jobs(models_dir, monkeypatch):
                 x = rng.random((1, 28, 28), dtype=np.float32)
             else:
                 x = rng.uniform(-1, 1, ib // 4 if ib >= 4 else 1).astype(np.float32)
-            if ib >= 4:
-                h[:ib] = np.frombuffer(x.tobytes(), np.uint8)[:ib]
+            nb = min(ib, x.nbytes)
+            h[:nb] = np.frombuffer(x.tobytes(), np.uint8)[:nb]
             bufs.append(t)
             meta[cookie] = (job, x, t)
             capi.check(L.pb_server_launch(s, ids[job], t.data_ptr(), cookie), "launch")
