@@ -120,7 +120,7 @@ def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps
     return res
 
 
-def roofline_leg(L, capi, models_dir, iters=20):
+def roofline_leg(L, capi, models_dir, iters=20, only=""):
     """Times every stage of Inception-v3 alone; returns the tensor-core convolution aggregate and a
     per-kind table (time share of one request)."""
     from paella_b200 import packer
@@ -134,6 +134,8 @@ def roofline_leg(L, capi, models_dir, iters=20):
     layers = []
     for s in range(L.pb_model_num_stages(model)):
         L.pb_model_stage_info(model, s, C.byref(li))
+        if only and only not in L.pb_model_stage_name(model, s).decode():
+            continue
         capi.check(L.pb_instance_time_stage(inst, s, iters, 192 << 20, C.byref(us)), "pb_instance_time_stage")
         k = capi.STAGE_NAMES[li.kind]
         d = per_kind.setdefault(k, {"launches": 0, "us": 0.0, "flops": 0, "bytes": 0})
@@ -186,6 +188,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
+    ap.add_argument("--only-roofline", default=None, metavar="SUBSTR",
+                    help="skip the serving legs; time only the Inception-v3 stages whose name contains SUBSTR "
+                         "('' = all).  Small enough to run under ncu.")
+    ap.add_argument("--iters", type=int, default=20, help="timed launches per stage in the roofline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -251,6 +257,12 @@ def main():
         devices = list(range(args.gpus))
         n_gpus = args.gpus
 
+    if args.only_roofline is not None:
+        roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters, args.only_roofline)
+        print(json.dumps({"roofline": roof, "kernel_table_inception_v3": table,
+                          "layers": [(n, k, round(u, 2), nb) for (n, k, u, _, _, nb) in layers]}))
+        return
+
     sampler = ClockSampler()
 
     def timed(resident):
@@ -299,7 +311,7 @@ def main():
             "records_consumed": int(r_dev.records_consumed), "decisions": int(r_dev.decisions)}
 
     if n_gpus == 1 and not args.no_roofline:
-        roof, table, layers = roofline_leg(L, capi, tmp.name)
+        roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters)
         line["roofline"] = roof
         line["kernel_table_inception_v3"] = table
         if args.layers:

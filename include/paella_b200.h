@@ -50,6 +50,7 @@ typedef struct pb_launch_info {
     uint32_t kind;               /* pb_stage_kind */
     uint64_t flops;              /* algorithmic 2*MAC */
     uint64_t bytes;              /* algorithmic bytes: inputs + weights + outputs once */
+    uint64_t scratch_bytes;      /* scratch memory the launch can use (0 = none); see pb_op_params.scratch */
 } pb_launch_info;
 
 /* ------------------------------------------------------------------------ *
@@ -141,6 +142,11 @@ typedef struct pb_op_params {
     const float* bias;        /* fp32 [K] or NULL */
     const void* residual;     /* same dtype as x, [P][Q][res_Cs], or NULL */
     void* y;                  /* output tensor base (slice offset applied by the kernel) */
+    /* Scratch memory (device, 16-byte aligned, zero-filled before its first use, private to one
+     * in-flight launch).  The tensor-core convolution splits its reduction over several thread
+     * blocks when given at least pb_launch_info.scratch_bytes here; NULL = no split. */
+    void* scratch;
+    uint64_t scratch_bytes;
 } pb_op_params;
 
 /* Geometry/resources the launch of `kind` with `p` will use. */

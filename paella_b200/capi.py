@@ -24,13 +24,14 @@ class PbError(RuntimeError):
 class LaunchInfo(C.Structure):
     _fields_ = [("num_blocks", C.c_uint32), ("threads_per_block", C.c_uint32), ("smem_per_block", C.c_uint32),
                 ("regs_per_thread", C.c_uint32), ("tmem_cols_per_block", C.c_uint32), ("kind", C.c_uint32),
-                ("flops", C.c_uint64), ("bytes", C.c_uint64)]
+                ("flops", C.c_uint64), ("bytes", C.c_uint64), ("scratch_bytes", C.c_uint64)]
 
 
 class OpParams(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("dtype", "C", "H", "W", "Cs", "K", "P", "Q", "Ks", "out_c_off", "R", "S",
                                          "stride_h", "stride_w", "pad_h", "pad_w", "groups", "act", "flags", "res_Cs")] + \
-               [("x", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p), ("y", C.c_void_p)]
+               [("x", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p), ("y", C.c_void_p),
+                ("scratch", C.c_void_p), ("scratch_bytes", C.c_uint64)]
 
 
 class ServerConfig(C.Structure):

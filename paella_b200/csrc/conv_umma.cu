@@ -5,14 +5,15 @@
 //
 // A is never materialised: 128 producer threads gather it from the channels-last bf16
 // activation tensor with 16-byte cp.async copies (zero fill for padding and for the k tail)
-// straight into the 128-byte-swizzled K-major shared-memory layout that tcgen05.mma reads.
+// straight into the 128-byte-swizzled K-major shared-memory layout that tcgen05.mma reads;
+// eight consecutive lanes fetch one 128-byte row, so a warp-wide copy touches four full lines.
 // B (packed weights [Kout_pad][Kdim_pad]) arrives by TMA (cp.async.bulk.tensor.2d, 128B
 // swizzle, no multicast).  One elected thread issues tcgen05.mma (M=128, N=BN, K=16, bf16 x
 // bf16 -> fp32) with the accumulator in tensor memory; tcgen05.commit releases pipeline
 // stages and signals the epilogue, which reads TMEM with tcgen05.ld, adds bias and residual,
 // applies the activation and stores bf16 into the channel slice of the output tensor.
 //
-// CTA = 5 warps: warps 0-3 produce A (one tile row per thread) and then run the epilogue
+// CTA = 5 warps: warps 0-3 produce A (16 rows x 8 chunks per pass, 8 passes) and then run the epilogue
 // (thread t owns accumulator lane t); warp 4 allocates TMEM and issues the MMAs.
 //
 // Every wait is bounded: when a wait runs out the CTA raises a device-global error flag,
@@ -25,6 +26,7 @@
 #include <cuda_bf16.h>
 #include <llis/job/finished_block_notifier.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -39,8 +41,17 @@ namespace {
 
 constexpr int kBM = 128;            // tile rows (output pixels) = TMEM lanes
 constexpr int kBK = 64;             // bf16 elements per k-block = one 128-byte swizzle row
-constexpr int kStages = 4;
-constexpr int kLag = 2;             // cp.async groups kept in flight per producer thread
+// Pipeline depth is a template parameter: kStages shared-memory stages.  Each producer thread keeps
+// kLag = kStages/2 cp.async groups in flight (it arrives on a stage's barrier kLag iterations after
+// issuing its copies).  The other half of the stages is slack for the hand-off round trip
+// (producer arrive -> MMA issue -> tcgen05.commit -> producer may refill), which the probe measured
+// at well over a microsecond: with only two stages of slack that round trip paced the whole loop.
+#ifndef PB_LAG_OF
+#define PB_LAG_OF(stages) ((stages) / 2)
+#endif
+constexpr int kMaxStages = 8;
+constexpr uint32_t kSmemBudget = 200u * 1024u;
+constexpr uint32_t kCounterBytes = 4096;        // split-K tile counters at the head of the scratch buffer
 constexpr int kATileBytes = kBM * kBK * 2;   // 16 KiB
 constexpr uint32_t kWaitLimit = 4u * 1000u * 1000u;  // polls of mbarrier.try_wait before giving up
 constexpr int kThreads = 160;
@@ -56,12 +67,17 @@ struct ConvArgs {
     int K, Ks, out_c_off, res_Cs;
     int R, S, sh, sw, ph, pw;
     int act;
-    int nkb;              // k-blocks of 64
+    int nkb;              // k-blocks of 64 = taps * chunks per tap
     int taps;             // R*S
+    int Cp;               // channels per tap rounded up to 64: k = tap*Cp + c
     int BN;               // output channels per CTA (multiple of 16, <= 256)
     uint32_t idesc;       // tcgen05 instruction descriptor
     uint32_t tmem_cols;   // power of two >= max(32, BN)
     uint32_t b_stage_bytes;
+    // split-K: blockIdx.z handles k-blocks [z*kb_per_split, ...); partial tiles meet in `ws`
+    int splits, kb_per_split;
+    float* ws;              // [tile][split][128][BN] fp32 partial accumulators
+    unsigned* counters;     // [tile] arrival counters, zero between launches
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -112,6 +128,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
+}
+
+// im2col-mode TMA: 128 consecutive output pixels (traversed W, then H, then N inside the bounding
+// box of filter-window origins) x 64 channels, at filter offset (w_off, h_off); elements outside
+// the tensor arrive as zeros.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap* map, int c, int w, int h, int n,
+                                                   uint16_t w_off, uint16_t h_off, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(w_off), "h"(h_off)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
 }
 
 __device__ __forceinline__ void tcgen05_alloc(uint32_t slot_smem, uint32_t cols) {
@@ -167,17 +198,142 @@ __device__ __forceinline__ float act_fn(float v, int act) {
     return v;
 }
 
+// Optional phase stamps for development builds (-DPB_CONV_TIMING): %globaltimer at eight points of
+// the first 64 CTAs, written to a device array the probe program reads back.
+#ifdef PB_CONV_TIMING
+__device__ unsigned long long g_conv_t[64 * 8];
+#define PB_T(i)                                                                                         \
+    do {                                                                                                \
+        const unsigned b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);             \
+        if (b_ < 64) g_conv_t[b_ * 8 + (i)] = globaltimer_ns();                                         \
+    } while (0)
+#else
+#define PB_T(i) do {} while (0)
+#endif
+
 // ---- the kernel -----------------------------------------------------------------------
+// Epilogue, run by warps 0-3 (thread t owns accumulator lane t = tile row t): wait for the
+// accumulator, optionally meet the other split-K CTAs of the tile in the workspace, then
+// bias + residual + activation and bf16 stores into the output channel slice.
+__device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, bool ok, int m0, int n0, const float* s_bias,
+                                     uint64_t* s_accum_p, volatile uint32_t* s_abort_p, uint32_t* s_is_last_p) {
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int m = m0 + tid;
+    const bool row_valid = m < a.M;
+    if (ok) ok = mbar_wait(smem_u32(s_accum_p), 0u, s_abort_p, a.err_flag, 3u);
+    ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
+    if (tid == 0) PB_T(5);
+    tcgen05_fence_after();
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+    // Partial tiles in the workspace are stored [BN/4][128 rows] x float4, so consecutive lanes
+    // (= rows) touch consecutive 16-byte words.
+    const size_t tile_floats = (size_t)kBM * a.BN;
+    bool finalize = ok;
+    if (a.splits > 1) {
+        // Park this CTA's partial tile; the CTA that arrives last on the tile's counter adds the
+        // others to its own accumulators and runs the epilogue.
+        float4* mine = reinterpret_cast<float4*>(a.ws + ((size_t)tile * a.splits + blockIdx.z) * tile_floats) + tid;
+        if (ok) {
+            for (int cb = 0; cb < a.BN; cb += 16) {
+                uint32_t v[16];
+                tcgen05_ld16(lane_addr + (uint32_t)cb, v);
+                tcgen05_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    mine[(size_t)(cb / 4 + j) * kBM] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                                    __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps only
+        if (tid == 0) {
+            const unsigned prev = atomicAdd(a.counters + tile, 1u);
+            const bool last = prev == (unsigned)a.splits - 1u;
+            if (last) a.counters[tile] = 0;                      // ready for the next launch
+            __threadfence();
+            *s_is_last_p = last ? 1u : 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        finalize = ok && *s_is_last_p != 0;
+    }
+    if (finalize) {
+        __nv_bfloat16* yrow = a.y + (size_t)m * a.Ks + a.out_c_off;
+        const __nv_bfloat16* rrow = a.residual ? a.residual + (size_t)m * a.res_Cs : nullptr;
+        for (int cb = 0; cb < a.BN; cb += 16) {
+            uint32_t v[16];
+            tcgen05_ld16(lane_addr + (uint32_t)cb, v);   // warp-collective: all lanes take part
+            const int k0 = n0 + cb;
+            const bool live = row_valid && k0 < a.K;
+            // loads that do not depend on the accumulator are issued before the TMEM wait
+            uint4 rv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (live && rrow) {
+                rv[0] = *reinterpret_cast<const uint4*>(rrow + k0);
+                if (k0 + 16 <= a.K) rv[1] = *reinterpret_cast<const uint4*>(rrow + k0 + 8);
+            }
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+            if (live && a.splits > 1) {
+                // every partial, this CTA's own included, comes from the workspace in split order,
+                // so the fp32 sum does not depend on which CTA arrived last
+                for (int z = 0; z < a.splits; ++z) {
+                    const float4* other = reinterpret_cast<const float4*>(a.ws + ((size_t)tile * a.splits + z) * tile_floats) + tid;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 o = __ldcg(other + (size_t)(cb / 4 + j) * kBM);
+                        acc[4 * j] += o.x; acc[4 * j + 1] += o.y; acc[4 * j + 2] += o.z; acc[4 * j + 3] += o.w;
+                    }
+                }
+            }
+            tcgen05_wait_ld();
+            if (live) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int kk = k0 + h * 8;
+                    if (kk + 8 <= a.K) {
+                        float f[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            f[j] = (a.splits > 1 ? acc[h * 8 + j] : __uint_as_float(v[h * 8 + j])) + s_bias[cb + h * 8 + j];
+                        if (rrow) {
+                            const uint32_t ru[4] = {rv[h].x, rv[h].y, rv[h].z, rv[h].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                f[2 * j] += __uint_as_float(ru[j] << 16);
+                                f[2 * j + 1] += __uint_as_float(ru[j] & 0xffff0000u);
+                            }
+                        }
+                        uint32_t o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const __nv_bfloat162 hv = __floats2bfloat162_rn(act_fn(f[2 * j], a.act), act_fn(f[2 * j + 1], a.act));
+                            o[j] = *reinterpret_cast<const uint32_t*>(&hv);
+                        }
+                        *reinterpret_cast<uint4*>(yrow + kk) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int kStages>
 __global__ void __launch_bounds__(kThreads, 1)
-conv_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[kStages];
     __shared__ __align__(8) uint64_t s_empty[kStages];
     __shared__ __align__(8) uint64_t s_accum;
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile uint32_t s_abort;
+    __shared__ uint32_t s_is_last;
+    __shared__ float s_bias[128];
+    constexpr int kLag = PB_LAG_OF(kStages);
 
     if (nf) nf->start(job_id);
+    if (threadIdx.x == 0) PB_T(0);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -185,41 +341,68 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a, u
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t stage_bytes = (uint32_t)kATileBytes + a.b_stage_bytes;
 
+    const int m0 = blockIdx.x * kBM;
+    const int n0 = blockIdx.y * a.BN;
+    const int kb_begin = blockIdx.z * a.kb_per_split;
+    const int kb_end = min(a.nkb, kb_begin + a.kb_per_split);
+    const int nkb = kb_end - kb_begin;          // >= 1 by construction of the grid
+
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&s_full[s]), 128);
+            mbar_init(smem_u32(&s_full[s]), 4);      // one arrival per producer warp
             mbar_init(smem_u32(&s_empty[s]), 1);
         }
         mbar_init(smem_u32(&s_accum), 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (tid < 128) {
+        const int k = n0 + tid;
+        s_bias[tid] = (a.bias && tid < a.BN && k < a.K) ? __ldg(a.bias + k) : 0.f;
+    }
     if (warp == 4) {
         tcgen05_alloc(smem_u32(&s_tmem_base), a.tmem_cols);
         tcgen05_relinquish();
     }
+
+    // A-gather geometry.  Eight consecutive lanes cover the eight 16-byte chunks of one 128-byte tile
+    // row, so one warp-wide cp.async touches 4 rows = 4 full 128-byte lines of the activation tensor
+    // (when a row's chunks share a filter tap) instead of 32 partial ones.  Thread t copies chunk
+    // t%8 of rows t/8 + 16*i, i = 0..7.
+    const int chunk = tid & 7;
+    const int rbase = (tid >> 3) & 15;
+    int ih0[8], iw0[8];
+    if (warp < 4) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int m = m0 + rbase + 16 * i;
+            if (m < a.M) {
+                const int p = m / a.Q, q = m - p * a.Q;
+                ih0[i] = p * a.sh - a.ph;
+                iw0[i] = q * a.sw - a.pw;
+            } else {
+                ih0[i] = -(1 << 28);      // fails every bounds check: the row is zero-filled
+                iw0[i] = 0;
+            }
+        }
+    }
+
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = s_tmem_base;
-
-    const int m0 = blockIdx.x * kBM;
-    const int n0 = blockIdx.y * a.BN;
+    if (threadIdx.x == 0) PB_T(1);
 
     if (warp < 4) {
-        // ===== A producer: thread `tid` owns tile row `tid` =====
-        const int m = m0 + tid;
-        const bool row_valid = m < a.M;
-        const int p = row_valid ? m / a.Q : 0;
-        const int q = row_valid ? m % a.Q : 0;
-        const int ih0 = p * a.sh - a.ph;
-        const int iw0 = q * a.sw - a.pw;
-        const uint32_t row_off = (uint32_t)tid * 128u;
-        const uint32_t sw = (uint32_t)(tid & 7);
-        // running position in k: filter tap (r, s) and channel c
-        int r = 0, s = 0, c = 0, tap = 0;
+        // ===== A producer =====
+        // position of this thread's chunk in k: filter tap (r, s) and first channel c
+        const int kk0 = kb_begin * kBK + chunk * 8;
+        int tap = kk0 / a.Cp;
+        int c = kk0 - tap * a.Cp;
+        int r = tap / a.S, s = tap - r * a.S;
+        const uint32_t dst_off = (uint32_t)rbase * 128u + (((uint32_t)chunk ^ (uint32_t)(rbase & 7)) << 4);
         bool ok = true;
-        for (int kb = 0; kb < a.nkb; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb) {
             const int st = kb % kStages;
             const uint32_t use = (uint32_t)(kb / kStages);
             if (ok) ok = mbar_wait(smem_u32(&s_empty[st]), (use & 1u) ^ 1u, &s_abort, a.err_flag, 1u);
@@ -227,84 +410,55 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a, u
             if (ok) {
                 if (tid == 0) {
                     mbar_expect_tx(smem_u32(&s_full[st]), a.b_stage_bytes);
-                    tma_load_2d(a_tile + kATileBytes, &tmap_w, kb * kBK, n0, smem_u32(&s_full[st]));
+                    tma_load_2d(a_tile + kATileBytes, &tmap_w, (kb_begin + kb) * kBK, n0, smem_u32(&s_full[st]));
                 }
+                const bool tap_ok = tap < a.taps && c < a.Cs;
+                const __nv_bfloat16* xc = a.x + c;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int ih = ih0 + r, iw = iw0 + s;
-                    const bool inb = row_valid && tap < a.taps && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W;
-                    const __nv_bfloat16* src = inb ? a.x + ((size_t)ih * a.W + iw) * a.Cs + c : a.x;
-                    cp_async_16(a_tile + row_off + (((uint32_t)j ^ sw) << 4), src, inb ? 16u : 0u);
-                    c += 8;
-                    if (c >= a.Cs) {
-                        c = 0; ++tap; ++s;
-                        if (s == a.S) { s = 0; ++r; }
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    const int ih = ih0[i] + r, iw = iw0[i] + s;
+                    const bool inb = tap_ok && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W;
+                    const __nv_bfloat16* src = inb ? xc + ((size_t)ih * a.W + iw) * a.Cs : a.x;
+                    cp_async_16(a_tile + dst_off + (uint32_t)i * 2048u, src, inb ? 16u : 0u);
+                }
+                c += kBK;
+                while (c >= a.Cp) {
+                    c -= a.Cp; ++tap; ++s;
+                    if (s == a.S) { s = 0; ++r; }
                 }
             }
             cp_async_commit();
+            if (kb == 0 && tid == 0) PB_T(2);
+            // One arrival per warp: 128 threads arriving on the same shared-memory word serialise
+            // (measured: ~0.2 us per k-block); every lane first makes its own copies visible to the
+            // async proxy, the warp converges, one lane arrives.
             if (kb >= kLag) {
                 cp_async_wait<kLag>();
                 fence_proxy_async();
-                mbar_arrive(smem_u32(&s_full[(kb - kLag) % kStages]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&s_full[(kb - kLag) % kStages]));
             }
         }
         // drain: the last kLag k-blocks
         cp_async_wait<0>();
         fence_proxy_async();
-        for (int kb = (a.nkb > kLag ? a.nkb - kLag : 0); kb < a.nkb; ++kb) mbar_arrive(smem_u32(&s_full[kb % kStages]));
+        __syncwarp();
+        if (lane == 0)
+            for (int kb = (nkb > kLag ? nkb - kLag : 0); kb < nkb; ++kb) mbar_arrive(smem_u32(&s_full[kb % kStages]));
 
         // ===== epilogue: accumulator lane `tid` = tile row `tid` =====
-        if (ok) ok = mbar_wait(smem_u32(&s_accum), 0u, &s_abort, a.err_flag, 3u);
-        ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
-        tcgen05_fence_after();
-        if (ok) {
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-            __nv_bfloat16* yrow = a.y + (size_t)m * a.Ks + a.out_c_off;
-            const __nv_bfloat16* rrow = a.residual ? a.residual + (size_t)m * a.res_Cs : nullptr;
-            for (int cb = 0; cb < a.BN; cb += 16) {
-                uint32_t v[16];
-                tcgen05_ld16(lane_addr + (uint32_t)cb, v);   // warp-collective: all lanes take part
-                tcgen05_wait_ld();
-                const int k0 = n0 + cb;
-                if (row_valid && k0 < a.K) {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int kk = k0 + h * 8;
-                        if (kk + 8 <= a.K) {
-                            float f[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[h * 8 + j]) + (a.bias ? __ldg(a.bias + kk + j) : 0.f);
-                            if (rrow) {
-                                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + kk);
-                                const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    f[2 * j] += __uint_as_float(ru[j] << 16);
-                                    f[2 * j + 1] += __uint_as_float(ru[j] & 0xffff0000u);
-                                }
-                            }
-                            uint32_t o[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const __nv_bfloat162 hv = __floats2bfloat162_rn(act_fn(f[2 * j], a.act), act_fn(f[2 * j + 1], a.act));
-                                o[j] = *reinterpret_cast<const uint32_t*>(&hv);
-                            }
-                            *reinterpret_cast<uint4*>(yrow + kk) = make_uint4(o[0], o[1], o[2], o[3]);
-                        }
-                    }
-                }
-            }
-        }
+        epilogue(a, tmem_base, ok, m0, n0, s_bias, &s_accum, &s_abort, &s_is_last);
+        if (tid == 0) PB_T(6);
     } else {
         // ===== MMA issuer: one thread =====
         if (lane == 0) {
             bool ok = true;
-            for (int kb = 0; kb < a.nkb && ok; ++kb) {
+            for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int st = kb % kStages;
                 const uint32_t use = (uint32_t)(kb / kStages);
                 ok = mbar_wait(smem_u32(&s_full[st]), use & 1u, &s_abort, a.err_flag, 2u);
                 if (!ok) break;
+                if (kb == 0) PB_T(3);
                 tcgen05_fence_after();
                 const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
                 const uint32_t b_tile = a_tile + kATileBytes;
@@ -316,6 +470,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a, u
                 tcgen05_commit(smem_u32(&s_empty[st]));   // frees the stage once these MMAs have read it
             }
             if (ok) tcgen05_commit(smem_u32(&s_accum));   // accumulator complete
+            PB_T(4);
         }
         __syncwarp();
     }
@@ -334,6 +489,139 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a, u
         tcgen05_fence_after();
         tcgen05_dealloc(tmem_base, a.tmem_cols);
     }
+    if (threadIdx.x == 0) PB_T(7);
+    if (nf) nf->end(job_id);
+}
+
+// ---- the kernel, operand A by im2col TMA ---------------------------------------------------------
+// CTA = 6 warps.  Warp 4: one thread issues, per k-block, one im2col TMA for A (128 output pixels x
+// 64 channels of one filter tap) and one tiled TMA for B.  Warp 5: allocates TMEM, one thread issues
+// the MMAs.  Warps 0-3 only run the epilogue.  No thread computes an address in the main loop.
+constexpr int kThreadsTma = 192;
+
+template <int kStages>
+__global__ void __launch_bounds__(kThreadsTma, 1)
+conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const ConvArgs a,
+                     uint32_t job_id, FinishedBlockNotifier* nf) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kStages];
+    __shared__ __align__(8) uint64_t s_empty[kStages];
+    __shared__ __align__(8) uint64_t s_accum;
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ uint32_t s_is_last;
+    __shared__ float s_bias[128];
+
+    if (nf) nf->start(job_id);
+    if (threadIdx.x == 0) PB_T(0);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t stage_bytes = (uint32_t)kATileBytes + a.b_stage_bytes;
+
+    const int m0 = blockIdx.x * kBM;
+    const int n0 = blockIdx.y * a.BN;
+    const int kb_begin = blockIdx.z * a.kb_per_split;
+    const int kb_end = min(a.nkb, kb_begin + a.kb_per_split);
+    const int nkb = kb_end - kb_begin;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&s_full[s]), 1);      // the producer's arrive.expect_tx
+            mbar_init(smem_u32(&s_empty[s]), 1);     // tcgen05.commit
+        }
+        mbar_init(smem_u32(&s_accum), 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < 128) {
+        const int k = n0 + tid;
+        s_bias[tid] = (a.bias && tid < a.BN && k < a.K) ? __ldg(a.bias + k) : 0.f;
+    }
+    if (warp == 5) {
+        tcgen05_alloc(smem_u32(&s_tmem_base), a.tmem_cols);
+        tcgen05_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    if (threadIdx.x == 0) PB_T(1);
+
+    if (warp < 4) {
+        epilogue(a, tmem_base, true, m0, n0, s_bias, &s_accum, &s_abort, &s_is_last);
+        if (tid == 0) PB_T(6);
+    } else if (warp == 4) {
+        // ===== producer: one thread =====
+        if (lane == 0) {
+            const int p0 = m0 / a.Q, q0 = m0 - p0 * a.Q;
+            const int w0 = q0 * a.sw - a.pw;          // filter-window origin of the tile's first pixel
+            const int h0 = p0 * a.sh - a.ph;
+            const int cpt = a.Cp / kBK;               // k-blocks per filter tap
+            int tap = kb_begin / cpt;
+            int chunk = kb_begin - tap * cpt;
+            int r = tap / a.S, s = tap - r * a.S;
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int st = kb % kStages;
+                const uint32_t use = (uint32_t)(kb / kStages);
+                ok = mbar_wait(smem_u32(&s_empty[st]), (use & 1u) ^ 1u, &s_abort, a.err_flag, 1u);
+                if (!ok) break;
+                const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
+                const uint32_t bar = smem_u32(&s_full[st]);
+                mbar_arrive_expect_tx(bar, (uint32_t)kATileBytes + a.b_stage_bytes);
+                tma_load_im2col_4d(a_tile, &tmap_x, chunk * kBK, w0, h0, 0, (uint16_t)s, (uint16_t)r, bar);
+                tma_load_2d(a_tile + kATileBytes, &tmap_w, (kb_begin + kb) * kBK, n0, bar);
+                if (kb == 0) PB_T(2);
+                if (++chunk == cpt) {
+                    chunk = 0;
+                    if (++s == a.S) { s = 0; ++r; }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ===== MMA issuer: one thread =====
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int st = kb % kStages;
+                const uint32_t use = (uint32_t)(kb / kStages);
+                ok = mbar_wait(smem_u32(&s_full[st]), use & 1u, &s_abort, a.err_flag, 2u);
+                if (!ok) break;
+                if (kb == 0) PB_T(3);
+                tcgen05_fence_after();
+                const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
+                const uint32_t b_tile = a_tile + kATileBytes;
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k) {
+                    tcgen05_mma_bf16(tmem_base, umma_desc_sw128(a_tile + k * 32), umma_desc_sw128(b_tile + k * 32), a.idesc,
+                                     (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(smem_u32(&s_empty[st]));
+            }
+            if (ok) tcgen05_commit(smem_u32(&s_accum));
+            PB_T(4);
+        }
+        __syncwarp();
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (s_abort) {
+        const unsigned long long t0 = globaltimer_ns();
+        for (uint32_t i = 0; i < (1u << 20); ++i) {
+            if (globaltimer_ns() - t0 > 50000ull) break;
+        }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tcgen05_fence_after();
+        tcgen05_dealloc(tmem_base, a.tmem_cols);
+    }
+    if (threadIdx.x == 0) PB_T(7);
     if (nf) nf->end(job_id);
 }
 
@@ -357,18 +645,51 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const int*, const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeIm2colFn encode_im2col_fn() {
+    static EncodeIm2colFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeIm2colFn)p;
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+// Operand A by im2col TMA unless PB_CONV_GATHER=1 asks for the cp.async gather kernel.
+bool use_tma_a() {
+    static const bool v = [] {
+        const char* e = getenv("PB_CONV_GATHER");
+        return !(e && e[0] == '1');
+    }();
+    return v;
+}
+
 struct Geometry {
-    int Kdim, Kdim_pad, nkb;
+    int cpt, Cp;                // 64-channel k-blocks per filter tap; Cp = cpt * 64
+    int Kdim_pad, nkb;          // k = tap * Cp + c
     int Kp16, n_tiles, BN, Kout_pad;
     int m_tiles;
+    int stages;                 // 4, 6 or 8
+    int splits, kb_per_split;   // split-K factor the kernel uses when scratch memory is supplied
+    uint64_t scratch_bytes;     // counters + partial tiles for that factor
     uint32_t tmem_cols, b_stage_bytes, smem_bytes, idesc;
 };
 
 Geometry geometry(const pb_op_params* p) {
     Geometry g;
-    g.Kdim = p->R * p->S * p->Cs;
-    g.Kdim_pad = round_up(g.Kdim, kBK);
-    g.nkb = g.Kdim_pad / kBK;
+    g.cpt = ceil_div(p->Cs, kBK);
+    g.Cp = g.cpt * kBK;
+    g.nkb = p->R * p->S * g.cpt;
+    g.Kdim_pad = g.nkb * kBK;
     g.Kp16 = round_up(p->K, 16);
     g.n_tiles = ceil_div(g.Kp16, 128);
     g.BN = round_up(ceil_div(g.Kp16, g.n_tiles), 16);
@@ -377,10 +698,51 @@ Geometry geometry(const pb_op_params* p) {
     g.tmem_cols = 32;
     while ((int)g.tmem_cols < g.BN) g.tmem_cols <<= 1;
     g.b_stage_bytes = (uint32_t)g.BN * 128u;
-    g.smem_bytes = kStages * ((uint32_t)kATileBytes + g.b_stage_bytes) + 1024u;
+    // Split the reduction over blockIdx.z when that shortens the launch.  Cost model fitted to phase
+    // timings on B200 (microseconds): a k-block costs 0.2 + 0.001*BN in the main loop; a split launch
+    // pays 1.5 for parking the partial tiles plus 0.0088*BN per partial tile the last CTA adds up.
+    const int tiles = g.m_tiles * g.n_tiles;
+    const double per_kb = 0.2 + 0.001 * g.BN, per_partial = 0.0088 * g.BN;
+    int want = 1;
+    double best = g.nkb * per_kb;
+    for (int sp = 2; sp <= 16 && tiles * sp <= 296 && sp * 4 <= g.nkb; ++sp) {
+        const double t = ceil_div(g.nkb, sp) * per_kb + 1.5 + sp * per_partial;
+        if (t < best - 0.5) { best = t; want = sp; }
+    }
+    g.kb_per_split = ceil_div(g.nkb, want);
+    g.splits = ceil_div(g.nkb, g.kb_per_split);
+    g.scratch_bytes = g.splits > 1 ? (uint64_t)kCounterBytes + (uint64_t)tiles * g.splits * kBM * g.BN * 4ull : 0;
+    if ((uint64_t)tiles * 4 > kCounterBytes) { g.splits = 1; g.kb_per_split = g.nkb; g.scratch_bytes = 0; }
+    // Pipeline depth: as many stages as the k-loop can use and shared memory holds.
+    const uint32_t stage_bytes = (uint32_t)kATileBytes + g.b_stage_bytes;
+    const int longest = g.kb_per_split;
+    g.stages = 8;
+    while (g.stages > 4 && ((uint32_t)g.stages * stage_bytes + 1024u > kSmemBudget || g.stages - 2 >= longest + 2)) g.stages -= 2;
+    g.smem_bytes = (uint32_t)g.stages * stage_bytes + 1024u;
     // c_format f32 (1 << 4), a/b format bf16 (1 << 7, 1 << 10), K-major both, N >> 3 at bit 17, M >> 4 at bit 24
     g.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(g.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
     return g;
+}
+
+// Without (enough) scratch memory the kernel runs the whole reduction in one CTA per tile.
+void drop_split(Geometry* g) {
+    g->splits = 1;
+    g->kb_per_split = g->nkb;
+}
+
+const void* kernel_for(int stages, bool tma) {
+    if (tma) {
+        switch (stages) {
+            case 4: return (const void*)conv_umma_tma_kernel<4>;
+            case 6: return (const void*)conv_umma_tma_kernel<6>;
+            default: return (const void*)conv_umma_tma_kernel<8>;
+        }
+    }
+    switch (stages) {
+        case 4: return (const void*)conv_umma_gather_kernel<4>;
+        case 6: return (const void*)conv_umma_gather_kernel<6>;
+        default: return (const void*)conv_umma_gather_kernel<8>;
+    }
 }
 
 }  // namespace
@@ -400,14 +762,16 @@ bool conv_umma_supported(const pb_op_params* p) {
 
 int conv_umma_info(const pb_op_params* p, pb_launch_info* out) {
     PB_REQUIRE(conv_umma_supported(p), "conv_umma: unsupported convolution");
-    const Geometry g = geometry(p);
+    Geometry g = geometry(p);
     memset(out, 0, sizeof(*out));
+    out->scratch_bytes = g.scratch_bytes;       // what a split launch needs
+    if (g.splits > 1 && (p->scratch == nullptr || p->scratch_bytes < g.scratch_bytes)) drop_split(&g);
     out->kind = PB_STAGE_CONV_UMMA;
-    out->num_blocks = (uint32_t)(g.m_tiles * g.n_tiles);
-    out->threads_per_block = kThreads;
+    out->num_blocks = (uint32_t)(g.m_tiles * g.n_tiles * g.splits);
+    out->threads_per_block = use_tma_a() ? kThreadsTma : kThreads;
     cudaFuncAttributes at;
     uint32_t regs = 64, sstatic = 128;
-    if (cudaFuncGetAttributes(&at, (const void*)conv_umma_kernel) == cudaSuccess) {
+    if (cudaFuncGetAttributes(&at, kernel_for(g.stages, use_tma_a())) == cudaSuccess) {
         regs = (uint32_t)at.numRegs;
         sstatic = (uint32_t)at.sharedSizeBytes;
     } else {
@@ -433,7 +797,7 @@ int64_t conv_umma_pack_weights(const pb_op_params* p, const float* w, void* dst)
             for (int c = 0; c < p->C; ++c)
                 for (int r = 0; r < p->R; ++r)
                     for (int s = 0; s < p->S; ++s)
-                        store_elem(dst, (size_t)k * g.Kdim_pad + (size_t)(r * p->S + s) * p->Cs + c,
+                        store_elem(dst, (size_t)k * g.Kdim_pad + (size_t)(r * p->S + s) * g.Cp + c,
                                    w[(((size_t)k * p->C + c) * p->R + r) * p->S + s], 1);
     }
     return (int64_t)(n * 2);
@@ -457,6 +821,44 @@ static int make_tmap(const Geometry& g, const void* w_dev, CUtensorMap* out) {
     return PB_OK;
 }
 
+// im2col tensor map over the channels-last activation tensor [N=1][H][W][Cs] (dims listed innermost
+// first).  The bounding box of filter-window origins is [-pad, dim + pad - (filter-1)); traversal
+// strides are the convolution strides; each load brings 128 pixels x 64 channels.
+static int make_xmap(const pb_op_params* p, CUtensorMap* out) {
+    EncodeIm2colFn enc = encode_im2col_fn();
+    PB_REQUIRE(enc != nullptr, "cuTensorMapEncodeIm2col is not available from this driver");
+    PB_REQUIRE(((uintptr_t)p->x & 15) == 0, "conv_umma: activations must be 16-byte aligned");
+    const cuuint64_t dims[4] = {(cuuint64_t)p->Cs, (cuuint64_t)p->W, (cuuint64_t)p->H, 1};
+    const cuuint64_t strides[3] = {(cuuint64_t)p->Cs * 2, (cuuint64_t)p->W * p->Cs * 2, (cuuint64_t)p->H * p->W * p->Cs * 2};
+    const int lower[2] = {-p->pad_w, -p->pad_h};
+    const int upper[2] = {p->pad_w - (p->S - 1), p->pad_h - (p->R - 1)};
+    const cuuint32_t estr[4] = {1, (cuuint32_t)p->stride_w, (cuuint32_t)p->stride_h, 1};
+    const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(p->x), dims, strides, lower, upper,
+                           (cuuint32_t)kBK, (cuuint32_t)kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeIm2col failed with CUresult %d (C %d W %d H %d pad %d,%d filter %dx%d stride %d,%d)", (int)r, p->Cs,
+                  p->W, p->H, p->pad_h, p->pad_w, p->R, p->S, p->stride_h, p->stride_w);
+        return PB_ERR_CUDA;
+    }
+    return PB_OK;
+}
+
+struct alignas(64) ConvUmmaXMap {
+    CUtensorMap map;
+};
+
+int conv_umma_xmap_create(const pb_op_params* p, ConvUmmaXMap** out) {
+    if (!use_tma_a()) { *out = nullptr; return PB_OK; }
+    ConvUmmaXMap* m = new ConvUmmaXMap();
+    const int rc = make_xmap(p, &m->map);
+    if (rc != PB_OK) { delete m; return rc; }
+    *out = m;
+    return PB_OK;
+}
+
+void conv_umma_xmap_destroy(ConvUmmaXMap* m) { delete m; }
+
 int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan** out) {
     PB_REQUIRE(conv_umma_supported(p), "conv_umma: unsupported convolution");
     ConvUmmaPlan* plan = new ConvUmmaPlan();
@@ -467,7 +869,9 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute((const void*)conv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+        for (int tma = 0; tma < 2; ++tma)
+            for (int st = 4; st <= kMaxStages && attr_err == cudaSuccess; st += 2)
+                attr_err = cudaFuncSetAttribute(kernel_for(st, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
     });
     if (attr_err != cudaSuccess) { delete plan; return cuda_fail(attr_err, "cudaFuncSetAttribute(conv_umma)", __FILE__, __LINE__); }
     *out = plan;
@@ -476,8 +880,10 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
 
 void conv_umma_plan_destroy(ConvUmmaPlan* plan) { delete plan; }
 
-int conv_umma_launch_planned(const ConvUmmaPlan* plan, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier) {
-    const Geometry& g = plan->g;
+int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
+                             uint32_t job_id, void* notifier) {
+    Geometry g = plan->g;
+    if (g.splits > 1 && (p->scratch == nullptr || p->scratch_bytes < g.scratch_bytes)) drop_split(&g);
     ConvArgs a;
     a.x = static_cast<const __nv_bfloat16*>(p->x);
     a.residual = static_cast<const __nv_bfloat16*>(p->residual);
@@ -488,10 +894,33 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const pb_op_params* p, cu
     a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.P = p->P; a.Q = p->Q; a.M = p->P * p->Q;
     a.K = p->K; a.Ks = p->Ks; a.out_c_off = p->out_c_off; a.res_Cs = p->res_Cs;
     a.R = p->R; a.S = p->S; a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w;
-    a.act = p->act; a.nkb = g.nkb; a.taps = p->R * p->S; a.BN = g.BN; a.idesc = g.idesc; a.tmem_cols = g.tmem_cols;
+    a.act = p->act; a.nkb = g.nkb; a.taps = p->R * p->S; a.Cp = g.Cp; a.BN = g.BN; a.idesc = g.idesc; a.tmem_cols = g.tmem_cols;
     a.b_stage_bytes = g.b_stage_bytes;
-    const dim3 grid((unsigned)g.m_tiles, (unsigned)g.n_tiles);
-    conv_umma_kernel<<<grid, kThreads, g.smem_bytes, st>>>(plan->tmap, a, job_id, static_cast<FinishedBlockNotifier*>(notifier));
+    a.splits = g.splits;
+    a.kb_per_split = g.kb_per_split;
+    a.counters = g.splits > 1 ? static_cast<unsigned*>(p->scratch) : nullptr;
+    a.ws = g.splits > 1 ? reinterpret_cast<float*>(static_cast<char*>(p->scratch) + kCounterBytes) : nullptr;
+    const dim3 grid((unsigned)g.m_tiles, (unsigned)g.n_tiles, (unsigned)g.splits);
+    FinishedBlockNotifier* nf = static_cast<FinishedBlockNotifier*>(notifier);
+    if (use_tma_a()) {
+        ConvUmmaXMap local;
+        if (!xmap) {
+            const int rc = make_xmap(p, &local.map);
+            if (rc != PB_OK) return rc;
+            xmap = &local;
+        }
+        switch (g.stages) {
+            case 4: conv_umma_tma_kernel<4><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
+            case 6: conv_umma_tma_kernel<6><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
+            default: conv_umma_tma_kernel<8><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
+        }
+    } else {
+        switch (g.stages) {
+            case 4: conv_umma_gather_kernel<4><<<grid, kThreads, g.smem_bytes, st>>>(plan->tmap, a, job_id, nf); break;
+            case 6: conv_umma_gather_kernel<6><<<grid, kThreads, g.smem_bytes, st>>>(plan->tmap, a, job_id, nf); break;
+            default: conv_umma_gather_kernel<8><<<grid, kThreads, g.smem_bytes, st>>>(plan->tmap, a, job_id, nf); break;
+        }
+    }
     return launch_check("conv_umma");
 }
 
@@ -499,8 +928,8 @@ int conv_umma_launch(const pb_op_params* p, cudaStream_t st, uint32_t job_id, vo
     ConvUmmaPlan* plan = nullptr;
     int rc = conv_umma_plan_create(p, p->w, &plan);
     if (rc != PB_OK) return rc;
-    rc = conv_umma_launch_planned(plan, p, st, job_id, notifier);
-    conv_umma_plan_destroy(plan);   // the tensor map was copied into the launch parameters
+    rc = conv_umma_launch_planned(plan, nullptr, p, st, job_id, notifier);
+    conv_umma_plan_destroy(plan);   // the tensor maps were copied into the launch parameters
     return rc;
 }
 

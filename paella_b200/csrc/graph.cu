@@ -61,6 +61,7 @@ struct pb_model {
     std::vector<Stage> stages;
     int t_in = 0, t_out = 0;
     size_t arena_bytes = 0;
+    size_t scratch_bytes = 0;     // largest per-stage scratch requirement (split-K partial tiles)
     size_t in_floats = 0, out_floats = 0;
     bool mnist_fused = false;
     // fused MNIST weights (device)
@@ -71,9 +72,11 @@ struct pb_model {
 struct pb_instance {
     pb_model* m = nullptr;
     char* arena = nullptr;
+    char* scratch = nullptr;
     float* in_dev = nullptr;
     float* out_dev = nullptr;
     std::vector<pb_op_params> params;   // per stage, pointers resolved
+    std::vector<pb::ConvUmmaXMap*> xmaps;   // per stage: im2col descriptor of the stage's input (tensor-core convs)
 };
 
 namespace {
@@ -322,7 +325,11 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         }
         p.w = st.w_dev;
         p.bias = st.bias_dev;
+        // every instance brings scratch memory of the model's largest requirement: size the launch for it
+        p.scratch = (void*)16;
+        p.scratch_bytes = ~0ull;
         PB_FAIL_LOAD(pb_op_info(st.kind, &p, &st.info));
+        if (st.info.scratch_bytes > m->scratch_bytes) m->scratch_bytes = st.info.scratch_bytes;
         if (st.kind == PB_STAGE_CONV_UMMA) PB_FAIL_LOAD(pb::conv_umma_plan_create(&p, st.w_dev, &st.plan));
         m->stages.push_back(st);
     }
@@ -361,6 +368,8 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
     in->m = m;
     cudaError_t e = cudaMalloc((void**)&in->arena, m->arena_bytes + 256);
     if (e == cudaSuccess) e = cudaMemset(in->arena, 0, m->arena_bytes + 256);
+    if (e == cudaSuccess && m->scratch_bytes) e = cudaMalloc((void**)&in->scratch, m->scratch_bytes);
+    if (e == cudaSuccess && m->scratch_bytes) e = cudaMemset(in->scratch, 0, m->scratch_bytes);
     if (e == cudaSuccess) e = cudaMalloc((void**)&in->in_dev, pb::round_up(m->in_floats * 4, (size_t)256));
     if (e == cudaSuccess) e = cudaMalloc((void**)&in->out_dev, pb::round_up(m->out_floats * 4, (size_t)256));
     if (e == cudaSuccess) e = cudaMemset(in->out_dev, 0, pb::round_up(m->out_floats * 4, (size_t)256));
@@ -369,13 +378,20 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
         return pb::cuda_fail(e, "instance buffers", __FILE__, __LINE__);
     }
     in->params.resize(m->stages.size());
+    in->xmaps.assign(m->stages.size(), nullptr);
     for (size_t i = 0; i < m->stages.size(); ++i) {
         const Stage& st = m->stages[i];
         pb_op_params p = st.p;
         p.x = st.x_is_input ? (const void*)in->in_dev : (const void*)(in->arena + st.x_off);
         p.y = st.y_is_output ? (void*)in->out_dev : (void*)(in->arena + st.y_off);
         p.residual = st.has_res ? (const void*)(in->arena + st.res_off) : nullptr;
+        p.scratch = in->scratch;
+        p.scratch_bytes = in->scratch ? m->scratch_bytes : 0;
         in->params[i] = p;
+        if (st.kind == PB_STAGE_CONV_UMMA) {
+            const int rc = pb::conv_umma_xmap_create(&p, &in->xmaps[i]);
+            if (rc != PB_OK) { pb_instance_destroy(in); return rc; }
+        }
     }
     *out = in;
     return PB_OK;
@@ -384,7 +400,9 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
 void pb_instance_destroy(pb_instance* in) {
     if (!in) return;
     if (in->m) cudaSetDevice(in->m->device);
+    for (pb::ConvUmmaXMap* x : in->xmaps) pb::conv_umma_xmap_destroy(x);
     if (in->arena) cudaFree(in->arena);
+    if (in->scratch) cudaFree(in->scratch);
     if (in->in_dev) cudaFree(in->in_dev);
     if (in->out_dev) cudaFree(in->out_dev);
     delete in;
@@ -404,7 +422,7 @@ int pb_instance_launch_stage(pb_instance* in, int stage, void* stream, uint32_t 
                                           job_id, notifier);
         }
         case PB_STAGE_CONV_UMMA:
-            return pb::conv_umma_launch_planned(st.plan, p, (cudaStream_t)stream, job_id, notifier);
+            return pb::conv_umma_launch_planned(st.plan, in->xmaps[stage], p, (cudaStream_t)stream, job_id, notifier);
         default:
             return pb::simple_op_launch(st.kind, p, (cudaStream_t)stream, job_id, notifier);
     }

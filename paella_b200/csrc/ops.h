@@ -42,7 +42,12 @@ int64_t conv_umma_pack_weights(const pb_op_params* p, const float* w_oihw, void*
 struct ConvUmmaPlan;
 int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan** out);
 void conv_umma_plan_destroy(ConvUmmaPlan* plan);
-int conv_umma_launch_planned(const ConvUmmaPlan* plan, const pb_op_params* p, cudaStream_t st, uint32_t job_id,
-                             void* notifier);
+// Per-instance state: the im2col TMA descriptor of one layer's INPUT tensor (`p->x`).
+struct ConvUmmaXMap;
+int conv_umma_xmap_create(const pb_op_params* p, ConvUmmaXMap** out);
+void conv_umma_xmap_destroy(ConvUmmaXMap* m);
+// xmap may be NULL: the descriptor is then encoded for this one launch.
+int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
+                             uint32_t job_id, void* notifier);
 
 }  // namespace pb

@@ -37,7 +37,8 @@ def _assert_close(got, ref, dtype):
         assert not bad.any(), f"{int(bad.sum())} of {bad.size} elements off; worst {float(np.abs(got - ref).max())} (scale {scale})"
 
 
-def _run_conv(kind, dtype, C_, H, W, K, R, S, sh, sw, ph, pw, groups=1, act=1, residual=False, out_total=None, off=0, bias=True):
+def _run_conv(kind, dtype, C_, H, W, K, R, S, sh, sw, ph, pw, groups=1, act=1, residual=False, out_total=None, off=0, bias=True,
+              scratch=False):
     import torch
     L = capi.load()
     x = RNG.standard_normal((C_, H, W), dtype=np.float32)
@@ -62,12 +63,26 @@ def _run_conv(kind, dtype, C_, H, W, K, R, S, sh, sw, ph, pw, groups=1, act=1, r
     li = capi.LaunchInfo()
     capi.check(L.pb_op_info(kind, C.byref(p), C.byref(li)), "pb_op_info")
     assert li.flops == 2 * K * P * Q * (C_ // groups) * R * S
-    capi.check(L.pb_op_launch(kind, C.byref(p), None, 0, None), "pb_op_launch")
-    gu.sync()
-    assert gu.error_flag() == 0
-    got_all = gu.from_device_cl(yd, out_total)
+    unsplit_blocks = li.num_blocks
+    launches = 1
+    if scratch:
+        if li.scratch_bytes == 0:
+            pytest.skip("this shape is not split")
+        sd = torch.zeros(li.scratch_bytes, dtype=torch.uint8, device="cuda")
+        p.scratch, p.scratch_bytes = sd.data_ptr(), li.scratch_bytes
+        capi.check(L.pb_op_info(kind, C.byref(p), C.byref(li)), "pb_op_info")
+        assert li.num_blocks > unsplit_blocks
+        launches = 3          # the tile counters must be back at zero after every launch
     ref = og.conv2d(x, w, b, (sh, sw), (ph, pw), groups, act, res)
-    _assert_close(got_all[off:off + K], ref, dtype)
+    for _ in range(launches):
+        yd.fill_(7.0)
+        capi.check(L.pb_op_launch(kind, C.byref(p), None, 0, None), "pb_op_launch")
+        gu.sync()
+        assert gu.error_flag() == 0
+        got_all = gu.from_device_cl(yd, out_total)
+        _assert_close(got_all[off:off + K], ref, dtype)
+    if scratch:
+        assert int(sd[:4096].to(torch.int32).sum()) == 0
     if out_total > K:   # channels outside the slice are untouched
         mask = np.ones(out_total, bool)
         mask[off:off + K] = False
@@ -110,9 +125,18 @@ UMMA_CASES = [
 
 @pytest.mark.parametrize("case", UMMA_CASES)
 def test_conv_umma(case):
-    L = capi.load()
-    C_, H, W, K = case[:4]
     _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=False)
+
+
+SPLIT_CASES = [c for c in UMMA_CASES if c[4] * c[5] * c[0] >= 256 and ((c[1] + 2 * c[8] - c[4]) // c[6] + 1) ** 2 <= 2048]
+
+
+@pytest.mark.parametrize("case", SPLIT_CASES)
+def test_conv_umma_split_reduction(case):
+    """Same cases with scratch memory supplied: the reduction is split over blockIdx.z and the last
+    block to arrive on a tile adds the partial tiles.  fp32 partial sums in a different order:
+    same tolerance as the unsplit kernel."""
+    _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=(case[3] % 64 == 0), scratch=True)
 
 
 def test_conv_umma_epilogue_variants():
