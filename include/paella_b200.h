@@ -157,6 +157,23 @@ PB_API int pb_op_launch(int kind, const pb_op_params* p, void* stream, uint32_t 
 PB_API int64_t pb_op_pack_weights(int kind, const pb_op_params* p, const float* w_oihw, void* dst_host);
 /* 1 if the tcgen05 implicit-GEMM kernel supports this convolution. */
 PB_API int pb_conv_umma_supported(const pb_op_params* p);
+/* Tensor-core convolution for callers that must not allocate: code running inside a CUDA memory-pool
+ * or allocator callback, a latency-critical thread that may not take the allocator's locks, or a host
+ * that pre-partitions all device memory and leaves none to ask for.  It has no counterpart in the
+ * reference (which allocates freely); it is the same kernel as pb_op_launch(PB_STAGE_CONV_UMMA) with its
+ * split-K scratch taken from a buffer built into the library instead of p->scratch.
+ *  - p->scratch / p->scratch_bytes are ignored.  Inputs, weights and outputs are still the caller's.
+ *  - Limit: the built-in buffer is 4 MiB (and is held by every GPU that loads the library until the
+ *    process exits).  A convolution whose split needs more (pb_launch_info.scratch_bytes) is refused
+ *    with PB_ERR_INVALID and a message; nothing is launched.
+ *  - The first call on each device looks up the buffer's device address and sets the kernels' shared
+ *    memory limit; make that first call outside any stream capture.
+ *  - All calls on a device share the one buffer: the tile counters are cleared (stream-ordered) at the
+ *    start of every call, the rest keeps the previous call's contents.  Two calls whose kernels can
+ *    overlap on the GPU (different streams, no dependency) race on it: keep them on one stream or
+ *    order them yourself.
+ *  - Never calls cudaMalloc, cudaFree or any allocating routine, on the host heap either. */
+PB_API int pb_conv2d_umma_noalloc(const pb_op_params* p, void* stream, uint32_t job_id, void* notifier);
 /* Device-side error flag raised by bounded waits inside kernels (0 = none). */
 PB_API int pb_device_error_flag(int device, uint32_t* flag_out, int reset);
 

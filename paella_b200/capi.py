@@ -115,6 +115,7 @@ SIGNATURES = {
     "pb_op_launch": (_I, [_I, C.POINTER(OpParams), _VP, _U32, _VP]),
     "pb_op_pack_weights": (C.c_int64, [_I, C.POINTER(OpParams), _VP, _VP]),
     "pb_conv_umma_supported": (_I, [C.POINTER(OpParams)]),
+    "pb_conv2d_umma_noalloc": (_I, [C.POINTER(OpParams), _VP, _U32, _VP]),
     "pb_device_error_flag": (_I, [_I, C.POINTER(_U32), _I]),
     "pb_model_load": (_I, [C.c_char_p, _I, _I, _PP]),
     "pb_model_destroy": (None, [_VP]),

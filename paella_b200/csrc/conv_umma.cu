@@ -52,6 +52,9 @@ constexpr int kBK = 64;             // bf16 elements per k-block = one 128-byte 
 constexpr int kMaxStages = 8;
 constexpr uint32_t kSmemBudget = 200u * 1024u;
 constexpr uint32_t kCounterBytes = 4096;        // split-K tile counters at the head of the scratch buffer
+#ifndef PB_NOALLOC_SCRATCH_BYTES
+#define PB_NOALLOC_SCRATCH_BYTES (4u << 20)      // built-in scratch of pb_conv2d_umma_noalloc: 4 MiB per GPU
+#endif
 constexpr int kATileBytes = kBM * kBK * 2;   // 16 KiB
 constexpr uint32_t kWaitLimit = 4u * 1000u * 1000u;  // polls of mbarrier.try_wait before giving up
 constexpr int kThreads = 160;
@@ -881,7 +884,7 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
 void conv_umma_plan_destroy(ConvUmmaPlan* plan) { delete plan; }
 
 int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
-                             uint32_t job_id, void* notifier) {
+                             uint32_t job_id, void* notifier, uint32_t* err_flag) {
     Geometry g = plan->g;
     if (g.splits > 1 && (p->scratch == nullptr || p->scratch_bytes < g.scratch_bytes)) drop_split(&g);
     ConvArgs a;
@@ -889,7 +892,7 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
     a.residual = static_cast<const __nv_bfloat16*>(p->residual);
     a.bias = p->bias;
     a.y = static_cast<__nv_bfloat16*>(p->y);
-    a.err_flag = device_error_flag_ptr(plan->device);
+    a.err_flag = err_flag ? err_flag : device_error_flag_ptr(plan->device);
     PB_REQUIRE(a.err_flag != nullptr, "conv_umma: no device error flag");
     a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.P = p->P; a.Q = p->Q; a.M = p->P * p->Q;
     a.K = p->K; a.Ks = p->Ks; a.out_c_off = p->out_c_off; a.res_Cs = p->res_Cs;
@@ -928,9 +931,75 @@ int conv_umma_launch(const pb_op_params* p, cudaStream_t st, uint32_t job_id, vo
     ConvUmmaPlan* plan = nullptr;
     int rc = conv_umma_plan_create(p, p->w, &plan);
     if (rc != PB_OK) return rc;
-    rc = conv_umma_launch_planned(plan, nullptr, p, st, job_id, notifier);
+    rc = conv_umma_launch_planned(plan, nullptr, p, st, job_id, notifier, nullptr);
     conv_umma_plan_destroy(plan);   // the tensor maps were copied into the launch parameters
     return rc;
+}
+
+// ---- launch without any allocation -----------------------------------------------------------------
+// Scratch for pb_conv2d_umma_noalloc: split-K tile counters (first kCounterBytes) and partial tiles.
+// It lives in the library image, so every GPU that loads the library holds these bytes until exit.
+constexpr size_t kStaticScratchBytes = PB_NOALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kStaticScratchBytes];
+static __device__ uint32_t g_noalloc_err_flag;
+
+namespace {
+struct NoAllocDevice {
+    bool ready = false;
+    void* scratch = nullptr;      // device address of g_noalloc_scratch on this device
+    uint32_t* err_flag = nullptr;
+};
+NoAllocDevice g_noalloc_dev[16];
+std::mutex g_noalloc_mu;
+}  // namespace
+
+uint32_t* noalloc_error_flag_ptr(int device) {
+    if (device < 0 || device >= 16) return nullptr;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    return g_noalloc_dev[device].ready ? g_noalloc_dev[device].err_flag : nullptr;
+}
+
+int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier) {
+    PB_REQUIRE(p != nullptr && conv_umma_supported(p), "pb_conv2d_umma_noalloc: unsupported convolution");
+    int device = -1;
+    PB_CUDA(cudaGetDevice(&device));
+    PB_REQUIRE(device >= 0 && device < 16, "pb_conv2d_umma_noalloc: device %d out of range", device);
+    NoAllocDevice& nd = g_noalloc_dev[device];
+    {
+        // First call on this device: resolve the device addresses of the file-scope arrays.  In host
+        // code their names are only stand-ins, not device addresses; the kernel must be given what
+        // cudaGetSymbolAddress returns, with this device current.
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!nd.ready) {
+            void* sp = nullptr;
+            void* fp = nullptr;
+            PB_CUDA(cudaGetSymbolAddress(&sp, g_noalloc_scratch));
+            PB_CUDA(cudaGetSymbolAddress(&fp, g_noalloc_err_flag));
+            for (int tma = 0; tma < 2; ++tma)
+                for (int stg = 4; stg <= kMaxStages; stg += 2)
+                    PB_CUDA(cudaFuncSetAttribute(kernel_for(stg, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048));
+            nd.scratch = sp;
+            nd.err_flag = static_cast<uint32_t*>(fp);
+            nd.ready = true;
+        }
+    }
+    ConvUmmaPlan plan;            // on the stack: no host allocation either
+    plan.g = geometry(p);
+    plan.device = device;
+    if (plan.g.scratch_bytes > kStaticScratchBytes) {
+        set_error("pb_conv2d_umma_noalloc: this convolution wants %llu bytes of scratch, the built-in buffer holds %llu "
+                  "(use pb_op_launch with caller-provided scratch instead)",
+                  (unsigned long long)plan.g.scratch_bytes, (unsigned long long)kStaticScratchBytes);
+        return PB_ERR_INVALID;
+    }
+    int rc = make_tmap(plan.g, p->w, &plan.tmap);
+    if (rc != PB_OK) return rc;
+    pb_op_params q = *p;
+    q.scratch = plan.g.scratch_bytes ? nd.scratch : nullptr;
+    q.scratch_bytes = plan.g.scratch_bytes ? kStaticScratchBytes : 0;
+    // The buffer keeps whatever the previous call left; only the tile counters have to start at zero.
+    if (plan.g.scratch_bytes) PB_CUDA(cudaMemsetAsync(nd.scratch, 0, kCounterBytes, st));
+    return conv_umma_launch_planned(&plan, nullptr, &q, st, job_id, notifier, nd.err_flag);
 }
 
 }  // namespace pb

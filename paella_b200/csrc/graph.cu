@@ -137,6 +137,10 @@ int64_t pb_op_pack_weights(int kind, const pb_op_params* p, const float* w_oihw,
 
 int pb_conv_umma_supported(const pb_op_params* p) { return p && pb::conv_umma_supported(p) ? 1 : 0; }
 
+int pb_conv2d_umma_noalloc(const pb_op_params* p, void* stream, uint32_t job_id, void* notifier) {
+    return pb::conv_umma_launch_noalloc(p, (cudaStream_t)stream, job_id, notifier);
+}
+
 int pb_model_load(const char* pack_path, int device, int precision, pb_model** out) {
     PB_REQUIRE(pack_path && out, "pb_model_load: NULL argument");
     FILE* f = fopen(pack_path, "rb");

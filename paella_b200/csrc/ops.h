@@ -47,7 +47,10 @@ struct ConvUmmaXMap;
 int conv_umma_xmap_create(const pb_op_params* p, ConvUmmaXMap** out);
 void conv_umma_xmap_destroy(ConvUmmaXMap* m);
 // xmap may be NULL: the descriptor is then encoded for this one launch.
+// err_flag: device word raised when a bounded wait runs out (NULL = the library's per-device flag).
 int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
-                             uint32_t job_id, void* notifier);
+                             uint32_t job_id, void* notifier, uint32_t* err_flag = nullptr);
+int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
+uint32_t* noalloc_error_flag_ptr(int device);   // NULL until the no-allocation path ran on the device
 
 }  // namespace pb

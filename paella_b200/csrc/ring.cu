@@ -11,6 +11,7 @@
 #include <mutex>
 #include <new>
 
+#include "ops.h"
 #include "pb_common.h"
 
 using llis::ipc::Gpu2SchedChannelDev;
@@ -186,6 +187,13 @@ int pb_device_error_flag(int device, uint32_t* flag_out, int reset) {
     PB_CUDA(cudaSetDevice(device));
     if (flag_out) PB_CUDA(cudaMemcpy(flag_out, p, sizeof(uint32_t), cudaMemcpyDeviceToHost));
     if (reset) PB_CUDA(cudaMemset(p, 0, sizeof(uint32_t)));
+    // the no-allocation convolution path keeps its own flag (it may not share one that was cudaMalloc'ed)
+    if (uint32_t* q = pb::noalloc_error_flag_ptr(device)) {
+        uint32_t v = 0;
+        PB_CUDA(cudaMemcpy(&v, q, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+        if (flag_out && v) *flag_out = v;
+        if (reset) PB_CUDA(cudaMemset(q, 0, sizeof(uint32_t)));
+    }
     return PB_OK;
 }
 
