@@ -3,7 +3,7 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-A "step" is one batch of --batch requests per GPU (default 200: ~180 MNIST + ~20 Inception-v3)
+A "step" is one batch of --batch requests per GPU (default 1000: ~900 MNIST + ~100 Inception-v3)
 pushed through the serving path: plugin -> scheduler -> one kernel at a time per job, released
 by ring notifications.  W un-timed warm-up steps are fully drained, then exactly K steps are
 timed between a device synchronise on both sides (CUDA events, max over GPUs/ranks).
@@ -83,6 +83,11 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def packer_name(model):
+    from paella_b200 import packer
+    return packer.pack_file_name(model)
 
 
 def write_packs(models_dir):
@@ -183,8 +188,12 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--batch", type=int, default=200, help="requests per GPU per step")
-    ap.add_argument("--concurrency", type=int, default=24, help="closed-loop clients per GPU")
+    ap.add_argument("--batch", type=int, default=1000, help="requests per GPU per step")
+    ap.add_argument("--concurrency", type=int, default=24, help="closed-loop clients per replica")
+    ap.add_argument("--inception-instances", type=int, default=8, help="Inception-v3 instances (max outstanding) per replica")
+    ap.add_argument("--replicas-per-gpu", type=int, default=0,
+                    help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU; "
+                         "0 = 2 when the host has at least 4 cores per GPU in use, else 1")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
@@ -195,14 +204,17 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if args.replicas_per_gpu <= 0:
+        n_for_cores = max(int(os.environ.get("WORLD_SIZE", "1")), args.gpus)
+        args.replicas_per_gpu = 2 if (os.cpu_count() or 1) >= 4 * n_for_cores else 1
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     config = {"workload": "mixed MNIST-CNN : Inception-v3@299 = 9:1 by request count, batch 1, random He-normal weights "
                           "(BASELINE configs[2]); closed loop",
-              "batch_per_step_per_gpu": args.batch, "clients_per_gpu": args.concurrency,
-              "instances_per_gpu": {"mnist": args.concurrency, "inception_v3": max(4, args.concurrency // 3)},
-              "scheduler": "full3", "precision": {"mnist": "fp32", "inception_v3": "bf16 x bf16 -> fp32 (tcgen05)"},
+              "batch_per_step_per_replica": args.batch, "clients_per_replica": args.concurrency,
+              "instances_per_replica": {"mnist": args.concurrency, "inception_v3": args.inception_instances},
+              "scheduler": "full3", "replicas_per_gpu": args.replicas_per_gpu, "precision": {"mnist": "fp32", "inception_v3": "bf16 x bf16 -> fp32 (tcgen05)"},
               "replicas": "one scheduler+pools per GPU, requests dealt round-robin, no collective",
               "l2": "not flushed between requests: the working set per GPU (47.6 MB of bf16 weights + 19 MB of activations "
                     "per in-flight Inception instance x instances) exceeds the 126 MB L2; the roofline leg flushes L2 "
@@ -244,17 +256,17 @@ def main():
     tmp = tempfile.TemporaryDirectory()
     os.environ["LLIS_MODELS_DIR"] = tmp.name
     graphs = write_packs(tmp.name)
-    caps = [args.concurrency, max(4, args.concurrency // 3)]
+    caps = [args.concurrency, args.inception_instances]
 
     dist = None
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("gloo", rank=rank, world_size=world)
-        devices = [local_rank]
+        devices = [local_rank] * args.replicas_per_gpu
         n_gpus = world
     else:
-        devices = list(range(args.gpus))
+        devices = [d for d in range(args.gpus) for _ in range(args.replicas_per_gpu)]
         n_gpus = args.gpus
 
     if args.only_roofline is not None:
@@ -275,11 +287,12 @@ def main():
             import torch
             t = torch.tensor([ms], dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            c = torch.tensor([n, float(r.kernels_launched), float(r.h2d_bytes), float(r.d2h_bytes)], dtype=torch.float64)
+            c = torch.tensor([n, float(r.kernels_launched), float(r.h2d_bytes), float(r.d2h_bytes)] +
+                             [float(r.per_type[i].count) for i in range(len(MIX))], dtype=torch.float64)
             dist.all_reduce(c, op=dist.ReduceOp.SUM)
             ms, n = float(t[0]), float(c[0])
-            return r, n, ms, float(c[1]), float(c[2]), float(c[3])
-        return r, n, ms, float(r.kernels_launched), float(r.h2d_bytes), float(r.d2h_bytes)
+            return r, n, ms, [float(v) for v in c[4:]], float(c[2]), float(c[3])
+        return r, n, ms, [float(r.per_type[i].count) for i in range(len(MIX))], float(r.h2d_bytes), float(r.d2h_bytes)
 
     if rank == 0:
         sampler.start()
@@ -293,8 +306,18 @@ def main():
 
     value = n_dev / (ms_dev * 1e-3)
     e2e = n_e2e / (ms_e2e * 1e-3)
-    # kernels of ours inside the timed region: compute stages + the one-block copy-done markers (2 per request)
-    gpu_launches = int(k_dev + 2 * n_dev)
+    # kernels of ours inside the timed region: every measured request runs all kernels of its model
+    # (a stage group replayed as a CUDA graph still launches each of its kernels on the device)
+    kernels_per_request = {}
+    for _, model, _ in MIX:
+        mh = C.c_void_p()
+        capi.check(L.pb_model_load(os.path.join(tmp.name, packer_name(model)).encode(), devices[0], -1, C.byref(mh)), "pb_model_load")
+        kernels_per_request[model] = (L.pb_model_num_stages(mh), L.pb_model_num_groups(mh))
+        L.pb_model_destroy(mh)
+    counts = k_dev          # measured requests per model, summed over GPUs
+    gpu_launches = int(sum(c * kernels_per_request[m][0] for c, (_, m, _) in zip(counts, MIX)))
+    config["kernels_per_request"] = {m: k[0] for m, k in kernels_per_request.items()}
+    config["scheduler_stages_per_request"] = {m: k[1] for m, k in kernels_per_request.items()}
 
     def lat(r):
         return {"all": r.all.as_dict(), "mnist": r.per_type[0].as_dict(), "inception_v3": r.per_type[1].as_dict()}

@@ -198,6 +198,21 @@ PB_API void pb_instance_destroy(pb_instance* inst);
 PB_API void* pb_instance_input_dev(pb_instance* inst);   /* device staging buffer, NCHW fp32 */
 PB_API void* pb_instance_output_dev(pb_instance* inst);  /* device fp32 output */
 PB_API int pb_instance_launch_stage(pb_instance* inst, int stage, void* stream, uint32_t job_id, void* notifier);
+/* Stage groups: consecutive kernels that the job adapter presents to the scheduler as ONE stage
+ * (default up to 12 kernels, PB_STAGE_GROUP=1 gives the reference's one-kernel-per-stage granularity).
+ * A multi-kernel group is replayed as a CUDA graph - one driver call instead of one per kernel - and
+ * only its last kernel reports block start/end on the notifier, so pb_model_group_info's block count
+ * is that kernel's grid and its per-block resources are the group's largest footprint spread over
+ * those blocks.  io_in / io_out: this request's input (NCHW fp32) and output buffers, device memory
+ * or host-mapped pinned memory; the first kernel reads io_in and the last writes io_out directly
+ * (no separate copy stages).  NULL = the instance's own device buffers. */
+PB_API int pb_model_num_groups(const pb_model* m);
+PB_API int pb_model_group_info(const pb_model* m, int group, pb_launch_info* out);
+PB_API int pb_model_group_stages(const pb_model* m, int group, int* first_stage, int* num_stages);
+PB_API int pb_instance_launch_group(pb_instance* inst, int group, void* stream, uint32_t job_id, void* notifier,
+                                    const void* io_in, void* io_out);
+/* Convenience for tests: H2D, every group, D2H on one stream, then synchronise. */
+PB_API int pb_instance_run_groups_sync(pb_instance* inst, const float* input_host, float* output_host);
 /* Convenience for tests: H2D, every stage, D2H on one stream, then synchronise. */
 PB_API int pb_instance_run_sync(pb_instance* inst, const float* input_host, float* output_host);
 /* Copies tensor `t` of the pack (as NCHW fp32) to host; for layer-by-layer parity tests. */

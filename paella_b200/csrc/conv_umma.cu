@@ -30,6 +30,7 @@
 #include <cstring>
 #include <mutex>
 
+#include "launch_slot.cuh"
 #include "ops.h"
 #include "pb_common.h"
 
@@ -335,6 +336,7 @@ conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvAr
     __shared__ float s_bias[128];
     constexpr int kLag = PB_LAG_OF(kStages);
 
+    resolve_slot(job_id, nf);
     if (nf) nf->start(job_id);
     if (threadIdx.x == 0) PB_T(0);
 
@@ -515,6 +517,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     __shared__ uint32_t s_is_last;
     __shared__ float s_bias[128];
 
+    resolve_slot(job_id, nf);
     if (nf) nf->start(job_id);
     if (threadIdx.x == 0) PB_T(0);
 

@@ -12,12 +12,14 @@
 // the kernels its graph executor launches between two scheduler yields.
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
 
+#include "launch_slot.cuh"
 #include "ops.h"
 #include "pb_common.h"
 
@@ -64,6 +66,10 @@ struct pb_model {
     size_t scratch_bytes = 0;     // largest per-stage scratch requirement (split-K partial tiles)
     size_t in_floats = 0, out_floats = 0;
     bool mnist_fused = false;
+    // Stage groups: what the job adapter hands to the scheduler as ONE stage.  A group of several
+    // kernels is replayed as a CUDA graph (one driver call); only its last kernel notifies.
+    struct Group { int first, count; pb_launch_info info; };
+    std::vector<Group> groups;
     // fused MNIST weights (device)
     float *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr, *wd = nullptr, *bd = nullptr;
     std::vector<void*> allocs;
@@ -77,6 +83,9 @@ struct pb_instance {
     float* out_dev = nullptr;
     std::vector<pb_op_params> params;   // per stage, pointers resolved
     std::vector<pb::ConvUmmaXMap*> xmaps;   // per stage: im2col descriptor of the stage's input (tensor-core convs)
+    pb::LaunchSlot* slot_host = nullptr;    // pinned mirror, filled before each graph launch
+    pb::LaunchSlot* slot_dev = nullptr;
+    std::vector<cudaGraphExec_t> graphs;    // per group; NULL = single kernel, launched directly
 };
 
 namespace {
@@ -110,6 +119,94 @@ bool is_mnist_topology(const std::vector<PackOp>& ops, const std::vector<TensorI
     };
     return conv5(c1, 1, 8) && pool(p1, 2) && conv5(c2, 8, 16) && pool(p2, 3) && fc.type == OP_DENSE && fc.cin == 256 &&
            fc.cout == 10 && fc.act == 0;
+}
+
+
+// Splits the stage list into groups of at most PB_STAGE_GROUP kernels (default 12; 1 = one kernel per
+// scheduler stage, the reference's granularity) and derives each group's stage declaration.
+// Only the LAST kernel of a group reports block start/end, so the declared block count is that
+// kernel's grid; the per-block resources are scaled so that blocks x per-block equals the largest
+// footprint any kernel of the group has on the GPU.
+void build_groups(pb_model* m) {
+    int gs = 12;
+    if (const char* e = getenv("PB_STAGE_GROUP")) gs = atoi(e);
+    if (gs < 1) gs = 1;
+    const int n = (int)m->stages.size();
+    for (int first = 0; first < n; first += gs) {
+        pb_model::Group g;
+        g.first = first;
+        g.count = first + gs <= n ? gs : n - first;
+        memset(&g.info, 0, sizeof(g.info));
+        uint64_t thr = 0, smem = 0, regs = 0, tmem = 0;
+        for (int i = first; i < first + g.count; ++i) {
+            const pb_launch_info& li = m->stages[i].info;
+            thr = std::max<uint64_t>(thr, (uint64_t)li.num_blocks * li.threads_per_block);
+            smem = std::max<uint64_t>(smem, (uint64_t)li.num_blocks * li.smem_per_block);
+            regs = std::max<uint64_t>(regs, (uint64_t)li.num_blocks * li.threads_per_block * li.regs_per_thread);
+            tmem = std::max<uint64_t>(tmem, (uint64_t)li.num_blocks * li.tmem_cols_per_block);
+            g.info.flops += li.flops;
+            g.info.bytes += li.bytes;
+        }
+        const pb_launch_info& last = m->stages[first + g.count - 1].info;
+        const uint64_t nb = last.num_blocks;
+        g.info.kind = g.count == 1 ? last.kind : 0xFFFFu;
+        g.info.num_blocks = (uint32_t)nb;
+        g.info.threads_per_block = (uint32_t)pb::ceil_div<uint64_t>(thr, nb);
+        g.info.smem_per_block = (uint32_t)pb::ceil_div<uint64_t>(smem, nb);
+        g.info.regs_per_thread = (uint32_t)pb::ceil_div<uint64_t>(regs, (uint64_t)g.info.threads_per_block * nb);
+        g.info.tmem_cols_per_block = (uint32_t)pb::ceil_div<uint64_t>(tmem, nb);
+        m->groups.push_back(g);
+    }
+}
+
+int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStream_t stream, uint32_t job_id, void* notifier,
+                      const float* mnist_x, float* mnist_y) {
+    const Stage& st = in->m->stages[stage];
+    switch (st.kind) {
+        case PB_STAGE_MNIST_FUSED: {
+            const pb_model* m = in->m;
+            return pb::mnist_fused_launch(mnist_x, m->w1, m->b1, m->w2, m->b2, m->wd, m->bd, mnist_y, stream, job_id, notifier);
+        }
+        case PB_STAGE_CONV_UMMA:
+            return pb::conv_umma_launch_planned(st.plan, in->xmaps[stage], p, stream, job_id, notifier);
+        default:
+            return pb::simple_op_launch(st.kind, p, stream, job_id, notifier);
+    }
+}
+
+// Captures group `g` of the instance into an executable graph: [slot copy] -> kernels.
+int capture_group(pb_instance* in, int g, cudaStream_t cap) {
+    const pb_model::Group& grp = in->m->groups[g];
+    const int n_stages = (int)in->m->stages.size();
+    PB_CUDA(cudaStreamBeginCapture(cap, cudaStreamCaptureModeRelaxed));
+    cudaError_t e = cudaMemcpyAsync(in->slot_dev, in->slot_host, sizeof(pb::LaunchSlot), cudaMemcpyHostToDevice, cap);
+    int rc = PB_OK;
+    for (int s = grp.first; e == cudaSuccess && rc == PB_OK && s < grp.first + grp.count; ++s) {
+        pb_op_params p = in->params[s];
+        const Stage& st = in->m->stages[s];
+        const bool reads_input = s == 0;                       // the request's input buffer
+        const bool writes_output = st.y_is_output;             // the request's output buffer
+        const bool last = s == grp.first + grp.count - 1;
+        if (reads_input) p.x = nullptr;                        // NULL = take it from the launch slot
+        if (writes_output) p.y = nullptr;
+        uint32_t jid = 0;
+        void* nfp = nullptr;
+        if (last) { jid = pb::kSlotNotify; nfp = in->slot_dev; }
+        else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = in->slot_dev; }
+        rc = launch_stage_with(in, s, &p, cap, jid, nfp, nullptr, nullptr);
+        (void)n_stages;
+    }
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e2 = cudaStreamEndCapture(cap, &graph);
+    if (rc != PB_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) { if (graph) cudaGraphDestroy(graph); return pb::cuda_fail(e, "graph capture", __FILE__, __LINE__); }
+    if (e2 != cudaSuccess) return pb::cuda_fail(e2, "cudaStreamEndCapture", __FILE__, __LINE__);
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t e3 = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e3 != cudaSuccess) return pb::cuda_fail(e3, "cudaGraphInstantiate", __FILE__, __LINE__);
+    in->graphs[g] = exec;
+    return PB_OK;
 }
 
 }  // namespace
@@ -230,6 +327,7 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         memset(&st.p, 0, sizeof(st.p));
         pb::mnist_fused_info(&st.info);
         m->stages.push_back(st);
+        build_groups(m);
         *out = m;
         return PB_OK;
     }
@@ -338,6 +436,7 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         m->stages.push_back(st);
     }
 #undef PB_FAIL_LOAD
+    build_groups(m);
     *out = m;
     return PB_OK;
 }
@@ -397,6 +496,25 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
             if (rc != PB_OK) { pb_instance_destroy(in); return rc; }
         }
     }
+    // launch slot and one executable graph per multi-kernel group
+    e = cudaHostAlloc((void**)&in->slot_host, sizeof(pb::LaunchSlot), cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&in->slot_dev, sizeof(pb::LaunchSlot));
+    if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "launch slot", __FILE__, __LINE__); }
+    memset(in->slot_host, 0, sizeof(pb::LaunchSlot));
+    in->graphs.assign(m->groups.size(), nullptr);
+    bool any_graph = false;
+    for (const pb_model::Group& g : m->groups) any_graph = any_graph || g.count > 1;
+    if (any_graph) {
+        (void)pb::device_error_flag_ptr(m->device);      // allocate it now: nothing may allocate during capture
+        cudaStream_t cap;
+        e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
+        if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "capture stream", __FILE__, __LINE__); }
+        int rc = PB_OK;
+        for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g)
+            if (m->groups[g].count > 1) rc = capture_group(in, (int)g, cap);
+        cudaStreamDestroy(cap);
+        if (rc != PB_OK) { pb_instance_destroy(in); return rc; }
+    }
     *out = in;
     return PB_OK;
 }
@@ -405,6 +523,9 @@ void pb_instance_destroy(pb_instance* in) {
     if (!in) return;
     if (in->m) cudaSetDevice(in->m->device);
     for (pb::ConvUmmaXMap* x : in->xmaps) pb::conv_umma_xmap_destroy(x);
+    for (cudaGraphExec_t g : in->graphs) if (g) cudaGraphExecDestroy(g);
+    if (in->slot_host) cudaFreeHost(in->slot_host);
+    if (in->slot_dev) cudaFree(in->slot_dev);
     if (in->arena) cudaFree(in->arena);
     if (in->scratch) cudaFree(in->scratch);
     if (in->in_dev) cudaFree(in->in_dev);
@@ -417,19 +538,62 @@ void* pb_instance_output_dev(pb_instance* in) { return in ? in->out_dev : nullpt
 
 int pb_instance_launch_stage(pb_instance* in, int stage, void* stream, uint32_t job_id, void* notifier) {
     PB_REQUIRE(in && stage >= 0 && stage < (int)in->params.size(), "pb_instance_launch_stage: bad stage %d", stage);
-    const Stage& st = in->m->stages[stage];
-    const pb_op_params* p = &in->params[stage];
-    switch (st.kind) {
-        case PB_STAGE_MNIST_FUSED: {
-            const pb_model* m = in->m;
-            return pb::mnist_fused_launch(in->in_dev, m->w1, m->b1, m->w2, m->b2, m->wd, m->bd, in->out_dev, (cudaStream_t)stream,
-                                          job_id, notifier);
-        }
-        case PB_STAGE_CONV_UMMA:
-            return pb::conv_umma_launch_planned(st.plan, in->xmaps[stage], p, (cudaStream_t)stream, job_id, notifier);
-        default:
-            return pb::simple_op_launch(st.kind, p, (cudaStream_t)stream, job_id, notifier);
+    return launch_stage_with(in, stage, &in->params[stage], (cudaStream_t)stream, job_id, notifier, in->in_dev, in->out_dev);
+}
+
+int pb_model_num_groups(const pb_model* m) { return m ? (int)m->groups.size() : 0; }
+
+int pb_model_group_info(const pb_model* m, int group, pb_launch_info* out) {
+    PB_REQUIRE(m && out && group >= 0 && group < (int)m->groups.size(), "pb_model_group_info: bad group %d", group);
+    *out = m->groups[group].info;
+    return PB_OK;
+}
+
+int pb_model_group_stages(const pb_model* m, int group, int* first, int* count) {
+    PB_REQUIRE(m && group >= 0 && group < (int)m->groups.size(), "pb_model_group_stages: bad group %d", group);
+    if (first) *first = m->groups[group].first;
+    if (count) *count = m->groups[group].count;
+    return PB_OK;
+}
+
+int pb_instance_launch_group(pb_instance* in, int group, void* stream, uint32_t job_id, void* notifier, const void* io_in,
+                             void* io_out) {
+    PB_REQUIRE(in && group >= 0 && group < (int)in->m->groups.size(), "pb_instance_launch_group: bad group %d", group);
+    const pb_model::Group& g = in->m->groups[group];
+    const float* xin = io_in ? static_cast<const float*>(io_in) : in->in_dev;
+    float* yout = io_out ? static_cast<float*>(io_out) : in->out_dev;
+    if (in->graphs[group]) {
+        pb::LaunchSlot* s = in->slot_host;
+        s->nf = static_cast<llis::job::FinishedBlockNotifier*>(notifier);
+        s->job_id = job_id;
+        s->io_in = xin;
+        s->io_out = yout;
+        PB_CUDA(cudaGraphLaunch(in->graphs[group], (cudaStream_t)stream));
+        return PB_OK;
     }
+    // single kernel: direct launch with this request's buffers
+    const int stage = g.first;
+    pb_op_params p = in->params[stage];
+    if (stage == 0) p.x = xin;
+    if (in->m->stages[stage].y_is_output) p.y = yout;
+    return launch_stage_with(in, stage, &p, (cudaStream_t)stream, job_id, notifier, xin, yout);
+}
+
+int pb_instance_run_groups_sync(pb_instance* in, const float* input_host, float* output_host) {
+    PB_REQUIRE(in && input_host && output_host, "pb_instance_run_groups_sync: NULL argument");
+    pb_model* m = in->m;
+    PB_CUDA(cudaSetDevice(m->device));
+    cudaStream_t st;
+    PB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    int rc = PB_OK;
+    cudaError_t e = cudaMemcpyAsync(in->in_dev, input_host, m->in_floats * 4, cudaMemcpyHostToDevice, st);
+    for (int g = 0; e == cudaSuccess && rc == PB_OK && g < (int)m->groups.size(); ++g) rc = pb_instance_launch_group(in, g, st, 0, nullptr, nullptr, nullptr);
+    if (e == cudaSuccess && rc == PB_OK) e = cudaMemcpyAsync(output_host, in->out_dev, m->out_floats * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && rc == PB_OK) e = cudaStreamSynchronize(st);
+    cudaStreamDestroy(st);
+    if (rc != PB_OK) return rc;
+    if (e != cudaSuccess) return pb::cuda_fail(e, "pb_instance_run_groups_sync", __FILE__, __LINE__);
+    return PB_OK;
 }
 
 int pb_instance_run_sync(pb_instance* in, const float* input_host, float* output_host) {

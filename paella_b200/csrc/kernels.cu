@@ -13,6 +13,7 @@
 
 #include <cstring>
 
+#include "launch_slot.cuh"
 #include "ops.h"
 #include "pb_common.h"
 
@@ -68,14 +69,18 @@ __device__ __forceinline__ float act_fn(float v, int act) {
     return v;
 }
 
-#define PB_NOTIFY_START() if (nf) nf->start(job_id)
+#define PB_NOTIFY_START()                                        \
+    const pb::LaunchSlot* slot_ = pb::resolve_slot(job_id, nf);  \
+    (void)slot_;                                                  \
+    if (nf) nf->start(job_id)
 #define PB_NOTIFY_END() if (nf) nf->end(job_id)
 
 // ---- NCHW fp32 -> channels-last T ------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) input_transform_kernel(const float* __restrict__ x, T* __restrict__ y, int C, int HW,
+__global__ void __launch_bounds__(256) input_transform_kernel(const float* x, T* __restrict__ y, int C, int HW,
                                                               int Cs, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
+    if (!x && slot_) x = slot_->io_in;       // the request's input buffer, known only at dispatch
     const int pix = blockIdx.x * blockDim.x + threadIdx.x;
     if (pix < HW) {
         for (int c0 = 0; c0 < Cs; c0 += Vec<T>::N) {
@@ -238,7 +243,7 @@ __global__ void __launch_bounds__(256) gap_kernel(OpArgs a, uint32_t job_id, Fin
             o[j] = s * inv;
         }
         if (a.flags & 2) {
-            float* y = static_cast<float*>(a.y);
+            float* y = (!a.y && slot_) ? slot_->io_out : static_cast<float*>(a.y);
 #pragma unroll
             for (int j = 0; j < N; ++j) if (v * N + j < a.C) y[v * N + j] = o[j];
         } else {
@@ -274,7 +279,7 @@ __global__ void __launch_bounds__(256) dense_kernel(OpArgs a, uint32_t job_id, F
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (lane == 0) {
             const float v = act_fn(acc + (a.bias ? a.bias[warp] : 0.f), a.act);
-            if (a.flags & 2) static_cast<float*>(a.y)[warp] = v;
+            if (a.flags & 2) ((!a.y && slot_) ? slot_->io_out : static_cast<float*>(a.y))[warp] = v;
             else static_cast<T*>(a.y)[warp] = from_f<T>(v);
         }
     }
@@ -329,7 +334,7 @@ __global__ void __launch_bounds__(256) softmax_kernel(OpArgs a, uint32_t job_id,
     const float inv = 1.f / bc;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = __expf(ld(i) - m) * inv;
-        if (a.flags & 2) static_cast<float*>(a.y)[i] = v;
+        if (a.flags & 2) ((!a.y && slot_) ? slot_->io_out : static_cast<float*>(a.y))[i] = v;
         else static_cast<T*>(a.y)[i] = from_f<T>(v);
     }
     PB_NOTIFY_END();
@@ -351,6 +356,8 @@ struct MnistArgs {
 
 __global__ void __launch_bounds__(256) mnist_fused_kernel(MnistArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
+    if (!a.x && slot_) a.x = slot_->io_in;
+    if (!a.y && slot_) a.y = slot_->io_out;
     __shared__ float s_in[32][33];          // 28x28 image with a 2-pixel zero border
     __shared__ float s_w1[25 * 8];
     __shared__ float s_p1[18][18][8];       // pool1 output 14x14x8 with a 2-pixel zero border

@@ -1,0 +1,45 @@
+// Launch slot: per-instance device record through which kernels captured in a CUDA graph learn,
+// at run time, what a graph cannot bake in: the job id and notifier of this dispatch and the
+// request's input/output buffers.  The first node of every stage graph copies the slot from a
+// pinned host mirror that the host fills right before cudaGraphLaunch.
+//
+// Kernel parameter convention (all instrumented kernels end with `uint32_t job_id, Notifier* nf`):
+//   job_id == kSlotNotify : `nf` is really a `const LaunchSlot*`; notify with the slot's job id / notifier
+//   job_id == kSlotQuiet  : `nf` is a `const LaunchSlot*` used for the I/O pointers only; no records
+//   otherwise             : direct arguments (nf may be NULL = no records)
+#pragma once
+
+#include <llis/job/finished_block_notifier.h>
+
+#include <cstdint>
+
+namespace pb {
+
+struct LaunchSlot {
+    llis::job::FinishedBlockNotifier* nf;
+    uint32_t job_id;
+    uint32_t reserved;
+    const float* io_in;   // request input, NCHW fp32 (host-mapped pinned or device memory)
+    float* io_out;        // request output, fp32
+};
+static_assert(sizeof(LaunchSlot) == 32, "launch slot is 32 bytes");
+
+constexpr uint32_t kSlotNotify = 0xFFFFFFFFu;
+constexpr uint32_t kSlotQuiet = 0xFFFFFFFEu;
+
+#ifdef __CUDACC__
+// Returns the slot (or NULL) and rewrites job_id / nf to what the notifier calls need.
+__device__ __forceinline__ const LaunchSlot* resolve_slot(uint32_t& job_id, llis::job::FinishedBlockNotifier*& nf) {
+    if (job_id < kSlotQuiet) return nullptr;
+    const LaunchSlot* s = reinterpret_cast<const LaunchSlot*>(nf);
+    if (job_id == kSlotNotify) {
+        nf = s->nf;
+        job_id = s->job_id;
+    } else {
+        nf = nullptr;
+    }
+    return s;
+}
+#endif
+
+}  // namespace pb

@@ -11,6 +11,7 @@
 #include <mutex>
 #include <new>
 
+#include "launch_slot.cuh"
 #include "ops.h"
 #include "pb_common.h"
 

@@ -1,8 +1,10 @@
-// Job adapter for a packed model: H2D copy stage, one stage per kernel of the model,
-// D2H copy stage with pre-notify.  Same stage protocol as the reference's TVM adapters
-// (jobs/tvm_mnist/tvm_mnist.cpp:35-47): init() leaves the job before its first (copy)
-// stage; each run_next() enqueues exactly one operation on the job's stream and declares
-// the resources of the next stage.  Written as a stage-index state machine instead of a
+// Job adapter for a packed model.  Stage protocol of the reference's TVM adapters
+// (jobs/tvm_mnist/tvm_mnist.cpp:35-47): init() leaves the job before its first stage with that
+// stage declared; each run_next() enqueues exactly one operation on the job's stream and declares
+// the resources of the next stage; the last stage carries pre-notify.  A stage here is one GROUP of
+// the model's kernels (one CUDA-graph launch), and by default the request's pinned slot is read and
+// written by the kernels themselves; PB_COPY_STAGES=1 restores the reference's H2D / D2H copy stages
+// and PB_STAGE_GROUP=1 its one-kernel-per-stage granularity.  Written as a stage-index state machine instead of a
 // boost coroutine; the server only sees the llis::job::Job interface.
 //
 // Differences from the reference adapters: the D2H stage copies the OUTPUT tensor (there
@@ -42,11 +44,16 @@ class ModelJob : public llis::job::Job {
         if (!model) { set_error(PB_ERR_IO); return; }
         if (pb_model_input_bytes(model) != in_bytes_ || pb_model_output_bytes(model) != out_bytes_) { set_error(PB_ERR_INVALID); return; }
         if (pb_instance_create(model, &inst_) != PB_OK) { set_error(PB_ERR_CUDA); return; }
-        const int n = pb_model_num_stages(model);
+        // PB_COPY_STAGES=1: the reference's protocol (H2D copy stage, kernels, D2H copy stage).  Default:
+        // the first kernel reads the pinned request slot and the last writes the result into it, so a
+        // request is nothing but its kernel stages.
+        const char* cs = std::getenv("PB_COPY_STAGES");
+        copy_stages_ = cs && cs[0] == '1';
+        const int n = pb_model_num_groups(model);
         decls_.resize((size_t)n);
         for (int i = 0; i < n; ++i) {
             pb_launch_info li;
-            pb_model_stage_info(model, i, &li);
+            pb_model_group_info(model, i, &li);
             llis::job::StageDecl& d = decls_[(size_t)i];
             d.num_blocks = li.num_blocks;
             d.num_threads_per_block = li.threads_per_block;
@@ -61,34 +68,48 @@ class ModelJob : public llis::job::Job {
         io_ptr_ = static_cast<char*>(io_ptr);
         next_ = 0;
         resident_ = llis::job::Context::device_resident();
-        set_is_mem();   // stage 0: host -> device copy of the input
+        declare();
     }
 
+    // Stage list: [H2D copy] group 0 .. group n-1 [D2H copy]; the copies exist only with PB_COPY_STAGES=1.
     void run_next() override {
         const int n = (int)decls_.size();
+        const int lead = copy_stages_ ? 1 : 0;
         cudaStream_t st = get_cuda_stream();
-        if (next_ == 0) {
-            if (!resident_ && inst_) check(cudaMemcpyAsync(pb_instance_input_dev(inst_), io_ptr_, in_bytes_, cudaMemcpyHostToDevice, st));
-        } else if (next_ <= n) {
-            if (inst_ && pb_instance_launch_stage(inst_, next_ - 1, st, get_id(), get_finished_block_notifier()) != PB_OK) set_error(PB_ERR_CUDA);
+        const int cur = next_++;
+        declare();      // the stage that follows is declared before this one is enqueued
+        if (!inst_) return;
+        if (cur < lead) {
+            if (!resident_) check(cudaMemcpyAsync(pb_instance_input_dev(inst_), io_ptr_, in_bytes_, cudaMemcpyHostToDevice, st));
+        } else if (cur < lead + n) {
+            const bool direct_io = !copy_stages_ && !resident_;
+            const void* in = direct_io ? io_ptr_ : nullptr;
+            void* out = direct_io ? io_ptr_ + get_output_offset() : nullptr;
+            if (pb_instance_launch_group(inst_, cur - lead, st, get_id(), get_finished_block_notifier(), in, out) != PB_OK) set_error(PB_ERR_CUDA);
         } else {
-            if (!resident_ && inst_) check(cudaMemcpyAsync(io_ptr_ + get_output_offset(), pb_instance_output_dev(inst_), out_bytes_, cudaMemcpyDeviceToHost, st));
-        }
-        ++next_;
-        // declare the stage that follows
-        if (next_ <= n) {
-            unset_is_mem();
-            set_next_stage(decls_[(size_t)(next_ - 1)]);
-        } else if (next_ == n + 1) {
-            set_is_mem();
-            set_pre_notify();
+            if (!resident_) check(cudaMemcpyAsync(io_ptr_ + get_output_offset(), pb_instance_output_dev(inst_), out_bytes_, cudaMemcpyDeviceToHost, st));
         }
     }
 
-    bool has_next() const override { return next_ < (int)decls_.size() + 2; }
+    bool has_next() const override { return next_ < (int)decls_.size() + (copy_stages_ ? 2 : 0); }
 
   private:
     void check(cudaError_t e) { if (e != cudaSuccess) set_error(PB_ERR_CUDA); }
+
+    // Declares stage `next_` (resources, copy or compute, pre-notify on the last one).
+    void declare() {
+        const int n = (int)decls_.size();
+        const int lead = copy_stages_ ? 1 : 0;
+        const int total = n + 2 * lead;
+        if (next_ >= total) return;
+        if (next_ < lead || next_ >= lead + n) {
+            set_is_mem();
+        } else {
+            unset_is_mem();
+            set_next_stage(decls_[(size_t)(next_ - lead)]);
+        }
+        if (next_ == total - 1) set_pre_notify();
+    }
 
     static pb_model* shared_model(int device, const std::string& path) {
         static std::mutex mu;
@@ -112,6 +133,7 @@ class ModelJob : public llis::job::Job {
     char* io_ptr_ = nullptr;
     int next_ = 0;
     bool resident_ = false;
+    bool copy_stages_ = false;
 };
 
 }  // namespace pbjobs

@@ -30,6 +30,13 @@ class Model:
         assert gu.error_flag() == 0
         return y
 
+    def run_groups(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.zeros(self.L.pb_model_output_bytes(self.m) // 4, np.float32)
+        capi.check(self.L.pb_instance_run_groups_sync(self.i, x.ctypes.data, y.ctypes.data), "run groups")
+        assert gu.error_flag() == 0
+        return y
+
     def kinds(self):
         li = capi.LaunchInfo()
         out = []
@@ -163,4 +170,30 @@ def test_same_input_same_output_and_instances_are_independent(models_dir):
     assert not np.array_equal(y, y1)
     np.testing.assert_array_equal(m.run(x1), y1)      # deterministic, not disturbed by the other instance
     m.L.pb_instance_destroy(i2)
+    m.close()
+
+
+@pytest.mark.parametrize("model,precision", [("mnist", 0), ("resnet18", 1), ("inception_v3", 1)])
+def test_stage_groups_replayed_as_graphs_give_the_same_bits(models_dir, model, precision):
+    """Launching a model group by group (CUDA graphs, launch-slot indirection) must reproduce the
+    kernel-by-kernel result bit for bit, launch after launch."""
+    m = Model(os.path.join(models_dir, packer.pack_file_name(model)), precision)
+    n_stages, n_groups = m.L.pb_model_num_stages(m.m), m.L.pb_model_num_groups(m.m)
+    assert 1 <= n_groups <= n_stages and n_groups == -(-n_stages // 12)
+    first, count, covered = C.c_int(), C.c_int(), 0
+    li = capi.LaunchInfo()
+    for g in range(n_groups):
+        capi.check(m.L.pb_model_group_stages(m.m, g, C.byref(first), C.byref(count)), "group stages")
+        assert first.value == covered
+        covered += count.value
+        capi.check(m.L.pb_model_group_info(m.m, g, C.byref(li)), "group info")
+        last = capi.LaunchInfo()
+        m.L.pb_model_stage_info(m.m, first.value + count.value - 1, C.byref(last))
+        assert li.num_blocks == last.num_blocks        # only the last kernel of a group notifies
+    assert covered == n_stages
+    for seed in (5, 6):
+        x = make_input(model, seed)
+        ref = m.run(x)
+        np.testing.assert_array_equal(m.run_groups(x), ref)
+        np.testing.assert_array_equal(m.run_groups(x), ref)
     m.close()

@@ -158,3 +158,39 @@ def test_loadgen_open_and_closed_loop(models_dir, monkeypatch):
     res3 = capi.LoadgenResult()
     capi.check(L.pb_loadgen_run(C.byref(cfg), C.byref(res3)), "device resident")
     assert res3.errors == 0 and res3.h2d_bytes == 0 and res3.d2h_bytes == 0
+
+
+def test_reference_protocol_copy_stages_one_kernel_per_stage(tmp_path, monkeypatch):
+    """PB_COPY_STAGES=1 + PB_STAGE_GROUP=1: H2D copy stage, one scheduler stage per kernel, D2H copy
+    stage - the reference adapters' protocol - gives the same logits."""
+    from paella_b200 import packer as pk
+    d = tmp_path / "models_ref_protocol"      # own directory: plugins cache loaded models by path
+    d.mkdir()
+    pk.write_all(str(d), ["mnist", "resnet18"])
+    monkeypatch.setenv("PB_COPY_STAGES", "1")
+    monkeypatch.setenv("PB_STAGE_GROUP", "1")
+    monkeypatch.setenv("PB_FUSE_MNIST", "0")
+    L, s = _server(str(d), monkeypatch)
+    ids = {}
+    for job in ["tvm_mnist", "tvm_resnet18"]:
+        j = C.c_uint32()
+        capi.check(L.pb_server_register_job(s, capi.plugin_path(job).encode(), C.byref(j)), "register")
+        ids[job] = j.value
+    bufs = {}
+    for job, shape, nout in (("tvm_mnist", (1, 28, 28), 10), ("tvm_resnet18", (3, 224, 224), 1000)):
+        x = np.random.default_rng(77).standard_normal(shape).astype(np.float32)
+        nb = x.nbytes
+        t = _pinned((nb + 7) // 8 * 8 + nout * 4 + 8)
+        t.numpy()[:nb] = np.frombuffer(x.tobytes(), np.uint8)
+        bufs[job] = (x, t, (nb + 7) // 8 * 8, nout)
+        capi.check(L.pb_server_launch(s, ids[job], t.data_ptr(), ids[job]), "launch")
+    done = _run_until(L, s, 2, 120.0)
+    assert len(done) == 2 and all(e == 0 for e in done.values())
+    assert L.pb_server_num_decisions(s) == (6 + 2) + (24 + 2)      # kernels + two copy stages, per request
+    for job, pack in (("tvm_mnist", pk.mnist_cnn(seed=1234)), ("tvm_resnet18", pk.resnet18(seed=1234))):
+        x, t, off, nout = bufs[job]
+        y = np.frombuffer(t.numpy()[off: off + 4 * nout].tobytes(), np.float32)
+        ref = og.run(og.Pack(pack.to_bytes()), x)
+        assert float(np.abs(y - ref).max()) <= 1e-2 * float(np.abs(ref).max())
+        assert int(y.argmax()) == int(ref.argmax())
+    L.pb_server_destroy(s)
