@@ -85,6 +85,19 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def reduce_over_ranks(dist, ms, sums):
+    """Max of the per-rank elapsed time and element-wise sum of the per-rank counters (gloo, CPU tensors).
+    With dist None (single process) returns its arguments."""
+    if dist is None:
+        return ms, list(sums)
+    import torch
+    t = torch.tensor([ms], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    c = torch.tensor(list(sums), dtype=torch.float64)
+    dist.all_reduce(c, op=dist.ReduceOp.SUM)
+    return float(t[0]), [float(v) for v in c]
+
+
 def packer_name(model):
     from paella_b200 import packer
     return packer.pack_file_name(model)
@@ -164,6 +177,8 @@ def roofline_leg(L, capi, models_dir, iters=20, only=""):
 
 def cpu_sample(graphs, n_mnist=9, n_inception=1, repeats=1):
     """Oracle (CPU fp32, OpenMP over all cores) on a bounded sample of the mix; returns req/s."""
+    # torchrun pins OMP_NUM_THREADS=1 in its workers; the CPU leg is meant to use every host core
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import numpy as np
     from oracle import graph as og
     og.build()
@@ -281,18 +296,9 @@ def main():
         if dist:
             dist.barrier()
         r = run_load(L, capi, devices, args.batch, args.steps, args.warmup, resident, args.concurrency, caps)
-        n = float(r.all.count)
-        ms = r.elapsed_event_ms
-        if dist:
-            import torch
-            t = torch.tensor([ms], dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            c = torch.tensor([n, float(r.kernels_launched), float(r.h2d_bytes), float(r.d2h_bytes)] +
-                             [float(r.per_type[i].count) for i in range(len(MIX))], dtype=torch.float64)
-            dist.all_reduce(c, op=dist.ReduceOp.SUM)
-            ms, n = float(t[0]), float(c[0])
-            return r, n, ms, [float(v) for v in c[4:]], float(c[2]), float(c[3])
-        return r, n, ms, [float(r.per_type[i].count) for i in range(len(MIX))], float(r.h2d_bytes), float(r.d2h_bytes)
+        sums = [float(r.all.count), float(r.h2d_bytes), float(r.d2h_bytes)] + [float(r.per_type[i].count) for i in range(len(MIX))]
+        ms, sums = reduce_over_ranks(dist, r.elapsed_event_ms, sums)
+        return r, sums[0], ms, sums[3:], sums[1], sums[2]
 
     if rank == 0:
         sampler.start()

@@ -303,6 +303,10 @@ typedef struct pb_loadgen_result {
 
 PB_API void pb_loadgen_config_default(pb_loadgen_config* cfg);
 PB_API int pb_loadgen_run(const pb_loadgen_config* cfg, pb_loadgen_result* out);
+/* The router alone (no GPU needed): the requests replica `replica` of cfg->num_gpus would play - job
+ * type, scheduled arrival (us from its phase start) and whether it is measured - in submission order. */
+PB_API int pb_loadgen_plan(const pb_loadgen_config* cfg, int replica, uint32_t* types, double* arrivals_us,
+                           uint8_t* measured, uint32_t max, uint32_t* n_out);
 
 /* ------------------------------------------------------------------------ *
  * Scheduler replay (no GPU needed): feeds a recorded event trace to the product

@@ -149,6 +149,8 @@ SIGNATURES = {
     "pb_server_jobs_in_flight": (_U32, [_VP]),
     "pb_loadgen_config_default": (None, [C.POINTER(LoadgenConfig)]),
     "pb_loadgen_run": (_I, [C.POINTER(LoadgenConfig), C.POINTER(LoadgenResult)]),
+    "pb_loadgen_plan": (_I, [C.POINTER(LoadgenConfig), _I, C.POINTER(_U32), C.POINTER(C.c_double), C.POINTER(C.c_uint8),
+                             _U32, C.POINTER(_U32)]),
     "pb_sched_replay": (_I, [C.POINTER(ReplayConfig), C.POINTER(ReplayType), _U32, C.POINTER(ReplayEvent), _U32,
                              C.POINTER(ReplayDecision), _U32, C.POINTER(_U32), C.POINTER(_U32)]),
 }

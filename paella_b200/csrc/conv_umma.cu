@@ -872,13 +872,16 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
     cudaGetDevice(&plan->device);
     int rc = make_tmap(plan->g, w_dev, &plan->tmap);
     if (rc != PB_OK) { delete plan; return rc; }
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
+    // The shared-memory limit is a per-device function attribute: raise it once on every device used.
+    static std::once_flag once[16];
+    static cudaError_t attr_errs[16] = {};
+    const int dev = plan->device >= 0 && plan->device < 16 ? plan->device : 0;
+    std::call_once(once[dev], [dev] {
         for (int tma = 0; tma < 2; ++tma)
-            for (int st = 4; st <= kMaxStages && attr_err == cudaSuccess; st += 2)
-                attr_err = cudaFuncSetAttribute(kernel_for(st, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
+            for (int st = 4; st <= kMaxStages && attr_errs[dev] == cudaSuccess; st += 2)
+                attr_errs[dev] = cudaFuncSetAttribute(kernel_for(st, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
     });
+    const cudaError_t attr_err = attr_errs[dev];
     if (attr_err != cudaSuccess) { delete plan; return cuda_fail(attr_err, "cudaFuncSetAttribute(conv_umma)", __FILE__, __LINE__); }
     *out = plan;
     return PB_OK;

@@ -73,6 +73,37 @@ pb_latency_stats stats_of(std::vector<double>& v) {
     return s;
 }
 
+// The router: one global, seeded arrival stream (warm-up requests, then measured ones; each phase
+// starts at t = 0) dealt round-robin to the replicas.  Pure host code.
+std::vector<std::vector<Request>> plan_requests(const pb_loadgen_config* cfg) {
+    const int G = cfg->num_gpus;
+    std::vector<float> cum(cfg->num_types);
+    float acc = 0;
+    for (int t = 0; t < cfg->num_types; ++t) { acc += cfg->proportions[t]; cum[t] = acc; }
+    std::mt19937 gen(cfg->seed);
+    std::uniform_real_distribution<float> d_type(0, 1);
+    const bool open_loop = cfg->mean_interarrival_us > 0;
+    const double mean_global = open_loop ? cfg->mean_interarrival_us / G : 1.0;
+    std::exponential_distribution<> d_exp(1. / mean_global);
+    const double mu = std::log(mean_global) - cfg->lognormal_sigma * cfg->lognormal_sigma / 2;
+    std::lognormal_distribution<> d_ln(mu, cfg->lognormal_sigma > 0 ? cfg->lognormal_sigma : 1.0);
+    std::vector<std::vector<Request>> reqs(G);
+    for (int phase = 0; phase < 2; ++phase) {
+        const uint64_t n = (uint64_t)(phase == 0 ? cfg->warmup_jobs : cfg->num_jobs) * G;
+        double t_next = 0;
+        for (uint64_t i = 0; i < n; ++i) {
+            Request r;
+            r.arrival_us = t_next;
+            int ty = (int)(std::lower_bound(cum.begin(), cum.end(), d_type(gen)) - cum.begin());
+            r.type = ty >= cfg->num_types ? cfg->num_types - 1 : ty;
+            r.measured = phase == 1;
+            reqs[i % G].push_back(r);
+            if (open_loop) t_next += cfg->lognormal_sigma > 0 ? d_ln(gen) : d_exp(gen);
+        }
+    }
+    return reqs;
+}
+
 // One replica: owns a server on `device` and plays its share of the request stream.
 void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<Request>* reqs, std::atomic<int>* ready,
                  std::atomic<int>* go, std::atomic<int>* phase2_ready, GpuResult* out) {
@@ -266,32 +297,7 @@ int pb_loadgen_run(const pb_loadgen_config* cfg, pb_loadgen_result* out) {
     PB_REQUIRE(cfg->num_types >= 1 && cfg->num_types <= PB_MAX_JOB_TYPES, "pb_loadgen_run: num_types %d out of range", cfg->num_types);
     memset(out, 0, sizeof(*out));
     const int G = cfg->num_gpus;
-
-    // One global arrival stream, dealt round-robin to the replicas.
-    std::vector<float> cum(cfg->num_types);
-    float acc = 0;
-    for (int t = 0; t < cfg->num_types; ++t) { acc += cfg->proportions[t]; cum[t] = acc; }
-    std::mt19937 gen(cfg->seed);
-    std::uniform_real_distribution<float> d_type(0, 1);
-    const bool open_loop = cfg->mean_interarrival_us > 0;
-    const double mean_global = open_loop ? cfg->mean_interarrival_us / G : 1.0;
-    std::exponential_distribution<> d_exp(1. / mean_global);
-    const double mu = std::log(mean_global) - cfg->lognormal_sigma * cfg->lognormal_sigma / 2;
-    std::lognormal_distribution<> d_ln(mu, cfg->lognormal_sigma > 0 ? cfg->lognormal_sigma : 1.0);
-    std::vector<std::vector<Request>> reqs(G);
-    for (int phase = 0; phase < 2; ++phase) {
-        const uint64_t n = (uint64_t)(phase == 0 ? cfg->warmup_jobs : cfg->num_jobs) * G;
-        double t_next = 0;
-        for (uint64_t i = 0; i < n; ++i) {
-            Request r;
-            r.arrival_us = t_next;
-            int ty = (int)(std::lower_bound(cum.begin(), cum.end(), d_type(gen)) - cum.begin());
-            r.type = ty >= cfg->num_types ? cfg->num_types - 1 : ty;
-            r.measured = phase == 1;
-            reqs[i % G].push_back(r);
-            if (open_loop) t_next += cfg->lognormal_sigma > 0 ? d_ln(gen) : d_exp(gen);
-        }
-    }
+    std::vector<std::vector<Request>> reqs = plan_requests(cfg);
 
     std::vector<GpuResult> res(G);
     std::atomic<int> ready(0), go(0), phase2(0);
@@ -331,6 +337,22 @@ int pb_loadgen_run(const pb_loadgen_config* cfg, pb_loadgen_result* out) {
     out->throughput_rps = out->elapsed_us > 0 ? measured / (out->elapsed_us * 1e-6) : 0;
     out->all = stats_of(all);
     for (int t = 0; t < cfg->num_types; ++t) out->per_type[t] = stats_of(per_type[t]);
+    return PB_OK;
+}
+
+int pb_loadgen_plan(const pb_loadgen_config* cfg, int replica, uint32_t* types, double* arrivals_us, uint8_t* measured,
+                    uint32_t max, uint32_t* n_out) {
+    PB_REQUIRE(cfg && n_out, "pb_loadgen_plan: NULL argument");
+    PB_REQUIRE(cfg->num_gpus >= 1 && cfg->num_gpus <= PB_MAX_GPUS && replica >= 0 && replica < cfg->num_gpus,
+               "pb_loadgen_plan: replica %d of %d", replica, cfg->num_gpus);
+    PB_REQUIRE(cfg->num_types >= 1 && cfg->num_types <= PB_MAX_JOB_TYPES, "pb_loadgen_plan: num_types %d out of range", cfg->num_types);
+    const std::vector<Request> r = plan_requests(cfg)[replica];
+    *n_out = (uint32_t)r.size();
+    for (uint32_t i = 0; i < r.size() && i < max; ++i) {
+        if (types) types[i] = (uint32_t)r[i].type;
+        if (arrivals_us) arrivals_us[i] = r[i].arrival_us;
+        if (measured) measured[i] = r[i].measured ? 1 : 0;
+    }
     return PB_OK;
 }
 
