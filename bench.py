@@ -164,9 +164,13 @@ def roofline_leg(L, capi, models_dir, iters=20, only=""):
     conv = per_kind.get("conv_umma", {"launches": 0, "us": 1.0, "flops": 0, "bytes": 0})
     achieved = conv["flops"] / (conv["us"] * 1e-6) / 1e12 if conv["launches"] else 0.0
     total_us = sum(d["us"] for d in per_kind.values())
-    roof = {"bound": "tensor", "kernel": "conv_umma_kernel (tcgen05 implicit GEMM), all Inception-v3 conv layers, batch 1",
+    # DRAM bytes per launch of this kernel, from the ncu capture summarised in
+    # profiles/conv_umma_tma_kernel__inception_v3_layers.md (mean over the 89 Mixed_* layers)
+    traffic = 798681 if not only else None
+    roof = {"bound": "tensor", "kernel": "conv_umma_tma_kernel (tcgen05 implicit GEMM, TMA im2col), all Inception-v3 conv layers, batch 1",
             "achieved": round(achieved, 3), "peak": tf, "unit": "TFLOP/s", "frac": round(achieved / tf, 5), "of": how,
-            "traffic": None, "launches": conv["launches"], "avg_launch_us": round(conv["us"] / max(conv["launches"], 1), 3),
+            "traffic": traffic, "algorithmic_bytes_per_launch": int(conv["bytes"] / max(conv["launches"], 1)),
+            "launches": conv["launches"], "avg_launch_us": round(conv["us"] / max(conv["launches"], 1), 3),
             "hbm_gbs_same_kernel": round(conv["bytes"] / (conv["us"] * 1e-6) / 1e9, 1),
             "time_share_of_request": round(conv["us"] / total_us, 4) if total_us else None}
     table = {k: {"launches": d["launches"], "us": round(d["us"], 2), "share": round(d["us"] / total_us, 4),
