@@ -51,7 +51,11 @@ constexpr int kBK = 64;             // bf16 elements per k-block = one 128-byte 
 #define PB_LAG_OF(stages) ((stages) / 2)
 #endif
 constexpr int kMaxStages = 8;
-constexpr uint32_t kSmemBudget = 200u * 1024u;
+constexpr uint32_t kSmemBudget = 200u * 1024u;   // one CTA per SM (gather kernel)
+// The TMA kernel is sized for TWO CTAs per SM: at batch 1 a CTA spends most of its life in fixed
+// latencies (set-up, first operand arrival, epilogue), so residency, not pipeline depth, sets the
+// GPU's convolution throughput once many requests are in flight.
+constexpr uint32_t kSmemBudgetTma = 110u * 1024u;
 constexpr uint32_t kCounterBytes = 4096;        // split-K tile counters at the head of the scratch buffer
 #ifndef PB_NOALLOC_SCRATCH_BYTES
 #define PB_NOALLOC_SCRATCH_BYTES (4u << 20)      // built-in scratch of pb_conv2d_umma_noalloc: 4 MiB per GPU
@@ -505,7 +509,7 @@ conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvAr
 constexpr int kThreadsTma = 192;
 
 template <int kStages>
-__global__ void __launch_bounds__(kThreadsTma, 1)
+__global__ void __launch_bounds__(kThreadsTma, 2)
 conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const ConvArgs a,
                      uint32_t job_id, FinishedBlockNotifier* nf) {
     extern __shared__ uint8_t smem_raw[];
@@ -719,11 +723,16 @@ Geometry geometry(const pb_op_params* p) {
     g.splits = ceil_div(g.nkb, g.kb_per_split);
     g.scratch_bytes = g.splits > 1 ? (uint64_t)kCounterBytes + (uint64_t)tiles * g.splits * kBM * g.BN * 4ull : 0;
     if ((uint64_t)tiles * 4 > kCounterBytes) { g.splits = 1; g.kb_per_split = g.nkb; g.scratch_bytes = 0; }
-    // Pipeline depth: as many stages as the k-loop can use and shared memory holds.
+    // Pipeline depth: as many stages as the k-loop can use and the shared-memory budget holds.
     const uint32_t stage_bytes = (uint32_t)kATileBytes + g.b_stage_bytes;
-    const int longest = g.kb_per_split;
-    g.stages = 8;
-    while (g.stages > 4 && ((uint32_t)g.stages * stage_bytes + 1024u > kSmemBudget || g.stages - 2 >= longest + 2)) g.stages -= 2;
+    const uint32_t budget = use_tma_a() ? kSmemBudgetTma : kSmemBudget;
+    static const int kDepths[] = {8, 6, 4, 3, 2};
+    g.stages = 2;
+    for (int d : kDepths) {
+        if (!use_tma_a() && d < 4) break;                       // the gather kernel exists for 4, 6, 8
+        if ((uint32_t)d * stage_bytes + 1024u <= budget && d <= g.kb_per_split + 1) { g.stages = d; break; }
+        if (d == (use_tma_a() ? 2 : 4)) g.stages = d;
+    }
     g.smem_bytes = (uint32_t)g.stages * stage_bytes + 1024u;
     // c_format f32 (1 << 4), a/b format bf16 (1 << 7, 1 << 10), K-major both, N >> 3 at bit 17, M >> 4 at bit 24
     g.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(g.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
@@ -739,6 +748,8 @@ void drop_split(Geometry* g) {
 const void* kernel_for(int stages, bool tma) {
     if (tma) {
         switch (stages) {
+            case 2: return (const void*)conv_umma_tma_kernel<2>;
+            case 3: return (const void*)conv_umma_tma_kernel<3>;
             case 4: return (const void*)conv_umma_tma_kernel<4>;
             case 6: return (const void*)conv_umma_tma_kernel<6>;
             default: return (const void*)conv_umma_tma_kernel<8>;
@@ -878,7 +889,7 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
     const int dev = plan->device >= 0 && plan->device < 16 ? plan->device : 0;
     std::call_once(once[dev], [dev] {
         for (int tma = 0; tma < 2; ++tma)
-            for (int st = 4; st <= kMaxStages && attr_errs[dev] == cudaSuccess; st += 2)
+            for (int st = tma ? 2 : 4; st <= kMaxStages && attr_errs[dev] == cudaSuccess; st += (st < 4 ? 1 : 2))
                 attr_errs[dev] = cudaFuncSetAttribute(kernel_for(st, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
     });
     const cudaError_t attr_err = attr_errs[dev];
@@ -919,6 +930,8 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
             xmap = &local;
         }
         switch (g.stages) {
+            case 2: conv_umma_tma_kernel<2><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
+            case 3: conv_umma_tma_kernel<3><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
             case 4: conv_umma_tma_kernel<4><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
             case 6: conv_umma_tma_kernel<6><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
             default: conv_umma_tma_kernel<8><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
@@ -982,7 +995,7 @@ int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t jo
             PB_CUDA(cudaGetSymbolAddress(&sp, g_noalloc_scratch));
             PB_CUDA(cudaGetSymbolAddress(&fp, g_noalloc_err_flag));
             for (int tma = 0; tma < 2; ++tma)
-                for (int stg = 4; stg <= kMaxStages; stg += 2)
+                for (int stg = tma ? 2 : 4; stg <= kMaxStages; stg += (stg < 4 ? 1 : 2))
                     PB_CUDA(cudaFuncSetAttribute(kernel_for(stg, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048));
             nd.scratch = sp;
             nd.err_flag = static_cast<uint32_t*>(fp);
