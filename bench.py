@@ -113,7 +113,7 @@ def write_packs(models_dir):
     return graphs
 
 
-def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1):
+def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2):
     cfg = capi.LoadgenConfig()
     L.pb_loadgen_config_default(C.byref(cfg))
     cfg.num_gpus = len(devices)
@@ -131,6 +131,7 @@ def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps
     cfg.seed = seed
     cfg.device_resident = 1 if resident else 0
     cfg.server.num_streams = 500
+    cfg.server.extra_kernels = extra_kernels
     res = capi.LoadgenResult()
     capi.check(L.pb_loadgen_run(C.byref(cfg), C.byref(res)), "pb_loadgen_run")
     if res.errors:
@@ -208,11 +209,12 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=1000, help="requests per GPU per step")
-    ap.add_argument("--concurrency", type=int, default=24, help="closed-loop clients per replica")
-    ap.add_argument("--inception-instances", type=int, default=8, help="Inception-v3 instances (max outstanding) per replica")
+    ap.add_argument("--concurrency", type=int, default=32, help="closed-loop clients per replica")
+    ap.add_argument("--inception-instances", type=int, default=12, help="Inception-v3 instances (max outstanding) per replica")
     ap.add_argument("--replicas-per-gpu", type=int, default=0,
                     help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU; "
                          "0 = 2 when the host has at least 4 cores per GPU in use, else 1")
+    ap.add_argument("--extra-kernels", type=int, default=32, help="scheduler: over-subscribed stages allowed in flight (--extra_kernels)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
@@ -233,7 +235,7 @@ def main():
                           "(BASELINE configs[2]); closed loop",
               "batch_per_step_per_replica": args.batch, "clients_per_replica": args.concurrency,
               "instances_per_replica": {"mnist": args.concurrency, "inception_v3": args.inception_instances},
-              "scheduler": "full3", "replicas_per_gpu": args.replicas_per_gpu, "precision": {"mnist": "fp32", "inception_v3": "bf16 x bf16 -> fp32 (tcgen05)"},
+              "scheduler": "full3", "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu, "precision": {"mnist": "fp32", "inception_v3": "bf16 x bf16 -> fp32 (tcgen05)"},
               "replicas": "one scheduler+pools per GPU, requests dealt round-robin, no collective",
               "l2": "not flushed between requests: the working set per GPU (47.6 MB of bf16 weights + 19 MB of activations "
                     "per in-flight Inception instance x instances) exceeds the 126 MB L2; the roofline leg flushes L2 "
@@ -299,7 +301,8 @@ def main():
     def timed(resident):
         if dist:
             dist.barrier()
-        r = run_load(L, capi, devices, args.batch, args.steps, args.warmup, resident, args.concurrency, caps)
+        r = run_load(L, capi, devices, args.batch, args.steps, args.warmup, resident, args.concurrency, caps,
+                     extra_kernels=args.extra_kernels)
         sums = [float(r.all.count), float(r.h2d_bytes), float(r.d2h_bytes)] + [float(r.per_type[i].count) for i in range(len(MIX))]
         ms, sums = reduce_over_ranks(dist, r.elapsed_event_ms, sums)
         return r, sums[0], ms, sums[3:], sums[1], sums[2]
@@ -332,7 +335,11 @@ def main():
     def lat(r):
         return {"all": r.all.as_dict(), "mnist": r.per_type[0].as_dict(), "inception_v3": r.per_type[1].as_dict()}
 
-    line = {"metric": "requests/s, mixed MNIST + Inception-v3 (9:1), p50/p99 reported", "value": round(value, 2), "unit": "req/s",
+    slo = {"inception_v3_p99_ms": 20.0, "mnist_p99_ms": 1.0}
+    config["slo"] = slo
+    slo_met = (r_e2e.per_type[1].p99_us <= slo["inception_v3_p99_ms"] * 1e3 and r_e2e.per_type[0].p99_us <= slo["mnist_p99_ms"] * 1e3)
+    line = {"metric": "requests/s at p99 SLO, mixed MNIST + Inception-v3 (9:1)", "slo_met": bool(slo_met),
+            "value": round(value, 2), "unit": "req/s",
             "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config, "clocks": clocks, "gpu_launches": gpu_launches,
@@ -341,7 +348,9 @@ def main():
                     "latency_us": lat(r_e2e)},
             "latency_us": lat(r_dev),
             "timing": "CUDA events on each GPU around the measured requests (device idle on both sides), max over GPUs",
-            "records_consumed": int(r_dev.records_consumed), "decisions": int(r_dev.decisions)}
+            "records_consumed": int(r_dev.records_consumed), "decisions": int(r_dev.decisions),
+            "per_replica_rps": {"resident": [round(r_dev.per_gpu_rps[i]) for i in range(len(devices))],
+                                "e2e": [round(r_e2e.per_gpu_rps[i]) for i in range(len(devices))]}}
 
     if n_gpus == 1 and not args.no_roofline:
         roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters)
