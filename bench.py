@@ -33,6 +33,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+METRIC = "requests/s at p99 SLO, mixed MNIST + Inception-v3 (9:1)"
 MIX = [("tvm_mnist", "mnist", 0.9), ("tvm_inception_v3", "inception_v3", 0.1)]
 
 
@@ -256,7 +257,7 @@ def main():
         total = sum(times)
         value = n_per * len(times) / total
         cores = os.cpu_count()
-        line = {"impl": "reference", "metric": "requests/s, mixed MNIST + Inception-v3 (9:1)", "value": round(value, 3),
+        line = {"impl": "reference", "metric": METRIC, "value": round(value, 3),
                 "unit": "req/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(1000 * total / len(times), 2), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
@@ -338,7 +339,7 @@ def main():
     slo = {"inception_v3_p99_ms": 20.0, "mnist_p99_ms": 1.0}
     config["slo"] = slo
     slo_met = (r_e2e.per_type[1].p99_us <= slo["inception_v3_p99_ms"] * 1e3 and r_e2e.per_type[0].p99_us <= slo["mnist_p99_ms"] * 1e3)
-    line = {"metric": "requests/s at p99 SLO, mixed MNIST + Inception-v3 (9:1)", "slo_met": bool(slo_met),
+    line = {"metric": METRIC, "slo_met": bool(slo_met),
             "value": round(value, 2), "unit": "req/s",
             "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
