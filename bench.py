@@ -34,7 +34,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "requests/s at p99 SLO, mixed MNIST + Inception-v3 (9:1)"
-MIX = [("tvm_mnist", "mnist", 0.9), ("tvm_inception_v3", "inception_v3", 0.1)]
+WORKLOADS = {
+    # BASELINE configs[2]: the headline
+    "mix": [("tvm_mnist", "mnist", 0.9), ("tvm_inception_v3", "inception_v3", 0.1)],
+    # configs[1]
+    "resnet18": [("tvm_resnet18", "resnet18", 1.0)],
+    # configs[3]
+    "mobilenet_resnet50": [("tvm_mobilenet", "mobilenet", 0.5), ("tvm_resnet50", "resnet50", 0.5)],
+    # configs[4]: scheduler stress (vec_add of 2^22 floats x 10 launches, 148-block spin kernels of 10 us / 1 ms)
+    "stress": [("vec_add", None, 1 / 3), ("dummy_short", None, 1 / 3), ("dummy_long", None, 1 / 3)],
+}
+MIX = WORKLOADS["mix"]
 
 
 def measured_peaks():
@@ -108,27 +118,30 @@ def write_packs(models_dir):
     from paella_b200 import packer
     graphs = {}
     for _, model, _ in MIX:
+        if model is None:
+            continue
         g = packer.MODELS[model](seed=1234)
         g.save(os.path.join(models_dir, packer.pack_file_name(model)))
         graphs[model] = g
     return graphs
 
 
-def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2):
+def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2, mix=None):
+    mix = mix or MIX
     cfg = capi.LoadgenConfig()
     L.pb_loadgen_config_default(C.byref(cfg))
     cfg.num_gpus = len(devices)
     for i, d in enumerate(devices):
         cfg.devices[i] = d
-    cfg.num_types = len(MIX)
-    for i, (job, _, prop) in enumerate(MIX):
+    cfg.num_types = len(mix)
+    for i, (job, _, prop) in enumerate(mix):
         cfg.plugin_paths[i] = capi.plugin_path(job).encode()
         cfg.proportions[i] = prop
         cfg.max_outstanding[i] = caps[i]
     cfg.concurrency = concurrency
     cfg.mean_interarrival_us = iat_us
-    cfg.num_jobs = batch * steps
-    cfg.warmup_jobs = batch * warmup
+    cfg.num_jobs = max(1, int(batch * steps))
+    cfg.warmup_jobs = int(batch * warmup)
     cfg.seed = seed
     cfg.device_resident = 1 if resident else 0
     cfg.server.num_streams = 500
@@ -181,6 +194,38 @@ def roofline_leg(L, capi, models_dir, iters=20, only=""):
     return roof, table, layers
 
 
+def fairness_leg(L, capi, device, mix, mixed_result):
+    """Jain's index over per-model slowdowns (mean latency in the mix / mean latency alone, one client):
+    tools/calculate_jains_fairness_index.py:17-21 of the reference."""
+    iso, slow = {}, []
+    for i, (job, model, _) in enumerate(mix):
+        r = run_load(L, capi, [device], 60 if model != "mnist" else 300, 1, 0.2, False, 1, [1], mix=[(job, model, 1.0)])
+        iso[model or job] = r.all.mean_us
+        slow.append(mixed_result.per_type[i].mean_us / r.all.mean_us)
+    jain = (sum(slow) ** 2) / (len(slow) * sum(x * x for x in slow))
+    return {"jain_index": round(jain, 4), "slowdown": {(m or j): round(x, 3) for (j, m, _), x in zip(mix, slow)},
+            "isolated_mean_us": {k: round(v, 1) for k, v in iso.items()}}
+
+
+def extras_leg(L, capi, device):
+    """Ring round trip, vec_add bandwidth, scheduler decisions/s under the synthetic stress mix."""
+    hbm, _, how = measured_peaks()
+    n = 2000
+    rtt = (C.c_double * n)()
+    capi.check(L.pb_ring_roundtrip_bench(device, n, rtt), "pb_ring_roundtrip_bench")
+    v = sorted(rtt[100:])
+    out = {"ring_roundtrip_us": {"p50": round(v[len(v) // 2], 2), "p99": round(v[int(len(v) * 0.99)], 2), "min": round(v[0], 2),
+                                 "note": "host ping (mapped memory) -> one-thread kernel -> record -> host poll; sum of both directions"}}
+    us = C.c_double()
+    va = {}
+    for lg in (20, 22, 24, 26):
+        capi.check(L.pb_vec_add_bench(device, 1 << lg, 10, 192 << 20, C.byref(us)), "pb_vec_add_bench")
+        gbs = 12.0 * (1 << lg) / (us.value * 1e-6) / 1e9
+        va[f"2^{lg}"] = {"us": round(us.value, 2), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4)}
+    out["vec_add"] = {"bytes_per_element": 12, "peak_GB/s": hbm, "of": how, "sizes": va}
+    return out
+
+
 def cpu_sample(graphs, n_mnist=9, n_inception=1, repeats=1):
     """Oracle (CPU fp32, OpenMP over all cores) on a bounded sample of the mix; returns req/s."""
     # torchrun pins OMP_NUM_THREADS=1 in its workers; the CPU leg is meant to use every host core
@@ -216,6 +261,9 @@ def main():
                     help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU; "
                          "0 = 2 when the host has at least 4 cores per GPU in use, else 1")
     ap.add_argument("--extra-kernels", type=int, default=32, help="scheduler: over-subscribed stages allowed in flight (--extra_kernels)")
+    ap.add_argument("--workload", default="mix", choices=sorted(WORKLOADS), help="mix = the headline (MNIST : Inception-v3 = 9 : 1)")
+    ap.add_argument("--extras", action="store_true", help="also measure ring round trip and vec_add bandwidth")
+    ap.add_argument("--iat-us", type=float, default=0.0, help="open loop: mean inter-arrival per replica in us (Poisson); 0 = closed loop")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
@@ -225,6 +273,9 @@ def main():
     ap.add_argument("--iters", type=int, default=20, help="timed launches per stage in the roofline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    global MIX
+    MIX = WORKLOADS[args.workload]
+    names = [m or j for j, m, _ in MIX]
 
     if args.replicas_per_gpu <= 0:
         n_for_cores = max(int(os.environ.get("WORLD_SIZE", "1")), args.gpus)
@@ -232,11 +283,15 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": "mixed MNIST-CNN : Inception-v3@299 = 9:1 by request count, batch 1, random He-normal weights "
-                          "(BASELINE configs[2]); closed loop",
+    wl_text = {"mix": "mixed MNIST-CNN : Inception-v3@299 = 9:1 by request count, batch 1, random He-normal weights (BASELINE configs[2])",
+               "resnet18": "ResNet-18 v1, batch 1, 224x224, BN folded, random He-normal weights (BASELINE configs[1])",
+               "mobilenet_resnet50": "MobileNetV2 : ResNet-50 = 1:1, batch 1, 224x224 (BASELINE configs[3])",
+               "stress": "vec_add : dummy_short : dummy_long = 1:1:1 synthetic scheduler stress (BASELINE configs[4])"}[args.workload]
+    config = {"workload": wl_text + ("; closed loop" if args.iat_us <= 0 else f"; open loop, Poisson, mean inter-arrival {args.iat_us} us per replica"),
               "batch_per_step_per_replica": args.batch, "clients_per_replica": args.concurrency,
-              "instances_per_replica": {"mnist": args.concurrency, "inception_v3": args.inception_instances},
-              "scheduler": "full3", "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu, "precision": {"mnist": "fp32", "inception_v3": "bf16 x bf16 -> fp32 (tcgen05)"},
+              "instances_per_replica": {names[0]: args.concurrency, **({names[-1]: args.inception_instances} if len(names) > 1 else {})},
+              "scheduler": "full3", "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu,
+              "precision": "MNIST fp32; other models bf16 x bf16 -> fp32 (tcgen05)",
               "replicas": "one scheduler+pools per GPU, requests dealt round-robin, no collective",
               "l2": "not flushed between requests: the working set per GPU (47.6 MB of bf16 weights + 19 MB of activations "
                     "per in-flight Inception instance x instances) exceeds the 126 MB L2; the roofline leg flushes L2 "
@@ -278,7 +333,10 @@ def main():
     tmp = tempfile.TemporaryDirectory()
     os.environ["LLIS_MODELS_DIR"] = tmp.name
     graphs = write_packs(tmp.name)
-    caps = [args.concurrency, args.inception_instances]
+    caps = [args.concurrency] * (len(MIX) - 1) + [args.inception_instances] if len(MIX) > 1 else [args.concurrency]
+    if args.workload == "stress":
+        os.environ.setdefault("PB_VEC_ADD_N", str(1 << 22))
+        caps = [args.inception_instances] * 3
 
     dist = None
     if world > 1:
@@ -303,7 +361,7 @@ def main():
         if dist:
             dist.barrier()
         r = run_load(L, capi, devices, args.batch, args.steps, args.warmup, resident, args.concurrency, caps,
-                     extra_kernels=args.extra_kernels)
+                     iat_us=args.iat_us, extra_kernels=args.extra_kernels)
         sums = [float(r.all.count), float(r.h2d_bytes), float(r.d2h_bytes)] + [float(r.per_type[i].count) for i in range(len(MIX))]
         ms, sums = reduce_over_ranks(dist, r.elapsed_event_ms, sums)
         return r, sums[0], ms, sums[3:], sums[1], sums[2]
@@ -323,23 +381,30 @@ def main():
     # kernels of ours inside the timed region: every measured request runs all kernels of its model
     # (a stage group replayed as a CUDA graph still launches each of its kernels on the device)
     kernels_per_request = {}
-    for _, model, _ in MIX:
+    for job, model, _ in MIX:
+        if model is None:     # synthetic jobs: PB_*_KERNELS launches per request (10 by default)
+            kernels_per_request[job] = (10, 10)
+            continue
         mh = C.c_void_p()
         capi.check(L.pb_model_load(os.path.join(tmp.name, packer_name(model)).encode(), devices[0], -1, C.byref(mh)), "pb_model_load")
         kernels_per_request[model] = (L.pb_model_num_stages(mh), L.pb_model_num_groups(mh))
         L.pb_model_destroy(mh)
     counts = k_dev          # measured requests per model, summed over GPUs
-    gpu_launches = int(sum(c * kernels_per_request[m][0] for c, (_, m, _) in zip(counts, MIX)))
+    gpu_launches = int(sum(c * kernels_per_request[m or j][0] for c, (j, m, _) in zip(counts, MIX)))
     config["kernels_per_request"] = {m: k[0] for m, k in kernels_per_request.items()}
     config["scheduler_stages_per_request"] = {m: k[1] for m, k in kernels_per_request.items()}
 
     def lat(r):
-        return {"all": r.all.as_dict(), "mnist": r.per_type[0].as_dict(), "inception_v3": r.per_type[1].as_dict()}
+        d = {"all": r.all.as_dict()}
+        for i, nm in enumerate(names):
+            d[nm] = r.per_type[i].as_dict()
+        return d
 
     slo = {"inception_v3_p99_ms": 20.0, "mnist_p99_ms": 1.0}
     config["slo"] = slo
-    slo_met = (r_e2e.per_type[1].p99_us <= slo["inception_v3_p99_ms"] * 1e3 and r_e2e.per_type[0].p99_us <= slo["mnist_p99_ms"] * 1e3)
-    line = {"metric": METRIC, "slo_met": bool(slo_met),
+    slo_met = args.workload != "mix" or (r_e2e.per_type[1].p99_us <= slo["inception_v3_p99_ms"] * 1e3 and
+                                         r_e2e.per_type[0].p99_us <= slo["mnist_p99_ms"] * 1e3)
+    line = {"metric": METRIC if args.workload == "mix" else f"requests/s, {args.workload}", "slo_met": bool(slo_met),
             "value": round(value, 2), "unit": "req/s",
             "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -353,7 +418,11 @@ def main():
             "per_replica_rps": {"resident": [round(r_dev.per_gpu_rps[i]) for i in range(len(devices))],
                                 "e2e": [round(r_e2e.per_gpu_rps[i]) for i in range(len(devices))]}}
 
-    if n_gpus == 1 and not args.no_roofline:
+    if args.workload in ("mix", "mobilenet_resnet50") and not dist:
+        line["fairness"] = fairness_leg(L, capi, devices[0], MIX, r_e2e)
+    if args.extras and not dist:
+        line["extras"] = extras_leg(L, capi, devices[0])
+    if n_gpus == 1 and not args.no_roofline and args.workload == "mix":
         roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters)
         line["roofline"] = roof
         line["kernel_table_inception_v3"] = table

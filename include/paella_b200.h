@@ -93,6 +93,15 @@ PB_API int pb_launch_latency_probe(void* stream, uint32_t num_blocks, void* noti
  * out[0] = host ns before, out[1] = device globaltimer ns, out[2] = host ns after. */
 PB_API int pb_clock_calibrate(int device, uint64_t out[3]);
 
+/* Ring round trip: a one-thread kernel answers `iters` host pings (a counter in host-mapped memory)
+ * with one record each; rtt_us_out[i] = host store of ping i -> host sees record i.  It is the sum
+ * of host->GPU visibility (the kernel's poll of host memory) and the GPU->host record; every device
+ * wait is bounded.  Counterpart of the reference's tests/ipc/shm_channel/latency/shmpc_latency_gpu.cu. */
+PB_API int pb_ring_roundtrip_bench(int device, uint32_t iters, double* rtt_us_out);
+/* vec_add over n floats on private buffers, `iters` timed launches between CUDA events with an L2
+ * flush (a write of flush_bytes) before each; mean microseconds per launch in *us_out. */
+PB_API int pb_vec_add_bench(int device, uint64_t n, int iters, size_t flush_bytes, double* us_out);
+
 /* ------------------------------------------------------------------------ *
  * Synthetic jobs of the scheduler stress configuration.
  * vec_add:  jobs/vec_add_coroutine/vec_add_coroutine.cu:8-20  (out[i] += in[i])

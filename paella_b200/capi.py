@@ -107,6 +107,8 @@ SIGNATURES = {
     "pb_launch_mem_done": (_I, [_VP, _U32, _VP]),
     "pb_launch_latency_probe": (_I, [_VP, _U32, _VP]),
     "pb_clock_calibrate": (_I, [_I, C.POINTER(_U64)]),
+    "pb_ring_roundtrip_bench": (_I, [_I, _U32, C.POINTER(C.c_double)]),
+    "pb_vec_add_bench": (_I, [_I, _U64, _I, _SZ, C.POINTER(C.c_double)]),
     "pb_vec_add_info": (_I, [_U64, C.POINTER(LaunchInfo)]),
     "pb_vec_add_launch": (_I, [_VP, _VP, _U64, _VP, _U32, _VP]),
     "pb_spin_info": (_I, [_U32, C.POINTER(LaunchInfo)]),

@@ -234,6 +234,22 @@ __global__ void latency_probe_kernel(FinishedBlockNotifier* n) {
 
 __global__ void read_globaltimer_kernel(unsigned long long* out) { *out = globaltimer_ns(); }
 
+// Ring round-trip probe: one thread answers `iters` host "pings" (a counter in host-mapped memory)
+// with one record each.  Every wait is bounded: after `max_polls` polls without the expected value
+// the kernel writes status 2 and returns.
+__global__ void ring_pingpong_kernel(const volatile uint32_t* ping, uint32_t iters, uint32_t max_polls, FinishedBlockNotifier* n,
+                                     uint32_t* status) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    for (uint32_t i = 1; i <= iters; ++i) {
+        uint32_t polls = 0;
+        while (*ping != i) {
+            if (++polls > max_polls) { *status = 2; return; }
+        }
+        n->channel_.write(InstrumentInfo::kEnd, 0, 1, i, true);
+    }
+    *status = 1;
+}
+
 // out[i] += in[i]; 128-bit vectors, grid-stride.
 __global__ void __launch_bounds__(256) vec_add_kernel(float* __restrict__ out, const float* __restrict__ in,
                                                       uint64_t n, uint32_t job_id, FinishedBlockNotifier* nf) {
@@ -316,6 +332,91 @@ int pb_clock_calibrate(int device, uint64_t out[3]) {
     cudaFreeHost(host);
     out[0] = best[0]; out[1] = best[1]; out[2] = best[2];
     return PB_OK;
+}
+
+int pb_ring_roundtrip_bench(int device, uint32_t iters, double* rtt_us_out) {
+    PB_REQUIRE(rtt_us_out && iters > 0 && iters <= 100000, "pb_ring_roundtrip_bench: bad arguments");
+    PB_CUDA(cudaSetDevice(device));
+    pb_ring* ring = nullptr;
+    void* nf = nullptr;
+    int rc = pb_ring_create(device, 1 << 12, &ring);
+    if (rc != PB_OK) return rc;
+    rc = pb_notifier_create_array(ring, 1, &nf);
+    if (rc != PB_OK) { pb_ring_destroy(ring); return rc; }
+    volatile uint32_t* ping = nullptr;
+    uint32_t* status = nullptr;
+    cudaStream_t st = nullptr;
+    cudaError_t e = cudaHostAlloc((void**)&ping, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&status, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        if (ping) cudaFreeHost((void*)ping);
+        if (status) cudaFreeHost(status);
+        pb_notifier_free_array(nf);
+        pb_ring_destroy(ring);
+        return pb::cuda_fail(e, "round-trip probe set-up", __FILE__, __LINE__);
+    }
+    *ping = 0;
+    *status = 0;
+    // about one second of polling per ping at most (a poll of host memory takes ~1 us)
+    ring_pingpong_kernel<<<1, 32, 0, st>>>(ping, iters, 1u << 20, (FinishedBlockNotifier*)nf, status);
+    rc = pb::launch_check("ring_pingpong");
+    uint64_t rec = 0;
+    for (uint32_t i = 1; rc == PB_OK && i <= iters; ++i) {
+        struct timespec a, b;
+        clock_gettime(CLOCK_MONOTONIC, &a);
+        __atomic_store_n((uint32_t*)ping, i, __ATOMIC_RELEASE);
+        int n = 0;
+        for (uint64_t spins = 0; n == 0 && spins < (1ull << 28); ++spins) n = pb_ring_poll(ring, &rec, 1);
+        clock_gettime(CLOCK_MONOTONIC, &b);
+        if (n != 1) { pb::set_error("ring round trip %u: no record (status %u)", i, *status); rc = n < 0 ? n : PB_ERR_TIMEOUT; break; }
+        rtt_us_out[i - 1] = ((double)(b.tv_sec - a.tv_sec) * 1e9 + (double)(b.tv_nsec - a.tv_nsec)) * 1e-3;
+    }
+    if (rc != PB_OK) __atomic_store_n((uint32_t*)ping, 0xffffffffu, __ATOMIC_RELEASE);   // lets the kernel run out its poll limit
+    cudaStreamSynchronize(st);
+    cudaStreamDestroy(st);
+    cudaFreeHost((void*)ping);
+    cudaFreeHost(status);
+    pb_notifier_free_array(nf);
+    pb_ring_destroy(ring);
+    return rc;
+}
+
+int pb_vec_add_bench(int device, uint64_t n, int iters, size_t flush_bytes, double* us_out) {
+    PB_REQUIRE(us_out && n > 0 && iters > 0, "pb_vec_add_bench: bad arguments");
+    PB_CUDA(cudaSetDevice(device));
+    float *a = nullptr, *b = nullptr;
+    void* flush = nullptr;
+    cudaStream_t st = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaError_t e = cudaMalloc((void**)&a, n * 4);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&b, n * 4);
+    if (e == cudaSuccess && flush_bytes) e = cudaMalloc(&flush, flush_bytes);
+    if (e == cudaSuccess) e = cudaMemset(a, 0, n * 4);
+    if (e == cudaSuccess) e = cudaMemset(b, 0, n * 4);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreate(&e0);
+    if (e == cudaSuccess) e = cudaEventCreate(&e1);
+    int rc = e == cudaSuccess ? PB_OK : pb::cuda_fail(e, "vec_add bench set-up", __FILE__, __LINE__);
+    double total_ms = 0;
+    for (int i = 0; rc == PB_OK && i < iters + 3; ++i) {
+        if (flush) cudaMemsetAsync(flush, i, flush_bytes, st);
+        cudaEventRecord(e0, st);
+        rc = pb_vec_add_launch(a, b, n, st, 0, nullptr);
+        cudaEventRecord(e1, st);
+        if (cudaEventSynchronize(e1) != cudaSuccess) { rc = PB_ERR_CUDA; break; }
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (i >= 3) total_ms += ms;
+    }
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    if (st) cudaStreamDestroy(st);
+    if (a) cudaFree(a);
+    if (b) cudaFree(b);
+    if (flush) cudaFree(flush);
+    if (rc == PB_OK) *us_out = total_ms * 1000.0 / iters;
+    return rc;
 }
 
 static int kernel_regs(const void* fn) {
