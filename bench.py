@@ -35,13 +35,13 @@ sys.path.insert(0, ROOT)
 
 METRIC = "requests/s at p99 SLO, mixed MNIST + Inception-v3 (9:1)"
 WORKLOADS = {
-    # BASELINE configs[2]: the headline
+    # the headline configuration
     "mix": [("tvm_mnist", "mnist", 0.9), ("tvm_inception_v3", "inception_v3", 0.1)],
-    # configs[1]
+    # single-model configuration
     "resnet18": [("tvm_resnet18", "resnet18", 1.0)],
-    # configs[3]
+    # depthwise + bottleneck mix
     "mobilenet_resnet50": [("tvm_mobilenet", "mobilenet", 0.5), ("tvm_resnet50", "resnet50", 0.5)],
-    # configs[4]: scheduler stress (vec_add of 2^22 floats x 10 launches, 148-block spin kernels of 10 us / 1 ms)
+    # scheduler stress (vec_add of 2^22 floats x 10 launches, 148-block spin kernels of 10 us / 1 ms)
     "stress": [("vec_add", None, 1 / 3), ("dummy_short", None, 1 / 3), ("dummy_long", None, 1 / 3)],
 }
 MIX = WORKLOADS["mix"]
@@ -126,7 +126,8 @@ def write_packs(models_dir):
     return graphs
 
 
-def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2, mix=None):
+def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2, mix=None,
+             sched="full3", streams=500):
     mix = mix or MIX
     cfg = capi.LoadgenConfig()
     L.pb_loadgen_config_default(C.byref(cfg))
@@ -144,7 +145,8 @@ def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps
     cfg.warmup_jobs = int(batch * warmup)
     cfg.seed = seed
     cfg.device_resident = 1 if resident else 0
-    cfg.server.num_streams = 500
+    cfg.server.num_streams = streams
+    cfg.server.scheduler = sched.encode()
     cfg.server.extra_kernels = extra_kernels
     res = capi.LoadgenResult()
     capi.check(L.pb_loadgen_run(C.byref(cfg), C.byref(res)), "pb_loadgen_run")
@@ -261,6 +263,9 @@ def main():
                     help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU; "
                          "0 = 2 when the host has at least 4 cores per GPU in use, else 1")
     ap.add_argument("--extra-kernels", type=int, default=32, help="scheduler: over-subscribed stages allowed in flight (--extra_kernels)")
+    ap.add_argument("--sched", default="full3", choices=["full3", "fifo", "fifo2"],
+                    help="full3 = the kernel-level scheduler; fifo (job by job) and fifo2 (stage by stage, arrival order) are the ablations")
+    ap.add_argument("--streams", type=int, default=500, help="scheduler stream pool (--num_streams); 1 with --sched fifo = single-stream baseline")
     ap.add_argument("--workload", default="mix", choices=sorted(WORKLOADS), help="mix = the headline (MNIST : Inception-v3 = 9 : 1)")
     ap.add_argument("--extras", action="store_true", help="also measure ring round trip and vec_add bandwidth")
     ap.add_argument("--iat-us", type=float, default=0.0, help="open loop: mean inter-arrival per replica in us (Poisson); 0 = closed loop")
@@ -283,14 +288,14 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    wl_text = {"mix": "mixed MNIST-CNN : Inception-v3@299 = 9:1 by request count, batch 1, random He-normal weights (BASELINE configs[2])",
-               "resnet18": "ResNet-18 v1, batch 1, 224x224, BN folded, random He-normal weights (BASELINE configs[1])",
-               "mobilenet_resnet50": "MobileNetV2 : ResNet-50 = 1:1, batch 1, 224x224 (BASELINE configs[3])",
-               "stress": "vec_add : dummy_short : dummy_long = 1:1:1 synthetic scheduler stress (BASELINE configs[4])"}[args.workload]
+    wl_text = {"mix": "mixed MNIST-CNN : Inception-v3@299 = 9:1 by request count, batch 1, random He-normal weights (headline configuration)",
+               "resnet18": "ResNet-18 v1, batch 1, 224x224, BN folded, random He-normal weights",
+               "mobilenet_resnet50": "MobileNetV2 : ResNet-50 = 1:1, batch 1, 224x224",
+               "stress": "vec_add : dummy_short : dummy_long = 1:1:1 synthetic scheduler stress"}[args.workload]
     config = {"workload": wl_text + ("; closed loop" if args.iat_us <= 0 else f"; open loop, Poisson, mean inter-arrival {args.iat_us} us per replica"),
               "batch_per_step_per_replica": args.batch, "clients_per_replica": args.concurrency,
               "instances_per_replica": {names[0]: args.concurrency, **({names[-1]: args.inception_instances} if len(names) > 1 else {})},
-              "scheduler": "full3", "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu,
+              "scheduler": args.sched, "num_streams": args.streams, "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu,
               "precision": "MNIST fp32; other models bf16 x bf16 -> fp32 (tcgen05)",
               "replicas": "one scheduler+pools per GPU, requests dealt round-robin, no collective",
               "l2": "not flushed between requests: the working set per GPU (47.6 MB of bf16 weights + 19 MB of activations "
@@ -361,7 +366,7 @@ def main():
         if dist:
             dist.barrier()
         r = run_load(L, capi, devices, args.batch, args.steps, args.warmup, resident, args.concurrency, caps,
-                     iat_us=args.iat_us, extra_kernels=args.extra_kernels)
+                     iat_us=args.iat_us, extra_kernels=args.extra_kernels, sched=args.sched, streams=args.streams)
         sums = [float(r.all.count), float(r.h2d_bytes), float(r.d2h_bytes)] + [float(r.per_type[i].count) for i in range(len(MIX))]
         ms, sums = reduce_over_ranks(dist, r.elapsed_event_ms, sums)
         return r, sums[0], ms, sums[3:], sums[1], sums[2]
