@@ -318,6 +318,37 @@ PB_API int pb_loadgen_plan(const pb_loadgen_config* cfg, int replica, uint32_t* 
                            uint8_t* measured, uint32_t max, uint32_t* n_out);
 
 /* ------------------------------------------------------------------------ *
+ * Client <-> server IPC (process boundary): the byte ring in POSIX shared memory
+ * (include/llis/ipc/shm_channel.h:59-130 of the reference; "llis:channel:<name>") and the client
+ * library (src/client/client.cpp, job_ref.cpp, job_instance_ref.cpp) against a running llis_server.
+ * ------------------------------------------------------------------------ */
+typedef struct pb_shm_channel pb_shm_channel;
+typedef struct pb_client pb_client;
+
+/* size > 0 creates ring "llis:channel:<name>" (name "" = anonymous, same process); size == 0 attaches. */
+PB_API int pb_shm_channel_open(const char* name, size_t size, pb_shm_channel** out);
+PB_API void pb_shm_channel_close(pb_shm_channel* ch);
+/* Blocking copies; max_spins > 0 bounds every wait (PB_ERR_TIMEOUT when it runs out). */
+PB_API int pb_shm_channel_write(pb_shm_channel* ch, const void* buf, size_t n, uint64_t max_spins);
+PB_API int pb_shm_channel_read(pb_shm_channel* ch, void* buf, size_t n, uint64_t max_spins);
+PB_API int pb_shm_channel_can_read(pb_shm_channel* ch);
+PB_API void pb_shm_channel_lock(pb_shm_channel* ch);     /* multi-writer spin lock */
+PB_API void pb_shm_channel_unlock(pb_shm_channel* ch);
+
+/* REGISTER_CLIENT handshake with the server named `server_name`. */
+PB_API int pb_client_connect(const char* server_name, pb_client** out);
+PB_API void pb_client_close(pb_client* c);
+PB_API uint32_t pb_client_id(const pb_client* c);
+/* REGISTER_JOB + first GROW_POOL; *job_out indexes this client's registered jobs. */
+PB_API int pb_client_register_job(pb_client* c, const char* plugin_path, uint32_t* job_out, size_t* in_bytes, size_t* out_bytes);
+/* A request slot in the shared pool; in_ptr/out_ptr are this process's addresses of its input and output. */
+PB_API int pb_client_create_instance(pb_client* c, uint32_t job, uint64_t* instance_out, void** in_ptr, void** out_ptr);
+PB_API int pb_client_launch(pb_client* c, uint64_t instance);                         /* LAUNCH_JOB */
+/* Next finished request: 1 and *instance_out set, 0 on timeout (timeout_ms < 0 blocks). */
+PB_API int pb_client_wait(pb_client* c, int timeout_ms, uint64_t* instance_out);
+PB_API int pb_client_kill_server(pb_client* c);                                       /* EXIT_CMD */
+
+/* ------------------------------------------------------------------------ *
  * Scheduler replay (no GPU needed): feeds a recorded event trace to the product
  * scheduler with fake streams/notifiers and returns its decision log, to be
  * compared bit-for-bit with the oracle's restatement of

@@ -153,6 +153,21 @@ SIGNATURES = {
     "pb_loadgen_run": (_I, [C.POINTER(LoadgenConfig), C.POINTER(LoadgenResult)]),
     "pb_loadgen_plan": (_I, [C.POINTER(LoadgenConfig), _I, C.POINTER(_U32), C.POINTER(C.c_double), C.POINTER(C.c_uint8),
                              _U32, C.POINTER(_U32)]),
+    "pb_shm_channel_open": (_I, [C.c_char_p, _SZ, _PP]),
+    "pb_shm_channel_close": (None, [_VP]),
+    "pb_shm_channel_write": (_I, [_VP, _VP, _SZ, _U64]),
+    "pb_shm_channel_read": (_I, [_VP, _VP, _SZ, _U64]),
+    "pb_shm_channel_can_read": (_I, [_VP]),
+    "pb_shm_channel_lock": (None, [_VP]),
+    "pb_shm_channel_unlock": (None, [_VP]),
+    "pb_client_connect": (_I, [C.c_char_p, _PP]),
+    "pb_client_close": (None, [_VP]),
+    "pb_client_id": (_U32, [_VP]),
+    "pb_client_register_job": (_I, [_VP, C.c_char_p, C.POINTER(_U32), C.POINTER(_SZ), C.POINTER(_SZ)]),
+    "pb_client_create_instance": (_I, [_VP, _U32, C.POINTER(_U64), _PP, _PP]),
+    "pb_client_launch": (_I, [_VP, _U64]),
+    "pb_client_wait": (_I, [_VP, _I, C.POINTER(_U64)]),
+    "pb_client_kill_server": (_I, [_VP]),
     "pb_sched_replay": (_I, [C.POINTER(ReplayConfig), C.POINTER(ReplayType), _U32, C.POINTER(ReplayEvent), _U32,
                              C.POINTER(ReplayDecision), _U32, C.POINTER(_U32), C.POINTER(_U32)]),
 }

@@ -74,7 +74,7 @@ int pb_server::register_job(const char* path, uint32_t* id_out) {
     return PB_OK;
 }
 
-int pb_server::launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie) {
+int pb_server::launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie, llis::ClientId client_id) {
     PB_REQUIRE(job_ref_id < types.size(), "launch: unknown job type %u", job_ref_id);
     llis::server::JobType& t = *types[job_ref_id];
     bool fresh = false;
@@ -84,7 +84,7 @@ int pb_server::launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie) {
     Context::set_device_resident(cfg.device_resident != 0);
     job->set_remote_ptr((void*)(uintptr_t)cookie);
     if (fresh) {
-        job->set_client_details(0, t.id);
+        job->set_client_details(client_id, t.id);
         Context::set_current_job(job);
         job->full_init(io_ptr);
     } else {

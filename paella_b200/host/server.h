@@ -12,6 +12,7 @@
 #include <llis/server/scheduler.h>
 
 #include <chrono>
+#include <functional>
 #include <memory>
 #include <string>
 #include <vector>
@@ -29,7 +30,7 @@ struct pb_server final : public llis::server::SchedulerHost {
     ~pb_server() override;
     int init(const pb_server_config& cfg);
     int register_job(const char* path, uint32_t* id_out);
-    int launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie);
+    int launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie, llis::ClientId client_id = 0);
     int step(int max_records);
 
     // SchedulerHost
@@ -43,8 +44,14 @@ struct pb_server final : public llis::server::SchedulerHost {
     double get_job_remaining_rl(llis::job::Job* job, unsigned from) override { return type_of(job).remaining_rl(from); }
     const std::vector<double>& get_job_stage_lengths(llis::job::Job* job) override { return type_of(job).stage_lengths; }
     const std::vector<float>& get_job_stage_resources(llis::job::Job* job) override { return type_of(job).stage_resources; }
-    void notify_job_starts(llis::job::Job*) override { ++num_pre_notified; }
-    void notify_job_ends(llis::job::Job* job) override { done.push_back(Done{(uint64_t)(uintptr_t)job->get_remote_ptr(), job->has_error()}); }
+    void notify_job_starts(llis::job::Job* job) override {
+        ++num_pre_notified;
+        if (on_job_starts) on_job_starts(job);
+    }
+    void notify_job_ends(llis::job::Job* job) override {
+        if (on_job_ends) on_job_ends(job);
+        else done.push_back(Done{(uint64_t)(uintptr_t)job->get_remote_ptr(), job->has_error()});
+    }
     void release_job_instance(llis::job::Job* job) override { type_of(job).give_back(job); }
     void on_dispatch(llis::job::Job*, bool is_mem, bool, unsigned, unsigned) override {
         if (is_mem) ++num_mem_stages; else ++num_kernels;
@@ -52,6 +59,8 @@ struct pb_server final : public llis::server::SchedulerHost {
 
     llis::server::JobType& type_of(llis::job::Job* job) { return *types[job->get_registered_job_id()]; }
 
+    // Set by the IPC front-end: completion goes to the client's rings instead of the `done` list.
+    std::function<void(llis::job::Job*)> on_job_starts, on_job_ends;
     pb_server_config cfg{};
     int device = 0;
     llis::ipc::Gpu2SchedChannel channel;
