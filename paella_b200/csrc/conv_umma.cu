@@ -220,6 +220,84 @@ __device__ unsigned long long g_conv_t[64 * 8];
 #endif
 
 // ---- the kernel -----------------------------------------------------------------------
+__device__ __forceinline__ void tcgen05_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+          "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+          "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// One group of NC (16 or 32) accumulator columns of this thread's row: TMEM -> registers, (+ split-K
+// partial tiles), + bias (+ residual), activation, bf16, 16-byte stores.  Everything that does not
+// depend on the accumulator is fetched before the TMEM wait.
+template <int NC>
+__device__ __forceinline__ void epilogue_chunk(const ConvArgs& a, uint32_t lane_addr, int cb, int n0, bool row_valid,
+                                               __nv_bfloat16* yrow, const __nv_bfloat16* rrow, const float* part, size_t tile_floats,
+                                               const float* s_bias) {
+    uint32_t v[NC];
+    if constexpr (NC == 32) tcgen05_ld32(lane_addr + (uint32_t)cb, v);   // warp-collective: all lanes take part
+    else tcgen05_ld16(lane_addr + (uint32_t)cb, v);
+    const int k0 = n0 + cb;
+    const bool live = row_valid && k0 < a.K;
+    uint4 rv[NC / 8];
+#pragma unroll
+    for (int h = 0; h < NC / 8; ++h) rv[h] = make_uint4(0, 0, 0, 0);
+    if (live && rrow) {
+#pragma unroll
+        for (int h = 0; h < NC / 8; ++h)
+            if (k0 + h * 8 + 8 <= a.K) rv[h] = *reinterpret_cast<const uint4*>(rrow + k0 + h * 8);
+    }
+    float bias[NC];
+#pragma unroll
+    for (int j = 0; j < NC; j += 4) {
+        const float4 b4 = *reinterpret_cast<const float4*>(s_bias + cb + j);
+        bias[j] = b4.x; bias[j + 1] = b4.y; bias[j + 2] = b4.z; bias[j + 3] = b4.w;
+    }
+    if (live && part) {
+        // every partial tile, this CTA's own included, is read from the workspace in split order, so
+        // the fp32 sum does not depend on which CTA arrived last; it starts from the bias
+        for (int z = 0; z < a.splits; ++z) {
+            const float4* other = reinterpret_cast<const float4*>(part + (size_t)z * tile_floats) + threadIdx.x;
+#pragma unroll
+            for (int j = 0; j < NC / 4; ++j) {
+                const float4 o = __ldcg(other + (size_t)(cb / 4 + j) * kBM);
+                bias[4 * j] += o.x; bias[4 * j + 1] += o.y; bias[4 * j + 2] += o.z; bias[4 * j + 3] += o.w;
+            }
+        }
+    }
+    tcgen05_wait_ld();
+    if (!live) return;
+#pragma unroll
+    for (int h = 0; h < NC / 8; ++h) {
+        const int kk = k0 + h * 8;
+        if (kk + 8 <= a.K) {
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = (part ? 0.f : __uint_as_float(v[h * 8 + j])) + bias[h * 8 + j];
+            if (rrow) {
+                const uint32_t ru[4] = {rv[h].x, rv[h].y, rv[h].z, rv[h].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    f[2 * j] += __uint_as_float(ru[j] << 16);
+                    f[2 * j + 1] += __uint_as_float(ru[j] & 0xffff0000u);
+                }
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 hv = __floats2bfloat162_rn(act_fn(f[2 * j], a.act), act_fn(f[2 * j + 1], a.act));
+                o[j] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            *reinterpret_cast<uint4*>(yrow + kk) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 // Epilogue, run by warps 0-3 (thread t owns accumulator lane t = tile row t): wait for the
 // accumulator, optionally meet the other split-K CTAs of the tile in the workspace, then
 // bias + residual + activation and bf16 stores into the output channel slice.
@@ -269,61 +347,12 @@ __device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, 
     if (finalize) {
         __nv_bfloat16* yrow = a.y + (size_t)m * a.Ks + a.out_c_off;
         const __nv_bfloat16* rrow = a.residual ? a.residual + (size_t)m * a.res_Cs : nullptr;
-        for (int cb = 0; cb < a.BN; cb += 16) {
-            uint32_t v[16];
-            tcgen05_ld16(lane_addr + (uint32_t)cb, v);   // warp-collective: all lanes take part
-            const int k0 = n0 + cb;
-            const bool live = row_valid && k0 < a.K;
-            // loads that do not depend on the accumulator are issued before the TMEM wait
-            uint4 rv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-            if (live && rrow) {
-                rv[0] = *reinterpret_cast<const uint4*>(rrow + k0);
-                if (k0 + 16 <= a.K) rv[1] = *reinterpret_cast<const uint4*>(rrow + k0 + 8);
-            }
-            float acc[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-            if (live && a.splits > 1) {
-                // every partial, this CTA's own included, comes from the workspace in split order,
-                // so the fp32 sum does not depend on which CTA arrived last
-                for (int z = 0; z < a.splits; ++z) {
-                    const float4* other = reinterpret_cast<const float4*>(a.ws + ((size_t)tile * a.splits + z) * tile_floats) + tid;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float4 o = __ldcg(other + (size_t)(cb / 4 + j) * kBM);
-                        acc[4 * j] += o.x; acc[4 * j + 1] += o.y; acc[4 * j + 2] += o.z; acc[4 * j + 3] += o.w;
-                    }
-                }
-            }
-            tcgen05_wait_ld();
-            if (live) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int kk = k0 + h * 8;
-                    if (kk + 8 <= a.K) {
-                        float f[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            f[j] = (a.splits > 1 ? acc[h * 8 + j] : __uint_as_float(v[h * 8 + j])) + s_bias[cb + h * 8 + j];
-                        if (rrow) {
-                            const uint32_t ru[4] = {rv[h].x, rv[h].y, rv[h].z, rv[h].w};
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                f[2 * j] += __uint_as_float(ru[j] << 16);
-                                f[2 * j + 1] += __uint_as_float(ru[j] & 0xffff0000u);
-                            }
-                        }
-                        uint32_t o[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const __nv_bfloat162 hv = __floats2bfloat162_rn(act_fn(f[2 * j], a.act), act_fn(f[2 * j + 1], a.act));
-                            o[j] = *reinterpret_cast<const uint32_t*>(&hv);
-                        }
-                        *reinterpret_cast<uint4*>(yrow + kk) = make_uint4(o[0], o[1], o[2], o[3]);
-                    }
-                }
-            }
-        }
+        const float* part = a.splits > 1 ? a.ws + (size_t)tile * a.splits * tile_floats : nullptr;
+        int cb = 0;
+        for (; cb + 32 <= a.BN; cb += 32)
+            epilogue_chunk<32>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+        for (; cb < a.BN; cb += 16)
+            epilogue_chunk<16>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
     }
 }
 
@@ -337,7 +366,7 @@ conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvAr
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile uint32_t s_abort;
     __shared__ uint32_t s_is_last;
-    __shared__ float s_bias[128];
+    __shared__ __align__(16) float s_bias[128];
     constexpr int kLag = PB_LAG_OF(kStages);
 
     resolve_slot(job_id, nf);
@@ -519,7 +548,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile uint32_t s_abort;
     __shared__ uint32_t s_is_last;
-    __shared__ float s_bias[128];
+    __shared__ __align__(16) float s_bias[128];
 
     resolve_slot(job_id, nf);
     if (nf) nf->start(job_id);
