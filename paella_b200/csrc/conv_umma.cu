@@ -153,6 +153,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream (or graph) is still running; griddep_wait() blocks until
+// that predecessor has completed and its writes are visible, griddep_launch() lets the successor's
+// blocks be scheduled early.  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tcgen05_alloc(uint32_t slot_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
 }
@@ -588,8 +595,13 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     tcgen05_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     if (threadIdx.x == 0) PB_T(1);
+    // Everything above touched only this CTA's shared/tensor memory and constant weights (bias), so it
+    // may overlap the previous kernel's tail.  Activations, the residual, the output and the split-K
+    // workspace may only be touched once the previous kernel has completed.
+    griddep_wait();
 
     if (warp < 4) {
+        griddep_launch();      // the next kernel's blocks may be scheduled as SM resources free up
         epilogue(a, tmem_base, true, m0, n0, s_bias, &s_accum, &s_abort, &s_is_last);
         if (tid == 0) PB_T(6);
     } else if (warp == 4) {
@@ -621,6 +633,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             }
         }
         __syncwarp();
+        griddep_launch();
     } else {
         // ===== MMA issuer: one thread =====
         if (lane == 0) {
@@ -645,6 +658,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             PB_T(4);
         }
         __syncwarp();
+        griddep_launch();
     }
 
     tcgen05_fence_before();
@@ -929,8 +943,24 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
 
 void conv_umma_plan_destroy(ConvUmmaPlan* plan) { delete plan; }
 
+template <typename Kern>
+static cudaError_t launch_tma(Kern kern, dim3 grid, uint32_t smem, cudaStream_t st, bool pdl, const CUtensorMap& tw, const CUtensorMap& tx,
+                              const ConvArgs& a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreadsTma);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, tw, tx, a, job_id, nf);
+}
+
 int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
-                             uint32_t job_id, void* notifier, uint32_t* err_flag) {
+                             uint32_t job_id, void* notifier, uint32_t* err_flag, bool pdl) {
     Geometry g = plan->g;
     if (g.splits > 1 && (p->scratch == nullptr || p->scratch_bytes < g.scratch_bytes)) drop_split(&g);
     ConvArgs a;
@@ -958,13 +988,16 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
             if (rc != PB_OK) return rc;
             xmap = &local;
         }
+        cudaError_t e;
         switch (g.stages) {
-            case 2: conv_umma_tma_kernel<2><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
-            case 3: conv_umma_tma_kernel<3><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
-            case 4: conv_umma_tma_kernel<4><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
-            case 6: conv_umma_tma_kernel<6><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
-            default: conv_umma_tma_kernel<8><<<grid, kThreadsTma, g.smem_bytes, st>>>(plan->tmap, xmap->map, a, job_id, nf); break;
+            case 2: e = launch_tma(conv_umma_tma_kernel<2>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
+            case 3: e = launch_tma(conv_umma_tma_kernel<3>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
+            case 4: e = launch_tma(conv_umma_tma_kernel<4>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
+            case 6: e = launch_tma(conv_umma_tma_kernel<6>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
+            default: e = launch_tma(conv_umma_tma_kernel<8>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
         }
+        if (e != cudaSuccess) return cuda_fail(e, "launch of conv_umma_tma_kernel", __FILE__, __LINE__);
+        return PB_OK;
     } else {
         switch (g.stages) {
             case 4: conv_umma_gather_kernel<4><<<grid, kThreads, g.smem_bytes, st>>>(plan->tmap, a, job_id, nf); break;

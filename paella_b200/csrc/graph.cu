@@ -160,7 +160,7 @@ void build_groups(pb_model* m) {
 }
 
 int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStream_t stream, uint32_t job_id, void* notifier,
-                      const float* mnist_x, float* mnist_y) {
+                      const float* mnist_x, float* mnist_y, bool pdl = false) {
     const Stage& st = in->m->stages[stage];
     switch (st.kind) {
         case PB_STAGE_MNIST_FUSED: {
@@ -168,14 +168,14 @@ int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStr
             return pb::mnist_fused_launch(mnist_x, m->w1, m->b1, m->w2, m->b2, m->wd, m->bd, mnist_y, stream, job_id, notifier);
         }
         case PB_STAGE_CONV_UMMA:
-            return pb::conv_umma_launch_planned(st.plan, in->xmaps[stage], p, stream, job_id, notifier);
+            return pb::conv_umma_launch_planned(st.plan, in->xmaps[stage], p, stream, job_id, notifier, nullptr, pdl);
         default:
             return pb::simple_op_launch(st.kind, p, stream, job_id, notifier);
     }
 }
 
 // Captures group `g` of the instance into an executable graph: [slot copy] -> kernels.
-int capture_group(pb_instance* in, int g, cudaStream_t cap) {
+int capture_group(pb_instance* in, int g, cudaStream_t cap, bool pdl_allowed) {
     const pb_model::Group& grp = in->m->groups[g];
     const int n_stages = (int)in->m->stages.size();
     PB_CUDA(cudaStreamBeginCapture(cap, cudaStreamCaptureModeRelaxed));
@@ -193,7 +193,10 @@ int capture_group(pb_instance* in, int g, cudaStream_t cap) {
         void* nfp = nullptr;
         if (last) { jid = pb::kSlotNotify; nfp = in->slot_dev; }
         else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = in->slot_dev; }
-        rc = launch_stage_with(in, s, &p, cap, jid, nfp, nullptr, nullptr);
+        // A tensor-core convolution that follows another kernel of the group overlaps its set-up with
+        // that kernel's tail (programmatic dependent launch) and waits for it on the device.
+        const bool pdl = pdl_allowed && s > grp.first && st.kind == PB_STAGE_CONV_UMMA;
+        rc = launch_stage_with(in, s, &p, cap, jid, nfp, nullptr, nullptr, pdl);
         (void)n_stages;
     }
     cudaGraph_t graph = nullptr;
@@ -510,8 +513,15 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
         e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
         if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "capture stream", __FILE__, __LINE__); }
         int rc = PB_OK;
-        for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g)
-            if (m->groups[g].count > 1) rc = capture_group(in, (int)g, cap);
+        const bool pdl = env_flag("PB_PDL", true);
+        for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g) {
+            if (m->groups[g].count <= 1) continue;
+            rc = capture_group(in, (int)g, cap, pdl);
+            if (rc != PB_OK && pdl) {        // a driver that cannot capture programmatic edges: plain edges
+                cudaGetLastError();
+                rc = capture_group(in, (int)g, cap, false);
+            }
+        }
         cudaStreamDestroy(cap);
         if (rc != PB_OK) { pb_instance_destroy(in); return rc; }
     }

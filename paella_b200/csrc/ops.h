@@ -48,8 +48,10 @@ int conv_umma_xmap_create(const pb_op_params* p, ConvUmmaXMap** out);
 void conv_umma_xmap_destroy(ConvUmmaXMap* m);
 // xmap may be NULL: the descriptor is then encoded for this one launch.
 // err_flag: device word raised when a bounded wait runs out (NULL = the library's per-device flag).
+// pdl: launch with the programmatic-serialization attribute (the kernel waits for its predecessor
+// itself, after its set-up); only meaningful when the previous operation in `st` is a kernel.
 int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
-                             uint32_t job_id, void* notifier, uint32_t* err_flag = nullptr);
+                             uint32_t job_id, void* notifier, uint32_t* err_flag = nullptr, bool pdl = false);
 int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
 uint32_t* noalloc_error_flag_ptr(int device);   // NULL until the no-allocation path ran on the device
 
