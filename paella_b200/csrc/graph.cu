@@ -170,7 +170,7 @@ int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStr
         case PB_STAGE_CONV_UMMA:
             return pb::conv_umma_launch_planned(st.plan, in->xmaps[stage], p, stream, job_id, notifier, nullptr, pdl);
         default:
-            return pb::simple_op_launch(st.kind, p, stream, job_id, notifier);
+            return pb::simple_op_launch(st.kind, p, stream, job_id, notifier, pdl);
     }
 }
 
@@ -193,9 +193,10 @@ int capture_group(pb_instance* in, int g, cudaStream_t cap, bool pdl_allowed) {
         void* nfp = nullptr;
         if (last) { jid = pb::kSlotNotify; nfp = in->slot_dev; }
         else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = in->slot_dev; }
-        // A tensor-core convolution that follows another kernel of the group overlaps its set-up with
-        // that kernel's tail (programmatic dependent launch) and waits for it on the device.
-        const bool pdl = pdl_allowed && s > grp.first && st.kind == PB_STAGE_CONV_UMMA;
+        // A kernel that follows another kernel of the group is launched as its programmatic dependent:
+        // it may be scheduled while the previous one drains (the convolution overlaps its whole set-up)
+        // and waits for it on the device before touching memory.
+        const bool pdl = pdl_allowed && s > grp.first && st.kind != PB_STAGE_MNIST_FUSED;
         rc = launch_stage_with(in, s, &p, cap, jid, nfp, nullptr, nullptr, pdl);
         (void)n_stages;
     }

@@ -69,7 +69,10 @@ __device__ __forceinline__ float act_fn(float v, int act) {
     return v;
 }
 
+// Every kernel here may be launched as a programmatic dependent of the previous kernel of its stage
+// graph: it waits for that kernel on the device before touching memory (a no-op otherwise).
 #define PB_NOTIFY_START()                                        \
+    pb::griddep_wait();                                           \
     const pb::LaunchSlot* slot_ = pb::resolve_slot(job_id, nf);  \
     (void)slot_;                                                  \
     if (nf) nf->start(job_id)
@@ -528,7 +531,21 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
     return PB_OK;
 }
 
-int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier) {
+template <typename... KArgs, typename... Args>
+static void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl) {
     FinishedBlockNotifier* nf = static_cast<FinishedBlockNotifier*>(notifier);
     pb_launch_info li;
     int rc = simple_op_info(kind, p, &li);
@@ -541,13 +558,13 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
     const dim3 grid(li.num_blocks), block(256);
 #define PB_DISPATCH(kern_f32, kern_bf16, ...)                                           \
     do {                                                                                \
-        if (f32) kern_f32<<<grid, block, 0, st>>>(__VA_ARGS__);                         \
-        else kern_bf16<<<grid, block, 0, st>>>(__VA_ARGS__);                            \
+        if (f32) launch_k(kern_f32, grid, block, st, pdl, __VA_ARGS__);                 \
+        else launch_k(kern_bf16, grid, block, st, pdl, __VA_ARGS__);                    \
     } while (0)
     switch (kind) {
         case PB_STAGE_INPUT:
-            if (f32) input_transform_kernel<float><<<grid, block, 0, st>>>((const float*)p->x, (float*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
-            else input_transform_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const float*)p->x, (__nv_bfloat16*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
+            if (f32) launch_k(input_transform_kernel<float>, grid, block, st, pdl, (const float*)p->x, (float*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
+            else launch_k(input_transform_kernel<__nv_bfloat16>, grid, block, st, pdl, (const float*)p->x, (__nv_bfloat16*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
             break;
         case PB_STAGE_CONV_SIMT:
             PB_REQUIRE(a.C % a.groups == 0 && a.K % a.groups == 0, "conv: groups must divide channels");
@@ -579,8 +596,8 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
             break;
         case PB_STAGE_SOFTMAX:
             // flags bit2: the input is fp32 regardless of dtype
-            if (f32 || (p->flags & 4)) softmax_kernel<float, true><<<1, block, 0, st>>>(a, job_id, nf);
-            else softmax_kernel<__nv_bfloat16, false><<<1, block, 0, st>>>(a, job_id, nf);
+            if (f32 || (p->flags & 4)) launch_k(softmax_kernel<float, true>, dim3(1), block, st, pdl, a, job_id, nf);
+            else launch_k(softmax_kernel<__nv_bfloat16, false>, dim3(1), block, st, pdl, a, job_id, nf);
             break;
         default:
             set_error("pb_op_launch: unknown stage kind %d", kind);

@@ -28,6 +28,13 @@ constexpr uint32_t kSlotNotify = 0xFFFFFFFFu;
 constexpr uint32_t kSlotQuiet = 0xFFFFFFFEu;
 
 #ifdef __CUDACC__
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream (or graph) is still running; griddep_wait() blocks until
+// that predecessor has completed and its writes are visible, griddep_launch() lets the successor's
+// blocks be scheduled early.  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Returns the slot (or NULL) and rewrites job_id / nf to what the notifier calls need.
 __device__ __forceinline__ const LaunchSlot* resolve_slot(uint32_t& job_id, llis::job::FinishedBlockNotifier*& nf) {
     if (job_id < kSlotQuiet) return nullptr;

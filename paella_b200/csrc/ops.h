@@ -25,7 +25,7 @@ struct OpArgs {
 
 // kernels.cu
 int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out);
-int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
+int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl = false);
 int64_t simple_pack_weights(int kind, const pb_op_params* p, const float* w_oihw, void* dst_host);
 void store_elem(void* dst, size_t i, float v, int dtype);
 int mnist_fused_info(pb_launch_info* out);
