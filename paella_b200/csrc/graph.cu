@@ -51,6 +51,8 @@ struct Stage {
     pb_launch_info info;
     std::string name;
     int out_tensor;
+    int in_tensor = -1, res_tensor = -1;   // tensors read (-1: the request input / none)
+    size_t scratch_off = 0;                // this stage's private slice of the instance's scratch buffer
 };
 
 }  // namespace
@@ -63,7 +65,8 @@ struct pb_model {
     std::vector<Stage> stages;
     int t_in = 0, t_out = 0;
     size_t arena_bytes = 0;
-    size_t scratch_bytes = 0;     // largest per-stage scratch requirement (split-K partial tiles)
+    size_t scratch_bytes = 0;     // sum of the stages' scratch requirements: every split-K layer has its own
+                                  // slice, so kernels of parallel branches never share partial tiles
     size_t in_floats = 0, out_floats = 0;
     bool mnist_fused = false;
     // Stage groups: what the job adapter hands to the scheduler as ONE stage.  A group of several
@@ -174,34 +177,95 @@ int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStr
     }
 }
 
-// Captures group `g` of the instance into an executable graph: [slot copy] -> kernels.
-int capture_group(pb_instance* in, int g, cudaStream_t cap, bool pdl_allowed) {
-    const pb_model::Group& grp = in->m->groups[g];
-    const int n_stages = (int)in->m->stages.size();
-    PB_CUDA(cudaStreamBeginCapture(cap, cudaStreamCaptureModeRelaxed));
-    cudaError_t e = cudaMemcpyAsync(in->slot_dev, in->slot_host, sizeof(pb::LaunchSlot), cudaMemcpyHostToDevice, cap);
+// Captures group `g` of the instance into an executable graph.  The kernels are not chained in
+// program order but by data dependence: the branches of an Inception block (or a down-sampling
+// shortcut) sit on parallel paths of the graph and may run concurrently.
+//   [slot copy] -> roots ...  each kernel after the producers of the tensors it reads ... -> last kernel
+// The last kernel of the group (the one that notifies) is ordered after every other kernel.
+// Kernels whose only dependence is the previous kernel on their path are programmatic dependents.
+int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed, bool parallel) {
+    const pb_model* m = in->m;
+    const pb_model::Group& grp = m->groups[g];
+    const int first = grp.first, last = grp.first + grp.count - 1;
+    constexpr int kMaxLanes = 6;
+    std::vector<cudaStream_t> lanes{origin};
+    std::vector<cudaEvent_t> events;
+    auto new_event = [&]() { cudaEvent_t e = nullptr; cudaEventCreateWithFlags(&e, cudaEventDisableTiming); events.push_back(e); return e; };
+    struct Done { int lane; cudaEvent_t ev; };
+    std::vector<Done> done(grp.count, Done{-1, nullptr});          // per stage of the group
+    std::vector<int> lane_tail{-1};                                // last stage launched on each lane (-1: none yet)
+    std::vector<std::vector<int>> writers(m->tensors.size());      // in-group stages that wrote each tensor
+
+    PB_CUDA(cudaStreamBeginCapture(origin, cudaStreamCaptureModeRelaxed));
+    cudaError_t e = cudaMemcpyAsync(in->slot_dev, in->slot_host, sizeof(pb::LaunchSlot), cudaMemcpyHostToDevice, origin);
+    cudaEvent_t root = new_event();
+    if (e == cudaSuccess) e = cudaEventRecord(root, origin);
     int rc = PB_OK;
-    for (int s = grp.first; e == cudaSuccess && rc == PB_OK && s < grp.first + grp.count; ++s) {
+    for (int s = first; e == cudaSuccess && rc == PB_OK && s <= last; ++s) {
+        const Stage& st = m->stages[s];
+        // in-group producers of what this stage reads
+        std::vector<int> deps;
+        for (int t : {st.in_tensor, st.res_tensor})
+            if (t >= 0)
+                for (int w : writers[t]) deps.push_back(w);
+        if (s == last)                                            // the notifying kernel closes the group
+            for (int w = first; w < last; ++w) deps.push_back(w);
+        std::sort(deps.begin(), deps.end());
+        deps.erase(std::unique(deps.begin(), deps.end()), deps.end());
+        // lane: continue the path of a producer that is still its lane's tail, else a fresh lane
+        int lane = -1;
+        if (!parallel || s == last) lane = 0;
+        for (size_t i = 0; lane < 0 && i < deps.size(); ++i) {
+            const int dl = done[deps[i] - first].lane;
+            if (lane_tail[dl] == deps[i]) lane = dl;
+        }
+        if (lane < 0) {
+            for (size_t l = 0; l < lanes.size() && lane < 0; ++l)
+                if (lane_tail[l] < 0 && (l > 0 || deps.empty())) lane = (int)l;
+            if (lane < 0 && (int)lanes.size() < kMaxLanes) {
+                cudaStream_t ns = nullptr;
+                e = cudaStreamCreateWithFlags(&ns, cudaStreamNonBlocking);
+                if (e != cudaSuccess) break;
+                lanes.push_back(ns);
+                lane_tail.push_back(-1);
+                lane = (int)lanes.size() - 1;
+            }
+            if (lane < 0) lane = 0;
+        }
+        // order this lane after everything the stage depends on
+        bool chained = lane_tail[lane] >= 0 && deps.size() == 1 && deps[0] == lane_tail[lane];
+        if (lane != 0 && lane_tail[lane] < 0 && e == cudaSuccess) e = cudaStreamWaitEvent(lanes[lane], root, 0);   // joins the capture
+        for (size_t i = 0; e == cudaSuccess && i < deps.size(); ++i) {
+            const Done& d = done[deps[i] - first];
+            if (d.lane != lane || lane_tail[lane] != deps[i]) {
+                if (d.lane != lane) e = cudaStreamWaitEvent(lanes[lane], d.ev, 0);
+                chained = chained && d.lane == lane;
+            }
+        }
+        if (e != cudaSuccess) break;
+
         pb_op_params p = in->params[s];
-        const Stage& st = in->m->stages[s];
         const bool reads_input = s == 0;                       // the request's input buffer
         const bool writes_output = st.y_is_output;             // the request's output buffer
-        const bool last = s == grp.first + grp.count - 1;
         if (reads_input) p.x = nullptr;                        // NULL = take it from the launch slot
         if (writes_output) p.y = nullptr;
         uint32_t jid = 0;
         void* nfp = nullptr;
-        if (last) { jid = pb::kSlotNotify; nfp = in->slot_dev; }
+        if (s == last) { jid = pb::kSlotNotify; nfp = in->slot_dev; }
         else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = in->slot_dev; }
-        // A kernel that follows another kernel of the group is launched as its programmatic dependent:
-        // it may be scheduled while the previous one drains (the convolution overlaps its whole set-up)
-        // and waits for it on the device before touching memory.
-        const bool pdl = pdl_allowed && s > grp.first && st.kind != PB_STAGE_MNIST_FUSED;
-        rc = launch_stage_with(in, s, &p, cap, jid, nfp, nullptr, nullptr, pdl);
-        (void)n_stages;
+        const bool pdl = pdl_allowed && chained && st.kind != PB_STAGE_MNIST_FUSED;
+        rc = launch_stage_with(in, s, &p, lanes[lane], jid, nfp, nullptr, nullptr, pdl);
+        if (rc != PB_OK) break;
+        cudaEvent_t ev = new_event();
+        e = cudaEventRecord(ev, lanes[lane]);
+        done[s - first] = Done{lane, ev};
+        lane_tail[lane] = s;
+        writers[st.out_tensor].push_back(s);
     }
     cudaGraph_t graph = nullptr;
-    const cudaError_t e2 = cudaStreamEndCapture(cap, &graph);
+    const cudaError_t e2 = cudaStreamEndCapture(origin, &graph);
+    for (cudaEvent_t ev : events) cudaEventDestroy(ev);
+    for (size_t l = 1; l < lanes.size(); ++l) cudaStreamDestroy(lanes[l]);
     if (rc != PB_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
     if (e != cudaSuccess) { if (graph) cudaGraphDestroy(graph); return pb::cuda_fail(e, "graph capture", __FILE__, __LINE__); }
     if (e2 != cudaSuccess) return pb::cuda_fail(e2, "cudaStreamEndCapture", __FILE__, __LINE__);
@@ -366,6 +430,8 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         Stage st{};
         st.name = std::string((const char*)pn + 64 * i, strnlen((const char*)pn + 64 * i, 64));
         st.out_tensor = (int)o.out;
+        st.in_tensor = (int)o.in0;
+        st.res_tensor = o.in1 != kNone ? (int)o.in1 : -1;
         pb_op_params& p = st.p;
         memset(&p, 0, sizeof(p));
         p.dtype = m->dtype;
@@ -435,7 +501,10 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         p.scratch = (void*)16;
         p.scratch_bytes = ~0ull;
         PB_FAIL_LOAD(pb_op_info(st.kind, &p, &st.info));
-        if (st.info.scratch_bytes > m->scratch_bytes) m->scratch_bytes = st.info.scratch_bytes;
+        if (st.info.scratch_bytes) {
+            st.scratch_off = m->scratch_bytes;
+            m->scratch_bytes += pb::round_up((size_t)st.info.scratch_bytes, (size_t)256);
+        }
         if (st.kind == PB_STAGE_CONV_UMMA) PB_FAIL_LOAD(pb::conv_umma_plan_create(&p, st.w_dev, &st.plan));
         m->stages.push_back(st);
     }
@@ -492,8 +561,8 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
         p.x = st.x_is_input ? (const void*)in->in_dev : (const void*)(in->arena + st.x_off);
         p.y = st.y_is_output ? (void*)in->out_dev : (void*)(in->arena + st.y_off);
         p.residual = st.has_res ? (const void*)(in->arena + st.res_off) : nullptr;
-        p.scratch = in->scratch;
-        p.scratch_bytes = in->scratch ? m->scratch_bytes : 0;
+        p.scratch = st.info.scratch_bytes ? in->scratch + st.scratch_off : nullptr;
+        p.scratch_bytes = st.info.scratch_bytes;
         in->params[i] = p;
         if (st.kind == PB_STAGE_CONV_UMMA) {
             const int rc = pb::conv_umma_xmap_create(&p, &in->xmaps[i]);
@@ -515,12 +584,13 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
         if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "capture stream", __FILE__, __LINE__); }
         int rc = PB_OK;
         const bool pdl = env_flag("PB_PDL", true);
+        const bool parallel = env_flag("PB_GRAPH_BRANCHES", true);
         for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g) {
             if (m->groups[g].count <= 1) continue;
-            rc = capture_group(in, (int)g, cap, pdl);
-            if (rc != PB_OK && pdl) {        // a driver that cannot capture programmatic edges: plain edges
+            rc = capture_group(in, (int)g, cap, pdl, parallel);
+            if (rc != PB_OK && (pdl || parallel)) {   // a driver that cannot capture this: a plain chain
                 cudaGetLastError();
-                rc = capture_group(in, (int)g, cap, false);
+                rc = capture_group(in, (int)g, cap, false, false);
             }
         }
         cudaStreamDestroy(cap);
