@@ -39,6 +39,9 @@ WORKLOADS = {
     "mix": [("tvm_mnist", "mnist", 0.9), ("tvm_inception_v3", "inception_v3", 0.1)],
     # single-model configuration
     "resnet18": [("tvm_resnet18", "resnet18", 1.0)],
+    # the two halves of the headline mix, each alone (to see which one bounds the mix)
+    "mnist": [("tvm_mnist", "mnist", 1.0)],
+    "inception_v3": [("tvm_inception_v3", "inception_v3", 1.0)],
     # depthwise + bottleneck mix
     "mobilenet_resnet50": [("tvm_mobilenet", "mobilenet", 0.5), ("tvm_resnet50", "resnet50", 0.5)],
     # scheduler stress (vec_add of 2^22 floats x 10 launches, 148-block spin kernels of 10 us / 1 ms)
@@ -257,11 +260,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=1000, help="requests per GPU per step")
-    ap.add_argument("--concurrency", type=int, default=48, help="closed-loop clients per replica")
-    ap.add_argument("--inception-instances", type=int, default=16, help="Inception-v3 instances (max outstanding) per replica")
+    ap.add_argument("--concurrency", type=int, default=64, help="closed-loop clients per replica")
+    ap.add_argument("--inception-instances", type=int, default=32, help="Inception-v3 instances (max outstanding) per replica")
     ap.add_argument("--replicas-per-gpu", type=int, default=1,
                     help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU")
-    ap.add_argument("--extra-kernels", type=int, default=32, help="scheduler: over-subscribed stages allowed in flight (--extra_kernels)")
+    ap.add_argument("--extra-kernels", type=int, default=64, help="scheduler: over-subscribed stages allowed in flight (--extra_kernels)")
     ap.add_argument("--sched", default="full3", choices=["full3", "fifo", "fifo2"],
                     help="full3 = the kernel-level scheduler; fifo (job by job) and fifo2 (stage by stage, arrival order) are the ablations")
     ap.add_argument("--streams", type=int, default=500, help="scheduler stream pool (--num_streams); 1 with --sched fifo = single-stream baseline")
@@ -287,6 +290,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     wl_text = {"mix": "mixed MNIST-CNN : Inception-v3@299 = 9:1 by request count, batch 1, random He-normal weights (headline configuration)",
                "resnet18": "ResNet-18 v1, batch 1, 224x224, BN folded, random He-normal weights",
+               "mnist": "MNIST-CNN alone, batch 1, 28x28, fp32",
+               "inception_v3": "Inception-v3 alone, batch 1, 299x299, BN folded, random He-normal weights",
                "mobilenet_resnet50": "MobileNetV2 : ResNet-50 = 1:1, batch 1, 224x224",
                "stress": "vec_add : dummy_short : dummy_long = 1:1:1 synthetic scheduler stress"}[args.workload]
     config = {"workload": wl_text + ("; closed loop" if args.iat_us <= 0 else f"; open loop, Poisson, mean inter-arrival {args.iat_us} us per replica"),
@@ -417,6 +422,11 @@ def main():
             "latency_us": lat(r_dev),
             "timing": "CUDA events on each GPU around the measured requests (device idle on both sides), max over GPUs",
             "records_consumed": int(r_dev.records_consumed), "decisions": int(r_dev.decisions),
+            # this rank's replica threads during the e2e leg: share of their time inside CUDA launch calls, in
+            # notification handling + scheduling, and polling with nothing to do (GPU-bound when large)
+            "host_time_share": (lambda t: {"launch": round(r_e2e.host_launch_us / t, 3), "sched": round(r_e2e.host_sched_us / t, 3),
+                                           "idle": round(r_e2e.host_idle_us / t, 3)})(
+                max(r_e2e.host_launch_us + r_e2e.host_sched_us + r_e2e.host_idle_us, 1e-9)),
             "per_replica_rps": {"resident": [round(r_dev.per_gpu_rps[i]) for i in range(len(devices))],
                                 "e2e": [round(r_e2e.per_gpu_rps[i]) for i in range(len(devices))]}}
 

@@ -9,6 +9,7 @@
 // against a recorded trace.
 #pragma once
 
+#include <chrono>
 #include <memory>
 #include <string>
 #include <vector>
@@ -77,7 +78,17 @@ class Scheduler {
 
     static std::unique_ptr<Scheduler> create(const std::string& name, const SchedulerConfig& cfg, SchedulerHost* host);
 
+    // Host time spent inside plugins' run_next() so far (CUDA launch calls), nanoseconds.
+    uint64_t run_next_ns() const { return run_next_ns_; }
+
   protected:
+    void run_stage(job::Job* job) {
+        const auto t0 = std::chrono::steady_clock::now();
+        job->run_next();
+        run_next_ns_ += (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
+    }
+    uint64_t run_next_ns_ = 0;
+
     // Closes the stage a failed run_next() left open (see take_synthetic).
     void close_failed_stage(job::Job* job, bool is_mem) {
         job::InstrumentInfo r{};

@@ -308,6 +308,10 @@ typedef struct pb_loadgen_result {
     uint64_t decisions;
     uint64_t h2d_bytes, d2h_bytes;
     int32_t errors;
+    /* where the replicas' host threads spent the measured phase, summed over replicas (us):
+     * inside the plugins' run_next() (CUDA launches), inside notification handling and scheduling
+     * around it, and in polls that found nothing to do (the GPU was the slower side) */
+    double host_launch_us, host_sched_us, host_idle_us;
 } pb_loadgen_result;
 
 PB_API void pb_loadgen_config_default(pb_loadgen_config* cfg);

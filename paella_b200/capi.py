@@ -61,7 +61,8 @@ class LoadgenResult(C.Structure):
     _fields_ = [("elapsed_us", C.c_double), ("elapsed_event_ms", C.c_double), ("throughput_rps", C.c_double), ("all", LatencyStats),
                 ("per_type", LatencyStats * PB_MAX_JOB_TYPES), ("per_gpu_rps", C.c_double * PB_MAX_GPUS),
                 ("kernels_launched", C.c_uint64), ("records_consumed", C.c_uint64), ("decisions", C.c_uint64),
-                ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("errors", C.c_int32)]
+                ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("errors", C.c_int32),
+                ("host_launch_us", C.c_double), ("host_sched_us", C.c_double), ("host_idle_us", C.c_double)]
 
 
 class ReplayType(C.Structure):

@@ -200,12 +200,6 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     return t;
 }
 
-__device__ __forceinline__ float act_fn(float v, int act) {
-    if (act == 1) return fmaxf(v, 0.f);
-    if (act == 2) return fminf(fmaxf(v, 0.f), 6.f);
-    return v;
-}
-
 // Optional phase stamps for development builds (-DPB_CONV_TIMING): %globaltimer at eight points of
 // the first 64 CTAs, written to a device array the probe program reads back.
 #ifdef PB_CONV_TIMING
@@ -215,8 +209,16 @@ __device__ unsigned long long g_conv_t[64 * 8];
         const unsigned b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);             \
         if (b_ < 64) g_conv_t[b_ * 8 + (i)] = globaltimer_ns();                                         \
     } while (0)
+// per-k-block SM-clock stamps of the first 8 CTAs: [cta][kb][0 = loads issued, 1 = operands landed, 2 = MMAs issued]
+__device__ unsigned long long g_conv_kb[8 * 64 * 3];
+#define PB_TK(kb, i)                                                                                    \
+    do {                                                                                                \
+        const unsigned b_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);             \
+        if (b_ < 8 && (kb) < 64) g_conv_kb[(b_ * 64 + (kb)) * 3 + (i)] = (unsigned long long)clock64();              \
+    } while (0)
 #else
 #define PB_T(i) do {} while (0)
+#define PB_TK(kb, i) do {} while (0)
 #endif
 
 // ---- the kernel -----------------------------------------------------------------------
@@ -232,10 +234,39 @@ __device__ __forceinline__ void tcgen05_ld32(uint32_t taddr, uint32_t (&r)[32]) 
         : "memory");
 }
 
+// Packed fp32 pairs (sm_100 has two-wide fp32 adds) and the bf16 pair conversion with the activation
+// folded in: cvt's .relu clamps negatives to zero, ReLU6 is one more packed min against 6.0.
+// Rounding is monotonic and 0 and 6 are bf16 values, so activation-after-rounding equals
+// rounding-after-activation.
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t x, uint64_t y) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(x), "l"(y));
+    return r;
+}
+template <int ACT>
+__device__ __forceinline__ uint32_t to_bf16x2_act(uint64_t v) {
+    uint32_t lo, hi, d;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    if constexpr (ACT == 0) {
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+    } else {
+        asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+        if constexpr (ACT == 2) asm("min.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(d), "r"(0x40C040C0u));
+    }
+    return d;
+}
+
 // One group of NC (16 or 32) accumulator columns of this thread's row: TMEM -> registers, (+ split-K
 // partial tiles), + bias (+ residual), activation, bf16, 16-byte stores.  Everything that does not
-// depend on the accumulator is fetched before the TMEM wait.
-template <int NC>
+// depend on the accumulator is fetched before the TMEM wait.  The four epilogue warps run one per
+// scheduler with nothing to hide instruction latency behind, so the column loop is kept to one
+// packed add and one convert per two columns.
+template <int NC, int ACT>
 __device__ __forceinline__ void epilogue_chunk(const ConvArgs& a, uint32_t lane_addr, int cb, int n0, bool row_valid,
                                                __nv_bfloat16* yrow, const __nv_bfloat16* rrow, const float* part, size_t tile_floats,
                                                const float* s_bias) {
@@ -252,21 +283,23 @@ __device__ __forceinline__ void epilogue_chunk(const ConvArgs& a, uint32_t lane_
         for (int h = 0; h < NC / 8; ++h)
             if (k0 + h * 8 + 8 <= a.K) rv[h] = *reinterpret_cast<const uint4*>(rrow + k0 + h * 8);
     }
-    float bias[NC];
+    uint64_t bias2[NC / 2];
 #pragma unroll
     for (int j = 0; j < NC; j += 4) {
-        const float4 b4 = *reinterpret_cast<const float4*>(s_bias + cb + j);
-        bias[j] = b4.x; bias[j + 1] = b4.y; bias[j + 2] = b4.z; bias[j + 3] = b4.w;
+        const uint4 b4 = *reinterpret_cast<const uint4*>(s_bias + cb + j);
+        bias2[j / 2] = pack_f32x2(b4.x, b4.y);
+        bias2[j / 2 + 1] = pack_f32x2(b4.z, b4.w);
     }
     if (live && part) {
         // every partial tile, this CTA's own included, is read from the workspace in split order, so
         // the fp32 sum does not depend on which CTA arrived last; it starts from the bias
         for (int z = 0; z < a.splits; ++z) {
-            const float4* other = reinterpret_cast<const float4*>(part + (size_t)z * tile_floats) + threadIdx.x;
+            const uint4* other = reinterpret_cast<const uint4*>(part + (size_t)z * tile_floats) + threadIdx.x;
 #pragma unroll
             for (int j = 0; j < NC / 4; ++j) {
-                const float4 o = __ldcg(other + (size_t)(cb / 4 + j) * kBM);
-                bias[4 * j] += o.x; bias[4 * j + 1] += o.y; bias[4 * j + 2] += o.z; bias[4 * j + 3] += o.w;
+                const uint4 o = __ldcg(other + (size_t)(cb / 4 + j) * kBM);
+                bias2[2 * j] = add_f32x2(bias2[2 * j], pack_f32x2(o.x, o.y));
+                bias2[2 * j + 1] = add_f32x2(bias2[2 * j + 1], pack_f32x2(o.z, o.w));
             }
         }
     }
@@ -276,31 +309,36 @@ __device__ __forceinline__ void epilogue_chunk(const ConvArgs& a, uint32_t lane_
     for (int h = 0; h < NC / 8; ++h) {
         const int kk = k0 + h * 8;
         if (kk + 8 <= a.K) {
-            float f[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = (part ? 0.f : __uint_as_float(v[h * 8 + j])) + bias[h * 8 + j];
-            if (rrow) {
-                const uint32_t ru[4] = {rv[h].x, rv[h].y, rv[h].z, rv[h].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    f[2 * j] += __uint_as_float(ru[j] << 16);
-                    f[2 * j + 1] += __uint_as_float(ru[j] & 0xffff0000u);
-                }
-            }
+            const uint32_t ru[4] = {rv[h].x, rv[h].y, rv[h].z, rv[h].w};
             uint32_t o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 hv = __floats2bfloat162_rn(act_fn(f[2 * j], a.act), act_fn(f[2 * j + 1], a.act));
-                o[j] = *reinterpret_cast<const uint32_t*>(&hv);
+                uint64_t f = bias2[h * 4 + j];
+                if (!part) f = add_f32x2(pack_f32x2(v[h * 8 + 2 * j], v[h * 8 + 2 * j + 1]), f);
+                if (rrow) f = add_f32x2(f, pack_f32x2(ru[j] << 16, ru[j] & 0xffff0000u));
+                o[j] = to_bf16x2_act<ACT>(f);
             }
             *reinterpret_cast<uint4*>(yrow + kk) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }
 
+template <int ACT>
+__device__ __forceinline__ void epilogue_columns(const ConvArgs& a, uint32_t lane_addr, int n0, bool row_valid, __nv_bfloat16* yrow,
+                                                 const __nv_bfloat16* rrow, const float* part, size_t tile_floats,
+                                                 const float* s_bias) {
+    int cb = 0;
+    for (; cb + 32 <= a.BN; cb += 32)
+        epilogue_chunk<32, ACT>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+    for (; cb < a.BN; cb += 16)
+        epilogue_chunk<16, ACT>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+}
+
 // Epilogue, run by warps 0-3 (thread t owns accumulator lane t = tile row t): wait for the
 // accumulator, optionally meet the other split-K CTAs of the tile in the workspace, then
-// bias + residual + activation and bf16 stores into the output channel slice.
+// bias + residual + activation and bf16 stores into the output channel slice.  (Staging the bf16
+// tile in shared memory for row-contiguous stores was measured slower: the epilogue is bound by its
+// instruction count, not by the scattered 16-byte stores.)
 __device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, bool ok, int m0, int n0, const float* s_bias,
                                      uint64_t* s_accum_p, volatile uint32_t* s_abort_p, uint32_t* s_is_last_p) {
     const int tid = threadIdx.x;
@@ -348,11 +386,9 @@ __device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, 
         __nv_bfloat16* yrow = a.y + (size_t)m * a.Ks + a.out_c_off;
         const __nv_bfloat16* rrow = a.residual ? a.residual + (size_t)m * a.res_Cs : nullptr;
         const float* part = a.splits > 1 ? a.ws + (size_t)tile * a.splits * tile_floats : nullptr;
-        int cb = 0;
-        for (; cb + 32 <= a.BN; cb += 32)
-            epilogue_chunk<32>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
-        for (; cb < a.BN; cb += 16)
-            epilogue_chunk<16>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+        if (a.act == 1) epilogue_columns<1>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+        else if (a.act == 2) epilogue_columns<2>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+        else epilogue_columns<0>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
     }
 }
 
@@ -619,6 +655,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                 tma_load_im2col_4d(a_tile, &tmap_x, chunk * kBK, w0, h0, 0, (uint16_t)s, (uint16_t)r, bar);
                 tma_load_2d(a_tile + kATileBytes, &tmap_w, (kb_begin + kb) * kBK, n0, bar);
                 if (kb == 0) PB_T(2);
+                PB_TK(kb, 0);
                 if (++chunk == cpt) {
                     chunk = 0;
                     if (++s == a.S) { s = 0; ++r; }
@@ -637,6 +674,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                 ok = mbar_wait(smem_u32(&s_full[st]), use & 1u, &s_abort, a.err_flag, 2u);
                 if (!ok) break;
                 if (kb == 0) PB_T(3);
+                PB_TK(kb, 1);
                 tcgen05_fence_after();
                 const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
                 const uint32_t b_tile = a_tile + kATileBytes;
@@ -646,6 +684,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                                      (kb > 0 || k > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(smem_u32(&s_empty[st]));
+                PB_TK(kb, 2);
             }
             if (ok) tcgen05_commit(smem_u32(&s_accum));
             PB_T(4);

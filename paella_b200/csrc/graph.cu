@@ -125,13 +125,13 @@ bool is_mnist_topology(const std::vector<PackOp>& ops, const std::vector<TensorI
 }
 
 
-// Splits the stage list into groups of at most PB_STAGE_GROUP kernels (default 12; 1 = one kernel per
+// Splits the stage list into groups of at most PB_STAGE_GROUP kernels (default 24; 1 = one kernel per
 // scheduler stage, the reference's granularity) and derives each group's stage declaration.
 // Only the LAST kernel of a group reports block start/end, so the declared block count is that
 // kernel's grid; the per-block resources are scaled so that blocks x per-block equals the largest
 // footprint any kernel of the group has on the GPU.
 void build_groups(pb_model* m) {
-    int gs = 12;
+    int gs = 24;
     if (const char* e = getenv("PB_STAGE_GROUP")) gs = atoi(e);
     if (gs < 1) gs = 1;
     const int n = (int)m->stages.size();
@@ -196,8 +196,13 @@ int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed,
     std::vector<int> lane_tail{-1};                                // last stage launched on each lane (-1: none yet)
     std::vector<std::vector<int>> writers(m->tensors.size());      // in-group stages that wrote each tensor
 
+    // A single small kernel reads the launch slot straight from the pinned host mirror (one PCIe read,
+    // no copy node: about 1 us less host time per launch); larger groups get a device copy first.
+    const bool host_slot = grp.count == 1 && m->stages[first].info.num_blocks <= 4;
+    void* const slot_ptr = host_slot ? (void*)in->slot_host : (void*)in->slot_dev;
     PB_CUDA(cudaStreamBeginCapture(origin, cudaStreamCaptureModeRelaxed));
-    cudaError_t e = cudaMemcpyAsync(in->slot_dev, in->slot_host, sizeof(pb::LaunchSlot), cudaMemcpyHostToDevice, origin);
+    cudaError_t e = host_slot ? cudaSuccess
+                              : cudaMemcpyAsync(in->slot_dev, in->slot_host, sizeof(pb::LaunchSlot), cudaMemcpyHostToDevice, origin);
     cudaEvent_t root = new_event();
     if (e == cudaSuccess) e = cudaEventRecord(root, origin);
     int rc = PB_OK;
@@ -233,7 +238,10 @@ int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed,
             if (lane < 0) lane = 0;
         }
         // order this lane after everything the stage depends on
-        bool chained = lane_tail[lane] >= 0 && deps.size() == 1 && deps[0] == lane_tail[lane];
+        // A programmatic dependent waits (griddepcontrol.wait) for the completion of the kernel right
+        // before it on its lane, which itself waited for its own predecessor: on a single lane that
+        // covers every earlier kernel of the graph; with parallel lanes only a sole same-lane producer.
+        bool chained = lane_tail[lane] >= 0 && (!parallel || (deps.size() == 1 && deps[0] == lane_tail[lane]));
         if (lane != 0 && lane_tail[lane] < 0 && e == cudaSuccess) e = cudaStreamWaitEvent(lanes[lane], root, 0);   // joins the capture
         for (size_t i = 0; e == cudaSuccess && i < deps.size(); ++i) {
             const Done& d = done[deps[i] - first];
@@ -251,8 +259,8 @@ int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed,
         if (writes_output) p.y = nullptr;
         uint32_t jid = 0;
         void* nfp = nullptr;
-        if (s == last) { jid = pb::kSlotNotify; nfp = in->slot_dev; }
-        else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = in->slot_dev; }
+        if (s == last) { jid = pb::kSlotNotify; nfp = slot_ptr; }
+        else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = slot_ptr; }
         const bool pdl = pdl_allowed && chained && st.kind != PB_STAGE_MNIST_FUSED;
         rc = launch_stage_with(in, s, &p, lanes[lane], jid, nfp, nullptr, nullptr, pdl);
         if (rc != PB_OK) break;
@@ -569,13 +577,15 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
             if (rc != PB_OK) { pb_instance_destroy(in); return rc; }
         }
     }
-    // launch slot and one executable graph per multi-kernel group
-    e = cudaHostAlloc((void**)&in->slot_host, sizeof(pb::LaunchSlot), cudaHostAllocDefault);
+    // launch slot and one executable graph per group
+    e = cudaHostAlloc((void**)&in->slot_host, sizeof(pb::LaunchSlot), cudaHostAllocMapped);
     if (e == cudaSuccess) e = cudaMalloc((void**)&in->slot_dev, sizeof(pb::LaunchSlot));
     if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "launch slot", __FILE__, __LINE__); }
     memset(in->slot_host, 0, sizeof(pb::LaunchSlot));
     in->graphs.assign(m->groups.size(), nullptr);
-    bool any_graph = false;
+    // PB_GRAPH_SINGLE=0: single-kernel groups are launched as plain kernels (about 3 us more host time each)
+    const bool single_graphs = env_flag("PB_GRAPH_SINGLE", true);
+    bool any_graph = single_graphs && !m->groups.empty();
     for (const pb_model::Group& g : m->groups) any_graph = any_graph || g.count > 1;
     if (any_graph) {
         (void)pb::device_error_flag_ptr(m->device);      // allocate it now: nothing may allocate during capture
@@ -584,9 +594,9 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
         if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "capture stream", __FILE__, __LINE__); }
         int rc = PB_OK;
         const bool pdl = env_flag("PB_PDL", true);
-        const bool parallel = env_flag("PB_GRAPH_BRANCHES", true);
+        const bool parallel = env_flag("PB_GRAPH_BRANCHES", false);
         for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g) {
-            if (m->groups[g].count <= 1) continue;
+            if (m->groups[g].count <= 1 && !single_graphs) continue;
             rc = capture_group(in, (int)g, cap, pdl, parallel);
             if (rc != PB_OK && (pdl || parallel)) {   // a driver that cannot capture this: a plain chain
                 cudaGetLastError();

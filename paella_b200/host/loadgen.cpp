@@ -50,6 +50,7 @@ struct GpuResult {
     double first_arrival_us = 0, last_done_us = 0;
     double event_ms = 0;   // CUDA-event time around the measured phase (device clock)
     uint64_t measured = 0, kernels = 0, records = 0, decisions = 0, h2d = 0, d2h = 0;
+    double host_launch_us = 0, host_busy_us = 0, host_idle_us = 0;
     int errors = 0;
     int rc = PB_OK;
     char err[256] = "";
@@ -155,9 +156,11 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
     // cookie = slot index << 32 | request index (or 0xffffffff for warm-up launches)
     std::vector<uint64_t> cookies(256);
     std::vector<int32_t> errs(256);
+    int last_step_records = 0;
     auto drain = [&](auto&& on_done) -> int {
         const int st = pb_server_step(srv, 256);
         if (st < 0) return st;
+        last_step_records = st;
         int n;
         while ((n = pb_server_poll_done(srv, cookies.data(), errs.data(), 256)) > 0)
             for (int i = 0; i < n; ++i) on_done(cookies[i], errs[i]);
@@ -202,7 +205,9 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
             return pb_server_launch(srv, type_id[r.type], slots[slot].io, ((uint64_t)slot << 32) | ri);
         };
         const Clock::time_point run0 = Clock::now();
+        Clock::time_point it0 = run0;
         while (done_reqs < hi - lo && loop_rc == PB_OK) {
+            const size_t next_before = next_req;
             while (next_req < hi && outstanding < cap) {
                 const Request& r = (*reqs)[next_req];
                 if (!closed_loop && us_since(start) < r.arrival_us) break;
@@ -237,6 +242,12 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
                 }
             });
             if (drc != PB_OK && loop_rc == PB_OK) loop_rc = drc;
+            // an iteration that neither submitted nor saw a notification is waiting for the GPU
+            const Clock::time_point it1 = Clock::now();
+            const double it_us = std::chrono::duration<double, std::micro>(it1 - it0).count();
+            if (next_req == next_before && last_step_records == 0) out->host_idle_us += it_us;
+            else out->host_busy_us += it_us;
+            it0 = it1;
             if (us_since(run0) > 600e6) { pb::set_error("load run exceeded 600 s"); loop_rc = PB_ERR_TIMEOUT; }
         }
     };
@@ -254,6 +265,8 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
     phase2_ready->fetch_add(1);
     while (phase2_ready->load(std::memory_order_acquire) < cfg->num_gpus) std::this_thread::yield();
     const uint64_t kernels0 = srv->num_kernels, records0 = srv->num_records, decisions0 = srv->scheduler->num_decisions();
+    const uint64_t launch_ns0 = srv->scheduler->run_next_ns();
+    out->host_idle_us = out->host_busy_us = 0;
     cudaEventRecord(ev0, 0);
     play(n_warm, reqs->size(), Clock::now());
     cudaDeviceSynchronize();
@@ -265,6 +278,7 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
     cudaEventDestroy(ev1);
 
     out->kernels = srv->num_kernels - kernels0;
+    out->host_launch_us = (double)(srv->scheduler->run_next_ns() - launch_ns0) * 1e-3;
     out->records = srv->num_records - records0;
     out->decisions = srv->scheduler->num_decisions() - decisions0;
     if (loop_rc != PB_OK) {
@@ -325,6 +339,9 @@ int pb_loadgen_run(const pb_loadgen_config* cfg, pb_loadgen_result* out) {
         }
         measured += res[g].measured;
         out->kernels_launched += res[g].kernels;
+        out->host_launch_us += res[g].host_launch_us;
+        out->host_sched_us += res[g].host_busy_us - res[g].host_launch_us;
+        out->host_idle_us += res[g].host_idle_us;
         out->records_consumed += res[g].records;
         out->decisions += res[g].decisions;
         out->h2d_bytes += res[g].h2d;

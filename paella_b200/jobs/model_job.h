@@ -84,6 +84,13 @@ class ModelJob : public llis::job::Job {
         } else if (cur < lead + n) {
             const bool direct_io = !copy_stages_ && !resident_;
             const void* in = direct_io ? io_ptr_ : nullptr;
+            // Loads issued by SMs keep few PCIe reads in flight (about 11 GB/s measured); a copy engine
+            // streams several times faster.  Large inputs therefore go through the instance's device
+            // input buffer, enqueued on the same stream right before the first kernel group.
+            if (direct_io && cur == lead && in_bytes_ >= kDmaInputBytes) {
+                check(cudaMemcpyAsync(pb_instance_input_dev(inst_), io_ptr_, in_bytes_, cudaMemcpyHostToDevice, st));
+                in = nullptr;
+            }
             void* out = direct_io ? io_ptr_ + get_output_offset() : nullptr;
             if (pb_instance_launch_group(inst_, cur - lead, st, get_id(), get_finished_block_notifier(), in, out) != PB_OK) set_error(PB_ERR_CUDA);
         } else {
@@ -94,6 +101,7 @@ class ModelJob : public llis::job::Job {
     bool has_next() const override { return next_ < (int)decls_.size() + (copy_stages_ ? 2 : 0); }
 
   private:
+    static constexpr size_t kDmaInputBytes = 64 * 1024;
     void check(cudaError_t e) { if (e != cudaSuccess) set_error(PB_ERR_CUDA); }
 
     // Declares stage `next_` (resources, copy or compute, pre-notify on the last one).
