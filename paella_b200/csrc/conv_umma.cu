@@ -52,10 +52,15 @@ constexpr int kBK = 64;             // bf16 elements per k-block = one 128-byte 
 #endif
 constexpr int kMaxStages = 8;
 constexpr uint32_t kSmemBudget = 200u * 1024u;   // one CTA per SM (gather kernel)
-// The TMA kernel is sized for TWO CTAs per SM: at batch 1 a CTA spends most of its life in fixed
-// latencies (set-up, first operand arrival, epilogue), so residency, not pipeline depth, sets the
-// GPU's convolution throughput once many requests are in flight.
-constexpr uint32_t kSmemBudgetTma = 110u * 1024u;
+// The TMA kernel is sized for THREE CTAs per SM (73 KB of pipeline + ~2 KB static and reserved each
+// out of 228 KB; <= 112 registers; <= 128 of 512 TMEM columns).  One CTA cannot pull more than about
+// 60 bytes per clock through its SM and spends a third of its life in fixed latencies (set-up, first
+// operand arrival, epilogue), so with many requests in flight residency, not pipeline depth, sets the
+// GPU's convolution throughput: the co-resident CTAs keep the SM's load path busy between them.
+#ifndef PB_CONV_SMEM_KB
+#define PB_CONV_SMEM_KB 73
+#endif
+constexpr uint32_t kSmemBudgetTma = PB_CONV_SMEM_KB * 1024u;
 constexpr uint32_t kCounterBytes = 4096;        // split-K tile counters at the head of the scratch buffer
 #ifndef PB_NOALLOC_SCRATCH_BYTES
 #define PB_NOALLOC_SCRATCH_BYTES (4u << 20)      // built-in scratch of pb_conv2d_umma_noalloc: 4 MiB per GPU
@@ -75,6 +80,7 @@ struct ConvArgs {
     int K, Ks, out_c_off, res_Cs;
     int R, S, sh, sw, ph, pw;
     int act;
+    int a_tiled;          // 1: pointwise convolution, operand A is the plain [M][Cs] matrix (tiled TMA, no im2col)
     int nkb;              // k-blocks of 64 = taps * chunks per tap
     int taps;             // R*S
     int Cp;               // channels per tap rounded up to 64: k = tap*Cp + c
@@ -222,18 +228,6 @@ __device__ unsigned long long g_conv_kb[8 * 64 * 3];
 #endif
 
 // ---- the kernel -----------------------------------------------------------------------
-__device__ __forceinline__ void tcgen05_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
-          "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
-          "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-
 // Packed fp32 pairs (sm_100 has two-wide fp32 adds) and the bf16 pair conversion with the activation
 // folded in: cvt's .relu clamps negatives to zero, ReLU6 is one more packed min against 6.0.
 // Rounding is monotonic and 0 and 6 are bf16 values, so activation-after-rounding equals
@@ -261,7 +255,7 @@ __device__ __forceinline__ uint32_t to_bf16x2_act(uint64_t v) {
     return d;
 }
 
-// One group of NC (16 or 32) accumulator columns of this thread's row: TMEM -> registers, (+ split-K
+// One group of NC (= 16) accumulator columns of this thread's row: TMEM -> registers, (+ split-K
 // partial tiles), + bias (+ residual), activation, bf16, 16-byte stores.  Everything that does not
 // depend on the accumulator is fetched before the TMEM wait.  The four epilogue warps run one per
 // scheduler with nothing to hide instruction latency behind, so the column loop is kept to one
@@ -271,8 +265,8 @@ __device__ __forceinline__ void epilogue_chunk(const ConvArgs& a, uint32_t lane_
                                                __nv_bfloat16* yrow, const __nv_bfloat16* rrow, const float* part, size_t tile_floats,
                                                const float* s_bias) {
     uint32_t v[NC];
-    if constexpr (NC == 32) tcgen05_ld32(lane_addr + (uint32_t)cb, v);   // warp-collective: all lanes take part
-    else tcgen05_ld16(lane_addr + (uint32_t)cb, v);
+    static_assert(NC == 16, "16 accumulator columns per step keep the kernel within 112 registers (three CTAs per SM)");
+    tcgen05_ld16(lane_addr + (uint32_t)cb, v);   // warp-collective: all lanes take part
     const int k0 = n0 + cb;
     const bool live = row_valid && k0 < a.K;
     uint4 rv[NC / 8];
@@ -328,8 +322,6 @@ __device__ __forceinline__ void epilogue_columns(const ConvArgs& a, uint32_t lan
                                                  const __nv_bfloat16* rrow, const float* part, size_t tile_floats,
                                                  const float* s_bias) {
     int cb = 0;
-    for (; cb + 32 <= a.BN; cb += 32)
-        epilogue_chunk<32, ACT>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
     for (; cb < a.BN; cb += 16)
         epilogue_chunk<16, ACT>(a, lane_addr, cb, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
 }
@@ -574,7 +566,7 @@ conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvAr
 constexpr int kThreadsTma = 192;
 
 template <int kStages>
-__global__ void __launch_bounds__(kThreadsTma, 2)
+__global__ void __launch_bounds__(kThreadsTma, 3)
 conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const ConvArgs a,
                      uint32_t job_id, FinishedBlockNotifier* nf) {
     extern __shared__ uint8_t smem_raw[];
@@ -652,7 +644,8 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                 const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
                 const uint32_t bar = smem_u32(&s_full[st]);
                 mbar_arrive_expect_tx(bar, (uint32_t)kATileBytes + a.b_stage_bytes);
-                tma_load_im2col_4d(a_tile, &tmap_x, chunk * kBK, w0, h0, 0, (uint16_t)s, (uint16_t)r, bar);
+                if (a.a_tiled) tma_load_2d(a_tile, &tmap_x, chunk * kBK, m0, bar);
+                else tma_load_im2col_4d(a_tile, &tmap_x, chunk * kBK, w0, h0, 0, (uint16_t)s, (uint16_t)r, bar);
                 tma_load_2d(a_tile + kATileBytes, &tmap_w, (kb_begin + kb) * kBK, n0, bar);
                 if (kb == 0) PB_T(2);
                 PB_TK(kb, 0);
@@ -916,7 +909,30 @@ static int make_tmap(const Geometry& g, const void* w_dev, CUtensorMap* out) {
 // im2col tensor map over the channels-last activation tensor [N=1][H][W][Cs] (dims listed innermost
 // first).  The bounding box of filter-window origins is [-pad, dim + pad - (filter-1)); traversal
 // strides are the convolution strides; each load brings 128 pixels x 64 channels.
+// A 1x1, stride-1, unpadded convolution reads its input as the matrix [pixels][channels]: a tiled
+// load moves the same 128 x 64 tile with far fewer requests than the im2col mode's per-pixel walk.
+static bool pointwise(const pb_op_params* p) {
+    return p->R == 1 && p->S == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_h == 0 && p->pad_w == 0;
+}
+
 static int make_xmap(const pb_op_params* p, CUtensorMap* out) {
+    if (pointwise(p)) {
+        EncodeTiledFn enc2 = encode_fn();
+        PB_REQUIRE(enc2 != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+        PB_REQUIRE(((uintptr_t)p->x & 15) == 0, "conv_umma: activations must be 16-byte aligned");
+        const cuuint64_t dims2[2] = {(cuuint64_t)p->Cs, (cuuint64_t)p->H * p->W};
+        const cuuint64_t strides2[1] = {(cuuint64_t)p->Cs * 2};
+        const cuuint32_t box2[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+        const cuuint32_t estr2[2] = {1, 1};
+        const CUresult r2 = enc2(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p->x), dims2, strides2, box2, estr2,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r2 != CUDA_SUCCESS) {
+            set_error("cuTensorMapEncodeTiled (activations) failed with CUresult %d (C %d, %d pixels)", (int)r2, p->Cs, p->H * p->W);
+            return PB_ERR_CUDA;
+        }
+        return PB_OK;
+    }
     EncodeIm2colFn enc = encode_im2col_fn();
     PB_REQUIRE(enc != nullptr, "cuTensorMapEncodeIm2col is not available from this driver");
     PB_REQUIRE(((uintptr_t)p->x & 15) == 0, "conv_umma: activations must be 16-byte aligned");
@@ -1005,7 +1021,7 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
     a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.P = p->P; a.Q = p->Q; a.M = p->P * p->Q;
     a.K = p->K; a.Ks = p->Ks; a.out_c_off = p->out_c_off; a.res_Cs = p->res_Cs;
     a.R = p->R; a.S = p->S; a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w;
-    a.act = p->act; a.nkb = g.nkb; a.taps = p->R * p->S; a.Cp = g.Cp; a.BN = g.BN; a.idesc = g.idesc; a.tmem_cols = g.tmem_cols;
+    a.act = p->act; a.a_tiled = pointwise(p) ? 1 : 0; a.nkb = g.nkb; a.taps = p->R * p->S; a.Cp = g.Cp; a.BN = g.BN; a.idesc = g.idesc; a.tmem_cols = g.tmem_cols;
     a.b_stage_bytes = g.b_stage_bytes;
     a.splits = g.splits;
     a.kb_per_split = g.kb_per_split;
