@@ -208,7 +208,7 @@ PB_API void* pb_instance_input_dev(pb_instance* inst);   /* device staging buffe
 PB_API void* pb_instance_output_dev(pb_instance* inst);  /* device fp32 output */
 PB_API int pb_instance_launch_stage(pb_instance* inst, int stage, void* stream, uint32_t job_id, void* notifier);
 /* Stage groups: consecutive kernels that the job adapter presents to the scheduler as ONE stage
- * (default up to 12 kernels, PB_STAGE_GROUP=1 gives the reference's one-kernel-per-stage granularity).
+ * (default up to 24 kernels, PB_STAGE_GROUP=1 gives the reference's one-kernel-per-stage granularity).
  * A multi-kernel group is replayed as a CUDA graph - one driver call instead of one per kernel - and
  * only its last kernel reports block start/end on the notifier, so pb_model_group_info's block count
  * is that kernel's grid and its per-block resources are the group's largest footprint spread over
@@ -218,6 +218,14 @@ PB_API int pb_instance_launch_stage(pb_instance* inst, int stage, void* stream, 
 PB_API int pb_model_num_groups(const pb_model* m);
 PB_API int pb_model_group_info(const pb_model* m, int group, pb_launch_info* out);
 PB_API int pb_model_group_stages(const pb_model* m, int group, int* first_stage, int* num_stages);
+/* The group's launch plan: its stages in launch order (dependence depth first, then program order) and,
+ * for each, the index of the launch it belongs to.  Stages that share a launch index are independent
+ * tensor-core convolutions issued as ONE grid (the parallel branches of an Inception block, a ResNet
+ * shortcut beside the block's first convolution); the group's last launch is the one that notifies, so
+ * pb_model_group_info's block count is the sum of its stages' grids.  Returns the number of stages
+ * written (<= max_stages).  PB_FUSE_BRANCHES=0 at load time: program order, one stage per launch.
+ * No counterpart in the reference (it launches one TVM kernel at a time). */
+PB_API int pb_model_group_plan(const pb_model* m, int group, int32_t* stage_order, int32_t* launch_index, int max_stages);
 PB_API int pb_instance_launch_group(pb_instance* inst, int group, void* stream, uint32_t job_id, void* notifier,
                                     const void* io_in, void* io_out);
 /* Convenience for tests: H2D, every group, D2H on one stream, then synchronise. */

@@ -137,6 +137,7 @@ SIGNATURES = {
     "pb_model_num_groups": (_I, [_VP]),
     "pb_model_group_info": (_I, [_VP, _I, C.POINTER(LaunchInfo)]),
     "pb_model_group_stages": (_I, [_VP, _I, C.POINTER(_I), C.POINTER(_I)]),
+    "pb_model_group_plan": (_I, [_VP, _I, C.POINTER(C.c_int32), C.POINTER(C.c_int32), _I]),
     "pb_instance_launch_group": (_I, [_VP, _I, _VP, _U32, _VP, _VP, _VP]),
     "pb_instance_read_tensor": (_I, [_VP, _I, _VP, _SZ]),
     "pb_instance_time_stage": (_I, [_VP, _I, _I, _SZ, C.POINTER(C.c_double)]),

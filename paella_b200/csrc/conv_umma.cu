@@ -28,7 +28,9 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "launch_slot.cuh"
 #include "ops.h"
@@ -331,8 +333,8 @@ __device__ __forceinline__ void epilogue_columns(const ConvArgs& a, uint32_t lan
 // bias + residual + activation and bf16 stores into the output channel slice.  (Staging the bf16
 // tile in shared memory for row-contiguous stores was measured slower: the epilogue is bound by its
 // instruction count, not by the scattered 16-byte stores.)
-__device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, bool ok, int m0, int n0, const float* s_bias,
-                                     uint64_t* s_accum_p, volatile uint32_t* s_abort_p, uint32_t* s_is_last_p) {
+__device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, bool ok, int m0, int n0, uint32_t tile, uint32_t split,
+                                     const float* s_bias, uint64_t* s_accum_p, volatile uint32_t* s_abort_p, uint32_t* s_is_last_p) {
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int m = m0 + tid;
@@ -342,7 +344,6 @@ __device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, 
     if (tid == 0) PB_T(5);
     tcgen05_fence_after();
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
     // Partial tiles in the workspace are stored [BN/4][128 rows] x float4, so consecutive lanes
     // (= rows) touch consecutive 16-byte words.
     const size_t tile_floats = (size_t)kBM * a.BN;
@@ -350,7 +351,7 @@ __device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, 
     if (a.splits > 1) {
         // Park this CTA's partial tile; the CTA that arrives last on the tile's counter adds the
         // others to its own accumulators and runs the epilogue.
-        float4* mine = reinterpret_cast<float4*>(a.ws + ((size_t)tile * a.splits + blockIdx.z) * tile_floats) + tid;
+        float4* mine = reinterpret_cast<float4*>(a.ws + ((size_t)tile * a.splits + split) * tile_floats) + tid;
         if (ok) {
             for (int cb = 0; cb < a.BN; cb += 16) {
                 uint32_t v[16];
@@ -513,7 +514,7 @@ conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvAr
             for (int kb = (nkb > kLag ? nkb - kLag : 0); kb < nkb; ++kb) mbar_arrive(smem_u32(&s_full[kb % kStages]));
 
         // ===== epilogue: accumulator lane `tid` = tile row `tid` =====
-        epilogue(a, tmem_base, ok, m0, n0, s_bias, &s_accum, &s_abort, &s_is_last);
+        epilogue(a, tmem_base, ok, m0, n0, blockIdx.y * gridDim.x + blockIdx.x, blockIdx.z, s_bias, &s_accum, &s_abort, &s_is_last);
         if (tid == 0) PB_T(6);
     } else {
         // ===== MMA issuer: one thread =====
@@ -565,42 +566,31 @@ conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvAr
 // the MMAs.  Warps 0-3 only run the epilogue.  No thread computes an address in the main loop.
 constexpr int kThreadsTma = 192;
 
-template <int kStages>
-__global__ void __launch_bounds__(kThreadsTma, 3)
-conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const ConvArgs a,
-                     uint32_t job_id, FinishedBlockNotifier* nf) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[kStages];
-    __shared__ __align__(8) uint64_t s_empty[kStages];
-    __shared__ __align__(8) uint64_t s_accum;
-    __shared__ uint32_t s_tmem_base;
-    __shared__ volatile uint32_t s_abort;
-    __shared__ uint32_t s_is_last;
-    __shared__ __align__(16) float s_bias[128];
-
-    resolve_slot(job_id, nf);
-    if (nf) nf->start(job_id);
-    if (threadIdx.x == 0) PB_T(0);
-
+// One CTA's share of one convolution: output tile (bx, by) of a grid gx tiles wide, reduction
+// slice bz, `stages` pipeline buffers.  Shared by the single-convolution kernel and the grouped one.
+__device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const CUtensorMap* tmap_x, const ConvArgs& a, const int stages,
+                                              const int bx, const int by, const int bz, const int gx, uint8_t* smem_raw,
+                                              uint64_t* s_full, uint64_t* s_empty, uint64_t* s_accum, uint32_t* s_tmem_base,
+                                              volatile uint32_t* s_abort, uint32_t* s_is_last, float* s_bias) {
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t stage_bytes = (uint32_t)kATileBytes + a.b_stage_bytes;
 
-    const int m0 = blockIdx.x * kBM;
-    const int n0 = blockIdx.y * a.BN;
-    const int kb_begin = blockIdx.z * a.kb_per_split;
+    const int m0 = bx * kBM;
+    const int n0 = by * a.BN;
+    const int kb_begin = bz * a.kb_per_split;
     const int kb_end = min(a.nkb, kb_begin + a.kb_per_split);
     const int nkb = kb_end - kb_begin;
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);      // the producer's arrive.expect_tx
             mbar_init(smem_u32(&s_empty[s]), 1);     // tcgen05.commit
         }
-        mbar_init(smem_u32(&s_accum), 1);
-        s_abort = 0;
+        mbar_init(smem_u32(s_accum), 1);
+        *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 128) {
@@ -608,13 +598,13 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         s_bias[tid] = (a.bias && tid < a.BN && k < a.K) ? __ldg(a.bias + k) : 0.f;
     }
     if (warp == 5) {
-        tcgen05_alloc(smem_u32(&s_tmem_base), a.tmem_cols);
+        tcgen05_alloc(smem_u32(s_tmem_base), a.tmem_cols);
         tcgen05_relinquish();
     }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    const uint32_t tmem_base = s_tmem_base;
+    const uint32_t tmem_base = *s_tmem_base;
     if (threadIdx.x == 0) PB_T(1);
     // Everything above touched only this CTA's shared/tensor memory and constant weights (bias), so it
     // may overlap the previous kernel's tail.  Activations, the residual, the output and the split-K
@@ -623,7 +613,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
 
     if (warp < 4) {
         griddep_launch();      // the next kernel's blocks may be scheduled as SM resources free up
-        epilogue(a, tmem_base, true, m0, n0, s_bias, &s_accum, &s_abort, &s_is_last);
+        epilogue(a, tmem_base, true, m0, n0, (uint32_t)(by * gx + bx), (uint32_t)bz, s_bias, s_accum, s_abort, s_is_last);
         if (tid == 0) PB_T(6);
     } else if (warp == 4) {
         // ===== producer: one thread =====
@@ -635,24 +625,25 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             int tap = kb_begin / cpt;
             int chunk = kb_begin - tap * cpt;
             int r = tap / a.S, s = tap - r * a.S;
+            int st = 0;
+            uint32_t parity = 1u;                     // a fresh barrier passes a wait on the "previous" phase
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int st = kb % kStages;
-                const uint32_t use = (uint32_t)(kb / kStages);
-                ok = mbar_wait(smem_u32(&s_empty[st]), (use & 1u) ^ 1u, &s_abort, a.err_flag, 1u);
+                ok = mbar_wait(smem_u32(&s_empty[st]), parity, s_abort, a.err_flag, 1u);
                 if (!ok) break;
                 const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
                 const uint32_t bar = smem_u32(&s_full[st]);
                 mbar_arrive_expect_tx(bar, (uint32_t)kATileBytes + a.b_stage_bytes);
-                if (a.a_tiled) tma_load_2d(a_tile, &tmap_x, chunk * kBK, m0, bar);
-                else tma_load_im2col_4d(a_tile, &tmap_x, chunk * kBK, w0, h0, 0, (uint16_t)s, (uint16_t)r, bar);
-                tma_load_2d(a_tile + kATileBytes, &tmap_w, (kb_begin + kb) * kBK, n0, bar);
+                if (a.a_tiled) tma_load_2d(a_tile, tmap_x, chunk * kBK, m0, bar);
+                else tma_load_im2col_4d(a_tile, tmap_x, chunk * kBK, w0, h0, 0, (uint16_t)s, (uint16_t)r, bar);
+                tma_load_2d(a_tile + kATileBytes, tmap_w, (kb_begin + kb) * kBK, n0, bar);
                 if (kb == 0) PB_T(2);
                 PB_TK(kb, 0);
                 if (++chunk == cpt) {
                     chunk = 0;
                     if (++s == a.S) { s = 0; ++r; }
                 }
+                if (++st == stages) { st = 0; parity ^= 1u; }
             }
         }
         __syncwarp();
@@ -660,11 +651,11 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     } else {
         // ===== MMA issuer: one thread =====
         if (lane == 0) {
+            int st = 0;
+            uint32_t parity = 0u;
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int st = kb % kStages;
-                const uint32_t use = (uint32_t)(kb / kStages);
-                ok = mbar_wait(smem_u32(&s_full[st]), use & 1u, &s_abort, a.err_flag, 2u);
+                ok = mbar_wait(smem_u32(&s_full[st]), parity, s_abort, a.err_flag, 2u);
                 if (!ok) break;
                 if (kb == 0) PB_T(3);
                 PB_TK(kb, 1);
@@ -678,8 +669,9 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                 }
                 tcgen05_commit(smem_u32(&s_empty[st]));
                 PB_TK(kb, 2);
+                if (++st == stages) { st = 0; parity ^= 1u; }
             }
-            if (ok) tcgen05_commit(smem_u32(&s_accum));
+            if (ok) tcgen05_commit(smem_u32(s_accum));
             PB_T(4);
         }
         __syncwarp();
@@ -688,7 +680,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
 
     tcgen05_fence_before();
     __syncthreads();
-    if (s_abort) {
+    if (*s_abort) {
         const unsigned long long t0 = globaltimer_ns();
         for (uint32_t i = 0; i < (1u << 20); ++i) {
             if (globaltimer_ns() - t0 > 50000ull) break;
@@ -700,6 +692,72 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         tcgen05_dealloc(tmem_base, a.tmem_cols);
     }
     if (threadIdx.x == 0) PB_T(7);
+}
+
+__global__ void __launch_bounds__(kThreadsTma, 3)
+conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const ConvArgs a,
+                     int stages, uint32_t job_id, FinishedBlockNotifier* nf) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kMaxStages];
+    __shared__ __align__(8) uint64_t s_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t s_accum;
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ uint32_t s_is_last;
+    __shared__ __align__(16) float s_bias[128];
+
+    resolve_slot(job_id, nf);
+    if (nf) nf->start(job_id);
+    if (threadIdx.x == 0) PB_T(0);
+    conv_tile_tma(&tmap_w, &tmap_x, a, stages, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)gridDim.x, smem_raw, s_full,
+                  s_empty, &s_accum, &s_tmem_base, &s_abort, &s_is_last, s_bias);
+    if (nf) nf->end(job_id);
+}
+
+// Grouped launch: several independent convolutions (the parallel branches of an Inception block at the
+// same depth, a ResNet block's shortcut beside its first convolution) in ONE grid.  Kernel-level
+// concurrency on a GPU is capped by its hardware queues, and a batch-1 convolution rarely has more
+// than a dozen tiles, so running the branches side by side in one launch is what fills the SMs.
+// Block b belongs to the sub-problem i with first_block[i] <= b < first_block[i + 1]; the table with
+// each sub-problem's tensor maps and arguments lives in device memory, written once per instance.
+struct alignas(128) SubConv {
+    CUtensorMap tmap_w;
+    CUtensorMap tmap_x;
+    ConvArgs a;
+    uint32_t first_block, gx, gy, stages;
+};
+constexpr int kMaxSubConvs = 8;
+
+__global__ void __launch_bounds__(kThreadsTma, 3)
+conv_umma_multi_kernel(const SubConv* __restrict__ table, int n_sub, uint32_t job_id, FinishedBlockNotifier* nf) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kMaxStages];
+    __shared__ __align__(8) uint64_t s_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t s_accum;
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ uint32_t s_is_last;
+    __shared__ __align__(16) float s_bias[128];
+    __shared__ __align__(16) ConvArgs s_args;
+
+    resolve_slot(job_id, nf);
+    if (nf) nf->start(job_id);
+    if (threadIdx.x == 0) PB_T(0);
+
+    int sub = 0;
+    while (sub + 1 < n_sub && blockIdx.x >= table[sub + 1].first_block) ++sub;
+    const SubConv* sc = table + sub;
+    // the table is constant for the life of the instance: it may be read before griddepcontrol.wait
+    static_assert(sizeof(ConvArgs) % 4 == 0, "ConvArgs is copied word by word");
+    if (threadIdx.x < sizeof(ConvArgs) / 4)
+        reinterpret_cast<uint32_t*>(&s_args)[threadIdx.x] = reinterpret_cast<const uint32_t*>(&sc->a)[threadIdx.x];
+    __syncthreads();
+    const uint32_t local = blockIdx.x - sc->first_block;
+    const uint32_t gx = sc->gx, gy = sc->gy;
+    const uint32_t bx = local % gx, rest = local / gx;
+    const uint32_t by = rest % gy, bz = rest / gy;
+    conv_tile_tma(&sc->tmap_w, &sc->tmap_x, s_args, (int)sc->stages, (int)bx, (int)by, (int)bz, (int)gx, smem_raw, s_full, s_empty,
+                  &s_accum, &s_tmem_base, &s_abort, &s_is_last, s_bias);
     if (nf) nf->end(job_id);
 }
 
@@ -814,20 +872,24 @@ void drop_split(Geometry* g) {
 }
 
 const void* kernel_for(int stages, bool tma) {
-    if (tma) {
-        switch (stages) {
-            case 2: return (const void*)conv_umma_tma_kernel<2>;
-            case 3: return (const void*)conv_umma_tma_kernel<3>;
-            case 4: return (const void*)conv_umma_tma_kernel<4>;
-            case 6: return (const void*)conv_umma_tma_kernel<6>;
-            default: return (const void*)conv_umma_tma_kernel<8>;
-        }
-    }
+    if (tma) return (const void*)conv_umma_tma_kernel;
     switch (stages) {
         case 4: return (const void*)conv_umma_gather_kernel<4>;
         case 6: return (const void*)conv_umma_gather_kernel<6>;
         default: return (const void*)conv_umma_gather_kernel<8>;
     }
+}
+
+// Raises the dynamic shared-memory limit of every kernel of this file on the current device.
+cudaError_t raise_smem_limits() {
+    const void* kernels[] = {(const void*)conv_umma_tma_kernel, (const void*)conv_umma_multi_kernel,
+                             (const void*)conv_umma_gather_kernel<4>, (const void*)conv_umma_gather_kernel<6>,
+                             (const void*)conv_umma_gather_kernel<8>};
+    for (const void* k : kernels) {
+        const cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 }  // namespace
@@ -978,11 +1040,7 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
     static std::once_flag once[16];
     static cudaError_t attr_errs[16] = {};
     const int dev = plan->device >= 0 && plan->device < 16 ? plan->device : 0;
-    std::call_once(once[dev], [dev] {
-        for (int tma = 0; tma < 2; ++tma)
-            for (int st = tma ? 2 : 4; st <= kMaxStages && attr_errs[dev] == cudaSuccess; st += (st < 4 ? 1 : 2))
-                attr_errs[dev] = cudaFuncSetAttribute(kernel_for(st, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
-    });
+    std::call_once(once[dev], [dev] { attr_errs[dev] = raise_smem_limits(); });
     const cudaError_t attr_err = attr_errs[dev];
     if (attr_err != cudaSuccess) { delete plan; return cuda_fail(attr_err, "cudaFuncSetAttribute(conv_umma)", __FILE__, __LINE__); }
     *out = plan;
@@ -991,27 +1049,10 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
 
 void conv_umma_plan_destroy(ConvUmmaPlan* plan) { delete plan; }
 
-template <typename Kern>
-static cudaError_t launch_tma(Kern kern, dim3 grid, uint32_t smem, cudaStream_t st, bool pdl, const CUtensorMap& tw, const CUtensorMap& tx,
-                              const ConvArgs& a, uint32_t job_id, FinishedBlockNotifier* nf) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreadsTma);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, tw, tx, a, job_id, nf);
-}
-
-int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
-                             uint32_t job_id, void* notifier, uint32_t* err_flag, bool pdl) {
-    Geometry g = plan->g;
-    if (g.splits > 1 && (p->scratch == nullptr || p->scratch_bytes < g.scratch_bytes)) drop_split(&g);
-    ConvArgs a;
+// Kernel arguments of one convolution; `g` may have had its split dropped for lack of scratch.
+static int fill_args(const ConvUmmaPlan* plan, const Geometry& g, const pb_op_params* p, uint32_t* err_flag, ConvArgs* out) {
+    ConvArgs& a = *out;
+    memset(&a, 0, sizeof(a));
     a.x = static_cast<const __nv_bfloat16*>(p->x);
     a.residual = static_cast<const __nv_bfloat16*>(p->residual);
     a.bias = p->bias;
@@ -1027,6 +1068,31 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
     a.kb_per_split = g.kb_per_split;
     a.counters = g.splits > 1 ? static_cast<unsigned*>(p->scratch) : nullptr;
     a.ws = g.splits > 1 ? reinterpret_cast<float*>(static_cast<char*>(p->scratch) + kCounterBytes) : nullptr;
+    return PB_OK;
+}
+
+template <typename... Args>
+static cudaError_t launch_pdl(void (*kern)(Args...), dim3 grid, uint32_t smem, cudaStream_t st, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreadsTma);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
+                             uint32_t job_id, void* notifier, uint32_t* err_flag, bool pdl) {
+    Geometry g = plan->g;
+    if (g.splits > 1 && (p->scratch == nullptr || p->scratch_bytes < g.scratch_bytes)) drop_split(&g);
+    ConvArgs a;
+    const int frc = fill_args(plan, g, p, err_flag, &a);
+    if (frc != PB_OK) return frc;
     const dim3 grid((unsigned)g.m_tiles, (unsigned)g.n_tiles, (unsigned)g.splits);
     FinishedBlockNotifier* nf = static_cast<FinishedBlockNotifier*>(notifier);
     if (use_tma_a()) {
@@ -1036,14 +1102,7 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
             if (rc != PB_OK) return rc;
             xmap = &local;
         }
-        cudaError_t e;
-        switch (g.stages) {
-            case 2: e = launch_tma(conv_umma_tma_kernel<2>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
-            case 3: e = launch_tma(conv_umma_tma_kernel<3>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
-            case 4: e = launch_tma(conv_umma_tma_kernel<4>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
-            case 6: e = launch_tma(conv_umma_tma_kernel<6>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
-            default: e = launch_tma(conv_umma_tma_kernel<8>, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, job_id, nf); break;
-        }
+        const cudaError_t e = launch_pdl(conv_umma_tma_kernel, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, g.stages, job_id, nf);
         if (e != cudaSuccess) return cuda_fail(e, "launch of conv_umma_tma_kernel", __FILE__, __LINE__);
         return PB_OK;
     } else {
@@ -1054,6 +1113,74 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
         }
     }
     return launch_check("conv_umma");
+}
+
+// ---- grouped launch ----------------------------------------------------------------------------
+struct ConvUmmaMulti {
+    SubConv* table_dev = nullptr;
+    int n = 0;
+    unsigned total_blocks = 0;
+    uint32_t smem = 0;
+    uint32_t tmem_cols = 0;
+};
+
+bool conv_umma_multi_available() { return use_tma_a(); }
+
+int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, int n,
+                           ConvUmmaMulti** out) {
+    PB_REQUIRE(out && plans && xmaps && params && n >= 1 && n <= kMaxSubConvs, "conv_umma_multi_create: 1..%d convolutions", kMaxSubConvs);
+    PB_REQUIRE(use_tma_a(), "conv_umma_multi_create: needs the TMA operand path");
+    std::vector<SubConv> table((size_t)n);
+    ConvUmmaMulti* m = new ConvUmmaMulti();
+    m->n = n;
+    for (int i = 0; i < n; ++i) {
+        PB_REQUIRE(plans[i] && xmaps[i] && params[i], "conv_umma_multi_create: NULL entry %d", i);
+        Geometry g = plans[i]->g;
+        if (g.splits > 1 && (params[i]->scratch == nullptr || params[i]->scratch_bytes < g.scratch_bytes)) drop_split(&g);
+        SubConv& sc = table[(size_t)i];
+        sc.tmap_w = plans[i]->tmap;
+        sc.tmap_x = xmaps[i]->map;
+        const int rc = fill_args(plans[i], g, params[i], nullptr, &sc.a);
+        if (rc != PB_OK) { delete m; return rc; }
+        sc.first_block = m->total_blocks;
+        sc.gx = (uint32_t)g.m_tiles;
+        sc.gy = (uint32_t)g.n_tiles;
+        sc.stages = (uint32_t)g.stages;
+        m->total_blocks += (unsigned)(g.m_tiles * g.n_tiles * g.splits);
+        m->smem = std::max(m->smem, g.smem_bytes);
+        m->tmem_cols = std::max(m->tmem_cols, g.tmem_cols);
+    }
+    cudaError_t e = cudaMalloc((void**)&m->table_dev, sizeof(SubConv) * (size_t)n);
+    if (e == cudaSuccess) e = cudaMemcpy(m->table_dev, table.data(), sizeof(SubConv) * (size_t)n, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { conv_umma_multi_destroy(m); return cuda_fail(e, "conv_umma_multi_create", __FILE__, __LINE__); }
+    *out = m;
+    return PB_OK;
+}
+
+void conv_umma_multi_destroy(ConvUmmaMulti* m) {
+    if (!m) return;
+    if (m->table_dev) cudaFree(m->table_dev);
+    delete m;
+}
+
+void conv_umma_multi_info(const ConvUmmaMulti* m, pb_launch_info* out) {
+    memset(out, 0, sizeof(*out));
+    out->num_blocks = m->total_blocks;
+    out->threads_per_block = kThreadsTma;
+    out->smem_per_block = m->smem;
+    cudaFuncAttributes at;
+    out->regs_per_thread = 112;
+    if (cudaFuncGetAttributes(&at, (const void*)conv_umma_multi_kernel) == cudaSuccess) out->regs_per_thread = (uint32_t)at.numRegs;
+    else cudaGetLastError();
+    out->tmem_cols_per_block = m->tmem_cols;
+    out->kind = PB_STAGE_CONV_UMMA;
+}
+
+int conv_umma_multi_launch(const ConvUmmaMulti* m, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl) {
+    const cudaError_t e = launch_pdl(conv_umma_multi_kernel, dim3(m->total_blocks), m->smem, st, pdl, (const SubConv*)m->table_dev, m->n,
+                                     job_id, static_cast<FinishedBlockNotifier*>(notifier));
+    if (e != cudaSuccess) return cuda_fail(e, "launch of conv_umma_multi_kernel", __FILE__, __LINE__);
+    return PB_OK;
 }
 
 int conv_umma_launch(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier) {
@@ -1104,9 +1231,7 @@ int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t jo
             void* fp = nullptr;
             PB_CUDA(cudaGetSymbolAddress(&sp, g_noalloc_scratch));
             PB_CUDA(cudaGetSymbolAddress(&fp, g_noalloc_err_flag));
-            for (int tma = 0; tma < 2; ++tma)
-                for (int stg = tma ? 2 : 4; stg <= kMaxStages; stg += (stg < 4 ? 1 : 2))
-                    PB_CUDA(cudaFuncSetAttribute(kernel_for(stg, tma != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048));
+            PB_CUDA(raise_smem_limits());
             nd.scratch = sp;
             nd.err_flag = static_cast<uint32_t*>(fp);
             nd.ready = true;

@@ -71,8 +71,11 @@ struct pb_model {
     bool mnist_fused = false;
     // Stage groups: what the job adapter hands to the scheduler as ONE stage.  A group of several
     // kernels is replayed as a CUDA graph (one driver call); only its last kernel notifies.
-    struct Group { int first, count; pb_launch_info info; };
+    // `launches`: the group's kernels in launch order (by dependence depth); an entry with several
+    // stages is ONE grouped launch of independent tensor-core convolutions.
+    struct Group { int first, count; pb_launch_info info; std::vector<std::vector<int>> launches; };
     std::vector<Group> groups;
+    bool fuse_branches = false;
     // fused MNIST weights (device)
     float *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr, *wd = nullptr, *bd = nullptr;
     std::vector<void*> allocs;
@@ -89,6 +92,7 @@ struct pb_instance {
     pb::LaunchSlot* slot_host = nullptr;    // pinned mirror, filled before each graph launch
     pb::LaunchSlot* slot_dev = nullptr;
     std::vector<cudaGraphExec_t> graphs;    // per group; NULL = single kernel, launched directly
+    std::vector<std::vector<pb::ConvUmmaMulti*>> multis;   // [group][launch]: descriptor table of a grouped conv launch
 };
 
 namespace {
@@ -134,25 +138,64 @@ void build_groups(pb_model* m) {
     int gs = 24;
     if (const char* e = getenv("PB_STAGE_GROUP")) gs = atoi(e);
     if (gs < 1) gs = 1;
+    // Independent tensor-core convolutions of equal dependence depth share one launch, unless the
+    // graphs are captured with parallel branches (PB_GRAPH_BRANCHES=1) or PB_FUSE_BRANCHES=0.
+    m->fuse_branches = env_flag("PB_FUSE_BRANCHES", true) && !env_flag("PB_GRAPH_BRANCHES", false) && pb::conv_umma_multi_available();
     const int n = (int)m->stages.size();
+    std::vector<std::vector<int>> writers(m->tensors.size());
     for (int first = 0; first < n; first += gs) {
         pb_model::Group g;
         g.first = first;
         g.count = first + gs <= n ? gs : n - first;
         memset(&g.info, 0, sizeof(g.info));
-        uint64_t thr = 0, smem = 0, regs = 0, tmem = 0;
+        // dependence depth inside the group
+        std::vector<int> level((size_t)g.count, 0);
+        for (auto& w : writers) w.clear();
         for (int i = first; i < first + g.count; ++i) {
-            const pb_launch_info& li = m->stages[i].info;
-            thr = std::max<uint64_t>(thr, (uint64_t)li.num_blocks * li.threads_per_block);
-            smem = std::max<uint64_t>(smem, (uint64_t)li.num_blocks * li.smem_per_block);
-            regs = std::max<uint64_t>(regs, (uint64_t)li.num_blocks * li.threads_per_block * li.regs_per_thread);
-            tmem = std::max<uint64_t>(tmem, (uint64_t)li.num_blocks * li.tmem_cols_per_block);
-            g.info.flops += li.flops;
-            g.info.bytes += li.bytes;
+            const Stage& st = m->stages[i];
+            int lv = 0;
+            for (int t : {st.in_tensor, st.res_tensor})
+                if (t >= 0)
+                    for (int w : writers[(size_t)t]) lv = std::max(lv, level[(size_t)(w - first)] + 1);
+            level[(size_t)(i - first)] = lv;
+            writers[(size_t)st.out_tensor].push_back(i);
         }
-        const pb_launch_info& last = m->stages[first + g.count - 1].info;
-        const uint64_t nb = last.num_blocks;
-        g.info.kind = g.count == 1 ? last.kind : 0xFFFFu;
+        std::vector<int> order((size_t)g.count);
+        for (int i = 0; i < g.count; ++i) order[(size_t)i] = first + i;
+        if (m->fuse_branches)
+            std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return level[(size_t)(a - first)] < level[(size_t)(b - first)]; });
+        for (int s : order) {
+            const Stage& st = m->stages[s];
+            const bool fusable = m->fuse_branches && st.kind == PB_STAGE_CONV_UMMA && !st.x_is_input && !st.y_is_output;
+            if (fusable && !g.launches.empty()) {
+                std::vector<int>& prev = g.launches.back();
+                const Stage& ps = m->stages[prev.back()];
+                const bool prev_fusable = ps.kind == PB_STAGE_CONV_UMMA && !ps.x_is_input && !ps.y_is_output;
+                if (prev_fusable && level[(size_t)(prev.back() - first)] == level[(size_t)(s - first)] && (int)prev.size() < 8) {
+                    prev.push_back(s);
+                    continue;
+                }
+            }
+            g.launches.push_back(std::vector<int>{s});
+        }
+        // footprint of each launch; the group declares its last launch's blocks (the only ones that notify)
+        uint64_t thr = 0, smem = 0, regs = 0, tmem = 0, nb = 0;
+        for (const std::vector<int>& l : g.launches) {
+            uint64_t lt = 0, ls = 0, lr = 0, lm = 0, lb = 0;
+            for (int i : l) {
+                const pb_launch_info& li = m->stages[i].info;
+                lb += li.num_blocks;
+                lt += (uint64_t)li.num_blocks * li.threads_per_block;
+                ls += (uint64_t)li.num_blocks * li.smem_per_block;
+                lr += (uint64_t)li.num_blocks * li.threads_per_block * li.regs_per_thread;
+                lm += (uint64_t)li.num_blocks * li.tmem_cols_per_block;
+                g.info.flops += li.flops;
+                g.info.bytes += li.bytes;
+            }
+            thr = std::max(thr, lt); smem = std::max(smem, ls); regs = std::max(regs, lr); tmem = std::max(tmem, lm);
+            nb = lb;
+        }
+        g.info.kind = g.count == 1 ? m->stages[first].info.kind : 0xFFFFu;
         g.info.num_blocks = (uint32_t)nb;
         g.info.threads_per_block = (uint32_t)pb::ceil_div<uint64_t>(thr, nb);
         g.info.smem_per_block = (uint32_t)pb::ceil_div<uint64_t>(smem, nb);
@@ -175,6 +218,60 @@ int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStr
         default:
             return pb::simple_op_launch(st.kind, p, stream, job_id, notifier, pdl);
     }
+}
+
+// Captures group `g` as ONE chain of launches in the group's planned order (dependence depth, then
+// program order): [slot copy] -> launch 0 -> launch 1 -> ...  A launch is either one kernel or a grouped
+// launch of independent tensor-core convolutions.  Every kernel after the first is a programmatic
+// dependent of its predecessor: it waits (griddepcontrol.wait) for the completion of the kernel right
+// before it, which itself waited for its own predecessor, so the chain order is a total order.
+// The last launch is the one that notifies.
+int capture_group_chain(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed) {
+    const pb_model* m = in->m;
+    const pb_model::Group& grp = m->groups[g];
+    // A single small kernel reads the launch slot straight from the pinned host mirror (one PCIe read,
+    // no copy node: about 1 us less host time per launch); larger groups get a device copy first.
+    const bool host_slot = grp.count == 1 && m->stages[grp.first].info.num_blocks <= 4;
+    void* const slot_ptr = host_slot ? (void*)in->slot_host : (void*)in->slot_dev;
+    PB_CUDA(cudaStreamBeginCapture(origin, cudaStreamCaptureModeRelaxed));
+    cudaError_t e = host_slot ? cudaSuccess
+                              : cudaMemcpyAsync(in->slot_dev, in->slot_host, sizeof(pb::LaunchSlot), cudaMemcpyHostToDevice, origin);
+    int rc = PB_OK;
+    bool after_kernel = false;
+    for (size_t li = 0; e == cudaSuccess && rc == PB_OK && li < grp.launches.size(); ++li) {
+        const std::vector<int>& l = grp.launches[li];
+        const bool is_last = li + 1 == grp.launches.size();
+        if (l.size() > 1) {
+            rc = pb::conv_umma_multi_launch(in->multis[(size_t)g][li], origin, is_last ? pb::kSlotNotify : 0u, is_last ? slot_ptr : nullptr,
+                                            pdl_allowed && after_kernel);
+        } else {
+            const int s = l[0];
+            const Stage& st = m->stages[s];
+            pb_op_params p = in->params[s];
+            const bool reads_input = s == 0;                       // the request's input buffer
+            const bool writes_output = st.y_is_output;             // the request's output buffer
+            if (reads_input) p.x = nullptr;                        // NULL = take it from the launch slot
+            if (writes_output) p.y = nullptr;
+            uint32_t jid = 0;
+            void* nfp = nullptr;
+            if (is_last) { jid = pb::kSlotNotify; nfp = slot_ptr; }
+            else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = slot_ptr; }
+            const bool pdl = pdl_allowed && after_kernel && st.kind != PB_STAGE_MNIST_FUSED;
+            rc = launch_stage_with(in, s, &p, origin, jid, nfp, nullptr, nullptr, pdl);
+        }
+        after_kernel = true;
+    }
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e2 = cudaStreamEndCapture(origin, &graph);
+    if (rc != PB_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) { if (graph) cudaGraphDestroy(graph); return pb::cuda_fail(e, "graph capture", __FILE__, __LINE__); }
+    if (e2 != cudaSuccess) return pb::cuda_fail(e2, "cudaStreamEndCapture", __FILE__, __LINE__);
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t e3 = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e3 != cudaSuccess) return pb::cuda_fail(e3, "cudaGraphInstantiate", __FILE__, __LINE__);
+    in->graphs[g] = exec;
+    return PB_OK;
 }
 
 // Captures group `g` of the instance into an executable graph.  The kernels are not chained in
@@ -595,12 +692,32 @@ int pb_instance_create(pb_model* m, pb_instance** out) {
         int rc = PB_OK;
         const bool pdl = env_flag("PB_PDL", true);
         const bool parallel = env_flag("PB_GRAPH_BRANCHES", false);
+        in->multis.resize(m->groups.size());
         for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g) {
-            if (m->groups[g].count <= 1 && !single_graphs) continue;
-            rc = capture_group(in, (int)g, cap, pdl, parallel);
-            if (rc != PB_OK && (pdl || parallel)) {   // a driver that cannot capture this: a plain chain
+            const pb_model::Group& grp = m->groups[g];
+            if (grp.count <= 1 && !single_graphs) continue;
+            if (parallel && !m->fuse_branches) {
+                rc = capture_group(in, (int)g, cap, pdl, true);
+                if (rc == PB_OK) continue;
+                cudaGetLastError();                   // a driver that cannot capture this: the chain below
+            }
+            // descriptor tables of the grouped launches
+            in->multis[g].assign(grp.launches.size(), nullptr);
+            rc = PB_OK;
+            for (size_t li = 0; rc == PB_OK && li < grp.launches.size(); ++li) {
+                const std::vector<int>& l = grp.launches[li];
+                if (l.size() < 2) continue;
+                std::vector<const pb::ConvUmmaPlan*> plans;
+                std::vector<const pb::ConvUmmaXMap*> xm;
+                std::vector<const pb_op_params*> pp;
+                for (int s : l) { plans.push_back(m->stages[s].plan); xm.push_back(in->xmaps[s]); pp.push_back(&in->params[s]); }
+                rc = pb::conv_umma_multi_create(plans.data(), xm.data(), pp.data(), (int)l.size(), &in->multis[g][li]);
+            }
+            if (rc != PB_OK) break;
+            rc = capture_group_chain(in, (int)g, cap, pdl);
+            if (rc != PB_OK && pdl) {                 // a driver that cannot capture programmatic edges: plain edges
                 cudaGetLastError();
-                rc = capture_group(in, (int)g, cap, false, false);
+                rc = capture_group_chain(in, (int)g, cap, false);
             }
         }
         cudaStreamDestroy(cap);
@@ -615,6 +732,7 @@ void pb_instance_destroy(pb_instance* in) {
     if (in->m) cudaSetDevice(in->m->device);
     for (pb::ConvUmmaXMap* x : in->xmaps) pb::conv_umma_xmap_destroy(x);
     for (cudaGraphExec_t g : in->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto& v : in->multis) for (pb::ConvUmmaMulti* mu : v) pb::conv_umma_multi_destroy(mu);
     if (in->slot_host) cudaFreeHost(in->slot_host);
     if (in->slot_dev) cudaFree(in->slot_dev);
     if (in->arena) cudaFree(in->arena);
@@ -645,6 +763,20 @@ int pb_model_group_stages(const pb_model* m, int group, int* first, int* count) 
     if (first) *first = m->groups[group].first;
     if (count) *count = m->groups[group].count;
     return PB_OK;
+}
+
+int pb_model_group_plan(const pb_model* m, int group, int32_t* stage_order, int32_t* launch_index, int max_stages) {
+    PB_REQUIRE(m && stage_order && launch_index && group >= 0 && group < (int)m->groups.size(), "pb_model_group_plan: bad argument (group %d)", group);
+    int n = 0;
+    const pb_model::Group& g = m->groups[group];
+    for (size_t li = 0; li < g.launches.size(); ++li)
+        for (int s : g.launches[li]) {
+            if (n >= max_stages) return n;
+            stage_order[n] = s;
+            launch_index[n] = (int32_t)li;
+            ++n;
+        }
+    return n;
 }
 
 int pb_instance_launch_group(pb_instance* in, int group, void* stream, uint32_t job_id, void* notifier, const void* io_in,

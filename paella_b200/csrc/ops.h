@@ -52,6 +52,15 @@ void conv_umma_xmap_destroy(ConvUmmaXMap* m);
 // itself, after its set-up); only meaningful when the previous operation in `st` is a kernel.
 int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
                              uint32_t job_id, void* notifier, uint32_t* err_flag = nullptr, bool pdl = false);
+// Grouped launch: up to 8 independent convolutions (their plans, input descriptors and resolved
+// parameters) run as ONE grid; the table of descriptors is copied to device memory here.
+struct ConvUmmaMulti;
+bool conv_umma_multi_available();
+int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, int n,
+                           ConvUmmaMulti** out);
+void conv_umma_multi_destroy(ConvUmmaMulti* m);
+void conv_umma_multi_info(const ConvUmmaMulti* m, pb_launch_info* out);
+int conv_umma_multi_launch(const ConvUmmaMulti* m, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl);
 int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
 uint32_t* noalloc_error_flag_ptr(int device);   // NULL until the no-allocation path ran on the device
 

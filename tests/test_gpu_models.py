@@ -180,17 +180,29 @@ def test_stage_groups_replayed_as_graphs_give_the_same_bits(models_dir, model, p
     m = Model(os.path.join(models_dir, packer.pack_file_name(model)), precision)
     n_stages, n_groups = m.L.pb_model_num_stages(m.m), m.L.pb_model_num_groups(m.m)
     assert 1 <= n_groups <= n_stages and n_groups == -(-n_stages // 24)
-    first, count, covered = C.c_int(), C.c_int(), 0
+    first, count, covered, n_fused = C.c_int(), C.c_int(), 0, 0
     li = capi.LaunchInfo()
     for g in range(n_groups):
         capi.check(m.L.pb_model_group_stages(m.m, g, C.byref(first), C.byref(count)), "group stages")
         assert first.value == covered
         covered += count.value
         capi.check(m.L.pb_model_group_info(m.m, g, C.byref(li)), "group info")
-        last = capi.LaunchInfo()
-        m.L.pb_model_stage_info(m.m, first.value + count.value - 1, C.byref(last))
-        assert li.num_blocks == last.num_blocks        # only the last kernel of a group notifies
+        order, launch = (C.c_int32 * count.value)(), (C.c_int32 * count.value)()
+        assert m.L.pb_model_group_plan(m.m, g, order, launch, count.value) == count.value
+        assert sorted(order) == list(range(first.value, first.value + count.value))      # a permutation of the group
+        assert list(launch) == sorted(launch) and launch[0] == 0
+        n_fused += len(launch) - (launch[-1] + 1)
+        last_blocks = 0                                 # only the last launch of a group notifies
+        for s_idx, l_idx in zip(order, launch):
+            if l_idx == launch[-1]:
+                si = capi.LaunchInfo()
+                m.L.pb_model_stage_info(m.m, s_idx, C.byref(si))
+                assert len([x for x in launch if x == l_idx]) == 1 or si.kind == 2  # PB_STAGE_CONV_UMMA
+                last_blocks += si.num_blocks
+        assert li.num_blocks == last_blocks
     assert covered == n_stages
+    if model == "inception_v3":
+        assert n_fused >= 40        # the branches of every Inception block share launches
     for seed in (5, 6):
         x = make_input(model, seed)
         ref = m.run(x)
