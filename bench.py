@@ -273,6 +273,7 @@ def main():
     ap.add_argument("--iat-us", type=float, default=0.0, help="open loop: mean inter-arrival per replica in us (Poisson); 0 = closed loop")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-roofline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the open-loop Poisson rate sweep of the mix")
     ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
     ap.add_argument("--only-roofline", default=None, metavar="SUBSTR",
                     help="skip the serving legs; time only the Inception-v3 stages whose name contains SUBSTR "
@@ -432,6 +433,22 @@ def main():
 
     if args.workload in ("mix", "mobilenet_resnet50") and not dist:
         line["fairness"] = fairness_leg(L, capi, devices[0], MIX, r_e2e)
+    if args.workload == "mix" and not dist and args.iat_us <= 0 and not args.no_sweep:
+        # Open loop: Poisson arrivals at fractions of the closed-loop rate, through host buffers; the highest
+        # offered rate whose p99s stay inside the SLO is the "requests/s at p99 SLO" of an open system.
+        sweep, best = [], None
+        for frac in (0.5, 0.7, 0.8, 0.9):
+            rate = frac * e2e
+            r = run_load(L, capi, devices, args.batch, max(2, args.steps // 2), 1, False, args.concurrency, caps,
+                         iat_us=1e6 * len(devices) / rate, extra_kernels=args.extra_kernels, sched=args.sched, streams=args.streams, seed=7)
+            ok = r.per_type[1].p99_us <= slo["inception_v3_p99_ms"] * 1e3 and r.per_type[0].p99_us <= slo["mnist_p99_ms"] * 1e3
+            sweep.append({"offered_rps": round(rate), "achieved_rps": round(r.throughput_rps), "slo_met": bool(ok),
+                          "mnist_p50_p99_us": [round(r.per_type[0].p50_us), round(r.per_type[0].p99_us)],
+                          "inception_v3_p50_p99_us": [round(r.per_type[1].p50_us), round(r.per_type[1].p99_us)]})
+            if ok:
+                best = round(rate)
+        line["poisson_sweep"] = {"arrivals": "Poisson, exponential inter-arrival, latency = completion - scheduled arrival",
+                                 "points": sweep, "max_offered_rps_meeting_slo": best}
     if args.extras and not dist:
         line["extras"] = extras_leg(L, capi, devices[0])
     if n_gpus == 1 and not args.no_roofline and args.workload == "mix":

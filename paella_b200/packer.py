@@ -312,6 +312,11 @@ def resnet18(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
     return _resnet("resnet18", _basic_block, [2, 2, 2, 2], seed, precision, num_classes, **kw)
 
 
+def resnet34(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
+    """ResNet-34 v1 (basic blocks 3-4-6-3), batch-norm folded (jobs/tvm_resnet34 of the reference)."""
+    return _resnet("resnet34", _basic_block, [3, 4, 6, 3], seed, precision, num_classes, **kw)
+
+
 def resnet50(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
     """ResNet-50 v1.5 bottlenecks 3-4-6-3 (stride on the 3x3), batch-norm folded."""
     return _resnet("resnet50", _bottleneck, [3, 4, 6, 3], seed, precision, num_classes, **kw)
@@ -453,6 +458,7 @@ def inception_v3(seed=1234, precision=1, num_classes=1000, size=299, **kw) -> Gr
 MODELS = {
     "mnist": mnist_cnn,
     "resnet18": resnet18,
+    "resnet34": resnet34,
     "resnet50": resnet50,
     "mobilenet": mobilenet_v2,
     "inception_v3": inception_v3,

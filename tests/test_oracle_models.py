@@ -39,6 +39,7 @@ def _load_into_torch(model, g, bn_eps):
 
 CASES = [
     ("resnet18", lambda: torchvision.models.resnet18(weights=None), 1e-5, 224),
+    ("resnet34", lambda: torchvision.models.resnet34(weights=None), 1e-5, 224),
     ("resnet50", lambda: torchvision.models.resnet50(weights=None), 1e-5, 224),
     ("mobilenet", lambda: torchvision.models.mobilenet_v2(weights=None), 1e-5, 224),
     ("inception_v3", lambda: torchvision.models.inception_v3(weights=None, aux_logits=False,
