@@ -40,6 +40,7 @@ def lib():
         L.orc_conv2d.argtypes = [_f, _i, _i, _i, _f, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i]
         L.orc_dense.argtypes = [_f, _i, _f, _f, _i, _i, _f]
         L.orc_maxpool.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
+        L.orc_maxpool_pq.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
         L.orc_avgpool.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
         L.orc_gap.argtypes = [_f, _i, _i, _i, _f]
         L.orc_add.argtypes = [_f, _f, ctypes.c_long, _i, _f]
@@ -81,14 +82,26 @@ def dense(x, w, b=None, act=0):
     return y
 
 
-def maxpool(x, k, stride, pad=(0, 0), out=None, out_c_off=0):
+def pool_extent(n, k, stride, pad, ceil_mode):
+    """Output extent of a pooling window sweep; ceil mode drops a last window that would start in
+    the padding (torch.nn.MaxPool2d / ONNX MaxPool rule)."""
+    if not ceil_mode:
+        return (n + 2 * pad - k) // stride + 1
+    o = -((n + 2 * pad - k) // -stride) + 1
+    if (o - 1) * stride >= n + pad:
+        o -= 1
+    return o
+
+
+def maxpool(x, k, stride, pad=(0, 0), out=None, out_c_off=0, ceil_mode=False):
     c, h, w = x.shape
-    p = (h + 2 * pad[0] - k[0]) // stride[0] + 1
-    q = (w + 2 * pad[1] - k[1]) // stride[1] + 1
+    p = pool_extent(h, k[0], stride[0], pad[0], ceil_mode)
+    q = pool_extent(w, k[1], stride[1], pad[1], ceil_mode)
     if out is None:
         out = np.zeros((c, p, q), np.float32)
+    assert out.shape[1:] == (p, q)
     x = np.ascontiguousarray(x, np.float32)
-    lib().orc_maxpool(_p(x), c, h, w, k[0], k[1], stride[0], stride[1], pad[0], pad[1], _p(out), out.shape[0], out_c_off)
+    lib().orc_maxpool_pq(_p(x), c, h, w, k[0], k[1], stride[0], stride[1], pad[0], pad[1], p, q, _p(out), out.shape[0], out_c_off)
     return out
 
 
@@ -177,7 +190,7 @@ def run(pack: Pack, x: np.ndarray, emulate_bf16: bool = False, keep_all: bool = 
             b = np.ascontiguousarray(W[boff: boff + cout])
             bufs[out][:] = dense(xin, w, b, act).reshape(oc, oh, ow)
         elif typ == OP_MAXPOOL:
-            maxpool(xin, (r, s), (sh, sw), (ph, pw), bufs[out], ooff)
+            maxpool(xin, (r, s), (sh, sw), (ph, pw), bufs[out], ooff, ceil_mode=bool(flags & 4))
         elif typ == OP_AVGPOOL:
             avgpool(xin, (r, s), (sh, sw), (ph, pw), bool(flags & 1), bufs[out], ooff)
         elif typ == OP_GAP:

@@ -38,6 +38,7 @@ NONE = 0xFFFFFFFF
 OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX = 1, 2, 3, 4, 5, 6, 7
 ACT_NONE, ACT_RELU, ACT_RELU6 = 0, 1, 2
 FLAG_COUNT_INCLUDE_PAD = 1
+FLAG_CEIL_MODE = 4          # informational: the output tensor's extent already says it
 
 OP_FIELDS = ("type", "in0", "in1", "out", "rsv0", "out_c_off", "cin", "cout", "r", "s",
              "stride_h", "stride_w", "pad_h", "pad_w", "groups", "act", "flags", "rsv1",
@@ -72,6 +73,17 @@ class Op:
             self.cout, self.r, self.s, self.stride_h, self.stride_w, self.pad_h, self.pad_w,
             self.groups, self.act, self.flags, 0, self.w_off & 0xFFFFFFFF, self.w_off >> 32,
             self.b_off & 0xFFFFFFFF, self.b_off >> 32, 0, 0)
+
+
+def _pool_extent(n, k, stride, pad, ceil_mode):
+    """Output extent of a pooling sweep; in ceil mode the last window may hang over the edge but must
+    start inside the input or its left/top padding (ONNX MaxPool ceil_mode / torch MaxPool2d rule)."""
+    if not ceil_mode:
+        return (n + 2 * pad - k) // stride + 1
+    o = -((n + 2 * pad - k) // -stride) + 1
+    if (o - 1) * stride >= n + pad:
+        o -= 1
+    return o
 
 
 def _pair(v):
@@ -165,17 +177,19 @@ class Graph:
         r, s = _pair(k)
         sh, sw = _pair(stride)
         ph, pw = _pair(pad)
-        p = (h + 2 * ph - r) // sh + 1
-        q = (w + 2 * pw - s) // sw + 1
+        p = _pool_extent(h, r, sh, ph, bool(flags & FLAG_CEIL_MODE))
+        q = _pool_extent(w, s, sw, pw, bool(flags & FLAG_CEIL_MODE))
         if out is None:
             out = self.tensor(c, p, q)
+        else:
+            assert self.shape(out)[1:] == (p, q), (name, self.shape(out), p, q)
         self.ops.append(Op(typ, x, out, out_c_off=out_c_off, cin=c, cout=c, r=r, s=s,
                            stride_h=sh, stride_w=sw, pad_h=ph, pad_w=pw, flags=flags, name=name))
         self.output = out
         return out
 
-    def maxpool(self, x, k, stride, pad=0, out=None, out_c_off=0, name=""):
-        return self._pool(OP_MAXPOOL, x, k, stride, pad, out, out_c_off, 0, name)
+    def maxpool(self, x, k, stride, pad=0, out=None, out_c_off=0, name="", ceil_mode=False):
+        return self._pool(OP_MAXPOOL, x, k, stride, pad, out, out_c_off, FLAG_CEIL_MODE if ceil_mode else 0, name)
 
     def avgpool(self, x, k, stride, pad=0, count_include_pad=True, out=None, out_c_off=0, name=""):
         return self._pool(OP_AVGPOOL, x, k, stride, pad, out, out_c_off,
@@ -455,6 +469,78 @@ def inception_v3(seed=1234, precision=1, num_classes=1000, size=299, **kw) -> Gr
     return g
 
 
+def squeezenet1_1(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
+    """SqueezeNet 1.1 (jobs/tvm_squeezenet1_1 of the reference): fire modules, ceil-mode max pooling,
+    convolutional classifier + global average pool.  Convolutions carry biases (no batch-norm)."""
+    g = Graph("squeezenet1_1", (3, 224, 224), seed, precision, **kw)
+
+    def fire(x, squeeze, e1, e3, n):
+        _, h, w = g.shape(x)
+        y = g.conv(x, squeeze, 1, name=n + ".squeeze")
+        out = g.tensor(e1 + e3, h, w)
+        g.conv(y, e1, 1, name=n + ".expand1x1", out=out, out_c_off=0)
+        g.conv(y, e3, 3, 1, 1, name=n + ".expand3x3", out=out, out_c_off=e1)
+        return out
+
+    x = g.conv(g.input, 64, 3, 2, 0, name="features.0")
+    x = g.maxpool(x, 3, 2, ceil_mode=True, name="features.2")
+    x = fire(x, 16, 64, 64, "features.3")
+    x = fire(x, 16, 64, 64, "features.4")
+    x = g.maxpool(x, 3, 2, ceil_mode=True, name="features.5")
+    x = fire(x, 32, 128, 128, "features.6")
+    x = fire(x, 32, 128, 128, "features.7")
+    x = g.maxpool(x, 3, 2, ceil_mode=True, name="features.8")
+    x = fire(x, 48, 192, 192, "features.9")
+    x = fire(x, 48, 192, 192, "features.10")
+    x = fire(x, 64, 256, 256, "features.11")
+    x = fire(x, 64, 256, 256, "features.12")
+    x = g.conv(x, num_classes, 1, name="classifier.1")
+    g.gap(x, name="classifier.3")
+    return g
+
+
+def googlenet(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
+    """GoogLeNet / Inception-v1 (jobs/tvm_googlenet of the reference) in torchvision's form: batch-norm
+    (eps 1e-3) folded, no auxiliary heads, 3x3 in the "5x5" branch, ceil-mode max pooling."""
+    eps = 1e-3
+    g = Graph("googlenet", (3, 224, 224), seed, precision, **kw)
+
+    def bc(x, cout, k, stride=1, pad=0, name="", out=None, off=0):
+        return g.conv(x, cout, k, stride, pad, bn_eps=eps, name=name + ".conv", out=out, out_c_off=off)
+
+    def inception(x, c1, c3r, c3, c5r, c5, cp, n):
+        _, h, w = g.shape(x)
+        out = g.tensor(c1 + c3 + c5 + cp, h, w)
+        bc(x, c1, 1, name=n + ".branch1", out=out, off=0)
+        y = bc(x, c3r, 1, name=n + ".branch2.0")
+        bc(y, c3, 3, 1, 1, n + ".branch2.1", out=out, off=c1)
+        y = bc(x, c5r, 1, name=n + ".branch3.0")
+        bc(y, c5, 3, 1, 1, n + ".branch3.1", out=out, off=c1 + c3)
+        y = g.maxpool(x, 3, 1, 1, ceil_mode=True, name=n + ".branch4.0")
+        bc(y, cp, 1, name=n + ".branch4.1", out=out, off=c1 + c3 + c5)
+        return out
+
+    x = bc(g.input, 64, 7, 2, 3, "conv1")
+    x = g.maxpool(x, 3, 2, ceil_mode=True, name="maxpool1")
+    x = bc(x, 64, 1, name="conv2")
+    x = bc(x, 192, 3, 1, 1, "conv3")
+    x = g.maxpool(x, 3, 2, ceil_mode=True, name="maxpool2")
+    x = inception(x, 64, 96, 128, 16, 32, 32, "inception3a")
+    x = inception(x, 128, 128, 192, 32, 96, 64, "inception3b")
+    x = g.maxpool(x, 3, 2, ceil_mode=True, name="maxpool3")
+    x = inception(x, 192, 96, 208, 16, 48, 64, "inception4a")
+    x = inception(x, 160, 112, 224, 24, 64, 64, "inception4b")
+    x = inception(x, 128, 128, 256, 24, 64, 64, "inception4c")
+    x = inception(x, 112, 144, 288, 32, 64, 64, "inception4d")
+    x = inception(x, 256, 160, 320, 32, 128, 128, "inception4e")
+    x = g.maxpool(x, 2, 2, ceil_mode=True, name="maxpool4")
+    x = inception(x, 256, 160, 320, 32, 128, 128, "inception5a")
+    x = inception(x, 384, 192, 384, 48, 128, 128, "inception5b")
+    x = g.gap(x, name="avgpool")
+    g.dense(x, num_classes, name="fc")
+    return g
+
+
 MODELS = {
     "mnist": mnist_cnn,
     "resnet18": resnet18,
@@ -462,6 +548,8 @@ MODELS = {
     "resnet50": resnet50,
     "mobilenet": mobilenet_v2,
     "inception_v3": inception_v3,
+    "squeezenet1_1": squeezenet1_1,
+    "googlenet": googlenet,
 }
 
 

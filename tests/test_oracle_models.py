@@ -22,8 +22,11 @@ def _load_into_torch(model, g, bn_eps):
             assert isinstance(m, nn.Conv2d), name
             w = pack.weights[woff: woff + cout * (cin // groups) * r * s].reshape(cout, cin // groups, r, s)
             with torch.no_grad():
-                m.weight.copy_(torch.from_numpy(w * np.float32(scale)))
-                assert m.bias is None
+                if m.bias is None:           # conv + batch-norm: the pack holds the folded weight
+                    m.weight.copy_(torch.from_numpy(w * np.float32(scale)))
+                else:                        # plain biased convolution
+                    m.weight.copy_(torch.from_numpy(w))
+                    m.bias.copy_(torch.from_numpy(pack.weights[boff: boff + cout]))
         elif typ == og.OP_DENSE:
             m = mods[name]
             assert isinstance(m, nn.Linear), name
@@ -42,6 +45,8 @@ CASES = [
     ("resnet34", lambda: torchvision.models.resnet34(weights=None), 1e-5, 224),
     ("resnet50", lambda: torchvision.models.resnet50(weights=None), 1e-5, 224),
     ("mobilenet", lambda: torchvision.models.mobilenet_v2(weights=None), 1e-5, 224),
+    ("squeezenet1_1", lambda: torchvision.models.squeezenet1_1(weights=None), 0.0, 224),
+    ("googlenet", lambda: torchvision.models.googlenet(weights=None, aux_logits=False, init_weights=False), 1e-3, 224),
     ("inception_v3", lambda: torchvision.models.inception_v3(weights=None, aux_logits=False,
                                                               transform_input=False, init_weights=False), 1e-3, 299),
 ]
@@ -49,7 +54,8 @@ CASES = [
 
 @pytest.mark.parametrize("name,ctor,eps,size", CASES, ids=[c[0] for c in CASES])
 def test_pack_matches_torchvision(oracle_lib, name, ctor, eps, size):
-    g = packer.MODELS[name](seed=1234)
+    kw = {"bias_std": 0.1} if name == "squeezenet1_1" else {}      # the one model whose convolutions carry biases
+    g = packer.MODELS[name](seed=1234, **kw)
     model = ctor().eval()
     pack = _load_into_torch(model, g, eps)
     x = np.random.default_rng(5).standard_normal((3, size, size), dtype=np.float32)

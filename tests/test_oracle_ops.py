@@ -70,6 +70,18 @@ def test_pools_match_torch(oracle_lib, k, s, p, hw):
         np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("k,s,p,hw", [(3, 2, 0, 111), (3, 2, 0, 112), (3, 2, 0, 13), (2, 2, 0, 14), (2, 2, 0, 7), (3, 1, 1, 14), (3, 2, 1, 8)])
+def test_ceil_mode_maxpool_matches_torch(oracle_lib, k, s, p, hw):
+    """SqueezeNet / GoogLeNet pooling: the last window may hang over the bottom/right edge."""
+    x = RNG.standard_normal((4, hw, hw), dtype=np.float32)
+    got = og.maxpool(x, (k, k), (s, s), (p, p), ceil_mode=True)
+    ref = F.max_pool2d(_t(x)[None], k, s, p, ceil_mode=True)[0].numpy()
+    assert got.shape == ref.shape
+    np.testing.assert_array_equal(got, ref)
+    from paella_b200 import packer
+    assert packer._pool_extent(hw, k, s, p, True) == ref.shape[1]
+
+
 def test_dense_gap_add_softmax(oracle_lib):
     x = RNG.standard_normal(300, dtype=np.float32)
     w = RNG.standard_normal((17, 300), dtype=np.float32)
