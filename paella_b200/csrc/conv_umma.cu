@@ -3,18 +3,22 @@
 //   D[m, n] = sum_k A[m, k] * B[n, k]     m = output pixel (p*Q + q), n = output channel,
 //                                          k = (r*S + s)*Cs + c   (filter tap, input channel)
 //
-// A is never materialised: 128 producer threads gather it from the channels-last bf16
-// activation tensor with 16-byte cp.async copies (zero fill for padding and for the k tail)
-// straight into the 128-byte-swizzled K-major shared-memory layout that tcgen05.mma reads;
-// eight consecutive lanes fetch one 128-byte row, so a warp-wide copy touches four full lines.
-// B (packed weights [Kout_pad][Kdim_pad]) arrives by TMA (cp.async.bulk.tensor.2d, 128B
-// swizzle, no multicast).  One elected thread issues tcgen05.mma (M=128, N=BN, K=16, bf16 x
-// bf16 -> fp32) with the accumulator in tensor memory; tcgen05.commit releases pipeline
-// stages and signals the epilogue, which reads TMEM with tcgen05.ld, adds bias and residual,
-// applies the activation and stores bf16 into the channel slice of the output tensor.
+// A is never materialised.  One thread per CTA issues, per 64-deep k-block, an im2col-mode TMA
+// (cp.async.bulk.tensor.4d...im2col: 128 consecutive output pixels x 64 channels of one filter tap,
+// padding and the ragged last tile zero-filled by the hardware; a plain tiled TMA when the layer is
+// pointwise) that lands A in the 128-byte-swizzled K-major shared-memory layout tcgen05.mma reads,
+// and a tiled TMA for B (packed weights [Kout_pad][Kdim_pad], no multicast).  One elected thread
+// issues tcgen05.mma (M=128, N=BN, K=16, bf16 x bf16 -> fp32) with the accumulator in tensor
+// memory; tcgen05.commit releases pipeline stages and signals the epilogue, which reads TMEM with
+// tcgen05.ld, adds bias and residual, applies the activation and stores bf16 into the channel
+// slice of the output tensor.
 //
-// CTA = 5 warps: warps 0-3 produce A (16 rows x 8 chunks per pass, 8 passes) and then run the epilogue
-// (thread t owns accumulator lane t); warp 4 allocates TMEM and issues the MMAs.
+// CTA = 6 warps: warps 0-3 run the epilogue (thread t owns accumulator lane t), warp 4 is the TMA
+// producer, warp 5 allocates TMEM and issues the MMAs.  Sized for three CTAs per SM.
+// Two entry points share the body (conv_tile_tma): conv_umma_tma_kernel runs one convolution,
+// conv_umma_multi_kernel runs several independent ones as one grid from a descriptor table in
+// device memory.  conv_umma_gather_kernel (PB_CONV_GATHER=1) is the earlier design, kept for
+// comparison: 128 producer threads gather A with 16-byte cp.async copies.
 //
 // Every wait is bounded: when a wait runs out the CTA raises a device-global error flag,
 // sets a shared abort flag that releases all other waits of the CTA, skips the epilogue,

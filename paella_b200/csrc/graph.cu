@@ -6,6 +6,8 @@
 //   tcgen05 implicit GEMM for dense convolutions in bf16, the vectorised depthwise / pool /
 //   dense / add / softmax kernels, direct convolution as the fp32 path.
 // An instance owns the activation buffers of one in-flight request.
+// Stages are handed to the scheduler in GROUPS; a group is replayed as one CUDA graph whose kernels
+// form a chain ordered by dependence depth, independent tensor-core convolutions sharing a launch.
 //
 // Replaces what the reference gets from tvm::runtime (Module::LoadFromFile, "run",
 // "get_input", "get_output": jobs/tvm_mnist/tvm_mnist.cpp:24-33); one stage here is one of
