@@ -813,6 +813,19 @@ bool use_tma_a() {
     return v;
 }
 
+// A split of the reduction must save at least this much (us) of a lone launch's modelled time.
+// Measured on Inception-v3 (us per request alone / GPU time per request with 32 / 64 in flight):
+// threshold 0 -> 727 / 52.7 / 52.6, 0.5 -> 709 / 46.8 / 45.0, 2 -> 706 / 45.7 / 43.3, never split ->
+// 721 / 45.4 / 42.0: the partial tiles cost load bandwidth that a busy GPU does not have to spare.
+// PB_CONV_SPLIT_GAIN_US overrides it (a large value disables splitting).
+double split_gain_us() {
+    static const double v = [] {
+        const char* e = getenv("PB_CONV_SPLIT_GAIN_US");
+        return e ? atof(e) : 2.0;
+    }();
+    return v;
+}
+
 struct Geometry {
     int cpt, Cp;                // 64-channel k-blocks per filter tap; Cp = cpt * 64
     int Kdim_pad, nkb;          // k = tap * Cp + c
@@ -847,7 +860,7 @@ Geometry geometry(const pb_op_params* p) {
     double best = g.nkb * per_kb;
     for (int sp = 2; sp <= 16 && tiles * sp <= 296 && sp * 4 <= g.nkb; ++sp) {
         const double t = ceil_div(g.nkb, sp) * per_kb + 1.5 + sp * per_partial;
-        if (t < best - 0.5) { best = t; want = sp; }
+        if (t < best - split_gain_us()) { best = t; want = sp; }
     }
     g.kb_per_split = ceil_div(g.nkb, want);
     g.splits = ceil_div(g.nkb, g.kb_per_split);

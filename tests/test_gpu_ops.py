@@ -139,6 +139,19 @@ def test_conv_umma_split_reduction(case):
     _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=(case[3] % 64 == 0), scratch=True)
 
 
+@pytest.mark.parametrize("case,residual", [((448, 8, 8, 384, 3, 3, 1, 1, 1, 1), False), ((512, 7, 7, 512, 3, 3, 1, 1, 1, 1), True),
+                                           ((1024, 14, 14, 256, 3, 3, 1, 1, 1, 1), True)])
+def test_conv_umma_long_reductions_do_split(case, residual):
+    """Long reductions on small maps (the last blocks of Inception-v3 / ResNet): these must split at the
+    library's default threshold, so the split path is exercised whatever the threshold is tuned to."""
+    L = capi.load()
+    p = _params(1, case[:3], case[3], case[1], case[2], case[3], case[4], case[5], 1, 1, 1, 1, 1, 1, 0, 0, case[0])
+    li = capi.LaunchInfo()
+    capi.check(L.pb_op_info(capi.STAGE_CONV_UMMA, C.byref(p), C.byref(li)), "pb_op_info")
+    assert li.scratch_bytes > 0, "this shape should split"
+    _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=residual, scratch=True)
+
+
 def test_conv_umma_epilogue_variants():
     # residual add + relu, relu6, no activation, no bias, write into a channel slice of a wider tensor
     _run_conv(capi.STAGE_CONV_UMMA, 1, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, act=1, residual=True)
