@@ -134,7 +134,8 @@ typedef enum pb_stage_kind {
     PB_STAGE_GAP = 7,
     PB_STAGE_ADD = 8,
     PB_STAGE_SOFTMAX = 9,
-    PB_STAGE_MNIST_FUSED = 10
+    PB_STAGE_MNIST_FUSED = 10,
+    PB_STAGE_AFFINE = 11     /* per-channel scale + bias (+ activation): a batch-norm that precedes its convolution (DenseNet) */
 } pb_stage_kind;
 
 typedef struct pb_op_params {

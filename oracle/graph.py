@@ -20,7 +20,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
-OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX = 1, 2, 3, 4, 5, 6, 7
+OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE = 1, 2, 3, 4, 5, 6, 7, 8
 NONE = 0xFFFFFFFF
 _f = ctypes.POINTER(ctypes.c_float)
 _i = ctypes.c_int
@@ -41,6 +41,7 @@ def lib():
         L.orc_dense.argtypes = [_f, _i, _f, _f, _i, _i, _f]
         L.orc_maxpool.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
         L.orc_maxpool_pq.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
+        L.orc_affine.argtypes = [_f, _i, ctypes.c_long, _f, _f, _i, _f]
         L.orc_avgpool.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
         L.orc_gap.argtypes = [_f, _i, _i, _i, _f]
         L.orc_add.argtypes = [_f, _f, ctypes.c_long, _i, _f]
@@ -115,6 +116,14 @@ def avgpool(x, k, stride, pad=(0, 0), count_include_pad=True, out=None, out_c_of
     lib().orc_avgpool(_p(x), c, h, w, k[0], k[1], stride[0], stride[1], pad[0], pad[1],
                       1 if count_include_pad else 0, _p(out), out.shape[0], out_c_off)
     return out
+
+
+def affine(x, scale, bias, act=1):
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.zeros_like(x)
+    lib().orc_affine(_p(x), x.shape[0], x.shape[1] * x.shape[2], _p(np.ascontiguousarray(scale, np.float32)),
+                     _p(np.ascontiguousarray(bias, np.float32)), act, _p(y))
+    return y
 
 
 def gap(x):
@@ -197,12 +206,14 @@ def run(pack: Pack, x: np.ndarray, emulate_bf16: bool = False, keep_all: bool = 
             bufs[out][:] = gap(xin).reshape(oc, 1, 1)
         elif typ == OP_ADD:
             bufs[out][:] = add(xin, bufs[in1], act)
+        elif typ == OP_AFFINE:
+            bufs[out][ooff: ooff + cin] = affine(xin[:cin], W[woff: woff + cin], W[boff: boff + cin], act)
         elif typ == OP_SOFTMAX:
             bufs[out][:] = softmax(xin).reshape(oc, oh, ow)
         else:
             raise ValueError(f"unknown op type {typ}")
         if emulate_bf16 and out != pack.output:
-            sl = bufs[out][ooff: ooff + cout] if typ in (OP_CONV, OP_MAXPOOL, OP_AVGPOOL) else bufs[out]
+            sl = bufs[out][ooff: ooff + cout] if typ in (OP_CONV, OP_MAXPOOL, OP_AVGPOOL, OP_AFFINE) else bufs[out]
             sl[...] = round_bf16(sl)
     y = bufs[pack.output].ravel().copy()
     return (y, bufs) if keep_all else y

@@ -28,7 +28,7 @@
 namespace {
 
 constexpr uint32_t kNone = 0xFFFFFFFFu;
-enum { OP_CONV = 1, OP_DENSE = 2, OP_MAXPOOL = 3, OP_AVGPOOL = 4, OP_GAP = 5, OP_ADD = 6, OP_SOFTMAX = 7 };
+enum { OP_CONV = 1, OP_DENSE = 2, OP_MAXPOOL = 3, OP_AVGPOOL = 4, OP_GAP = 5, OP_ADD = 6, OP_SOFTMAX = 7, OP_AFFINE = 8 };
 
 struct PackOp {
     uint32_t type, in0, in1, out, rsv0, out_c_off, cin, cout, r, s, stride_h, stride_w, pad_h, pad_w, groups, act, flags,
@@ -593,6 +593,15 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
             case OP_AVGPOOL: st.kind = PB_STAGE_AVGPOOL; p.K = tx.C; break;
             case OP_GAP: st.kind = PB_STAGE_GAP; p.K = tx.C; break;
             case OP_ADD: st.kind = PB_STAGE_ADD; break;
+            case OP_AFFINE: {
+                // reads the first `cin` channels of its input tensor (a prefix of a concatenation)
+                if (o.cin == 0 || (int)o.cin > tx.C || o.cout != o.cin) { pb::set_error("%s: affine op %u has bad channel counts", pack_path, i); PB_FAIL_LOAD(PB_ERR_INVALID); }
+                st.kind = PB_STAGE_AFFINE;
+                p.C = (int)o.cin; p.K = (int)o.cin;
+                PB_FAIL_LOAD(upload(m, W + w_off, (size_t)p.C * 4, &st.w_dev));
+                PB_FAIL_LOAD(upload(m, W + b_off, (size_t)p.C * 4, (void**)&st.bias_dev));
+                break;
+            }
             case OP_SOFTMAX: st.kind = PB_STAGE_SOFTMAX; p.C = tx.C * tx.H * tx.W; break;
             default:
                 pb::set_error("%s: unknown operator type %u", pack_path, o.type);

@@ -307,6 +307,30 @@ __global__ void __launch_bounds__(256) add_kernel(OpArgs a, uint32_t job_id, Fin
     PB_NOTIFY_END();
 }
 
+// ---- per-channel affine (+activation) over [HW][C] of a tensor with channel stride Cs ----------
+// y[pix][c] = act(x[pix][c] * scale[c] + bias[c]) for the first a.C channels: the folded batch-norm +
+// ReLU that DenseNet applies to the concatenated features BEFORE each convolution.
+template <typename T>
+__global__ void __launch_bounds__(256) affine_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    constexpr int N = Vec<T>::N;
+    const int cv = (a.C + N - 1) / N;
+    const size_t total = (size_t)a.H * a.W * cv;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) {
+        const int c0 = (int)(i % cv) * N;
+        const size_t pix = i / cv;
+        const Vec<T> u = Vec<T>::load(static_cast<const T*>(a.x) + pix * a.Cs + c0);
+        const float* __restrict__ sc = static_cast<const float*>(a.w);
+        Vec<T> o;
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+            o.v[j] = (c0 + j < a.C) ? act_fn(u.v[j] * __ldg(sc + c0 + j) + __ldg(a.bias + c0 + j), a.act) : 0.f;
+        o.store(static_cast<T*>(a.y) + pix * a.Ks + a.out_c_off + c0);
+    }
+    PB_NOTIFY_END();
+}
+
 // ---- softmax over a.C values, one block --------------------------------------------
 template <typename T, bool kInF32>
 __global__ void __launch_bounds__(256) softmax_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
@@ -518,6 +542,12 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
             out->regs_per_thread = f32 ? regs_of(add_kernel<float>) : regs_of(add_kernel<__nv_bfloat16>);
             out->bytes = es * 3 * in_elems;
             break;
+        case PB_STAGE_AFFINE:
+            out->num_blocks = blocks_for((size_t)p->H * p->W * pb::ceil_div(p->C, N));
+            out->regs_per_thread = f32 ? regs_of(affine_kernel<float>) : regs_of(affine_kernel<__nv_bfloat16>);
+            out->flops = 2ull * p->C * p->H * p->W;
+            out->bytes = es * 2ull * p->C * p->H * p->W + 8ull * p->C;
+            break;
         case PB_STAGE_SOFTMAX:
             out->num_blocks = 1;
             out->regs_per_thread = regs_of(softmax_kernel<float, true>);
@@ -593,6 +623,11 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
         case PB_STAGE_ADD:
             PB_REQUIRE(a.residual != nullptr, "add: second operand missing");
             PB_DISPATCH(add_kernel<float>, add_kernel<__nv_bfloat16>, a, job_id, nf);
+            break;
+        case PB_STAGE_AFFINE:
+            PB_REQUIRE(a.w != nullptr && a.bias != nullptr, "affine: scale and bias are required");
+            PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "affine: output slice must be vector aligned");
+            PB_DISPATCH(affine_kernel<float>, affine_kernel<__nv_bfloat16>, a, job_id, nf);
             break;
         case PB_STAGE_SOFTMAX:
             // flags bit2: the input is fp32 regardless of dtype

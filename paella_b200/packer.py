@@ -35,7 +35,7 @@ MAGIC = b"PB2PACK\0"
 VERSION = 1
 NONE = 0xFFFFFFFF
 
-OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX = 1, 2, 3, 4, 5, 6, 7
+OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE = 1, 2, 3, 4, 5, 6, 7, 8
 ACT_NONE, ACT_RELU, ACT_RELU6 = 0, 1, 2
 FLAG_COUNT_INCLUDE_PAD = 1
 FLAG_CEIL_MODE = 4          # informational: the output tensor's extent already says it
@@ -207,6 +207,22 @@ class Graph:
         assert self.shape(b) == (c, h, w)
         out = self.tensor(c, h, w)
         self.ops.append(Op(OP_ADD, a, out, in1=b, cin=c, cout=c, act=act, name=name))
+        self.output = out
+        return out
+
+    def affine(self, x, cin=None, act=ACT_RELU, bn_eps=1e-5, name=""):
+        """Batch-norm (inference form) + activation on the first `cin` channels of x, as a per-channel
+        scale and bias: scale = gamma / sqrt(var + eps), bias = beta - mean * scale with mean 0, var 1,
+        gamma ~ 1 + 0.1 N(0,1), beta ~ 0.1 N(0,1) from the seed."""
+        c, h, w = self.shape(x)
+        cin = c if cin is None else cin
+        assert 0 < cin <= c
+        out = self.tensor(cin, h, w)
+        gamma = (1.0 + 0.1 * self.rng.standard_normal(cin, dtype=np.float32)).astype(np.float32)
+        beta = (0.1 * self.rng.standard_normal(cin, dtype=np.float32)).astype(np.float32)
+        w_off = self._push(gamma / np.float32(np.sqrt(1.0 + bn_eps)))
+        b_off = self._push(beta)
+        self.ops.append(Op(OP_AFFINE, x, out, cin=cin, cout=cin, act=act, w_off=w_off, b_off=b_off, name=name))
         self.output = out
         return out
 
@@ -499,6 +515,42 @@ def squeezenet1_1(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
     return g
 
 
+def densenet121(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
+    """DenseNet-121 (jobs/tvm_densenet121 of the reference), growth 32, blocks 6-12-24-16.  Each dense
+    layer: norm1+relu1 on the concatenated features (a stand-alone affine operator: it precedes its
+    convolution and the input is shared, so it cannot be folded), conv1 1x1 with norm2+relu2 folded,
+    conv2 3x3 appended to the block's tensor."""
+    eps = 1e-5
+    growth, bn_size = 32, 4
+    g = Graph("densenet121", (3, 224, 224), seed, precision, **kw)
+    x = g.conv(g.input, 64, 7, 2, 3, bn_eps=eps, name="features.conv0")          # + norm0 + relu0
+    c = 64
+    feats = None
+    for bi, n_layers in enumerate([6, 12, 24, 16]):
+        _, h, w = g.shape(x)
+        if bi == 0:
+            h, w = _pool_extent(h, 3, 2, 1, False), _pool_extent(w, 3, 2, 1, False)
+            feats = g.tensor(c + growth * n_layers, h, w)
+            g.maxpool(x, 3, 2, 1, out=feats, out_c_off=0, name="features.pool0")
+        else:
+            feats = g.tensor(c + growth * n_layers, h // 2, w // 2)
+            g.avgpool(x, 2, 2, 0, True, out=feats, out_c_off=0, name=f"features.transition{bi}.pool")
+        for li in range(n_layers):
+            n = f"features.denseblock{bi + 1}.denselayer{li + 1}"
+            y = g.affine(feats, cin=c, bn_eps=eps, name=n + ".norm1")
+            y = g.conv(y, bn_size * growth, 1, bn_eps=eps, name=n + ".conv1")     # + norm2 + relu2
+            g.conv(y, growth, 3, 1, 1, act=ACT_NONE, out=feats, out_c_off=c, name=n + ".conv2")
+            c += growth
+        if bi < 3:
+            y = g.affine(feats, bn_eps=eps, name=f"features.transition{bi + 1}.norm")
+            x = g.conv(y, c // 2, 1, act=ACT_NONE, name=f"features.transition{bi + 1}.conv")
+            c //= 2
+    y = g.affine(feats, bn_eps=eps, name="features.norm5")
+    y = g.gap(y, name="avgpool")
+    g.dense(y, num_classes, name="classifier")
+    return g
+
+
 def googlenet(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
     """GoogLeNet / Inception-v1 (jobs/tvm_googlenet of the reference) in torchvision's form: batch-norm
     (eps 1e-3) folded, no auxiliary heads, 3x3 in the "5x5" branch, ceil-mode max pooling."""
@@ -550,6 +602,7 @@ MODELS = {
     "inception_v3": inception_v3,
     "squeezenet1_1": squeezenet1_1,
     "googlenet": googlenet,
+    "densenet121": densenet121,
 }
 
 

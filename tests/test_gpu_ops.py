@@ -240,6 +240,18 @@ def test_gap_dense_add_softmax(dtype):
     capi.check(L.pb_op_launch(capi.STAGE_ADD, C.byref(p), None, 0, None), "add")
     gu.sync()
     _assert_close(gu.from_device_cl(do, 64), og.add(a1, a2, 1), dtype)
+    # per-channel affine + relu on the first 40 of 64 channels, written at channel 8 of a 56-channel tensor
+    sc = (1 + 0.1 * RNG.standard_normal(40)).astype(np.float32)
+    bi = (0.1 * RNG.standard_normal(40)).astype(np.float32)
+    do, ks = gu.empty_cl(7, 7, 56, dtype, fill=3.0)
+    scd, bid = torch.from_numpy(sc).cuda(), torch.from_numpy(bi).cuda()
+    p = _params(dtype, (40, 7, 7), 40, 7, 7, ks, act=1, out_c_off=8, Cs=cs)
+    p.x, p.w, p.bias, p.y = d1.data_ptr(), scd.data_ptr(), bid.data_ptr(), do.data_ptr()
+    capi.check(L.pb_op_launch(capi.STAGE_AFFINE, C.byref(p), None, 0, None), "affine")
+    gu.sync()
+    got = gu.from_device_cl(do, 56)
+    _assert_close(got[8:48], og.affine(a1[:40], sc, bi, 1), dtype)
+    assert (got[:8] == 3.0).all() and (got[48:] == 3.0).all()       # neighbours untouched
     # softmax over 1000 logits to the fp32 output
     lg = rb(RNG.standard_normal(1000, dtype=np.float32) * 3)
     ld = torch.from_numpy(lg).cuda().to(torch.float32 if dtype == 0 else torch.bfloat16)

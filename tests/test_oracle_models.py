@@ -10,10 +10,13 @@ from oracle import graph as og
 from paella_b200 import packer
 
 
-def _load_into_torch(model, g, bn_eps):
+def _load_into_torch(model, g, bn_eps, folded=lambda name: True):
+    """Copies the pack's weights into the torch modules.  `folded(name)`: the convolution is followed by a
+    batch-norm that the pack folded into its weights (undone here, the torch model keeps its own)."""
     pack = og.Pack(g.to_bytes())
     mods = dict(model.named_modules())
     scale = np.sqrt(1.0 + bn_eps)
+    loaded_bn = set()
     for rec, name in zip(pack.ops, pack.names):
         typ, cin, cout, r, s, groups = rec[0], rec[6], rec[7], rec[8], rec[9], rec[14]
         woff, boff = rec[18] | (rec[19] << 32), rec[20] | (rec[21] << 32)
@@ -23,18 +26,26 @@ def _load_into_torch(model, g, bn_eps):
             w = pack.weights[woff: woff + cout * (cin // groups) * r * s].reshape(cout, cin // groups, r, s)
             with torch.no_grad():
                 if m.bias is None:           # conv + batch-norm: the pack holds the folded weight
-                    m.weight.copy_(torch.from_numpy(w * np.float32(scale)))
+                    m.weight.copy_(torch.from_numpy(w * np.float32(scale if folded(name) else 1.0)))
                 else:                        # plain biased convolution
                     m.weight.copy_(torch.from_numpy(w))
                     m.bias.copy_(torch.from_numpy(pack.weights[boff: boff + cout]))
+        elif typ == og.OP_AFFINE:        # a batch-norm kept as an operator: gamma = scale * sqrt(1 + eps), beta = bias
+            m = mods[name]
+            assert isinstance(m, nn.BatchNorm2d), name
+            with torch.no_grad():
+                m.weight.copy_(torch.from_numpy(pack.weights[woff: woff + cin] * np.float32(scale)))
+                m.bias.copy_(torch.from_numpy(pack.weights[boff: boff + cin]))
+                m.running_mean.zero_(); m.running_var.fill_(1.0)
+            loaded_bn.add(name)
         elif typ == og.OP_DENSE:
             m = mods[name]
             assert isinstance(m, nn.Linear), name
             with torch.no_grad():
                 m.weight.copy_(torch.from_numpy(pack.weights[woff: woff + cout * cin].reshape(cout, cin)))
                 m.bias.copy_(torch.from_numpy(pack.weights[boff: boff + cout]))
-    for m in model.modules():   # freshly initialised batch-norm statistics
-        if isinstance(m, nn.BatchNorm2d):
+    for name, m in model.named_modules():   # freshly initialised batch-norm statistics
+        if isinstance(m, nn.BatchNorm2d) and name not in loaded_bn:
             nn.init.ones_(m.weight); nn.init.zeros_(m.bias)
             m.running_mean.zero_(); m.running_var.fill_(1.0)
     return pack
@@ -46,6 +57,7 @@ CASES = [
     ("resnet50", lambda: torchvision.models.resnet50(weights=None), 1e-5, 224),
     ("mobilenet", lambda: torchvision.models.mobilenet_v2(weights=None), 1e-5, 224),
     ("squeezenet1_1", lambda: torchvision.models.squeezenet1_1(weights=None), 0.0, 224),
+    ("densenet121", lambda: torchvision.models.densenet121(weights=None), 1e-5, 224),
     ("googlenet", lambda: torchvision.models.googlenet(weights=None, aux_logits=False, init_weights=False), 1e-3, 224),
     ("inception_v3", lambda: torchvision.models.inception_v3(weights=None, aux_logits=False,
                                                               transform_input=False, init_weights=False), 1e-3, 299),
@@ -57,7 +69,9 @@ def test_pack_matches_torchvision(oracle_lib, name, ctor, eps, size):
     kw = {"bias_std": 0.1} if name == "squeezenet1_1" else {}      # the one model whose convolutions carry biases
     g = packer.MODELS[name](seed=1234, **kw)
     model = ctor().eval()
-    pack = _load_into_torch(model, g, eps)
+    # DenseNet: only conv0 and every conv1 are followed by a batch-norm; conv2 and the transition convs are not
+    folded = (lambda n: n.endswith("conv0") or n.endswith("conv1")) if name == "densenet121" else (lambda n: True)
+    pack = _load_into_torch(model, g, eps, folded)
     x = np.random.default_rng(5).standard_normal((3, size, size), dtype=np.float32)
     with torch.no_grad():
         ref = model(torch.from_numpy(x)[None])[0].numpy()

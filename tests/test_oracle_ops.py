@@ -82,6 +82,16 @@ def test_ceil_mode_maxpool_matches_torch(oracle_lib, k, s, p, hw):
     assert packer._pool_extent(hw, k, s, p, True) == ref.shape[1]
 
 
+def test_affine_matches_torch_batchnorm(oracle_lib):
+    x = RNG.standard_normal((24, 9, 7), dtype=np.float32)
+    gamma = (1 + 0.1 * RNG.standard_normal(24)).astype(np.float32)
+    beta = (0.1 * RNG.standard_normal(24)).astype(np.float32)
+    eps = 1e-5
+    ref = F.relu(F.batch_norm(_t(x)[None], torch.zeros(24), torch.ones(24), _t(gamma), _t(beta), False, 0.0, eps))[0].numpy()
+    got = og.affine(x, gamma / np.float32(np.sqrt(1 + eps)), beta, 1)
+    np.testing.assert_allclose(got, ref, rtol=1e-6, atol=1e-6)
+
+
 def test_dense_gap_add_softmax(oracle_lib):
     x = RNG.standard_normal(300, dtype=np.float32)
     w = RNG.standard_normal((17, 300), dtype=np.float32)
