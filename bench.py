@@ -236,6 +236,46 @@ def extras_leg(L, capi, device):
     return out
 
 
+def ipc_leg(capi, models_dir, rates=(50000, 100000, 150000)):
+    """The same mix through the PROCESS boundary: a llis_server process on GPU 0 and the llis_app_client load
+    generator (open loop, Poisson) talking to it over the shared-memory rings and the pinned request pool."""
+    bindir = os.path.join(os.path.dirname(capi.LIB_PATH), "bin")
+    name = f"pbbench{os.getpid()}"
+    env = dict(os.environ, LLIS_MODELS_DIR=models_dir, CUDA_DEVICE_MAX_CONNECTIONS="32")
+    srv = subprocess.Popen([os.path.join(bindir, "llis_server"), "--name", name, "--sched", "full3", "--num_streams", "128",
+                            "--extra_kernels", "64", "--gpu", "0"], env=env, stderr=subprocess.PIPE, text=True)
+    out = []
+    try:
+        t0 = time.time()
+        while not os.path.exists(f"/dev/shm/llis:channel:c2s:{name}"):
+            if srv.poll() is not None or time.time() - t0 > 60:
+                return {"error": "llis_server did not come up"}
+            time.sleep(0.05)
+        for rate in rates:
+            prefix = os.path.join(models_dir, f"ipc_{rate}")
+            n = 30000
+            r = subprocess.run([os.path.join(bindir, "llis_app_client"), "--server_name", name, "--iat", f"{1e6 / rate:.3f}",
+                                "--concurrency", "96", "--num_jobs", str(n), "--start_record_num", "3000", "--seed", "1", "--prefix", prefix,
+                                capi.plugin_path("tvm_mnist"), "0.9", "64", capi.plugin_path("tvm_inception_v3"), "0.1", "32"],
+                               capture_output=True, text=True, timeout=120, env=env)
+            if r.returncode != 0:
+                out.append({"offered_rps": rate, "error": r.stderr[-300:]})
+                continue
+            f = open(prefix + ".txt").read().strip().split(",")
+            # iat, jobs, elapsed_us, then mean,p50,p90,p95,p99,max,sd overall / MNIST / Inception-v3
+            out.append({"offered_rps": rate, "achieved_rps": round(n / (float(f[2]) * 1e-6)),
+                        "mnist_p50_p99_us": [round(float(f[11])), round(float(f[14]))],
+                        "inception_v3_p50_p99_us": [round(float(f[18])), round(float(f[21]))]})
+    finally:
+        if srv.poll() is None:
+            srv.terminate()
+            try:
+                srv.wait(10)
+            except subprocess.TimeoutExpired:
+                srv.kill()
+    return {"what": "llis_server process + llis_app_client process (open loop, Poisson), 9:1 MNIST : Inception-v3, one GPU", "points": out}
+
+
 def cpu_sample(graphs, n_mnist=9, n_inception=1, repeats=1):
     """Oracle (CPU fp32, OpenMP over all cores) on a bounded sample of the mix; returns req/s."""
     # torchrun pins OMP_NUM_THREADS=1 in its workers; the CPU leg is meant to use every host core
@@ -460,6 +500,8 @@ def main():
                                  "points": sweep, "max_offered_rps_meeting_slo": best}
     if args.extras and not dist:
         line["extras"] = extras_leg(L, capi, devices[0])
+        if args.workload == "mix":
+            line["extras"]["ipc"] = ipc_leg(capi, tmp.name)
     if n_gpus == 1 and not args.no_roofline and args.workload == "mix":
         roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters)
         # The same kernel while the GPU serves the whole mix: tensor-core convolution FLOPs retired per second of

@@ -26,6 +26,11 @@ class UnixDatagramSocket {
     // A sender on this socket addressed to `name` (does not own the descriptor).
     UnixDatagramSocket connect(const std::string& name);
     ssize_t write(const void* buf, size_t count);
+    // Non-blocking send that reports instead of throwing: bytes sent, or -errno (-EAGAIN / -ENOBUFS when
+    // the receiver's queue is full, -ECONNREFUSED / -ENOENT when nobody is bound to the name any more).
+    // Not in the reference, whose server blocks in sendto(); a blocked server and a client blocked on a
+    // full request ring would wait for each other.
+    ssize_t try_write(const void* buf, size_t count);
     ssize_t read(void* buf, size_t count);
     // As read(), but gives up after timeout_ms (returns 0).
     ssize_t read_timeout(void* buf, size_t count, int timeout_ms);

@@ -1,4 +1,5 @@
 // Client<->server IPC: shared-memory byte ring and abstract unix datagram socket.
+#include <cerrno>
 #include <llis/ipc/shm_channel.h>
 #include <llis/ipc/unix_datagram_socket.h>
 
@@ -191,6 +192,10 @@ ssize_t UnixDatagramSocket::write(const void* buf, size_t count) {
     const ssize_t n = sendto(socket_, buf, count, 0, reinterpret_cast<const sockaddr*>(&remote_addr_), sizeof(remote_addr_));
     if (n < 0) fail("sendto");
     return n;
+}
+ssize_t UnixDatagramSocket::try_write(const void* buf, size_t count) {
+    const ssize_t n = sendto(socket_, buf, count, MSG_DONTWAIT | MSG_NOSIGNAL, reinterpret_cast<const sockaddr*>(&remote_addr_), sizeof(remote_addr_));
+    return n >= 0 ? n : -(ssize_t)errno;
 }
 ssize_t UnixDatagramSocket::read(void* buf, size_t count) {
     const ssize_t n = ::read(socket_, buf, count);

@@ -7,7 +7,9 @@
 #include <sys/mman.h>
 #include <unistd.h>
 
+#include <cerrno>
 #include <cstdio>
+#include <cstring>
 #include <stdexcept>
 
 namespace llis {
@@ -17,14 +19,43 @@ IpcServer::IpcServer(std::string name, const pb_server_config& cfg) : name_(std:
     core_ = std::make_unique<pb_server>();
     if (core_->init(cfg) != PB_OK) throw std::runtime_error(pb_last_error());
     c2s_channel_.connect(ipc::c2s_channel_name(name_), c2s_channel_size);
-    core_->on_job_starts = [this](job::Job* job) {
-        const bool msg = true;
-        clients_[job->get_client_id()]->s2c_socket.write(&msg, sizeof(msg));
-    };
+    core_->on_job_starts = [this](job::Job* job) { wake(*clients_[job->get_client_id()]); };
     core_->on_job_ends = [this](job::Job* job) {
+        ClientConnection& c = *clients_[job->get_client_id()];
+        if (c.gone) return;             // nobody reads that ring any more
         void* remote = job->get_remote_ptr();
-        clients_[job->get_client_id()]->s2c_channel.write(remote);
+        c.s2c_channel.write(remote);
     };
+}
+
+// One wake-up datagram per finishing job.  The client's receive queue is short (net.unix.max_dgram_qlen,
+// typically 10): a send that does not fit is kept and retried from step(), never waited for - a server
+// blocked in sendto() and a client blocked writing the full request ring would deadlock.
+void IpcServer::wake(ClientConnection& c) {
+    if (c.gone) return;
+    if (c.pending_wakeups > 0) { ++c.pending_wakeups; return; }     // keep the order simple: queue behind the backlog
+    const bool msg = true;
+    const ssize_t n = c.s2c_socket.try_write(&msg, sizeof(msg));
+    if (n >= 0) return;
+    if (n == -EAGAIN || n == -EWOULDBLOCK || n == -ENOBUFS) { ++c.pending_wakeups; return; }
+    size_t id = 0;
+    while (id < clients_.size() && clients_[id].get() != &c) ++id;
+    fprintf(stderr, "llis_server: client %zu is gone (%s); dropping its notifications\n", id, strerror((int)-n));
+    c.gone = true;
+}
+
+void IpcServer::retry_wakeups() {
+    for (auto& cp : clients_) {
+        ClientConnection& c = *cp;
+        while (!c.gone && c.pending_wakeups > 0) {
+            const bool msg = true;
+            const ssize_t n = c.s2c_socket.try_write(&msg, sizeof(msg));
+            if (n >= 0) { --c.pending_wakeups; continue; }
+            if (n == -EAGAIN || n == -EWOULDBLOCK || n == -ENOBUFS) break;
+            c.gone = true;
+            c.pending_wakeups = 0;
+        }
+    }
 }
 
 IpcServer::~IpcServer() {
@@ -37,6 +68,7 @@ IpcServer::~IpcServer() {
 bool IpcServer::step() {
     if (c2s_channel_.can_read()) handle_c2s();
     if (core_->step(64) < 0) throw std::runtime_error(pb_last_error());
+    retry_wakeups();
     return running_;
 }
 

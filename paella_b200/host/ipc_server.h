@@ -32,7 +32,11 @@ class IpcServer {
         ipc::ShmChannel s2c_channel;
         ipc::UnixDatagramSocket s2c_socket;   // sender addressed to the client's socket
         bool in_use = false;
+        bool gone = false;              // its socket vanished: the process has exited
+        unsigned pending_wakeups = 0;   // datagrams that did not fit the client's receive queue yet
     };
+    void wake(ClientConnection& c);
+    void retry_wakeups();
     struct RegisteredJob {
         ClientId client_id = 0;
         std::string shm_name;

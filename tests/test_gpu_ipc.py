@@ -16,9 +16,13 @@ pytestmark = pytest.mark.gpu
 BIN = os.path.join(os.path.dirname(capi.LIB_PATH), "bin")
 
 
+_SERVERS = [0]
+
+
 @pytest.fixture()
 def server(models_dir):
-    name = f"pbsrv{os.getpid()}"
+    _SERVERS[0] += 1
+    name = f"pbsrv{os.getpid()}n{_SERVERS[0]}"      # a fresh name per server: a killed server leaves its rings in /dev/shm
     env = dict(os.environ, LLIS_MODELS_DIR=models_dir, CUDA_DEVICE_MAX_CONNECTIONS="32")
     p = subprocess.Popen([os.path.join(BIN, "llis_server"), "--name", name, "--sched", "full3", "--num_streams", "64", "--gpu", "0"],
                          env=env, stderr=subprocess.PIPE, text=True)
@@ -31,6 +35,12 @@ def server(models_dir):
     if p.poll() is None:
         p.terminate()
         p.wait(10)
+    for f in os.listdir("/dev/shm"):
+        if f.startswith("llis:") and f.endswith(name) or f":{name}:" in f:
+            try:
+                os.unlink(os.path.join("/dev/shm", f))
+            except OSError:
+                pass
 
 
 def test_requests_through_a_server_process(server):
@@ -90,3 +100,20 @@ def test_app_client_load_generator(server, tmp_path):
     thr = 2000 / (float(fields[2]) * 1e-6)
     assert 3000 < thr < 5500                          # open loop at 5000 req/s
     assert 0 < float(fields[4]) < 5000                # overall p50 latency (us)
+
+
+def test_bursts_and_a_second_client_on_the_same_server(server, tmp_path):
+    """More completions in flight than the client's datagram queue holds (the wake-ups must queue in the
+    server, not block it), then a second client process after the first has exited."""
+    name, proc = server
+    for run, (iat, conc) in enumerate([("25", "48"), ("25", "48")]):
+        prefix = str(tmp_path / f"burst{run}")
+        out = subprocess.run([os.path.join(BIN, "llis_app_client"), "--server_name", name, "--iat", iat, "--concurrency", conc,
+                              "--num_jobs", "6000", "--start_record_num", "500", "--seed", str(run + 1), "--prefix", prefix,
+                              capi.plugin_path("tvm_mnist"), "0.9", "40", capi.plugin_path("tvm_resnet18"), "0.1", "8"],
+                             capture_output=True, text=True, timeout=120, env=dict(os.environ))
+        assert out.returncode == 0, out.stderr
+        assert proc.poll() is None, "the server must survive a client that left"
+        fields = open(prefix + ".txt").read().strip().split(",")
+        assert int(fields[1]) == 6000
+        assert 6000 / (float(fields[2]) * 1e-6) > 15000          # offered 40k req/s
