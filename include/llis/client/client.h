@@ -104,6 +104,7 @@ class Client {
     ipc::ShmChannel c2s_channel_;
     ipc::ShmChannel s2c_channel_;
     ipc::UnixDatagramSocket s2c_socket_;
+    size_t entries_ahead_ = 0;   // ring entries consumed before their wake-up datagram arrived
     ClientId client_id_ = 0;
     std::mutex mtx_;
     std::vector<std::unique_ptr<JobInstanceRef>> job_instance_refs_;

@@ -139,20 +139,33 @@ void Client::release_job_instance_ref(JobInstanceRef* ref) {
     unused_job_instance_refs_.push_back(ref->get_id());
 }
 
+// One wake-up datagram and one ring entry per finished job (src/client/client.cpp:103-131 of the
+// reference: read the datagram, then the entry).  The datagram is only a hint - it is sent when the
+// job's last stage STARTS, and a server may deliver it late when this socket's short queue is full -
+// so an entry that is already in the ring is taken at once and the datagram it "owes" is swallowed
+// when it turns up.  Datagrams and entries stay paired one to one.
 JobInstanceRef* Client::wait() {
-    bool flag;
-    s2c_socket_.read(&flag, sizeof(flag));
-    JobInstanceRef* res = nullptr;
-    s2c_channel_.read(&res);
-    return res;
+    for (;;) {
+        JobInstanceRef* r = wait_timeout(1000);
+        if (r) return r;
+    }
 }
 
 JobInstanceRef* Client::wait_timeout(int timeout_ms) {
-    bool flag;
-    if (s2c_socket_.read_timeout(&flag, sizeof(flag), timeout_ms) <= 0) return nullptr;
-    JobInstanceRef* res = nullptr;
-    s2c_channel_.read(&res);
-    return res;
+    for (;;) {
+        if (s2c_channel_.can_read()) {
+            JobInstanceRef* res = nullptr;
+            s2c_channel_.read(&res);
+            ++entries_ahead_;
+            return res;
+        }
+        bool flag;
+        if (s2c_socket_.read_timeout(&flag, sizeof(flag), timeout_ms) <= 0) return nullptr;
+        if (entries_ahead_ > 0) { --entries_ahead_; continue; }      // pays for an entry taken earlier
+        JobInstanceRef* res = nullptr;                                // its entry follows shortly
+        s2c_channel_.read(&res);
+        return res;
+    }
 }
 
 void Client::kill_server() {

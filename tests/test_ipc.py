@@ -168,6 +168,20 @@ def test_client_library_wire_messages_against_a_played_server():
     sk.sendto(b"\x01", b"\0" + f"llis-socket-s2c-{server}-0".encode().ljust(107, b"\0"))
     _write(s2c, struct.pack("<Q", ptr))
     assert L.pb_client_wait(client, 2000, C.byref(got)) == 1 and got.value == inst.value
+    # --- a late wake-up: entries already in the ring are handed out at once; the datagrams they owe are
+    #     swallowed when they arrive, and the next datagram pairs with the next entry again
+    addr = b"\0" + f"llis-socket-s2c-{server}-0".encode().ljust(107, b"\0")
+    _write(s2c, struct.pack("<Q", 0x1111))
+    _write(s2c, struct.pack("<Q", 0x2222))
+    assert L.pb_client_wait(client, 0, C.byref(got)) == 1 and got.value == 0x1111
+    assert L.pb_client_wait(client, 0, C.byref(got)) == 1 and got.value == 0x2222
+    sk.sendto(b"\x01", addr)
+    sk.sendto(b"\x01", addr)                                  # the two owed datagrams
+    assert L.pb_client_wait(client, 50, C.byref(got)) == 0      # both swallowed, nothing to hand out
+    sk.sendto(b"\x01", addr)                                  # pre-notification of a third job ...
+    threading.Timer(0.2, lambda: _write(s2c, struct.pack("<Q", 0x3333))).start()   # ... whose entry follows
+    assert L.pb_client_wait(client, 2000, C.byref(got)) == 1 and got.value == 0x3333
+    assert L.pb_client_wait(client, 50, C.byref(got)) == 0
     # --- EXIT_CMD {u32 7}
     capi.check(L.pb_client_kill_server(client), "kill_server")
     assert struct.unpack("<I", _read(c2s, 4))[0] == 7
