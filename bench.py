@@ -236,7 +236,7 @@ def extras_leg(L, capi, device):
     return out
 
 
-def ipc_leg(capi, models_dir, rates=(50000, 100000, 150000)):
+def ipc_leg(capi, models_dir, rates=(50000, 75000, 100000)):
     """The same mix through the PROCESS boundary: a llis_server process on GPU 0 and the llis_app_client load
     generator (open loop, Poisson) talking to it over the shared-memory rings and the pinned request pool."""
     bindir = os.path.join(os.path.dirname(capi.LIB_PATH), "bin")

@@ -66,7 +66,8 @@ IpcServer::~IpcServer() {
 }
 
 bool IpcServer::step() {
-    if (c2s_channel_.can_read()) handle_c2s();
+    // drain what the clients have queued (bounded, so that notifications are still polled in between)
+    for (int i = 0; i < 32 && running_ && c2s_channel_.can_read(); ++i) handle_c2s();
     if (core_->step(64) < 0) throw std::runtime_error(pb_last_error());
     retry_wakeups();
     return running_;
