@@ -507,23 +507,62 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         return PB_OK;
     }
 
-    // ---- stage 0: NCHW fp32 -> channels-last ----
+    const bool use_umma = m->dtype == 1 && !env_flag("PB_DISABLE_UMMA", false);
+
+    // ---- patch-matrix lowering of the stem ----
+    // When the model input (<= 4 channels) feeds exactly one dense convolution and the tensor-core path is
+    // on, stage 0 writes that convolution's im2col rows instead of a channels-last image and the
+    // convolution runs pointwise over R*S*C channels (PB_PATCH_INPUT=0 turns this off).
+    int patch_op = -1, patch_tensor = -1;
+    if (use_umma && env_flag("PB_PATCH_INPUT", true) && m->tensors[t_in].C <= 4) {
+        int readers = 0, first = -1;
+        for (uint32_t i = 0; i < no; ++i) {
+            if (ops[i].in0 == t_in || ops[i].in1 == t_in) { ++readers; if (first < 0) first = (int)i; }
+        }
+        if (readers == 1 && ops[first].type == OP_CONV && ops[first].in0 == t_in && ops[first].in1 == kNone &&
+            (ops[first].groups == 0 || ops[first].groups == 1) && ops[first].r * ops[first].s > 1 && ops[first].out < nt &&
+            ops[first].cout % 8 == 0 && ops[first].out_c_off % 8 == 0 && (int)ops[first].out != m->t_out) {   // = what the tensor-core path needs
+            patch_op = first;
+            const PackOp& o = ops[first];
+            const TensorInfo& ty = m->tensors[o.out];
+            TensorInfo tp;
+            tp.C = (int)(o.r * o.s) * m->tensors[t_in].C; tp.H = ty.H; tp.W = ty.W;
+            tp.Cs = pb::round_up(tp.C, vec);
+            tp.bytes = pb::round_up((size_t)tp.H * tp.W * tp.Cs * es, (size_t)256);
+            tp.offset = m->arena_bytes;
+            m->arena_bytes += tp.bytes;
+            patch_tensor = (int)m->tensors.size();
+            m->tensors.push_back(tp);
+        }
+    }
+
+    // ---- stage 0: NCHW fp32 -> channels-last image, or -> patch matrix ----
     {
         Stage st{};
         st.kind = PB_STAGE_INPUT;
-        st.name = "input_layout";
         const TensorInfo& ti = m->tensors[t_in];
         memset(&st.p, 0, sizeof(st.p));
         st.p.dtype = m->dtype; st.p.C = ti.C; st.p.H = ti.H; st.p.W = ti.W; st.p.Cs = ti.C;
-        st.p.K = ti.C; st.p.P = ti.H; st.p.Q = ti.W; st.p.Ks = ti.Cs;
         st.x_is_input = true; st.y_is_output = false; st.has_res = false;
-        st.y_off = ti.offset;
-        st.out_tensor = (int)t_in;
+        if (patch_op >= 0) {
+            const PackOp& o = ops[patch_op];
+            const TensorInfo& tp = m->tensors[patch_tensor];
+            st.name = "input_patches";
+            st.p.K = tp.C; st.p.P = tp.H; st.p.Q = tp.W; st.p.Ks = tp.Cs;
+            st.p.R = (int)o.r; st.p.S = (int)o.s; st.p.stride_h = (int)o.stride_h; st.p.stride_w = (int)o.stride_w;
+            st.p.pad_h = (int)o.pad_h; st.p.pad_w = (int)o.pad_w;
+            st.y_off = tp.offset;
+            st.out_tensor = patch_tensor;
+        } else {
+            st.name = "input_layout";
+            st.p.K = ti.C; st.p.P = ti.H; st.p.Q = ti.W; st.p.Ks = ti.Cs;
+            st.y_off = ti.offset;
+            st.out_tensor = (int)t_in;
+        }
         PB_FAIL_LOAD(pb::simple_op_info(st.kind, &st.p, &st.info));
         m->stages.push_back(st);
     }
 
-    const bool use_umma = m->dtype == 1 && !env_flag("PB_DISABLE_UMMA", false);
     for (uint32_t i = 0; i < no; ++i) {
         const PackOp& o = ops[i];
         if (o.in0 >= nt || o.out >= nt || (o.in1 != kNone && o.in1 >= nt)) {
@@ -560,15 +599,37 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         switch (o.type) {
             case OP_CONV: {
                 if (st.y_is_output) { pb::set_error("a convolution cannot write the fp32 model output"); PB_FAIL_LOAD(PB_ERR_INVALID); }
+                std::vector<float> w_patch;
+                const float* w_src = W + w_off;
+                if ((int)i == patch_op) {
+                    // pointwise over the patch matrix: input channel k = (r*S + s)*C + c, weights reordered to match
+                    const TensorInfo& tp = m->tensors[patch_tensor];
+                    const int C0 = tx.C, R0 = (int)o.r, S0 = (int)o.s;
+                    w_patch.resize((size_t)p.K * tp.C);
+                    for (int k = 0; k < p.K; ++k)
+                        for (int c = 0; c < C0; ++c)
+                            for (int r = 0; r < R0; ++r)
+                                for (int s2 = 0; s2 < S0; ++s2)
+                                    w_patch[(size_t)k * tp.C + (size_t)(r * S0 + s2) * C0 + c] = w_src[(((size_t)k * C0 + c) * R0 + r) * S0 + s2];
+                    w_src = w_patch.data();
+                    p.C = tp.C; p.H = tp.H; p.W = tp.W; p.Cs = tp.Cs;
+                    p.R = p.S = 1; p.stride_h = p.stride_w = 1; p.pad_h = p.pad_w = 0;
+                    st.x_off = tp.offset;
+                    st.in_tensor = patch_tensor;
+                }
                 const bool dw = p.groups > 1 && p.groups == p.C && p.K == p.C;
                 if (dw) st.kind = PB_STAGE_DWCONV;
                 else if (use_umma && pb::conv_umma_supported(&p)) st.kind = PB_STAGE_CONV_UMMA;
                 else st.kind = PB_STAGE_CONV_SIMT;
                 // UMMA sees the padded channel stride as its input-channel count; SIMT uses the real one.
-                const int64_t nbytes = pb_op_pack_weights(st.kind, &p, W + w_off, nullptr);
+                if ((int)i == patch_op && st.kind != PB_STAGE_CONV_UMMA) {
+                    pb::set_error("%s: the stem convolution does not fit the tensor-core path after patch lowering", pack_path);
+                    PB_FAIL_LOAD(PB_ERR_INVALID);
+                }
+                const int64_t nbytes = pb_op_pack_weights(st.kind, &p, w_src, nullptr);
                 if (nbytes < 0) PB_FAIL_LOAD((int)nbytes);
                 packed.resize((size_t)nbytes);
-                pb_op_pack_weights(st.kind, &p, W + w_off, packed.data());
+                pb_op_pack_weights(st.kind, &p, w_src, packed.data());
                 PB_FAIL_LOAD(upload(m, packed.data(), packed.size(), &st.w_dev));
                 PB_FAIL_LOAD(upload(m, W + b_off, (size_t)p.K * 4, (void**)&st.bias_dev));
                 break;

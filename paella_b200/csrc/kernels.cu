@@ -96,6 +96,44 @@ __global__ void __launch_bounds__(256) input_transform_kernel(const float* x, T*
     PB_NOTIFY_END();
 }
 
+// ---- NCHW fp32 -> patch matrix [P*Q][Ks] ------------------------------------------------
+// The first convolution of an image model has 3 input channels: as an implicit GEMM every filter tap
+// would be padded to a 64-channel k-block (1/21 useful).  This kernel writes the im2col rows themselves,
+// y[(p, q)][k] with k = (r*S + s)*C + c (zero for k >= R*S*C and outside the image), so that the
+// convolution becomes a pointwise one over R*S*C "channels": 1 k-block instead of 9 for a 3x3 stem,
+// 3 instead of 49 for a 7x7 one.  One thread per (output pixel, 8 consecutive k).
+template <typename T>
+__global__ void __launch_bounds__(256) input_patch_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    const float* __restrict__ x = static_cast<const float*>(a.x);
+    if (!x && slot_) x = slot_->io_in;       // the request's input buffer, known only at dispatch
+    constexpr int N = Vec<T>::N;
+    const int kv = a.Ks / N;
+    const int total = a.P * a.Q * kv;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) {
+        const int k0 = (idx % kv) * N;
+        const int pix = idx / kv;
+        const int q = pix % a.Q, p = pix / a.Q;
+        const int taps_c = a.R * a.S * a.C;
+        Vec<T> o;
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            const int k = k0 + j;
+            float v = 0.f;
+            if (k < taps_c) {
+                const int tap = k / a.C, c = k - tap * a.C;
+                const int r = tap / a.S, s = tap - r * a.S;
+                const int ih = p * a.stride_h + r - a.pad_h, iw = q * a.stride_w + s - a.pad_w;
+                if (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W) v = __ldg(x + ((size_t)c * a.H + ih) * a.W + iw);
+            }
+            o.v[j] = v;
+        }
+        o.store(static_cast<T*>(a.y) + (size_t)pix * a.Ks + k0);
+    }
+    PB_NOTIFY_END();
+}
+
 // ---- direct convolution ------------------------------------------------------
 // One thread per (output pixel, output channel).  Weights [R][S][C/groups][K]: a warp
 // reads consecutive k (coalesced) and shares the input value (broadcast).
@@ -499,6 +537,12 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
     const size_t out_elems = (size_t)p->K * p->P * p->Q;
     switch (kind) {
         case PB_STAGE_INPUT:
+            if (p->R * p->S > 1) {      // patch-matrix form (see input_patch_kernel)
+                out->num_blocks = blocks_for((size_t)p->P * p->Q * (p->Ks / N));
+                out->regs_per_thread = f32 ? regs_of(input_patch_kernel<float>) : regs_of(input_patch_kernel<__nv_bfloat16>);
+                out->bytes = in_elems * 4 + (size_t)p->P * p->Q * p->Ks * es;
+                break;
+            }
             out->num_blocks = blocks_for((size_t)p->H * p->W);
             out->regs_per_thread = f32 ? regs_of(input_transform_kernel<float>) : regs_of(input_transform_kernel<__nv_bfloat16>);
             out->bytes = in_elems * 4 + in_elems * es;
@@ -593,6 +637,11 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
     } while (0)
     switch (kind) {
         case PB_STAGE_INPUT:
+            if (p->R * p->S > 1) {
+                PB_REQUIRE(p->Ks >= p->R * p->S * p->C, "input patches: row stride %d is shorter than R*S*C = %d", p->Ks, p->R * p->S * p->C);
+                PB_DISPATCH(input_patch_kernel<float>, input_patch_kernel<__nv_bfloat16>, a, job_id, nf);
+                break;
+            }
             if (f32) launch_k(input_transform_kernel<float>, grid, block, st, pdl, (const float*)p->x, (float*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
             else launch_k(input_transform_kernel<__nv_bfloat16>, grid, block, st, pdl, (const float*)p->x, (__nv_bfloat16*)p->y, p->C, p->H * p->W, p->Ks, job_id, nf);
             break;

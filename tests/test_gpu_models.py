@@ -109,8 +109,10 @@ def test_small_net_layer_by_layer_bf16(tmp_path):
     for t_id, shape in enumerate(g.tensors):
         if t_id == g.output:
             continue
+        if t_id == g.input:
+            continue        # the stem is lowered to a patch matrix: the channels-last image is never materialised
         got = m.tensor(t_id, shape)
-        want = og.round_bf16(bufs[t_id]) if t_id != g.input else og.round_bf16(x)
+        want = og.round_bf16(bufs[t_id])
         scale = max(float(np.abs(want).max()), 1e-6)
         tol = np.abs(want) * 2.0 ** -6 + 4e-3 * scale
         assert (np.abs(got - want) <= tol).all(), f"tensor {t_id} {shape}: worst {float(np.abs(got - want).max())} scale {scale}"
@@ -129,6 +131,28 @@ def test_imagenet_models_bf16_vs_fp32_oracle(models_dir, model):
     assert rel <= 1e-2, rel
     assert int(y.argmax()) == int(ref.argmax())
     m.close()
+
+
+@pytest.mark.parametrize("model", ["resnet18", "inception_v3"])
+def test_stem_as_patch_matrix_and_as_image_agree(models_dir, monkeypatch, model):
+    """The 3-channel stem convolution is lowered to a pointwise convolution over a patch matrix written by
+    stage 0; PB_PATCH_INPUT=0 keeps the channels-last image and the filter taps.  Same arithmetic, other
+    summation order inside the tensor core: results agree to bf16 accuracy and with the fp32 oracle."""
+    path = os.path.join(models_dir, packer.pack_file_name(model))
+    x = make_input(model)
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("PB_PATCH_INPUT", flag)
+        m = Model(path, 1)
+        name0 = m.L.pb_model_stage_name(m.m, 0).decode()
+        assert name0 == ("input_patches" if flag == "1" else "input_layout")
+        outs[flag] = m.run(x)
+        m.close()
+    ref = GOLDEN[model]
+    scale = float(np.abs(ref).max())
+    for y in outs.values():
+        assert float(np.abs(y - ref).max()) <= 1e-2 * scale and int(y.argmax()) == int(ref.argmax())
+    assert float(np.abs(outs["1"] - outs["0"]).max()) <= 5e-3 * scale
 
 
 def test_resnet18_fp32_path(models_dir):

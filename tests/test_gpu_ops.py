@@ -278,3 +278,30 @@ def test_input_layout_conversion(dtype):
     ref = og.round_bf16(x) if dtype == 1 else x
     np.testing.assert_array_equal(np.transpose(full[:, :, :3], (2, 0, 1)), ref)
     assert (full[:, :, 3:] == 0).all()
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("geom", [(3, 31, 29, 3, 3, 2, 0), (3, 30, 30, 7, 7, 2, 3), (1, 12, 12, 5, 5, 1, 2)])
+def test_input_patch_matrix(dtype, geom):
+    """Stage 0 in its patch-matrix form: row (p, q) holds the stem convolution's receptive field,
+    k = (r*S + s)*C + c, zeros outside the image and beyond R*S*C."""
+    import torch
+    L = capi.load()
+    C_, H, W, R, S, st, pad = geom
+    x = RNG.standard_normal((C_, H, W), dtype=np.float32)
+    P, Q = (H + 2 * pad - R) // st + 1, (W + 2 * pad - S) // st + 1
+    kp = R * S * C_
+    xd = torch.from_numpy(x).cuda()
+    yd, ks = gu.empty_cl(P, Q, kp, dtype, fill=9.0)
+    p = _params(dtype, (C_, H, W), kp, P, Q, ks, R, S, st, st, pad, pad, Cs=C_)
+    p.x, p.y = xd.data_ptr(), yd.data_ptr()
+    capi.check(L.pb_op_launch(capi.STAGE_INPUT, C.byref(p), None, 0, None), "input patches")
+    gu.sync()
+    full = yd.float().cpu().numpy()                      # [P][Q][ks]
+    xp = np.pad(x, ((0, 0), (pad, pad), (pad, pad)))
+    ref = np.zeros((P, Q, kp), np.float32)
+    for r in range(R):
+        for s_ in range(S):
+            ref[:, :, (r * S + s_) * C_:(r * S + s_ + 1) * C_] = np.transpose(xp[:, r:r + st * P:st, s_:s_ + st * Q:st], (1, 2, 0))
+    np.testing.assert_array_equal(full[:, :, :kp], og.round_bf16(ref) if dtype == 1 else ref)
+    assert (full[:, :, kp:] == 0).all()
