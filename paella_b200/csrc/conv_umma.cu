@@ -57,6 +57,7 @@ constexpr int kBK = 64;             // bf16 elements per k-block = one 128-byte 
 #define PB_LAG_OF(stages) ((stages) / 2)
 #endif
 constexpr int kMaxStages = 8;
+constexpr int kMaxBN = 256;          // output channels per CTA tile at most (tcgen05.mma N <= 256)
 constexpr uint32_t kSmemBudget = 200u * 1024u;   // one CTA per SM (gather kernel)
 // The TMA kernel is sized for THREE CTAs per SM (73 KB of pipeline + ~2 KB static and reserved each
 // out of 228 KB; <= 112 registers; <= 128 of 512 TMEM columns).  One CTA cannot pull more than about
@@ -597,9 +598,9 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < 128) {
-        const int k = n0 + tid;
-        s_bias[tid] = (a.bias && tid < a.BN && k < a.K) ? __ldg(a.bias + k) : 0.f;
+    for (int j = tid; j < a.BN; j += kThreadsTma) {
+        const int k = n0 + j;
+        s_bias[j] = (a.bias && k < a.K) ? __ldg(a.bias + k) : 0.f;
     }
     if (warp == 5) {
         tcgen05_alloc(smem_u32(s_tmem_base), a.tmem_cols);
@@ -708,7 +709,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile uint32_t s_abort;
     __shared__ uint32_t s_is_last;
-    __shared__ __align__(16) float s_bias[128];
+    __shared__ __align__(16) float s_bias[kMaxBN];
 
     resolve_slot(job_id, nf);
     if (nf) nf->start(job_id);
@@ -741,7 +742,7 @@ conv_umma_multi_kernel(const SubConv* __restrict__ table, int n_sub, uint32_t jo
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile uint32_t s_abort;
     __shared__ uint32_t s_is_last;
-    __shared__ __align__(16) float s_bias[128];
+    __shared__ __align__(16) float s_bias[kMaxBN];
     __shared__ __align__(16) ConvArgs s_args;
 
     resolve_slot(job_id, nf);
@@ -813,6 +814,20 @@ bool use_tma_a() {
     return v;
 }
 
+// Widest output-channel tile of the TMA kernel.  A tile of N channels re-reads operand A once per tile,
+// so wide tiles cut the bytes an SM pulls; they also take 2 x 48 KB of pipeline and 256 TMEM columns
+// (two CTAs per SM instead of three) and halve the CTAs of a launch.  Measured (GPU us per request, 1 / 32 /
+// 64 requests in flight): Inception-v3 696 / 46.0 / 43.4 at 128 against 750 / 46.3 / 40.3 at 256; ResNet-50
+// 583 / 39.0 / 34.9 against 737 / 43.1 / 37.5: 128 is the default, PB_CONV_MAX_BN=256 selects the wide tile.
+int max_bn() {
+    static const int v = [] {
+        const char* e = getenv("PB_CONV_MAX_BN");
+        const int n = e ? atoi(e) : 128;
+        return n >= 256 ? 256 : 128;
+    }();
+    return v;
+}
+
 // A split of the reduction must save at least this much (us) of a lone launch's modelled time.
 // Measured on Inception-v3 (us per request alone / GPU time per request with 32 / 64 in flight):
 // threshold 0 -> 727 / 52.7 / 52.6, 0.5 -> 709 / 46.8 / 45.0, 2 -> 706 / 45.7 / 43.3, never split ->
@@ -844,7 +859,7 @@ Geometry geometry(const pb_op_params* p) {
     g.nkb = p->R * p->S * g.cpt;
     g.Kdim_pad = g.nkb * kBK;
     g.Kp16 = round_up(p->K, 16);
-    g.n_tiles = ceil_div(g.Kp16, 128);
+    g.n_tiles = ceil_div(g.Kp16, use_tma_a() ? max_bn() : 128);
     g.BN = round_up(ceil_div(g.Kp16, g.n_tiles), 16);
     g.Kout_pad = g.n_tiles * g.BN;
     g.m_tiles = ceil_div(p->P * p->Q, kBM);
