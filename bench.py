@@ -435,20 +435,29 @@ def main():
 
     value = n_dev / (ms_dev * 1e-3)
     e2e = n_e2e / (ms_e2e * 1e-3)
-    # kernels of ours inside the timed region: every measured request runs all kernels of its model
-    # (a stage group replayed as a CUDA graph still launches each of its kernels on the device)
+    # kernels of ours inside the timed region: every measured request runs all launches of its model's plan
+    # (a stage group replayed as a CUDA graph still launches each of its kernels on the device; independent
+    # tensor-core convolutions that share a launch count once)
     kernels_per_request = {}
+    layers_per_request = {}
     for job, model, _ in MIX:
         if model is None:     # synthetic jobs: PB_*_KERNELS launches per request (10 by default)
             kernels_per_request[job] = (10, 10)
             continue
         mh = C.c_void_p()
         capi.check(L.pb_model_load(os.path.join(tmp.name, packer_name(model)).encode(), devices[0], -1, C.byref(mh)), "pb_model_load")
-        kernels_per_request[model] = (L.pb_model_num_stages(mh), L.pb_model_num_groups(mh))
+        n_stages, n_groups, n_launches = L.pb_model_num_stages(mh), L.pb_model_num_groups(mh), 0
+        for g in range(n_groups):
+            order, launch = (C.c_int32 * n_stages)(), (C.c_int32 * n_stages)()
+            k = L.pb_model_group_plan(mh, g, order, launch, n_stages)
+            n_launches += (launch[k - 1] + 1) if k > 0 else 0
+        kernels_per_request[model] = (n_launches, n_groups)
+        layers_per_request[model] = n_stages
         L.pb_model_destroy(mh)
     counts = k_dev          # measured requests per model, summed over GPUs
     gpu_launches = int(sum(c * kernels_per_request[m or j][0] for c, (j, m, _) in zip(counts, MIX)))
     config["kernels_per_request"] = {m: k[0] for m, k in kernels_per_request.items()}
+    config["layers_per_request"] = layers_per_request
     config["scheduler_stages_per_request"] = {m: k[1] for m, k in kernels_per_request.items()}
 
     def lat(r):
