@@ -318,6 +318,7 @@ def main():
     ap.add_argument("--iat-us", type=float, default=0.0, help="open loop: mean inter-arrival per replica in us (Poisson); 0 = closed loop")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-roofline", action="store_true")
+    ap.add_argument("--no-fairness", action="store_true", help="skip the isolated runs behind Jain's index")
     ap.add_argument("--no-sweep", action="store_true", help="skip the open-loop Poisson rate sweep of the mix")
     ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
     ap.add_argument("--only-roofline", default=None, metavar="SUBSTR",
@@ -481,6 +482,8 @@ def main():
             "latency_us": lat(r_dev),
             "timing": "CUDA events on each GPU around the measured requests (device idle on both sides), max over GPUs",
             "records_consumed": int(r_dev.records_consumed), "decisions": int(r_dev.decisions),
+            "scheduler_decisions_per_s": round(r_dev.decisions / (ms_dev * 1e-3)),
+            "notification_records_per_s": round(r_dev.records_consumed / (ms_dev * 1e-3)),
             # this rank's replica threads during the e2e leg: share of their time inside CUDA launch calls, in
             # notification handling + scheduling, and polling with nothing to do (GPU-bound when large)
             "host_time_share": (lambda t: {"launch": round(r_e2e.host_launch_us / t, 3), "sched": round(r_e2e.host_sched_us / t, 3),
@@ -489,7 +492,7 @@ def main():
             "per_replica_rps": {"resident": [round(r_dev.per_gpu_rps[i]) for i in range(len(devices))],
                                 "e2e": [round(r_e2e.per_gpu_rps[i]) for i in range(len(devices))]}}
 
-    if args.workload in ("mix", "mobilenet_resnet50") and not dist:
+    if args.workload in ("mix", "mobilenet_resnet50") and not dist and not args.no_fairness:
         line["fairness"] = fairness_leg(L, capi, devices[0], MIX, r_e2e)
     if args.workload == "mix" and not dist and args.iat_us <= 0 and not args.no_sweep:
         # Open loop: Poisson arrivals at fractions of the closed-loop rate, through host buffers; the highest
