@@ -510,6 +510,24 @@ def main():
                 best = round(rate)
         line["poisson_sweep"] = {"arrivals": "Poisson, exponential inter-arrival, latency = completion - scheduled arrival",
                                  "points": sweep, "max_offered_rps_meeting_slo": best}
+    if args.extras and not dist and args.workload == "mix":
+        # Job-event timeline of a short e2e run (the server records it when PB_PROFILE_PREFIX is set) and the
+        # reference's overhead stack computed from it, per model (MNIST = 1 scheduler stage per request).
+        from paella_b200 import overhead_stack as ost
+        prefix = os.path.join(tmp.name, "timeline")
+        os.environ["PB_PROFILE_PREFIX"] = prefix
+        try:
+            run_load(L, capi, devices[:1], 4000, 1, 0.25, False, args.concurrency, caps, extra_kernels=args.extra_kernels,
+                     sched=args.sched, streams=args.streams, seed=11)
+        finally:
+            del os.environ["PB_PROFILE_PREFIX"]
+        jobs = ost.read_job_events(prefix + "_job_events.txt")
+        n_inc_stages = kernels_per_request[names[1]][1]
+        line["overhead_stack"] = {"what": "means per request from the server's job-event timeline (closed loop, host buffers): queueing = "
+                                          "submission -> first dispatch, scheduling = dispatch -> run_next(), launch = inside run_next(), "
+                                          "runtime = run_next() returned -> stage's last block-end record handled, interval = stage finished -> "
+                                          "next stage submitted",
+                                  "mnist": ost.overhead_stack(jobs, stages=1), "inception_v3": ost.overhead_stack(jobs, stages=n_inc_stages)}
     if args.extras and not dist:
         line["extras"] = extras_leg(L, capi, devices[0])
         if args.workload == "mix":

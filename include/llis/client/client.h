@@ -92,6 +92,9 @@ class Client {
     // As wait(), but returns NULL when nothing finished within timeout_ms.
     JobInstanceRef* wait_timeout(int timeout_ms);
     void kill_server();
+    // PROFILER_CMD + sub-command (src/client/profiler_client.cpp of the reference: set/unset_record_job_events,
+    // set/unset_record_run_next_times, ..., save(path)); `path` travels only with ProfilerMsgType::SAVE.
+    void profiler_cmd(ProfilerMsgType cmd, const std::string& path = std::string());
 
     ClientId get_client_id() const { return client_id_; }
     ipc::ShmChannel* get_c2s_channel() { return &c2s_channel_; }

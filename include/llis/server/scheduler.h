@@ -38,6 +38,8 @@ class SchedulerHost {
     virtual void notify_job_starts(job::Job* job) = 0;
     virtual void notify_job_ends(job::Job* job) = 0;
     virtual void release_job_instance(job::Job* job) = 0;
+    // Observation hook: host time around a stage's run_next() (profiler: KERNEL_SUBMIT_START / _END).
+    virtual void on_stage_submitted(job::Job* job, double start_us, double end_us) { (void)job; (void)start_us; (void)end_us; }
     // Observation hook: one call per dispatched stage (decision log for replay parity).
     virtual void on_dispatch(job::Job* job, bool is_mem, bool unfit, unsigned stream_slot, unsigned notifier_slot) {
         (void)job; (void)is_mem; (void)unfit; (void)stream_slot; (void)notifier_slot;
@@ -82,10 +84,13 @@ class Scheduler {
     uint64_t run_next_ns() const { return run_next_ns_; }
 
   protected:
-    void run_stage(job::Job* job) {
+    void run_stage(job::Job* job, SchedulerHost* host) {
         const auto t0 = std::chrono::steady_clock::now();
         job->run_next();
-        run_next_ns_ += (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
+        const auto t1 = std::chrono::steady_clock::now();
+        run_next_ns_ += (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(t1 - t0).count();
+        host->on_stage_submitted(job, std::chrono::duration<double, std::micro>(t0.time_since_epoch()).count(),
+                                 std::chrono::duration<double, std::micro>(t1.time_since_epoch()).count());
     }
     uint64_t run_next_ns_ = 0;
 

@@ -275,6 +275,14 @@ PB_API int pb_server_step(pb_server* s, int max_records);
 PB_API int pb_server_poll_done(pb_server* s, uint64_t* cookies, int32_t* errors, int max);
 PB_API uint64_t pb_server_num_decisions(const pb_server* s);
 PB_API uint32_t pb_server_jobs_in_flight(const pb_server* s);
+/* Job-event timeline and run_next() timings of the reference's Profiler (include/llis/server/profiler.h:15-23,
+ * src/server/profiler.cpp:10-131).  `cmd` is a llis::ProfilerMsgType value: 8 / 9 start / stop recording job
+ * events (0 JOB_SUBMITTED, 1 KERNEL_SCHED_START, 3 KERNEL_SUBMIT_START, 4 KERNEL_SUBMIT_END, 5 KERNEL_FINISHED,
+ * 6 JOB_FINISHED with steady-clock microseconds), 6 / 7 run_next() timings, 12 SAVE writes
+ * "<path>_job_events.txt" (one line per finished job: "code time " pairs) and "<path>_run_next_times.txt"
+ * ("start end duration blocks") in the reference's formats; the other commands are accepted and record nothing.
+ * PB_PROFILE_PREFIX=<path> in the environment records from server creation and saves at destruction. */
+PB_API int pb_server_profiler_cmd(pb_server* s, uint32_t cmd, const char* path);
 
 /* ------------------------------------------------------------------------ *
  * Load generator + request router over one server per GPU
@@ -359,6 +367,7 @@ PB_API int pb_client_create_instance(pb_client* c, uint32_t job, uint64_t* insta
 PB_API int pb_client_launch(pb_client* c, uint64_t instance);                         /* LAUNCH_JOB */
 /* Next finished request: 1 and *instance_out set, 0 on timeout (timeout_ms < 0 blocks). */
 PB_API int pb_client_wait(pb_client* c, int timeout_ms, uint64_t* instance_out);
+PB_API int pb_client_profiler_cmd(pb_client* c, uint32_t cmd, const char* path);      /* PROFILER_CMD + sub-command (+ path for SAVE = 12) */
 PB_API int pb_client_kill_server(pb_client* c);                                       /* EXIT_CMD */
 
 /* ------------------------------------------------------------------------ *

@@ -170,6 +170,8 @@ SIGNATURES = {
     "pb_client_launch": (_I, [_VP, _U64]),
     "pb_client_wait": (_I, [_VP, _I, C.POINTER(_U64)]),
     "pb_client_kill_server": (_I, [_VP]),
+    "pb_client_profiler_cmd": (_I, [_VP, _U32, C.c_char_p]),
+    "pb_server_profiler_cmd": (_I, [_VP, _U32, C.c_char_p]),
     "pb_sched_replay": (_I, [C.POINTER(ReplayConfig), C.POINTER(ReplayType), _U32, C.POINTER(ReplayEvent), _U32,
                              C.POINTER(ReplayDecision), _U32, C.POINTER(_U32), C.POINTER(_U32)]),
 }

@@ -89,4 +89,11 @@ int pb_client_kill_server(pb_client* c) {
     return PB_OK;
 }
 
+int pb_client_profiler_cmd(pb_client* c, uint32_t cmd, const char* path) {
+    PB_REQUIRE(c != nullptr && cmd <= (uint32_t)llis::ProfilerMsgType::SAVE, "pb_client_profiler_cmd: bad argument");
+    PB_REQUIRE(cmd != (uint32_t)llis::ProfilerMsgType::SAVE || (path && path[0]), "pb_client_profiler_cmd: SAVE needs a path prefix");
+    PB_TRY(c->client.profiler_cmd((llis::ProfilerMsgType)cmd, path ? path : ""));
+    return PB_OK;
+}
+
 }  // extern "C"

@@ -174,5 +174,13 @@ void Client::kill_server() {
     c2s_channel_.release_writer_lock();
 }
 
+void Client::profiler_cmd(ProfilerMsgType cmd, const std::string& path) {
+    c2s_channel_.acquire_writer_lock();
+    c2s_channel_.write(MsgType::PROFILER_CMD);
+    c2s_channel_.write(cmd);
+    if (cmd == ProfilerMsgType::SAVE) c2s_channel_.write(path);
+    c2s_channel_.release_writer_lock();
+}
+
 }  // namespace client
 }  // namespace llis

@@ -83,8 +83,15 @@ void IpcServer::handle_c2s() {
         case MsgType::GROW_POOL: handle_grow_pool(); break;
         case MsgType::CUDA_PROFILER_START:
         case MsgType::CUDA_PROFILER_STOP:
-        case MsgType::PROFILER_CMD:
-            break;   // profiling commands are accepted and ignored (the profiler is not rebuilt)
+            break;   // accepted and ignored
+        case MsgType::PROFILER_CMD: {
+            ProfilerMsgType cmd;
+            c2s_channel_.read(&cmd);
+            std::string path;
+            if (cmd == ProfilerMsgType::SAVE) c2s_channel_.read(&path);
+            if (core_->profiler_cmd((uint32_t)cmd, path.c_str()) != PB_OK) fprintf(stderr, "llis_server: profiler command %u: %s\n", (unsigned)cmd, pb_last_error());
+            break;
+        }
         case MsgType::EXIT_CMD: running_ = false; break;
     }
 }

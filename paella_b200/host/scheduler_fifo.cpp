@@ -140,7 +140,7 @@ class SchedulerFifo final : public PoolsBase {
                 job->set_finished_block_notifier(all_notifiers_[ns]);
                 ++num_decisions_;
                 host_->on_dispatch(job, is_mem, false, ss, ns);
-                run_stage(job);
+                run_stage(job, host_);
                 if (job->has_error()) close_failed_stage(job, is_mem);
                 else if (is_mem) host_->after_mem_stage(job);
             }
@@ -206,7 +206,7 @@ class SchedulerFifo2 final : public PoolsBase {
             if (job->is_pre_notify()) host_->notify_job_starts(job);
             ++num_decisions_;
             host_->on_dispatch(job, is_mem, false, ss, ns);
-            run_stage(job);
+            run_stage(job, host_);
             if (job->has_error()) close_failed_stage(job, is_mem);
             else if (is_mem) host_->after_mem_stage(job);
         }

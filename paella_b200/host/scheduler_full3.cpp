@@ -175,7 +175,7 @@ class SchedulerFull3 final : public Scheduler {
             ++num_decisions_;
             host_->on_dispatch(job, is_mem, unfit, sslot, nslot);
 
-            run_stage(job);
+            run_stage(job, host_);
             if (job->has_error()) close_failed_stage(job, is_mem);
             else if (is_mem) host_->after_mem_stage(job);
             if (free_streams_.empty()) break;

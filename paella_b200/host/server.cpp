@@ -1,5 +1,7 @@
 #include "server.h"
 
+#include <llis/ipc/defs.h>
+
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <llis/job/context.h>
@@ -15,15 +17,59 @@ using llis::job::Job;
 pb_server::~pb_server() {
     cudaSetDevice(device);
     cudaDeviceSynchronize();
+    if (!profile_prefix.empty()) profiler_save(profile_prefix);
     for (cudaStream_t s : streams) cudaStreamDestroy(s);
     if (notifiers_raw) llis::job::FinishedBlockNotifier::free_array(notifiers_raw);
     // Plugin instances are never destroyed (their class has no virtual destructor in the
     // plugin ABI); device memory they hold goes away with the context.
 }
 
+void pb_server::finish_job_events(Job* job) {
+    auto it = events_cur.find(job);
+    if (it == events_cur.end()) return;
+    it->second.emplace_back((int)kJobFinished, now_us());
+    events_all.push_back(std::move(it->second));
+    events_cur.erase(it);
+}
+
+int pb_server::profiler_cmd(uint32_t msg_type, const char* path) {
+    switch ((llis::ProfilerMsgType)msg_type) {
+        case llis::ProfilerMsgType::SET_RECORD_JOB_EVENTS: job_events_flag = true; return PB_OK;
+        case llis::ProfilerMsgType::UNSET_RECORD_JOB_EVENTS: job_events_flag = false; return PB_OK;
+        case llis::ProfilerMsgType::SET_RECORD_RUN_NEXT_TIMES: run_next_times_flag = true; return PB_OK;
+        case llis::ProfilerMsgType::UNSET_RECORD_RUN_NEXT_TIMES: run_next_times_flag = false; return PB_OK;
+        case llis::ProfilerMsgType::SAVE:
+            PB_REQUIRE(path != nullptr && path[0], "profiler SAVE needs a path prefix");
+            return profiler_save(path);
+        default:
+            // kernel info, per-block execution times, block placement and resource events: accepted, nothing recorded
+            return msg_type <= (uint32_t)llis::ProfilerMsgType::SAVE ? PB_OK : PB_ERR_INVALID;
+    }
+}
+
+// Files and line formats of src/server/profiler.cpp:101-121: "<prefix>_run_next_times.txt" with
+// "start_us end_us duration_us num_blocks", "<prefix>_job_events.txt" with one line per finished job.
+int pb_server::profiler_save(const std::string& path) {
+    FILE* fp = fopen((path + "_run_next_times.txt").c_str(), "w");
+    if (!fp) { pb::set_error("cannot write %s_run_next_times.txt", path.c_str()); return PB_ERR_IO; }
+    for (const RunNext& r : run_next_times) fprintf(fp, "%f %f %f %u\n", r.start_us, r.end_us, r.end_us - r.start_us, r.num_blocks);
+    fclose(fp);
+    fp = fopen((path + "_job_events.txt").c_str(), "w");
+    if (!fp) { pb::set_error("cannot write %s_job_events.txt", path.c_str()); return PB_ERR_IO; }
+    for (const auto& job : events_all) {
+        for (const auto& ev : job) fprintf(fp, "%u %f ", (unsigned)ev.first, ev.second);
+        fprintf(fp, "\n");
+    }
+    fclose(fp);
+    return PB_OK;
+}
+
 int pb_server::init(const pb_server_config& c) {
     cfg = c;
     device = c.device;
+    if (const char* pp = getenv("PB_PROFILE_PREFIX")) {
+        if (pp[0]) { profile_prefix = pp; job_events_flag = run_next_times_flag = true; }
+    }
     PB_CUDA(cudaSetDevice(device));
     Context::set_device(device);
     llis::server::SchedulerConfig sc;
@@ -97,6 +143,7 @@ int pb_server::launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie, llis::
         t.give_back(job);
         return job->has_error();
     }
+    if (job_events_flag) record_job_event(job, kJobSubmitted, now_us());
     scheduler->handle_new_job(job);
     return PB_OK;
 }
@@ -205,5 +252,10 @@ int pb_server_poll_done(pb_server* s, uint64_t* cookies, int32_t* errors, int ma
 
 uint64_t pb_server_num_decisions(const pb_server* s) { return s ? s->scheduler->num_decisions() : 0; }
 uint32_t pb_server_jobs_in_flight(const pb_server* s) { return s ? s->scheduler->num_jobs() : 0; }
+
+int pb_server_profiler_cmd(pb_server* s, uint32_t cmd, const char* path) {
+    PB_REQUIRE(s != nullptr, "pb_server_profiler_cmd: NULL server");
+    return s->profiler_cmd(cmd, path);
+}
 
 }  // extern "C"
