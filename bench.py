@@ -47,6 +47,7 @@ WORKLOADS = {
     "googlenet": [("tvm_googlenet", "googlenet", 1.0)],
     "squeezenet1_1": [("tvm_squeezenet1_1", "squeezenet1_1", 1.0)],
     "densenet121": [("tvm_densenet121", "densenet121", 1.0)],
+    "arcfaceresnet100": [("tvm_arcfaceresnet100", "arcfaceresnet100", 1.0)],
     # depthwise + bottleneck mix
     "mobilenet_resnet50": [("tvm_mobilenet", "mobilenet", 0.5), ("tvm_resnet50", "resnet50", 0.5)],
     # scheduler stress (vec_add of 2^22 floats x 10 launches, 148-block spin kernels of 10 us / 1 ms)
@@ -343,6 +344,7 @@ def main():
                "googlenet": "GoogLeNet (torchvision form) alone, batch 1, 224x224, BN folded, random He-normal weights",
                "squeezenet1_1": "SqueezeNet 1.1 alone, batch 1, 224x224, random He-normal weights",
                "densenet121": "DenseNet-121 alone, batch 1, 224x224, random He-normal weights",
+               "arcfaceresnet100": "ArcFace LResNet100E-IR alone, batch 1, 112x112, random He-normal weights",
                "mobilenet_resnet50": "MobileNetV2 : ResNet-50 = 1:1, batch 1, 224x224",
                "stress": "vec_add : dummy_short : dummy_long = 1:1:1 synthetic scheduler stress"}[args.workload]
     config = {"workload": wl_text + ("; closed loop" if args.iat_us <= 0 else f"; open loop, Poisson, mean inter-arrival {args.iat_us} us per replica"),

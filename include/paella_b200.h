@@ -144,7 +144,8 @@ typedef struct pb_op_params {
     int32_t K, P, Q, Ks;      /* output: channels written, height, width, channel stride of the output tensor */
     int32_t out_c_off;        /* first output channel written (concatenation slice) */
     int32_t R, S, stride_h, stride_w, pad_h, pad_w, groups;
-    int32_t act;              /* 0 none, 1 relu, 2 relu6 */
+    int32_t act;              /* 0 none, 1 relu, 2 relu6, 3 prelu (dense convolutions only: `bias` then holds 2*K floats,
+                               *   the K biases followed by the K per-channel slopes) */
     int32_t flags;            /* bit0 count_include_pad (avg pool); bit1 output is fp32 */
     int32_t res_Cs;           /* channel stride of the residual tensor (0 = none) */
     const void* x;            /* input activations */

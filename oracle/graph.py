@@ -193,7 +193,13 @@ def run(pack: Pack, x: np.ndarray, emulate_bf16: bool = False, keep_all: bool = 
             w = rb(W[woff: woff + cout * (cin // groups) * r * s].reshape(cout, cin // groups, r, s))
             b = np.ascontiguousarray(W[boff: boff + cout])
             res = None if in1 == NONE else np.ascontiguousarray(bufs[in1])
-            conv2d(xin, w, b, (sh, sw), (ph, pw), groups, act, res, bufs[out], ooff)
+            if act == 3:     # PReLU: slopes follow the biases; y = v if v > 0 else slope[c] * v
+                conv2d(xin, w, b, (sh, sw), (ph, pw), groups, 0, res, bufs[out], ooff)
+                v = bufs[out][ooff: ooff + cout]
+                slope = W[boff + cout: boff + 2 * cout].reshape(-1, 1, 1)
+                bufs[out][ooff: ooff + cout] = np.where(v > 0, v, v * slope).astype(np.float32)
+            else:
+                conv2d(xin, w, b, (sh, sw), (ph, pw), groups, act, res, bufs[out], ooff)
         elif typ == OP_DENSE:
             w = rb(W[woff: woff + cout * cin].reshape(cout, cin))
             b = np.ascontiguousarray(W[boff: boff + cout])

@@ -250,10 +250,15 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t x, uint64_t y) {
     return r;
 }
 template <int ACT>
-__device__ __forceinline__ uint32_t to_bf16x2_act(uint64_t v) {
+__device__ __forceinline__ uint32_t to_bf16x2_act(uint64_t v, float slope_lo = 0.f, float slope_hi = 0.f) {
     uint32_t lo, hi, d;
     asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
-    if constexpr (ACT == 0) {
+    if constexpr (ACT == 3) {       // PReLU: v > 0 ? v : slope * v, per channel
+        const float a = __uint_as_float(lo), b = __uint_as_float(hi);
+        lo = __float_as_uint(a > 0.f ? a : a * slope_lo);
+        hi = __float_as_uint(b > 0.f ? b : b * slope_hi);
+    }
+    if constexpr (ACT == 0 || ACT == 3) {
         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
     } else {
         asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
@@ -317,7 +322,12 @@ __device__ __forceinline__ void epilogue_chunk(const ConvArgs& a, uint32_t lane_
                 uint64_t f = bias2[h * 4 + j];
                 if (!part) f = add_f32x2(pack_f32x2(v[h * 8 + 2 * j], v[h * 8 + 2 * j + 1]), f);
                 if (rrow) f = add_f32x2(f, pack_f32x2(ru[j] << 16, ru[j] & 0xffff0000u));
-                o[j] = to_bf16x2_act<ACT>(f);
+                if constexpr (ACT == 3) {
+                    const float2 sl = __ldg(reinterpret_cast<const float2*>(a.bias + a.K + kk) + j);   // slopes follow the biases
+                    o[j] = to_bf16x2_act<ACT>(f, sl.x, sl.y);
+                } else {
+                    o[j] = to_bf16x2_act<ACT>(f);
+                }
             }
             *reinterpret_cast<uint4*>(yrow + kk) = make_uint4(o[0], o[1], o[2], o[3]);
         }
@@ -384,7 +394,8 @@ __device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, 
         __nv_bfloat16* yrow = a.y + (size_t)m * a.Ks + a.out_c_off;
         const __nv_bfloat16* rrow = a.residual ? a.residual + (size_t)m * a.res_Cs : nullptr;
         const float* part = a.splits > 1 ? a.ws + (size_t)tile * a.splits * tile_floats : nullptr;
-        if (a.act == 1) epilogue_columns<1>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+        if (a.act == 3) epilogue_columns<3>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
+        else if (a.act == 1) epilogue_columns<1>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
         else if (a.act == 2) epilogue_columns<2>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
         else epilogue_columns<0>(a, lane_addr, n0, row_valid, yrow, rrow, part, tile_floats, s_bias);
     }

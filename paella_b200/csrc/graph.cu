@@ -631,7 +631,8 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
                 packed.resize((size_t)nbytes);
                 pb_op_pack_weights(st.kind, &p, w_src, packed.data());
                 PB_FAIL_LOAD(upload(m, packed.data(), packed.size(), &st.w_dev));
-                PB_FAIL_LOAD(upload(m, W + b_off, (size_t)p.K * 4, (void**)&st.bias_dev));
+                if (p.act == 3 && dw) { pb::set_error("%s: PReLU on a depthwise convolution is not supported", pack_path); PB_FAIL_LOAD(PB_ERR_INVALID); }
+                PB_FAIL_LOAD(upload(m, W + b_off, (size_t)p.K * 4 * (p.act == 3 ? 2 : 1), (void**)&st.bias_dev));   // PReLU: [bias | slope]
                 break;
             }
             case OP_DENSE: {

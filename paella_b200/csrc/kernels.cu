@@ -164,7 +164,9 @@ __global__ void __launch_bounds__(256) conv_simt_kernel(OpArgs a, uint32_t job_i
         }
         if (a.bias) acc += a.bias[k];
         if (a.residual) acc += to_f<T>(static_cast<const T*>(a.residual)[(size_t)pix * a.res_Cs + k]);
-        static_cast<T*>(a.y)[(size_t)pix * a.Ks + a.out_c_off + k] = from_f<T>(act_fn(acc, a.act));
+        if (a.act == 3) acc = acc > 0.f ? acc : acc * a.bias[a.K + k];      // PReLU: slopes follow the biases
+        else acc = act_fn(acc, a.act);
+        static_cast<T*>(a.y)[(size_t)pix * a.Ks + a.out_c_off + k] = from_f<T>(acc);
     }
     PB_NOTIFY_END();
 }

@@ -36,7 +36,7 @@ VERSION = 1
 NONE = 0xFFFFFFFF
 
 OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE = 1, 2, 3, 4, 5, 6, 7, 8
-ACT_NONE, ACT_RELU, ACT_RELU6 = 0, 1, 2
+ACT_NONE, ACT_RELU, ACT_RELU6, ACT_PRELU = 0, 1, 2, 3   # PReLU: the conv's bias block is [bias | per-channel slope]
 FLAG_COUNT_INCLUDE_PAD = 1
 FLAG_CEIL_MODE = 4          # informational: the output tensor's extent already says it
 
@@ -141,7 +141,7 @@ class Graph:
 
     # -- operators -----------------------------------------------------------
     def conv(self, x, cout, k, stride=1, pad=0, groups=1, act=ACT_RELU, residual=None,
-             out=None, out_c_off=0, bn_eps=None, name=""):
+             out=None, out_c_off=0, bn_eps=None, name="", w_scale=1.0):
         c, h, w = self.shape(x)
         r, s = _pair(k)
         sh, sw = _pair(stride)
@@ -153,20 +153,29 @@ class Graph:
         else:
             assert self.shape(out)[1:] == (p, q), (name, self.shape(out), p, q)
         fan_in = (c // groups) * r * s
-        scale = 1.0 if bn_eps is None else 1.0 / np.sqrt(1.0 + bn_eps)
+        scale = w_scale * (1.0 if bn_eps is None else 1.0 / np.sqrt(1.0 + bn_eps))
         w_off = self._push(self._he((cout, c // groups, r, s), fan_in, scale))
         b_off = self._push(self._bias(cout))
+        if act == ACT_PRELU:     # slopes right behind the biases: 0.25 (the usual initial value) +- 0.1
+            self._push((0.25 + 0.2 * (self.rng.random(cout, dtype=np.float32) - 0.5)).astype(np.float32))
         self.ops.append(Op(OP_CONV, x, out, NONE if residual is None else residual, out_c_off,
                            c, cout, r, s, sh, sw, ph, pw, groups, act, 0, w_off, b_off, name))
         self.output = out
         return out
 
-    def dense(self, x, n_out, act=ACT_NONE, name=""):
+    def dense(self, x, n_out, act=ACT_NONE, name="", out_scale=None, out_bias=None):
+        """Fully connected layer; out_scale / out_bias fold a following per-output affine (a 1-D batch-norm
+        on the features) into the weights and biases."""
         c, h, w = self.shape(x)
         n_in = c * h * w
         out = self.tensor(n_out, 1, 1)
-        w_off = self._push(self._he((n_out, n_in), n_in))
-        b_off = self._push(self._bias(n_out))
+        wt = self._he((n_out, n_in), n_in)
+        bs = self._bias(n_out)
+        if out_scale is not None:
+            wt = (wt * np.asarray(out_scale, np.float32).reshape(-1, 1)).astype(np.float32)
+            bs = (bs * np.asarray(out_scale, np.float32) + np.asarray(out_bias, np.float32)).astype(np.float32)
+        w_off = self._push(wt)
+        b_off = self._push(bs)
         self.ops.append(Op(OP_DENSE, x, out, cin=n_in, cout=n_out, act=act, w_off=w_off,
                            b_off=b_off, name=name))
         self.output = out
@@ -551,6 +560,32 @@ def densenet121(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
     return g
 
 
+def arcface_r100(seed=1234, precision=1, **kw) -> Graph:
+    """ArcFace LResNet100E-IR (jobs/tvm_arcfaceresnet100 of the reference: 3x112x112 in, 512-d embedding out):
+    3x3 stem + batch-norm + PReLU; improved residual units bn -> conv3x3 -> bn -> PReLU -> conv3x3(stride) -> bn
+    (+ 1x1 stride-2 projection with batch-norm on the first unit of a stage), 3-13-30-3 units of 64-128-256-512
+    channels; bn -> flatten -> fc 512 -> bn.  Batch-norms that follow a convolution (or the fc) are folded;
+    the one that opens a unit is an affine operator.  The input is taken as already normalised."""
+    eps = 2e-5
+    g = Graph("arcfaceresnet100", (3, 112, 112), seed, precision, **kw)
+    x = g.conv(g.input, 64, 3, 1, 1, act=ACT_PRELU, bn_eps=eps, name="conv0")
+    for si, (units, ch) in enumerate(zip([3, 13, 30, 3], [64, 128, 256, 512])):
+        for ui in range(units):
+            n = f"stage{si + 1}_unit{ui + 1}"
+            first = ui == 0
+            sc = g.conv(x, ch, 1, 2, 0, act=ACT_NONE, bn_eps=eps, name=n + "_conv1sc") if first else x
+            y = g.affine(x, act=ACT_NONE, bn_eps=eps, name=n + "_bn1")
+            y = g.conv(y, ch, 3, 1, 1, act=ACT_PRELU, bn_eps=eps, name=n + "_conv1")
+            # the unit's last batch-norm starts small (gamma 0.25), as deep residual nets are initialised, so that
+            # activations do not grow by a constant factor in each of the 49 units
+            x = g.conv(y, ch, 3, 2 if first else 1, 1, act=ACT_NONE, residual=sc, bn_eps=eps, name=n + "_conv2", w_scale=0.25)
+    y = g.affine(x, act=ACT_NONE, bn_eps=eps, name="bn1")
+    gamma = (1.0 + 0.1 * g.rng.standard_normal(512, dtype=np.float32)).astype(np.float32)
+    beta = (0.1 * g.rng.standard_normal(512, dtype=np.float32)).astype(np.float32)
+    g.dense(y, 512, name="pre_fc1", out_scale=gamma / np.float32(np.sqrt(1.0 + eps)), out_bias=beta)
+    return g
+
+
 def googlenet(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
     """GoogLeNet / Inception-v1 (jobs/tvm_googlenet of the reference) in torchvision's form: batch-norm
     (eps 1e-3) folded, no auxiliary heads, 3x3 in the "5x5" branch, ceil-mode max pooling."""
@@ -603,6 +638,7 @@ MODELS = {
     "squeezenet1_1": squeezenet1_1,
     "googlenet": googlenet,
     "densenet121": densenet121,
+    "arcfaceresnet100": arcface_r100,
 }
 
 

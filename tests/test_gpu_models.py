@@ -120,7 +120,7 @@ def test_small_net_layer_by_layer_bf16(tmp_path):
     m.close()
 
 
-@pytest.mark.parametrize("model", ["resnet18", "resnet34", "inception_v3", "resnet50", "googlenet", "squeezenet1_1", "densenet121"])
+@pytest.mark.parametrize("model", ["resnet18", "resnet34", "inception_v3", "resnet50", "googlenet", "squeezenet1_1", "densenet121", "arcfaceresnet100"])
 def test_imagenet_models_bf16_vs_fp32_oracle(models_dir, model):
     m = Model(os.path.join(models_dir, packer.pack_file_name(model)), 1)
     kinds = m.kinds()

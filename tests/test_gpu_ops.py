@@ -152,6 +152,32 @@ def test_conv_umma_long_reductions_do_split(case, residual):
     _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=residual, scratch=True)
 
 
+def test_conv_prelu_both_paths():
+    """PReLU epilogue (per-channel slopes stored behind the biases): tensor-core path and direct path."""
+    import torch
+    L = capi.load()
+    for kind, dtype in ((capi.STAGE_CONV_UMMA, 1), (capi.STAGE_CONV_SIMT, 0)):
+        C_, H, W, K = 64, 14, 14, 96
+        x = RNG.standard_normal((C_, H, W), dtype=np.float32)
+        w = RNG.standard_normal((K, C_, 3, 3), dtype=np.float32) * np.float32(np.sqrt(2.0 / (C_ * 9)))
+        b = (0.1 * RNG.standard_normal(K)).astype(np.float32)
+        slope = (0.05 + 0.4 * RNG.random(K)).astype(np.float32)
+        if dtype == 1:
+            x, w = og.round_bf16(x), og.round_bf16(w)
+        xd, cs = gu.to_device_cl(x, dtype)
+        yd, ks = gu.empty_cl(H, W, K, dtype, fill=7.0)
+        p = _params(dtype, (C_, H, W), K, H, W, ks, 3, 3, 1, 1, 1, 1, 1, 3, 0, 0, cs)
+        wd = gu.pack_weights(kind, p, w)
+        bd = torch.from_numpy(np.concatenate([b, slope])).cuda()
+        p.x, p.w, p.bias, p.y = xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), yd.data_ptr()
+        capi.check(L.pb_op_launch(kind, C.byref(p), None, 0, None), "prelu conv")
+        gu.sync()
+        v = og.conv2d(x, w, b, (1, 1), (1, 1), 1, 0, None)
+        ref = np.where(v > 0, v, v * slope.reshape(-1, 1, 1)).astype(np.float32)
+        assert (ref < 0).mean() > 0.2                      # the negative branch is exercised
+        _assert_close(gu.from_device_cl(yd, K), ref, dtype)
+
+
 def test_conv_umma_epilogue_variants():
     # residual add + relu, relu6, no activation, no bias, write into a channel slice of a wider tensor
     _run_conv(capi.STAGE_CONV_UMMA, 1, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, act=1, residual=True)

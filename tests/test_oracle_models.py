@@ -25,6 +25,8 @@ def _load_into_torch(model, g, bn_eps, folded=lambda name: True):
             assert isinstance(m, nn.Conv2d), name
             w = pack.weights[woff: woff + cout * (cin // groups) * r * s].reshape(cout, cin // groups, r, s)
             with torch.no_grad():
+                if rec[15] == 3:             # PReLU: the slopes follow the biases in the pack
+                    mods[name + "_prelu"].weight.copy_(torch.from_numpy(pack.weights[boff + cout: boff + 2 * cout]))
                 if m.bias is None:           # conv + batch-norm: the pack holds the folded weight
                     m.weight.copy_(torch.from_numpy(w * np.float32(scale if folded(name) else 1.0)))
                 else:                        # plain biased convolution
@@ -51,7 +53,53 @@ def _load_into_torch(model, g, bn_eps, folded=lambda name: True):
     return pack
 
 
+class ArcFaceR100(nn.Module):
+    """LResNet100E-IR written out in torch (insightface's fresnet, version_unit 3, output "E") with modules
+    named after the pack's operators; convolution batch-norms are separate modules here."""
+
+    def __init__(self):
+        super().__init__()
+        eps = 2e-5
+
+        def conv_bn(name, cin, cout, k, stride, pad, prelu):
+            setattr(self, name, nn.Conv2d(cin, cout, k, stride, pad, bias=False))
+            setattr(self, name + "_bn", nn.BatchNorm2d(cout, eps=eps))
+            if prelu:
+                setattr(self, name + "_prelu", nn.PReLU(cout))
+
+        conv_bn("conv0", 3, 64, 3, 1, 1, True)
+        self.plan = []
+        cin = 64
+        for si, (units, ch) in enumerate(zip([3, 13, 30, 3], [64, 128, 256, 512])):
+            for ui in range(units):
+                n = f"stage{si + 1}_unit{ui + 1}"
+                first = ui == 0
+                if first:
+                    conv_bn(n + "_conv1sc", cin, ch, 1, 2, 0, False)
+                setattr(self, n + "_bn1", nn.BatchNorm2d(cin, eps=eps))
+                conv_bn(n + "_conv1", cin, ch, 3, 1, 1, True)
+                conv_bn(n + "_conv2", ch, ch, 3, 2 if first else 1, 1, False)
+                self.plan.append((n, first))
+                cin = ch
+        self.bn1 = nn.BatchNorm2d(512, eps=eps)
+        self.pre_fc1 = nn.Linear(512 * 7 * 7, 512)          # the feature batch-norm is folded into it by the packer
+
+    def _cb(self, name, x):
+        x = getattr(self, name + "_bn")(getattr(self, name)(x))
+        return getattr(self, name + "_prelu")(x) if hasattr(self, name + "_prelu") else x
+
+    def forward(self, x):
+        x = self._cb("conv0", x)
+        for n, first in self.plan:
+            sc = self._cb(n + "_conv1sc", x) if first else x
+            y = getattr(self, n + "_bn1")(x)
+            y = self._cb(n + "_conv1", y)
+            x = self._cb(n + "_conv2", y) + sc
+        return self.pre_fc1(torch.flatten(self.bn1(x), 1))
+
+
 CASES = [
+    ("arcfaceresnet100", ArcFaceR100, 2e-5, 112),
     ("resnet18", lambda: torchvision.models.resnet18(weights=None), 1e-5, 224),
     ("resnet34", lambda: torchvision.models.resnet34(weights=None), 1e-5, 224),
     ("resnet50", lambda: torchvision.models.resnet50(weights=None), 1e-5, 224),
