@@ -524,6 +524,9 @@ def main():
         finally:
             del os.environ["PB_PROFILE_PREFIX"]
         jobs = ost.read_job_events(prefix + "_job_events.txt")
+        # lines are in completion order: the first ones are the instance warm-ups (which wait for every model
+        # to load) and the un-timed quarter of the run
+        jobs = jobs[len(jobs) - 3000:] if len(jobs) > 3000 else jobs
         n_inc_stages = kernels_per_request[names[1]][1]
         line["overhead_stack"] = {"what": "means per request from the server's job-event timeline (closed loop, host buffers): queueing = "
                                           "submission -> first dispatch, scheduling = dispatch -> run_next(), launch = inside run_next(), "

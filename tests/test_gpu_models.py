@@ -120,7 +120,7 @@ def test_small_net_layer_by_layer_bf16(tmp_path):
     m.close()
 
 
-@pytest.mark.parametrize("model", ["resnet18", "resnet34", "inception_v3", "resnet50", "googlenet", "squeezenet1_1", "densenet121", "arcfaceresnet100"])
+@pytest.mark.parametrize("model", ["resnet18", "resnet34", "inception_v3", "resnet50", "googlenet", "squeezenet1_1", "densenet121"])
 def test_imagenet_models_bf16_vs_fp32_oracle(models_dir, model):
     m = Model(os.path.join(models_dir, packer.pack_file_name(model)), 1)
     kinds = m.kinds()
@@ -180,6 +180,31 @@ def test_mobilenet_v2(models_dir):
     emu = og.run(og.Pack(packer.mobilenet_v2(seed=1234).to_bytes()), make_input("mobilenet"), emulate_bf16=True)
     assert float(np.abs(y - emu).max()) <= 1e-2 * float(np.abs(emu).max())
     assert int(y.argmax()) == int(ref.argmax())
+    m.close()
+
+
+def test_arcface_embedding(models_dir):
+    """ArcFace LResNet100E-IR: 100 convolutions deep, PReLU, a 512-d embedding out (no class scores, so no
+    argmax).  bf16 STORAGE through 49 residual units drifts by 1.3 % of the largest component from fp32 - the
+    bf16-emulating oracle shows the same 1.3 %, and per-tensor differences between the two bf16 executions
+    grow smoothly from 0.1 % after the stem to 1.7 % before the fc - so the bf16 path is held to 2.5e-2 against
+    the emulating oracle and, against the fp32 oracle, to the measure an embedding is used with (cosine
+    similarity >= 0.999; measured 0.99989).  The fp32 path of the same pack meets 1e-4."""
+    ref = GOLDEN["arcfaceresnet100"]
+    m = Model(os.path.join(models_dir, packer.pack_file_name("arcfaceresnet100")), 0)
+    y32 = m.run(make_input("arcfaceresnet100"))
+    assert float(np.abs(y32 - ref).max()) <= 1e-4 * float(np.abs(ref).max())
+    m.close()
+    m = Model(os.path.join(models_dir, packer.pack_file_name("arcfaceresnet100")), 1)
+    kinds = m.kinds()
+    assert kinds.count(capi.STAGE_CONV_UMMA) == 103 and capi.STAGE_CONV_SIMT not in kinds and capi.STAGE_AFFINE in kinds
+    x = make_input("arcfaceresnet100")
+    y = m.run(x)
+    emu = og.run(og.Pack(packer.arcface_r100(seed=1234).to_bytes()), x, emulate_bf16=True)
+    assert float(np.abs(y - emu).max()) <= 2.5e-2 * float(np.abs(emu).max())
+    cos = float(np.dot(y, ref) / (np.linalg.norm(y) * np.linalg.norm(ref)))
+    assert cos >= 0.999, cos
+    np.testing.assert_array_equal(m.run_groups(x), y)       # stage-group graphs give the same bits
     m.close()
 
 
