@@ -183,6 +183,23 @@ def test_mobilenet_v2(models_dir):
     m.close()
 
 
+@pytest.mark.parametrize("env", [{"PB_GRAPH_BRANCHES": "1"}, {"PB_FUSE_BRANCHES": "0"}, {"PB_PDL": "0"}, {"PB_GRAPH_SINGLE": "0", "PB_STAGE_GROUP": "1"}])
+def test_graph_capture_options_give_the_same_bits(models_dir, monkeypatch, env):
+    """The load-time switches of the stage graphs (parallel branch paths, no grouped launches, no programmatic
+    dependent launch, kernel-by-kernel without graphs) change scheduling only: bit-identical logits."""
+    path = os.path.join(models_dir, packer.pack_file_name("inception_v3"))
+    x = make_input("inception_v3")
+    m = Model(path, 1)
+    want = m.run_groups(x)
+    m.close()
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    m = Model(path, 1)
+    np.testing.assert_array_equal(m.run_groups(x), want)
+    np.testing.assert_array_equal(m.run_groups(x), want)
+    m.close()
+
+
 def test_arcface_embedding(models_dir):
     """ArcFace LResNet100E-IR: 100 convolutions deep, PReLU, a 512-d embedding out (no class scores, so no
     argmax).  bf16 STORAGE through 49 residual units drifts by 1.3 % of the largest component from fp32 - the
