@@ -237,6 +237,98 @@ def extras_leg(L, capi, device):
     return out
 
 
+def membound_leg(L, capi, device, scale="large", iters=10):
+    """The memory-bound operator kernels (depthwise convolution, pooling, elementwise, GEMV, layout
+    conversion, vec_add) on tensors larger than the 126 MB L2, through pb_op_launch, timed with CUDA events.
+
+    The batch-1 tensors of the served models are a few MB: at that size these kernels are launch- and
+    latency-bound whatever their code does.  This leg answers the other question, whether the kernels
+    themselves stream at HBM speed: bf16 channels-last tensors of 128 channels x H x W, every launch
+    reading and writing more than the L2 holds, algorithmic bytes (each input and output once, from
+    pb_op_info) over the CUDA-event time, against the measured copy bandwidth."""
+    import torch
+    hbm, _, how = measured_peaks()
+    torch.cuda.set_device(device)
+    hw = 1024 if scale == "large" else 768          # 128 ch x hw^2 x 2 B = 256 MB / 144 MB per tensor
+    Cc = 128
+    dev = torch.device("cuda", device)
+    x = torch.randn(hw * hw * Cc, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    x2 = torch.randn(hw * hw * Cc, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    y = torch.empty(hw * hw * Cc, device=dev, dtype=torch.bfloat16)
+    w9 = torch.randn(9 * Cc, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    fb = torch.randn(Cc, device=dev, dtype=torch.float32)
+    fs = torch.randn(Cc, device=dev, dtype=torch.float32)
+
+    def prm(kind, R=1, S=1, st=1, pad=0, groups=1, act=0, flags=0):
+        p = capi.OpParams()
+        p.dtype = 1
+        p.C, p.H, p.W, p.Cs = Cc, hw, hw, Cc
+        P = (hw + 2 * pad - R) // st + 1
+        p.K, p.P, p.Q, p.Ks = Cc, P, P, Cc
+        p.R, p.S, p.stride_h, p.stride_w, p.pad_h, p.pad_w, p.groups = R, S, st, st, pad, pad, groups
+        p.act, p.flags = act, flags
+        p.x, p.y = x.data_ptr(), y.data_ptr()
+        return p
+
+    cases = []
+    p = prm(capi.STAGE_DWCONV, 3, 3, 1, 1, groups=Cc, act=2); p.w, p.bias = w9.data_ptr(), fb.data_ptr()
+    cases.append(("dwconv 3x3 s1 (+bias, ReLU6)", capi.STAGE_DWCONV, p))
+    p = prm(capi.STAGE_DWCONV, 3, 3, 2, 1, groups=Cc, act=2); p.w, p.bias = w9.data_ptr(), fb.data_ptr()
+    cases.append(("dwconv 3x3 s2 (+bias, ReLU6)", capi.STAGE_DWCONV, p))
+    cases.append(("maxpool 3x3 s2", capi.STAGE_MAXPOOL, prm(capi.STAGE_MAXPOOL, 3, 3, 2, 0)))
+    cases.append(("maxpool 2x2 s2", capi.STAGE_MAXPOOL, prm(capi.STAGE_MAXPOOL, 2, 2, 2, 0)))
+    cases.append(("avgpool 3x3 s1 p1", capi.STAGE_AVGPOOL, prm(capi.STAGE_AVGPOOL, 3, 3, 1, 1, flags=1)))
+    p = prm(capi.STAGE_ADD, act=1); p.residual, p.res_Cs = x2.data_ptr(), Cc
+    cases.append(("add (+ReLU)", capi.STAGE_ADD, p))
+    p = prm(capi.STAGE_AFFINE, act=1); p.w, p.bias = fs.data_ptr(), fb.data_ptr()
+    cases.append(("affine (batch-norm + ReLU)", capi.STAGE_AFFINE, p))
+    # GEMV: rows x cols bf16 weights = the x2 buffer; input vector = head of x; fp32 results into y
+    cols = 16384
+    rows = (hw * hw * Cc) // cols
+    p = capi.OpParams()
+    p.dtype, p.C, p.H, p.W, p.Cs, p.K, p.P, p.Q, p.Ks = 1, cols, 1, 1, cols, rows, 1, 1, rows
+    p.R = p.S = p.stride_h = p.stride_w = p.groups = 1
+    p.x, p.w, p.y = x.data_ptr(), x2.data_ptr(), y.data_ptr()
+    cases.append((f"dense GEMV {rows}x{cols}", capi.STAGE_DENSE, p))
+    # NCHW fp32 -> channels-last bf16 (3 channels padded to 8): input = x viewed as fp32
+    # the output (8 bf16 per pixel = 16 B) is the larger side and has to fit y
+    side = int(((hw * hw * Cc * 2) // 16) ** 0.5) // 16 * 16
+    p = capi.OpParams()
+    p.dtype, p.C, p.H, p.W, p.Cs, p.K, p.P, p.Q, p.Ks = 1, 3, side, side, 8, 3, side, side, 8
+    p.R = p.S = p.stride_h = p.stride_w = p.groups = 1
+    p.x, p.y = x.data_ptr(), y.data_ptr()
+    cases.append((f"input layout 3x{side}x{side} fp32 -> channels-last bf16", capi.STAGE_INPUT, p))
+
+    out = {}
+    li = capi.LaunchInfo()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, kind, p in cases:
+        capi.check(L.pb_op_info(kind, C.byref(p), C.byref(li)), "pb_op_info")
+        for _ in range(3):
+            capi.check(L.pb_op_launch(kind, C.byref(p), None, 0, None), name)
+        torch.cuda.synchronize(device)
+        e0.record()
+        for _ in range(iters):
+            capi.check(L.pb_op_launch(kind, C.byref(p), None, 0, None), name)
+        e1.record()
+        torch.cuda.synchronize(device)
+        us = e0.elapsed_time(e1) * 1000.0 / iters
+        gbs = li.bytes / (us * 1e-6) / 1e9
+        out[name] = {"us": round(us, 1), "algorithmic_MB": round(li.bytes / 1e6, 1), "GB/s": round(gbs, 1),
+                     "frac_of_hbm_peak": round(gbs / hbm, 4)}
+    del x, x2, y
+    torch.cuda.empty_cache()
+    us = C.c_double()
+    n = 1 << (26 if scale == "large" else 25)
+    capi.check(L.pb_vec_add_bench(device, n, iters, 0, C.byref(us)), "pb_vec_add_bench")
+    gbs = 12.0 * n / (us.value * 1e-6) / 1e9
+    out[f"vec_add 2^{n.bit_length() - 1} fp32"] = {"us": round(us.value, 1), "algorithmic_MB": round(12.0 * n / 1e6, 1),
+                                                  "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4)}
+    return {"what": f"bf16 channels-last tensors of {Cc} x {hw} x {hw} ({hw * hw * Cc * 2 >> 20} MB each, larger than L2), "
+                    f"{iters} launches back to back after 3 warm-up launches, CUDA events",
+            "peak_GB/s": hbm, "of": how, "kernels": out}
+
+
 def ipc_leg(capi, models_dir, rates=(50000, 75000, 100000)):
     """The same mix through the PROCESS boundary: a llis_server process on GPU 0 and the llis_app_client load
     generator (open loop, Poisson) talking to it over the shared-memory rings and the pinned request pool."""
@@ -326,6 +418,9 @@ def main():
                     help="skip the serving legs; time only the Inception-v3 stages whose name contains SUBSTR "
                          "('' = all).  Small enough to run under ncu.")
     ap.add_argument("--iters", type=int, default=20, help="timed launches per stage in the roofline leg")
+    ap.add_argument("--only-membound", default=None, choices=["large", "small"],
+                    help="skip the serving legs; time only the memory-bound operator kernels on tensors larger than L2 "
+                         "(large: 256 MB per tensor; small: 144 MB per tensor, 3 launches each, for an ncu capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     global MIX
@@ -409,6 +504,10 @@ def main():
         devices = [d for d in range(args.gpus) for _ in range(args.replicas_per_gpu)]
         n_gpus = args.gpus
 
+    if args.only_membound is not None:
+        print(json.dumps({"membound": membound_leg(L, capi, devices[0], args.only_membound,
+                                                   10 if args.only_membound == "large" else 3)}))
+        return
     if args.only_roofline is not None:
         roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters, args.only_roofline)
         print(json.dumps({"roofline": roof, "kernel_table_inception_v3": table,
@@ -535,6 +634,7 @@ def main():
                                   "mnist": ost.overhead_stack(jobs, stages=1), "inception_v3": ost.overhead_stack(jobs, stages=n_inc_stages)}
     if args.extras and not dist:
         line["extras"] = extras_leg(L, capi, devices[0])
+        line["extras"]["membound"] = membound_leg(L, capi, devices[0])
         if args.workload == "mix":
             line["extras"]["ipc"] = ipc_leg(capi, tmp.name)
     if n_gpus == 1 and not args.no_roofline and args.workload == "mix":

@@ -250,6 +250,179 @@ __global__ void __launch_bounds__(256) pool_kernel(OpArgs a, uint32_t job_id, Fi
     PB_NOTIFY_END();
 }
 
+// ---- 3x3 windows over large tensors: a strip of output pixels per thread ------------------
+// dwconv_kernel and pool_kernel issue one guarded 128-bit load per filter tap and output vector: on a
+// tensor that fills the GPU each thread has about one load in flight at a time and every input vector is
+// fetched up to nine times through L1, so they run at the latency of the load path, not at HBM speed
+// (depthwise 3x3 stride 1 at 128 x 1024 x 1024 bf16: 19 % of the measured copy bandwidth).  Here a thread
+// owns one channel vector of kStrip consecutive output pixels of one output row.  Per input row it issues
+// ALL loads of the strip's window back to back, unconditionally (addresses clamped into the tensor, the
+// taps that fall outside are dropped afterwards), so 6-9 loads per thread are in flight; each loaded
+// vector feeds every output it belongs to, and a row of weights is loaded once per thread.
+// The order of the additions per output is the one of dwconv_kernel / pool_kernel (rows, then columns),
+// so results are bit-identical to theirs.  Used when the strips alone fill the GPU (strip_threads()).
+// With kStrip = 1 (every other 3x3 layer of stride 1 or 2, i.e. the batch-1 layers of the served models)
+// the thread owns one output vector as in dwconv_kernel / pool_kernel, but its nine loads are
+// unconditional and in flight together instead of one guarded load after the other.
+constexpr int kStripWide1 = 4, kStripWide2 = 2;   // stride 1: 18 loads per thread; stride 2: 15
+enum { kWinDw = 0, kWinMax = 1, kWinAvg = 2 };
+
+template <typename T> struct RawVec;
+template <> struct RawVec<float> { typedef float4 type; };
+template <> struct RawVec<__nv_bfloat16> { typedef uint4 type; };
+
+// Pairs of fp32 values in one 64-bit register, for the packed fp32 instructions of sm_100
+// (fma.rn.f32x2 / add.rn.f32x2: each half is the IEEE operation of the scalar instruction).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_max(uint64_t a, uint64_t b) {
+    float a0, a1, b0, b1;
+    f2_unpack(a, a0, a1);
+    f2_unpack(b, b0, b1);
+    return f2_pack(fmaxf(a0, b0), fmaxf(a1, b1));
+}
+// A 128-bit vector of activations as fp32 pairs: 2 pairs from float4, 4 pairs from 8 bf16.
+__device__ __forceinline__ void unpack_pairs(const float4& t, uint64_t (&r)[2]) {
+    r[0] = f2_pack(t.x, t.y);
+    r[1] = f2_pack(t.z, t.w);
+}
+__device__ __forceinline__ void unpack_pairs(const uint4& t, uint64_t (&r)[4]) {
+    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r[i] = f2_pack(__uint_as_float(u[i] << 16), __uint_as_float(u[i] & 0xffff0000u));
+}
+
+template <typename T, int kMode, int kStride, int kStrip>
+__global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    constexpr int N = Vec<T>::N;
+    constexpr int NP = N / 2;
+    constexpr int kCols = (kStrip - 1) * kStride + 3;
+    typedef typename RawVec<T>::type Raw;
+    const int cv = a.Cs / N;
+    const int strips = (a.Q + kStrip - 1) / kStrip;
+    const int total = a.P * strips * cv;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) {
+        const int c0 = (idx % cv) * N;
+        const int rest = idx / cv;
+        const int q0 = (rest % strips) * kStrip, p = rest / strips;
+        const T* __restrict__ x = static_cast<const T*>(a.x) + c0;
+        const T* __restrict__ w = static_cast<const T*>(a.w) + c0;
+        uint64_t acc[kStrip][NP];
+        const uint64_t init = (kMode == kWinMax) ? f2_pack(-INFINITY, -INFINITY) : f2_pack(0.f, 0.f);
+#pragma unroll
+        for (int t = 0; t < kStrip; ++t)
+#pragma unroll
+            for (int j = 0; j < NP; ++j) acc[t][j] = init;
+        const int iw0 = q0 * kStride - a.pad_w;
+        uint32_t col_ok = 0;                    // bit col: input column iw0 + col lies inside the tensor
+        int off[kCols];                         // element offset of that column within a row (clamped)
+#pragma unroll
+        for (int col = 0; col < kCols; ++col) {
+            const int iw = iw0 + col;
+            if (iw >= 0 && iw < a.W) col_ok |= 1u << col;
+            off[col] = min(max(iw, 0), a.W - 1) * a.Cs;
+        }
+        // every load of the 3 x kCols window first, so that all of them are in flight together
+        Raw raw[3][kCols];
+        uint32_t ok[3];
+        int rows = 0;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int ih = p * kStride + r - a.pad_h;
+            const bool row_ok = ih >= 0 && ih < a.H;
+            rows += row_ok ? 1 : 0;
+            ok[r] = row_ok ? col_ok : 0u;
+            const T* xrow = x + (size_t)min(max(ih, 0), a.H - 1) * a.W * a.Cs;
+#pragma unroll
+            for (int col = 0; col < kCols; ++col) raw[r][col] = *reinterpret_cast<const Raw*>(xrow + off[col]);
+        }
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            uint64_t wv[3][NP];
+            if (kMode == kWinDw) {
+#pragma unroll
+                for (int s = 0; s < 3; ++s) unpack_pairs(__ldg(reinterpret_cast<const Raw*>(w + (r * 3 + s) * a.Cs)), wv[s]);
+            }
+#pragma unroll
+            for (int col = 0; col < kCols; ++col) {
+                if (!((ok[r] >> col) & 1u)) continue;
+                uint64_t xv[NP];
+                unpack_pairs(raw[r][col], xv);
+#pragma unroll
+                for (int s = 0; s < 3; ++s) {
+                    // input column col is tap s of output t when col == t * kStride + s
+                    if (col - s < 0 || (col - s) % kStride != 0 || (col - s) / kStride >= kStrip) continue;
+                    const int t = (col - s) / kStride;
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) {
+                        if (kMode == kWinDw) acc[t][j] = f2_fma(xv[j], wv[s][j], acc[t][j]);
+                        else if (kMode == kWinMax) acc[t][j] = f2_max(acc[t][j], xv[j]);
+                        else acc[t][j] = f2_add(acc[t][j], xv[j]);
+                    }
+                }
+            }
+        }
+        T* yrow = static_cast<T*>(a.y) + ((size_t)p * a.Q + q0) * a.Ks + a.out_c_off + c0;
+        float bias[N];
+        if (kMode == kWinDw) {
+#pragma unroll
+            for (int j = 0; j < N; ++j) bias[j] = (a.bias && c0 + j < a.K) ? a.bias[c0 + j] : 0.f;
+        }
+#pragma unroll
+        for (int t = 0; t < kStrip; ++t) {
+            const int q = q0 + t;
+            if (q >= a.Q) break;
+            float v[N];
+#pragma unroll
+            for (int j = 0; j < NP; ++j) f2_unpack(acc[t][j], v[2 * j], v[2 * j + 1]);
+            Vec<T> o;
+            if (kMode == kWinDw) {
+                // the activation is the same for every element: branch once, not per element
+                if (a.act == 2) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.K) ? fminf(fmaxf(v[j] + bias[j], 0.f), 6.f) : 0.f;
+                } else if (a.act == 1) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.K) ? fmaxf(v[j] + bias[j], 0.f) : 0.f;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.K) ? v[j] + bias[j] : 0.f;
+                }
+            } else if (kMode == kWinMax) {
+#pragma unroll
+                for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.C) ? v[j] : 0.f;
+            } else {
+                float div = 9.f;
+                if (!(a.flags & 1)) {
+                    const int lo = max(q * kStride - a.pad_w, 0), hi = min(q * kStride - a.pad_w + 3, a.W);
+                    const int cnt = rows * max(hi - lo, 0);
+                    div = (float)(cnt > 0 ? cnt : 1);
+                }
+#pragma unroll
+                for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.C) ? v[j] / div : 0.f;
+            }
+            o.store(yrow + (size_t)t * a.Ks);
+        }
+    }
+    PB_NOTIFY_END();
+}
+
 // ---- global average pool: [HW][Cs] -> [Cs] ---------------------------------------
 // Block = 32 channel vectors x 8 pixel groups; shared-memory reduction over the groups.
 template <typename T>
@@ -312,6 +485,7 @@ __global__ void __launch_bounds__(256) dense_kernel(OpArgs a, uint32_t job_id, F
         const T* __restrict__ x = static_cast<const T*>(a.x);
         const T* __restrict__ w = static_cast<const T*>(a.w) + (size_t)warp * a.C;
         float acc = 0.f;
+#pragma unroll 4      // four weight vectors in flight per lane: a row is streamed once, from HBM
         for (int i = lane * N; i < a.C; i += 32 * N) {
             const Vec<T> xv = Vec<T>::load(x + i);
             const Vec<T> wv = Vec<T>::load(w + i);
@@ -356,17 +530,46 @@ __global__ void __launch_bounds__(256) affine_kernel(OpArgs a, uint32_t job_id, 
     constexpr int N = Vec<T>::N;
     const int cv = (a.C + N - 1) / N;
     const size_t total = (size_t)a.H * a.W * cv;
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < total) {
-        const int c0 = (int)(i % cv) * N;
-        const size_t pix = i / cv;
-        const Vec<T> u = Vec<T>::load(static_cast<const T*>(a.x) + pix * a.Cs + c0);
-        const float* __restrict__ sc = static_cast<const float*>(a.w);
-        Vec<T> o;
+    // Two vectors per thread, half the tensor apart, both loads issued before either is used: with one
+    // load in flight per thread the kernel ran at 54 % of the copy bandwidth on a tensor larger than L2.
+    const size_t half = (total + 1) / 2;
+    const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i0 < half) {
+        const bool two = i0 + half < total;
+        size_t pix[2];
+        int c0[2];
+        Vec<T> u[2];
 #pragma unroll
-        for (int j = 0; j < N; ++j)
-            o.v[j] = (c0 + j < a.C) ? act_fn(u.v[j] * __ldg(sc + c0 + j) + __ldg(a.bias + c0 + j), a.act) : 0.f;
-        o.store(static_cast<T*>(a.y) + pix * a.Ks + a.out_c_off + c0);
+        for (int h = 0; h < 2; ++h) {
+            const size_t i = (h == 1 && two) ? i0 + half : i0;
+            // 32-bit division whenever the index fits (always, short of a 64 GB tensor)
+            pix[h] = total <= 0xffffffffull ? (size_t)((uint32_t)i / (uint32_t)cv) : i / cv;
+            c0[h] = (int)(i - pix[h] * cv) * N;
+            u[h] = Vec<T>::load(static_cast<const T*>(a.x) + pix[h] * a.Cs + c0[h]);
+        }
+        const float* __restrict__ sc = static_cast<const float*>(a.w);
+        const bool aligned = ((reinterpret_cast<uintptr_t>(sc) | reinterpret_cast<uintptr_t>(a.bias)) & 15) == 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (h == 1 && !two) break;
+            Vec<T> o;
+            if (c0[h] + N <= a.C && aligned) {
+                // whole vector inside the tensor: scale and bias as 128-bit loads instead of 2 x N scalar ones
+                float scv[N], biv[N];
+#pragma unroll
+                for (int j = 0; j < N; j += 4) {
+                    *reinterpret_cast<float4*>(scv + j) = __ldg(reinterpret_cast<const float4*>(sc + c0[h] + j));
+                    *reinterpret_cast<float4*>(biv + j) = __ldg(reinterpret_cast<const float4*>(a.bias + c0[h] + j));
+                }
+#pragma unroll
+                for (int j = 0; j < N; ++j) o.v[j] = act_fn(u[h].v[j] * scv[j] + biv[j], a.act);
+            } else {
+#pragma unroll
+                for (int j = 0; j < N; ++j)
+                    o.v[j] = (c0[h] + j < a.C) ? act_fn(u[h].v[j] * __ldg(sc + c0[h] + j) + __ldg(a.bias + c0[h] + j), a.act) : 0.f;
+            }
+            o.store(static_cast<T*>(a.y) + pix[h] * a.Ks + a.out_c_off + c0[h]);
+        }
     }
     PB_NOTIFY_END();
 }
@@ -528,6 +731,37 @@ static uint32_t static_smem_of(F fn) {
 // Threads of work -> blocks of 256.
 static uint32_t blocks_for(size_t work) { return (uint32_t)((work + 255) / 256 > 0 ? (work + 255) / 256 : 1); }
 
+// Output pixels per thread of window3_strip_kernel for a depthwise convolution or pooling layer: 0 when the
+// window is not 3x3 with stride 1 or 2 (the layer keeps dwconv_kernel / pool_kernel); the wide strip when the
+// strips (4 pixels at stride 1, 2 at stride 2) alone give each SM 2048 threads; else 1 (all batch-1 layers of the
+// served models: there the launch is latency-bound and more, smaller threads finish sooner).
+static int strip_of(const pb_op_params* p) {
+    if (p->R != 3 || p->S != 3 || p->stride_h != p->stride_w || (p->stride_h != 1 && p->stride_h != 2)) return 0;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        cudaGetLastError();
+        sms = 148;
+    }
+    const int wide = p->stride_h == 1 ? kStripWide1 : kStripWide2;
+    const size_t n = (size_t)p->P * ((p->Q + wide - 1) / wide) * (p->Cs / vec_n(p->dtype));
+    return n >= (size_t)sms * 2048 ? wide : 1;
+}
+static size_t strip_threads(const pb_op_params* p, int strip) {
+    return (size_t)p->P * ((p->Q + strip - 1) / strip) * (p->Cs / vec_n(p->dtype));
+}
+
+template <int kMode>
+static const void* window3_fn(bool f32, int stride, int strip) {
+#define PB_W3(T) (stride == 1 ? (strip == 1 ? (const void*)window3_strip_kernel<T, kMode, 1, 1> : (const void*)window3_strip_kernel<T, kMode, 1, kStripWide1>) \
+                              : (strip == 1 ? (const void*)window3_strip_kernel<T, kMode, 2, 1> : (const void*)window3_strip_kernel<T, kMode, 2, kStripWide2>))
+    return f32 ? PB_W3(float) : PB_W3(__nv_bfloat16);
+#undef PB_W3
+}
+static const void* window3_fn(int kind, bool f32, int stride, int strip) {
+    return kind == PB_STAGE_DWCONV ? window3_fn<kWinDw>(f32, stride, strip)
+         : kind == PB_STAGE_MAXPOOL ? window3_fn<kWinMax>(f32, stride, strip) : window3_fn<kWinAvg>(f32, stride, strip);
+}
+
 int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
     memset(out, 0, sizeof(*out));
     out->kind = (uint32_t)kind;
@@ -559,6 +793,10 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
         case PB_STAGE_DWCONV:
             out->num_blocks = blocks_for((size_t)p->P * p->Q * (p->Cs / N));
             out->regs_per_thread = f32 ? regs_of(dwconv_kernel<float>) : regs_of(dwconv_kernel<__nv_bfloat16>);
+            if (const int strip = strip_of(p)) {
+                out->num_blocks = blocks_for(strip_threads(p, strip));
+                out->regs_per_thread = regs_of(window3_fn(kind, f32, p->stride_h, strip));
+            }
             out->flops = 2ull * out_elems * p->R * p->S;
             out->bytes = es * (in_elems + (size_t)p->K * p->R * p->S + out_elems) + 4ull * p->K;
             break;
@@ -569,6 +807,10 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
                 out->regs_per_thread = f32 ? regs_of(pool_kernel<float, true>) : regs_of(pool_kernel<__nv_bfloat16, true>);
             else
                 out->regs_per_thread = f32 ? regs_of(pool_kernel<float, false>) : regs_of(pool_kernel<__nv_bfloat16, false>);
+            if (const int strip = strip_of(p)) {
+                out->num_blocks = blocks_for(strip_threads(p, strip));
+                out->regs_per_thread = regs_of(window3_fn(kind, f32, p->stride_h, strip));
+            }
             out->bytes = es * (in_elems + out_elems);
             break;
         case PB_STAGE_GAP:
@@ -589,7 +831,7 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
             out->bytes = es * 3 * in_elems;
             break;
         case PB_STAGE_AFFINE:
-            out->num_blocks = blocks_for((size_t)p->H * p->W * pb::ceil_div(p->C, N));
+            out->num_blocks = blocks_for(((size_t)p->H * p->W * pb::ceil_div(p->C, N) + 1) / 2);    // two vectors per thread
             out->regs_per_thread = f32 ? regs_of(affine_kernel<float>) : regs_of(affine_kernel<__nv_bfloat16>);
             out->flops = 2ull * p->C * p->H * p->W;
             out->bytes = es * 2ull * p->C * p->H * p->W + 8ull * p->C;
@@ -654,14 +896,26 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
         case PB_STAGE_DWCONV:
             PB_REQUIRE(a.groups == a.C && a.K == a.C, "dwconv: needs groups == C == K");
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "dwconv: output slice must be vector aligned");
+            if (const int strip = strip_of(p)) {
+                launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
+                break;
+            }
             PB_DISPATCH(dwconv_kernel<float>, dwconv_kernel<__nv_bfloat16>, a, job_id, nf);
             break;
         case PB_STAGE_MAXPOOL:
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "pool: output slice must be vector aligned");
+            if (const int strip = strip_of(p)) {
+                launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
+                break;
+            }
             PB_DISPATCH((pool_kernel<float, true>), (pool_kernel<__nv_bfloat16, true>), a, job_id, nf);
             break;
         case PB_STAGE_AVGPOOL:
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "pool: output slice must be vector aligned");
+            if (const int strip = strip_of(p)) {
+                launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
+                break;
+            }
             PB_DISPATCH((pool_kernel<float, false>), (pool_kernel<__nv_bfloat16, false>), a, job_id, nf);
             break;
         case PB_STAGE_GAP:

@@ -331,3 +331,53 @@ def test_input_patch_matrix(dtype, geom):
             ref[:, :, (r * S + s_) * C_:(r * S + s_ + 1) * C_] = np.transpose(xp[:, r:r + st * P:st, s_:s_ + st * Q:st], (1, 2, 0))
     np.testing.assert_array_equal(full[:, :, :kp], og.round_bf16(ref) if dtype == 1 else ref)
     assert (full[:, :, kp:] == 0).all()
+
+
+# ---- tensors large enough for the strip / wide kernels (chosen by the library from the tensor's size) ----
+def _strip_blocks(P, Q, cs, dtype, stride):
+    strip = 4 if stride == 1 else 2          # output pixels per thread of the strip kernel
+    return -(-(P * (-(-Q // strip)) * (cs // gu.vec(dtype))) // 256)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("case", [(64, 402, 398, 1), (64, 803, 797, 2)])
+def test_dwconv_large_tensor_uses_strips(case, dtype):
+    """Depthwise 3x3 on a tensor whose strips (4 pixels at stride 1, 2 at stride 2) fill the GPU: the strip kernel must run (block count)
+    and agree with the oracle like the one-pixel kernel does, ragged last strip and borders included."""
+    L = capi.load()
+    C_, H, W, st = case
+    P, Q = (H + 2 - 3) // st + 1, (W + 2 - 3) // st + 1
+    p = _params(dtype, (C_, H, W), C_, P, Q, C_, 3, 3, st, st, 1, 1, groups=C_, act=2)
+    li = capi.LaunchInfo()
+    capi.check(L.pb_op_info(capi.STAGE_DWCONV, C.byref(p), C.byref(li)), "pb_op_info")
+    assert li.num_blocks == _strip_blocks(P, Q, C_, dtype, st)
+    _run_conv(capi.STAGE_DWCONV, dtype, C_, H, W, C_, 3, 3, st, st, 1, 1, groups=C_, act=2)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("s,pad,hw,include_pad", [(1, 1, 402, True), (1, 1, 402, False), (2, 0, 803, True), (2, 1, 805, False)])
+def test_pools_large_tensor_use_strips(dtype, s, pad, hw, include_pad):
+    L = capi.load()
+    c = 64
+    x = RNG.standard_normal((c, hw, hw), dtype=np.float32)
+    if dtype == 1:
+        x = og.round_bf16(x)
+    P = (hw + 2 * pad - 3) // s + 1
+    xd, cs = gu.to_device_cl(x, dtype)
+    for kind, ref in ((capi.STAGE_MAXPOOL, og.maxpool(x, (3, 3), (s, s), (pad, pad))),
+                      (capi.STAGE_AVGPOOL, og.avgpool(x, (3, 3), (s, s), (pad, pad), include_pad))):
+        yd, ks = gu.empty_cl(P, P, c + 16, dtype, fill=3.0)
+        prm = _params(dtype, (c, hw, hw), c, P, P, ks, 3, 3, s, s, pad, pad, flags=1 if include_pad else 0, out_c_off=8, Cs=cs)
+        prm.x, prm.y = xd.data_ptr(), yd.data_ptr()
+        li = capi.LaunchInfo()
+        capi.check(L.pb_op_info(kind, C.byref(prm), C.byref(li)), "pb_op_info")
+        assert li.num_blocks == _strip_blocks(P, P, cs, dtype, s)
+        capi.check(L.pb_op_launch(kind, C.byref(prm), None, 0, None), "pool")
+        gu.sync()
+        full = gu.from_device_cl(yd, c + 16)
+        got = full[8:8 + c]
+        if kind == capi.STAGE_MAXPOOL:
+            np.testing.assert_array_equal(got, ref)
+        else:
+            _assert_close(got, ref, dtype)
+        assert (full[:8] == 3.0).all() and (full[8 + c:] == 3.0).all()     # channels outside the slice untouched
