@@ -270,6 +270,19 @@ enum { kWinDw = 0, kWinMax = 1, kWinAvg = 2 };
 template <typename T> struct RawVec;
 template <> struct RawVec<float> { typedef float4 type; };
 template <> struct RawVec<__nv_bfloat16> { typedef uint4 type; };
+__device__ __forceinline__ Vec<float> vec_of(const float4& t) {
+    Vec<float> r; r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; return r;
+}
+__device__ __forceinline__ Vec<__nv_bfloat16> vec_of(const uint4& t) {
+    Vec<__nv_bfloat16> r;
+    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        r.v[2 * i] = __uint_as_float(u[i] << 16);
+        r.v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+    return r;
+}
 
 // Pairs of fp32 values in one 64-bit register, for the packed fp32 instructions of sm_100
 // (fma.rn.f32x2 / add.rn.f32x2: each half is the IEEE operation of the scalar instruction).
@@ -414,8 +427,18 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
                     const int cnt = rows * max(hi - lo, 0);
                     div = (float)(cnt > 0 ? cnt : 1);
                 }
+                // v / div, correctly rounded, in three instructions per element instead of the division
+                // sequence (which was more than half of this kernel's instructions): with inv the correctly
+                // rounded reciprocal, q = v * inv is within an ulp, the fused residual v - div * q is exact
+                // and q + r * inv rounds to the quotient (Markstein); non-finite q passes through.
+                const float inv = 1.f / div;
 #pragma unroll
-                for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.C) ? v[j] / div : 0.f;
+                for (int j = 0; j < N; ++j) {
+                    const float qv = v[j] * inv;
+                    const float rv = fmaf(-div, qv, v[j]);
+                    const float out = fabsf(qv) <= 3.0e38f ? fmaf(rv, inv, qv) : qv;
+                    o.v[j] = (c0 + j < a.C) ? out : 0.f;
+                }
             }
             o.store(yrow + (size_t)t * a.Ks);
         }
@@ -524,34 +547,38 @@ __global__ void __launch_bounds__(256) add_kernel(OpArgs a, uint32_t job_id, Fin
 // ---- per-channel affine (+activation) over [HW][C] of a tensor with channel stride Cs ----------
 // y[pix][c] = act(x[pix][c] * scale[c] + bias[c]) for the first a.C channels: the folded batch-norm +
 // ReLU that DenseNet applies to the concatenated features BEFORE each convolution.
+constexpr int kAffinePer = 4;      // vectors per thread
+
 template <typename T>
 __global__ void __launch_bounds__(256) affine_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
     constexpr int N = Vec<T>::N;
+    typedef typename RawVec<T>::type Raw;
     const int cv = (a.C + N - 1) / N;
     const size_t total = (size_t)a.H * a.W * cv;
-    // Two vectors per thread, half the tensor apart, both loads issued before either is used: with one
-    // load in flight per thread the kernel ran at 54 % of the copy bandwidth on a tensor larger than L2.
-    const size_t half = (total + 1) / 2;
+    // kAffinePer vectors per thread, a quarter of the tensor apart, all loads issued (as raw 128-bit words)
+    // before any is used: with one load in flight per thread the kernel ran at 54 % of the copy bandwidth
+    // on a tensor larger than L2, which needs about 50 KB in flight per SM.
+    const size_t part = (total + kAffinePer - 1) / kAffinePer;
     const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i0 < half) {
-        const bool two = i0 + half < total;
-        size_t pix[2];
-        int c0[2];
-        Vec<T> u[2];
+    if (i0 < part) {
+        size_t pix[kAffinePer];
+        int c0[kAffinePer];
+        Raw raw[kAffinePer];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const size_t i = (h == 1 && two) ? i0 + half : i0;
+        for (int h = 0; h < kAffinePer; ++h) {
+            const size_t i = (i0 + h * part < total) ? i0 + h * part : i0;
             // 32-bit division whenever the index fits (always, short of a 64 GB tensor)
             pix[h] = total <= 0xffffffffull ? (size_t)((uint32_t)i / (uint32_t)cv) : i / cv;
             c0[h] = (int)(i - pix[h] * cv) * N;
-            u[h] = Vec<T>::load(static_cast<const T*>(a.x) + pix[h] * a.Cs + c0[h]);
+            raw[h] = *reinterpret_cast<const Raw*>(static_cast<const T*>(a.x) + pix[h] * a.Cs + c0[h]);
         }
         const float* __restrict__ sc = static_cast<const float*>(a.w);
         const bool aligned = ((reinterpret_cast<uintptr_t>(sc) | reinterpret_cast<uintptr_t>(a.bias)) & 15) == 0;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            if (h == 1 && !two) break;
+        for (int h = 0; h < kAffinePer; ++h) {
+            if (h > 0 && i0 + h * part >= total) break;
+            const Vec<T> u = vec_of(raw[h]);
             Vec<T> o;
             if (c0[h] + N <= a.C && aligned) {
                 // whole vector inside the tensor: scale and bias as 128-bit loads instead of 2 x N scalar ones
@@ -562,11 +589,11 @@ __global__ void __launch_bounds__(256) affine_kernel(OpArgs a, uint32_t job_id, 
                     *reinterpret_cast<float4*>(biv + j) = __ldg(reinterpret_cast<const float4*>(a.bias + c0[h] + j));
                 }
 #pragma unroll
-                for (int j = 0; j < N; ++j) o.v[j] = act_fn(u[h].v[j] * scv[j] + biv[j], a.act);
+                for (int j = 0; j < N; ++j) o.v[j] = act_fn(u.v[j] * scv[j] + biv[j], a.act);
             } else {
 #pragma unroll
                 for (int j = 0; j < N; ++j)
-                    o.v[j] = (c0[h] + j < a.C) ? act_fn(u[h].v[j] * __ldg(sc + c0[h] + j) + __ldg(a.bias + c0[h] + j), a.act) : 0.f;
+                    o.v[j] = (c0[h] + j < a.C) ? act_fn(u.v[j] * __ldg(sc + c0[h] + j) + __ldg(a.bias + c0[h] + j), a.act) : 0.f;
             }
             o.store(static_cast<T*>(a.y) + pix[h] * a.Ks + a.out_c_off + c0[h]);
         }
@@ -831,7 +858,7 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
             out->bytes = es * 3 * in_elems;
             break;
         case PB_STAGE_AFFINE:
-            out->num_blocks = blocks_for(((size_t)p->H * p->W * pb::ceil_div(p->C, N) + 1) / 2);    // two vectors per thread
+            out->num_blocks = blocks_for(((size_t)p->H * p->W * pb::ceil_div(p->C, N) + kAffinePer - 1) / kAffinePer);
             out->regs_per_thread = f32 ? regs_of(affine_kernel<float>) : regs_of(affine_kernel<__nv_bfloat16>);
             out->flops = 2ull * p->C * p->H * p->W;
             out->bytes = es * 2ull * p->C * p->H * p->W + 8ull * p->C;
