@@ -284,39 +284,60 @@ __device__ __forceinline__ Vec<__nv_bfloat16> vec_of(const uint4& t) {
     return r;
 }
 
-// Pairs of fp32 values in one 64-bit register, for the packed fp32 instructions of sm_100
-// (fma.rn.f32x2 / add.rn.f32x2: each half is the IEEE operation of the scalar instruction).
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-    uint64_t r;
+// Pairs of fp32 values.  PB_F32X2=1 keeps a pair in one 64-bit register and uses the packed fp32
+// instructions of sm_100 (fma.rn.f32x2 / add.rn.f32x2: each half is the IEEE operation of the scalar
+// instruction); otherwise the pair is two scalars and the compiler schedules scalar instructions.
+#ifndef PB_F32X2
+#define PB_F32X2 0
+#endif
+#if PB_F32X2
+typedef uint64_t f2_t;
+__device__ __forceinline__ f2_t f2_pack(float lo, float hi) {
+    f2_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
     return r;
 }
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
+__device__ __forceinline__ void f2_unpack(f2_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f2_t f2_fma(f2_t a, f2_t b, f2_t c) {
+    f2_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-    uint64_t d;
+__device__ __forceinline__ f2_t f2_add(f2_t a, f2_t b) {
+    f2_t d;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-__device__ __forceinline__ uint64_t f2_max(uint64_t a, uint64_t b) {
+__device__ __forceinline__ f2_t f2_max(f2_t a, f2_t b) {
     float a0, a1, b0, b1;
     f2_unpack(a, a0, a1);
     f2_unpack(b, b0, b1);
     return f2_pack(fmaxf(a0, b0), fmaxf(a1, b1));
 }
+#else
+struct f2_t { float lo, hi; };
+__device__ __forceinline__ f2_t f2_pack(float lo, float hi) { f2_t r; r.lo = lo; r.hi = hi; return r; }
+__device__ __forceinline__ void f2_unpack(f2_t v, float& lo, float& hi) { lo = v.lo; hi = v.hi; }
+__device__ __forceinline__ f2_t f2_fma(f2_t a, f2_t b, f2_t c) { return f2_pack(fmaf(a.lo, b.lo, c.lo), fmaf(a.hi, b.hi, c.hi)); }
+__device__ __forceinline__ f2_t f2_add(f2_t a, f2_t b) { return f2_pack(a.lo + b.lo, a.hi + b.hi); }
+__device__ __forceinline__ f2_t f2_max(f2_t a, f2_t b) { return f2_pack(fmaxf(a.lo, b.lo), fmaxf(a.hi, b.hi)); }
+#endif
 // A 128-bit vector of activations as fp32 pairs: 2 pairs from float4, 4 pairs from 8 bf16.
-__device__ __forceinline__ void unpack_pairs(const float4& t, uint64_t (&r)[2]) {
+__device__ __forceinline__ void unpack_pairs(const float4& t, f2_t (&r)[2]) {
     r[0] = f2_pack(t.x, t.y);
     r[1] = f2_pack(t.z, t.w);
 }
-__device__ __forceinline__ void unpack_pairs(const uint4& t, uint64_t (&r)[4]) {
+__device__ __forceinline__ void unpack_pairs(const uint4& t, f2_t (&r)[4]) {
     const uint32_t u[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) r[i] = f2_pack(__uint_as_float(u[i] << 16), __uint_as_float(u[i] & 0xffff0000u));
+}
+
+// Dynamic shared memory of a depthwise launch: filter [3][3][Cs] + fp32 biases [Cs], or 0 when that
+// exceeds what a kernel gets without opting in (the kernel then reads the filter from global memory).
+__host__ __device__ __forceinline__ int window3_smem_bytes(int Cs, int elem_bytes) {
+    const int n = 9 * Cs * elem_bytes + 4 * Cs;
+    return n <= 40 * 1024 ? n : 0;
 }
 
 template <typename T, int kMode, int kStride, int kStrip>
@@ -330,14 +351,28 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
     const int strips = (a.Q + kStrip - 1) / kStrip;
     const int total = a.P * strips * cv;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    // Depthwise: the block's copy of the filter ([3][3][Cs]) and of the biases, in shared memory.  Read
+    // through L1 they compete with the streamed activations for cache lines, and a miss sits on every
+    // thread's critical path three times; the host passes window3_smem_bytes() of dynamic shared memory
+    // (0 = the filter does not fit: read it from global memory).
+    extern __shared__ __align__(16) unsigned char s_w3[];
+    const bool staged = kMode == kWinDw && window3_smem_bytes(a.Cs, (int)sizeof(T)) > 0;
+    if (staged) {
+        Raw* sw = reinterpret_cast<Raw*>(s_w3);
+        const Raw* gw = static_cast<const Raw*>(a.w);
+        for (int i = threadIdx.x; i < 9 * cv; i += blockDim.x) sw[i] = __ldg(gw + i);
+        float* sb = reinterpret_cast<float*>(s_w3 + (size_t)9 * a.Cs * sizeof(T));
+        for (int i = threadIdx.x; i < a.Cs; i += blockDim.x) sb[i] = (a.bias && i < a.K) ? a.bias[i] : 0.f;
+        __syncthreads();
+    }
     if (idx < total) {
         const int c0 = (idx % cv) * N;
         const int rest = idx / cv;
         const int q0 = (rest % strips) * kStrip, p = rest / strips;
         const T* __restrict__ x = static_cast<const T*>(a.x) + c0;
-        const T* __restrict__ w = static_cast<const T*>(a.w) + c0;
-        uint64_t acc[kStrip][NP];
-        const uint64_t init = (kMode == kWinMax) ? f2_pack(-INFINITY, -INFINITY) : f2_pack(0.f, 0.f);
+        const T* __restrict__ w = (staged ? reinterpret_cast<const T*>(s_w3) : static_cast<const T*>(a.w)) + c0;
+        f2_t acc[kStrip][NP];
+        const f2_t init = (kMode == kWinMax) ? f2_pack(-INFINITY, -INFINITY) : f2_pack(0.f, 0.f);
 #pragma unroll
         for (int t = 0; t < kStrip; ++t)
 #pragma unroll
@@ -367,15 +402,15 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
         }
 #pragma unroll
         for (int r = 0; r < 3; ++r) {
-            uint64_t wv[3][NP];
+            f2_t wv[3][NP];
             if (kMode == kWinDw) {
 #pragma unroll
-                for (int s = 0; s < 3; ++s) unpack_pairs(__ldg(reinterpret_cast<const Raw*>(w + (r * 3 + s) * a.Cs)), wv[s]);
+                for (int s = 0; s < 3; ++s) unpack_pairs(*reinterpret_cast<const Raw*>(w + (r * 3 + s) * a.Cs), wv[s]);
             }
 #pragma unroll
             for (int col = 0; col < kCols; ++col) {
                 if (!((ok[r] >> col) & 1u)) continue;
-                uint64_t xv[NP];
+                f2_t xv[NP];
                 unpack_pairs(raw[r][col], xv);
 #pragma unroll
                 for (int s = 0; s < 3; ++s) {
@@ -395,7 +430,9 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
         float bias[N];
         if (kMode == kWinDw) {
 #pragma unroll
-            for (int j = 0; j < N; ++j) bias[j] = (a.bias && c0 + j < a.K) ? a.bias[c0 + j] : 0.f;
+            for (int j = 0; j < N; ++j)
+                bias[j] = staged ? reinterpret_cast<const float*>(s_w3 + (size_t)9 * a.Cs * sizeof(T))[c0 + j]
+                                 : ((a.bias && c0 + j < a.K) ? a.bias[c0 + j] : 0.f);
         }
 #pragma unroll
         for (int t = 0; t < kStrip; ++t) {
@@ -823,6 +860,7 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
             if (const int strip = strip_of(p)) {
                 out->num_blocks = blocks_for(strip_threads(p, strip));
                 out->regs_per_thread = regs_of(window3_fn(kind, f32, p->stride_h, strip));
+                out->smem_per_block = (uint32_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2);
             }
             out->flops = 2ull * out_elems * p->R * p->S;
             out->bytes = es * (in_elems + (size_t)p->K * p->R * p->S + out_elems) + 4ull * p->K;
@@ -876,12 +914,16 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
     return PB_OK;
 }
 
+static thread_local size_t t_launch_smem = 0;      // dynamic shared memory of the next launch_k (reset by it)
+
 template <typename... KArgs, typename... Args>
 static void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, bool pdl, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.stream = st;
+    cfg.dynamicSmemBytes = t_launch_smem;
+    t_launch_smem = 0;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -924,6 +966,7 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
             PB_REQUIRE(a.groups == a.C && a.K == a.C, "dwconv: needs groups == C == K");
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "dwconv: output slice must be vector aligned");
             if (const int strip = strip_of(p)) {
+                t_launch_smem = (size_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2);
                 launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
                 break;
             }
