@@ -354,9 +354,10 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
     // Depthwise: the block's copy of the filter ([3][3][Cs]) and of the biases, in shared memory.  Read
     // through L1 they compete with the streamed activations for cache lines, and a miss sits on every
     // thread's critical path three times; the host passes window3_smem_bytes() of dynamic shared memory
-    // (0 = the filter does not fit: read it from global memory).
+    // (0 = the filter does not fit: read it from global memory).  Wide strips only: on a batch-1 layer the
+    // staging round trip would come before the first activation load of a block that lives a few microseconds.
     extern __shared__ __align__(16) unsigned char s_w3[];
-    const bool staged = kMode == kWinDw && window3_smem_bytes(a.Cs, (int)sizeof(T)) > 0;
+    const bool staged = kMode == kWinDw && kStrip > 1 && window3_smem_bytes(a.Cs, (int)sizeof(T)) > 0;
     if (staged) {
         Raw* sw = reinterpret_cast<Raw*>(s_w3);
         const Raw* gw = static_cast<const Raw*>(a.w);
@@ -860,7 +861,7 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
             if (const int strip = strip_of(p)) {
                 out->num_blocks = blocks_for(strip_threads(p, strip));
                 out->regs_per_thread = regs_of(window3_fn(kind, f32, p->stride_h, strip));
-                out->smem_per_block = (uint32_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2);
+                out->smem_per_block = strip > 1 ? (uint32_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2) : 0;
             }
             out->flops = 2ull * out_elems * p->R * p->S;
             out->bytes = es * (in_elems + (size_t)p->K * p->R * p->S + out_elems) + 4ull * p->K;
@@ -966,7 +967,7 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
             PB_REQUIRE(a.groups == a.C && a.K == a.C, "dwconv: needs groups == C == K");
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "dwconv: output slice must be vector aligned");
             if (const int strip = strip_of(p)) {
-                t_launch_smem = (size_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2);
+                t_launch_smem = strip > 1 ? (size_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2) : 0;
                 launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
                 break;
             }
