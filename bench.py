@@ -398,8 +398,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=1000, help="requests per GPU per step")
-    ap.add_argument("--concurrency", type=int, default=64, help="closed-loop clients per replica")
-    ap.add_argument("--inception-instances", type=int, default=32, help="Inception-v3 instances (max outstanding) per replica")
+    ap.add_argument("--concurrency", type=int, default=96, help="closed-loop clients per replica")
+    ap.add_argument("--inception-instances", type=int, default=48, help="Inception-v3 instances (max outstanding) per replica")
     ap.add_argument("--replicas-per-gpu", type=int, default=1,
                     help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU")
     ap.add_argument("--extra-kernels", type=int, default=64, help="scheduler: over-subscribed stages allowed in flight (--extra_kernels)")

@@ -210,7 +210,7 @@ PB_API void* pb_instance_input_dev(pb_instance* inst);   /* device staging buffe
 PB_API void* pb_instance_output_dev(pb_instance* inst);  /* device fp32 output */
 PB_API int pb_instance_launch_stage(pb_instance* inst, int stage, void* stream, uint32_t job_id, void* notifier);
 /* Stage groups: consecutive kernels that the job adapter presents to the scheduler as ONE stage
- * (default up to 24 kernels, PB_STAGE_GROUP=1 gives the reference's one-kernel-per-stage granularity).
+ * (default up to 48 kernels, PB_STAGE_GROUP=1 gives the reference's one-kernel-per-stage granularity).
  * A multi-kernel group is replayed as a CUDA graph - one driver call instead of one per kernel - and
  * only its last kernel reports block start/end on the notifier, so pb_model_group_info's block count
  * is that kernel's grid and its per-block resources are the group's largest footprint spread over

@@ -245,7 +245,7 @@ def test_stage_groups_replayed_as_graphs_give_the_same_bits(models_dir, model, p
     kernel-by-kernel result bit for bit, launch after launch."""
     m = Model(os.path.join(models_dir, packer.pack_file_name(model)), precision)
     n_stages, n_groups = m.L.pb_model_num_stages(m.m), m.L.pb_model_num_groups(m.m)
-    assert 1 <= n_groups <= n_stages and n_groups == -(-n_stages // 24)
+    assert 1 <= n_groups <= n_stages and n_groups == -(-n_stages // 48)
     first, count, covered, n_fused = C.c_int(), C.c_int(), 0, 0
     li = capi.LaunchInfo()
     for g in range(n_groups):
