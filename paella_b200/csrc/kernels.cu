@@ -802,10 +802,13 @@ static uint32_t blocks_for(size_t work) { return (uint32_t)((work + 255) / 256 >
 // served models: there the launch is latency-bound and more, smaller threads finish sooner).
 static int strip_of(const pb_op_params* p) {
     if (p->R != 3 || p->S != 3 || p->stride_h != p->stride_w || (p->stride_h != 1 && p->stride_h != 2)) return 0;
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
-        cudaGetLastError();
-        sms = 148;
+    static thread_local int sms = 0;      // of the device current at the first call of this thread (replicas: one GPU per thread)
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+            cudaGetLastError();
+            sms = 148;
+        }
     }
     const int wide = p->stride_h == 1 ? kStripWide1 : kStripWide2;
     const size_t n = (size_t)p->P * ((p->Q + wide - 1) / wide) * (p->Cs / vec_n(p->dtype));
