@@ -843,11 +843,14 @@ int max_bn() {
 // Measured on Inception-v3 (us per request alone / GPU time per request with 32 / 64 in flight):
 // threshold 0 -> 727 / 52.7 / 52.6, 0.5 -> 709 / 46.8 / 45.0, 2 -> 706 / 45.7 / 43.3, never split ->
 // 721 / 45.4 / 42.0: the partial tiles cost load bandwidth that a busy GPU does not have to spare.
+// On the serving mix (MNIST : Inception-v3 = 9 : 1, 48 Inception requests in flight): 2 -> 224k req/s,
+// 6 -> 229k, never -> 230k.  At 6 only the reductions that gain most still split (the 448 -> 384 3x3
+// convolutions on 8x8 maps of Inception-v3, the 512-channel 3x3 ones of a ResNet's last stage).
 // PB_CONV_SPLIT_GAIN_US overrides it (a large value disables splitting).
 double split_gain_us() {
     static const double v = [] {
         const char* e = getenv("PB_CONV_SPLIT_GAIN_US");
-        return e ? atof(e) : 2.0;
+        return e ? atof(e) : 6.0;
     }();
     return v;
 }
