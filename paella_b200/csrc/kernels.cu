@@ -546,10 +546,27 @@ __global__ void __launch_bounds__(256) dense_kernel(OpArgs a, uint32_t job_id, F
         const T* __restrict__ x = static_cast<const T*>(a.x);
         const T* __restrict__ w = static_cast<const T*>(a.w) + (size_t)warp * a.C;
         float acc = 0.f;
-#pragma unroll 4      // four weight vectors in flight per lane: a row is streamed once, from HBM
-        for (int i = lane * N; i < a.C; i += 32 * N) {
+        // A row of weights is streamed once, from HBM: four raw 128-bit loads per lane are issued before
+        // the first is used (cache-streaming, so they do not evict the input vector from L1); the sum keeps
+        // the order of the plain loop.
+        typedef typename RawVec<T>::type Raw;
+        constexpr int kStep = 32 * N;
+        int i = lane * N;
+        for (; i + 3 * kStep < a.C; i += 4 * kStep) {
+            Raw wr[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) wr[u] = __ldcs(reinterpret_cast<const Raw*>(w + i + u * kStep));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const Vec<T> xv = Vec<T>::load(x + i + u * kStep);
+                const Vec<T> wv = vec_of(wr[u]);
+#pragma unroll
+                for (int j = 0; j < N; ++j) acc = fmaf(xv.v[j], wv.v[j], acc);
+            }
+        }
+        for (; i < a.C; i += kStep) {
             const Vec<T> xv = Vec<T>::load(x + i);
-            const Vec<T> wv = Vec<T>::load(w + i);
+            const Vec<T> wv = vec_of(__ldcs(reinterpret_cast<const Raw*>(w + i)));
 #pragma unroll
             for (int j = 0; j < N; ++j) acc = fmaf(xv.v[j], wv.v[j], acc);
         }
