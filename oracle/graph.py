@@ -48,6 +48,7 @@ def lib():
         L.orc_softmax.argtypes = [_f, _i, _f]
         L.orc_round_bf16.argtypes = [_f, ctypes.c_long]
         L.orc_vec_add.argtypes = [_f, _f, ctypes.c_long]
+        L.orc_quotient3.argtypes = [_f, ctypes.c_long, ctypes.c_float, _f]
         _LIB = L
     return _LIB
 
@@ -139,6 +140,14 @@ def add(a, b, act=0):
     y = np.zeros_like(a)
     lib().orc_add(_p(a), _p(b), a.size, act, _p(y))
     return y
+
+
+def quotient3(v, div):
+    """v / div by the reciprocal + fused-residual sequence of the average-pooling kernel (orc_quotient3)."""
+    v = np.ascontiguousarray(v, np.float32)
+    out = np.empty_like(v)
+    lib().orc_quotient3(_p(v), v.size, float(div), _p(out))
+    return out
 
 
 def softmax(x):

@@ -468,7 +468,8 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
                 // v / div, correctly rounded, in three instructions per element instead of the division
                 // sequence (which was more than half of this kernel's instructions): with inv the correctly
                 // rounded reciprocal, q = v * inv is within an ulp, the fused residual v - div * q is exact
-                // and q + r * inv rounds to the quotient (Markstein); non-finite q passes through.
+                // and q + r * inv rounds to the quotient (Markstein); non-finite q passes through.  (-0.0
+                // would come out as +0.0, but a sum that starts from +0.0 is never -0.0.)
                 const float inv = 1.f / div;
 #pragma unroll
                 for (int j = 0; j < N; ++j) {

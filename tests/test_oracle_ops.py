@@ -109,3 +109,22 @@ def test_round_bf16_matches_torch(oracle_lib):
     x[:4] = [0.0, -0.0, np.inf, 1.0000001]
     ref = _t(x).to(torch.bfloat16).to(torch.float32).numpy()
     np.testing.assert_array_equal(og.round_bf16(x), ref)
+
+
+def test_average_pool_quotient_sequence_is_the_division():
+    """The 3x3 average-pooling kernel replaces v / div by reciprocal, fused residual and correction
+    (three instructions per element).  For every window size a 3x3 pool can have the sequence must
+    return the correctly rounded quotient: compared bit for bit with numpy's fp32 division on random bit
+    patterns (all normal magnitudes whose quotient is normal), zero and the largest finite values.  -0.0 is left
+    out: the sequence returns +0.0 for it, and the kernel's sums start from +0.0, so they are never -0.0."""
+    rng = np.random.default_rng(5)
+    bits = rng.integers(0, 2 ** 32, size=4_000_000, dtype=np.uint64).astype(np.uint32)
+    v = bits.view(np.float32)
+    v = v[np.isfinite(v) & (np.abs(v) > 1e-30)]
+    v = np.concatenate([v, np.array([0.0, 3.4028235e38, -3.4028235e38, 9.0, 1.0, 1e-30], np.float32)])
+    for div in range(1, 10):
+        got = og.quotient3(v, div)
+        ref = v / np.float32(div)
+        np.testing.assert_array_equal(got.view(np.uint32), ref.view(np.uint32))
+    inf = np.array([np.inf, -np.inf], np.float32)
+    np.testing.assert_array_equal(og.quotient3(inf, 9), inf)
