@@ -194,3 +194,64 @@ def test_reference_protocol_copy_stages_one_kernel_per_stage(tmp_path, monkeypat
         assert float(np.abs(y - ref).max()) <= 1e-2 * float(np.abs(ref).max())
         assert int(y.argmax()) == int(ref.argmax())
     L.pb_server_destroy(s)
+
+
+def test_headline_mix_inception_v3_and_mnist_concurrently(models_dir, monkeypatch):
+    """The benchmark's workload with its outputs checked: 16 Inception-v3 (299x299) and 48 MNIST requests in
+    flight together through the server, host-buffer mode (the 1 MB inputs go through the copy engine, the
+    results are written into the pinned slots), every slot with its own seeded input, two rounds so pooled
+    instances are reused.  Every slot's logits are compared with the oracle: <= 1e-2 of the largest |logit|
+    and the same argmax for the bf16 tensor-core path, 1e-5 for fp32 MNIST.  A race between instances
+    (shared scratch, launch slots, grouped-launch tables) would show up as a wrong slot."""
+    monkeypatch.delenv("PB_PRECISION", raising=False)
+    L, s = _server(models_dir, monkeypatch, streams=128)
+    ids, sizes = {}, {}
+    for job in ["tvm_mnist", "tvm_inception_v3"]:
+        j = C.c_uint32()
+        capi.check(L.pb_server_register_job(s, capi.plugin_path(job).encode(), C.byref(j)), "register " + job)
+        ids[job] = j.value
+        ib, ob, sb = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        L.pb_server_job_io_bytes(s, j, C.byref(ib), C.byref(ob), C.byref(sb))
+        sizes[job] = (ib.value, ob.value, sb.value)
+    assert sizes["tvm_inception_v3"][0] == 3 * 299 * 299 * 4
+    n_inc, n_mn = 16, 48
+    reqs = []                      # (job, x, pinned tensor)
+    for i in range(n_inc + n_mn):
+        # interleaved: three MNIST requests after every Inception request
+        job = "tvm_inception_v3" if i % 4 == 0 else "tvm_mnist"
+        rng = np.random.default_rng(5000 + i)
+        # every Inception input at its own amplitude: with random weights the logits of two N(0,1) images differ by
+        # only 1.5 % of the largest logit, too close to the tolerance to tell one slot's result from another's
+        x = (rng.standard_normal((3, 299, 299), dtype=np.float32) * np.float32(0.5 + 0.1 * (i // 4))
+             if job == "tvm_inception_v3" else rng.random((1, 28, 28), dtype=np.float32))
+        t = _pinned(sizes[job][2])
+        t.numpy()[:x.nbytes] = np.frombuffer(x.tobytes(), np.uint8)
+        reqs.append((job, x, t))
+    inc = og.Pack(packer.inception_v3(seed=1234).to_bytes())
+    mn = og.Pack(packer.mnist_cnn(seed=1234).to_bytes())
+    refs = [og.run(inc if job == "tvm_inception_v3" else mn, x) for job, x, _ in reqs]
+    worst = 0.0
+    for rnd in range(2):
+        for job, x, t in reqs:      # outputs of the previous round must not survive by accident
+            ib, ob, sb = sizes[job]
+            t.numpy()[(ib + 7) // 8 * 8:] = 0
+        for i, (job, x, t) in enumerate(reqs):
+            capi.check(L.pb_server_launch(s, ids[job], t.data_ptr(), 1000 * rnd + i), "launch")
+        done = _run_until(L, s, len(reqs), 120.0)
+        assert len(done) == len(reqs) and all(e == 0 for e in done.values()), done
+        flag = C.c_uint32(0)
+        capi.check(L.pb_device_error_flag(0, C.byref(flag), 1), "pb_device_error_flag")
+        assert flag.value == 0
+        for (job, x, t), ref in zip(reqs, refs):
+            ib, ob, sb = sizes[job]
+            off = (ib + 7) // 8 * 8
+            y = np.frombuffer(t.numpy()[off: off + ob].tobytes(), np.float32)
+            rel = float(np.abs(y - ref).max() / np.abs(ref).max())
+            if job == "tvm_inception_v3":
+                worst = max(worst, rel)
+                assert rel <= 1e-2, (rnd, rel)
+                assert int(y.argmax()) == int(ref.argmax())
+            else:
+                assert rel <= 1e-5, (rnd, rel)
+    assert L.pb_server_jobs_in_flight(s) == 0
+    L.pb_server_destroy(s)
