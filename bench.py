@@ -54,6 +54,7 @@ WORKLOADS = {
     "stress": [("vec_add", None, 1 / 3), ("dummy_short", None, 1 / 3), ("dummy_long", None, 1 / 3)],
 }
 MIX = WORKLOADS["mix"]
+GANG, DEFERRED = 1, 0      # set from the command line
 
 
 def measured_peaks():
@@ -136,7 +137,7 @@ def write_packs(models_dir):
 
 
 def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2, mix=None,
-             sched="full3", streams=500):
+             sched="full3", streams=500, gang=None, deferred=None):
     mix = mix or MIX
     cfg = capi.LoadgenConfig()
     L.pb_loadgen_config_default(C.byref(cfg))
@@ -157,6 +158,8 @@ def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps
     cfg.server.num_streams = streams
     cfg.server.scheduler = sched.encode()
     cfg.server.extra_kernels = extra_kernels
+    cfg.server.max_gang = GANG if gang is None else gang
+    cfg.server.deferred_schedule = DEFERRED if deferred is None else deferred
     res = capi.LoadgenResult()
     capi.check(L.pb_loadgen_run(C.byref(cfg), C.byref(res)), "pb_loadgen_run")
     if res.errors:
@@ -406,6 +409,8 @@ def main():
     ap.add_argument("--sched", default="full3", choices=["full3", "fifo", "fifo2"],
                     help="full3 = the kernel-level scheduler; fifo (job by job) and fifo2 (stage by stage, arrival order) are the ablations")
     ap.add_argument("--streams", type=int, default=500, help="scheduler stream pool (--num_streams); 1 with --sched fifo = single-stream baseline")
+    ap.add_argument("--gang", type=int, default=1, help="scheduler: up to this many queued requests of one model run as one launch per stage")
+    ap.add_argument("--deferred", type=int, default=0, help="scheduler: 1 = dispatch loop once per batch of notifications (implied by --gang > 1)")
     ap.add_argument("--workload", default="mix", choices=sorted(WORKLOADS), help="mix = the headline (MNIST : Inception-v3 = 9 : 1)")
     ap.add_argument("--extras", action="store_true", help="also measure ring round trip and vec_add bandwidth")
     ap.add_argument("--iat-us", type=float, default=0.0, help="open loop: mean inter-arrival per replica in us (Poisson); 0 = closed loop")
@@ -423,8 +428,9 @@ def main():
                          "(large: 256 MB per tensor; small: 144 MB per tensor, 3 launches each, for an ncu capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    global MIX
+    global MIX, GANG, DEFERRED
     MIX = WORKLOADS[args.workload]
+    GANG, DEFERRED = args.gang, args.deferred
     names = [m or j for j, m, _ in MIX]
 
     args.replicas_per_gpu = max(1, args.replicas_per_gpu)
@@ -445,7 +451,7 @@ def main():
     config = {"workload": wl_text + ("; closed loop" if args.iat_us <= 0 else f"; open loop, Poisson, mean inter-arrival {args.iat_us} us per replica"),
               "batch_per_step_per_replica": args.batch, "clients_per_replica": args.concurrency,
               "instances_per_replica": {names[0]: args.concurrency, **({names[-1]: args.inception_instances} if len(names) > 1 else {})},
-              "scheduler": args.sched, "num_streams": args.streams, "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu,
+              "scheduler": args.sched, "max_gang": args.gang, "deferred_schedule": int(args.deferred or args.gang > 1), "num_streams": args.streams, "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu,
               "precision": "MNIST fp32; other models bf16 x bf16 -> fp32 (tcgen05)",
               "replicas": "one scheduler+pools per GPU, requests dealt round-robin, no collective",
               "l2": "not flushed between requests: the working set per GPU (47.6 MB of bf16 weights + 19 MB of activations "

@@ -40,6 +40,8 @@ class ShmChannel {
     bool read(void* buf, size_t size, uint64_t max_spins = 0);
     bool write(const void* buf, size_t size, uint64_t max_spins = 0);
     bool can_read();
+    // Bytes a write() could place right now without waiting for the reader.
+    size_t writable_bytes();
 
     template <typename T> void read(T* v) { read(static_cast<void*>(v), sizeof(T)); }
     template <typename T> void write(T v) { write(static_cast<const void*>(&v), sizeof(T)); }

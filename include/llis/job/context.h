@@ -25,6 +25,13 @@ class Context {
     // there: model jobs then skip their host<->device copies (benchmark mode).
     static bool device_resident();
     static void set_device_resident(bool v);
+    // Gangs.  max_gang: how many jobs of one type the server's scheduler may run as one launch per stage
+    // (1 = never; a plugin sizes its buffers for it at full_init).  get_gang: during run_next() of a gang's
+    // leader, the other members (same type, same stage, their io_ptr given at init()); NULL / 0 otherwise.
+    static unsigned max_gang();
+    static void set_max_gang(unsigned n);
+    static Job* const* get_gang(unsigned* num_followers);
+    static void set_gang(Job* const* followers, unsigned num_followers);
 };
 
 }  // namespace job

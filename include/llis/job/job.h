@@ -20,6 +20,11 @@
 //    reports it to the client;
 //  * a stage index beyond the admission-time length table contributes 0 to the
 //    remaining-length decrement (the reference reads past the end, job.h:288-292).
+//  * gangs: a plugin may state that up to `capacity` of its jobs can run as ONE launch per
+//    stage (set_gang_decls); a scheduler that forms gangs dispatches the leader's stages
+//    with the followers listed in Context, and declares for it the resources of a gang of
+//    that size (apply_gang_size).  A job that never calls set_gang_decls has capacity 1 and
+//    is scheduled exactly as in the reference.
 #pragma once
 
 #include <cstddef>
@@ -157,6 +162,15 @@ class Job {
         if (i < stage_lengths_.size() && i < stage_resources_.size()) cur_rl_ -= stage_lengths_[i] * (double)stage_resources_[i];
     }
 
+    // ---- gangs ------------------------------------------------------------------
+    // Plugin: `row[n - 1]` is the declaration of the NEXT stage when it runs for a gang of n jobs
+    // (n = 1 .. capacity); the row must stay valid until the next call.  Called by the plugin each
+    // time it declares a stage (NULL / 1 = this stage runs one job per launch).
+    void set_gang_decls(const StageDecl* row, unsigned capacity) { gang_row_ = row; gang_capacity_ = row ? capacity : 1; }
+    unsigned get_gang_capacity() const { return gang_row_ ? gang_capacity_ : 1; }
+    // Scheduler: the next stage will run for a gang of n (<= capacity) jobs led by this one.
+    void apply_gang_size(unsigned n) { if (gang_row_ && n >= 1 && n <= gang_capacity_) next_ = gang_row_[n - 1]; }
+
     // ---- error reporting ------------------------------------------------------
     void set_error(int code) { if (!error_) error_ = code; }
     int has_error() const { return error_; }
@@ -171,6 +185,8 @@ class Job {
         cur_stage_ = -1;
         unset_unfit();
         error_ = 0;
+        gang_row_ = nullptr;
+        gang_capacity_ = 1;
     }
 
   private:
@@ -200,6 +216,8 @@ class Job {
     void* remote_ptr_ = nullptr;
     JobId id_ = 0;
     JobId unique_id_ = 0;
+    const StageDecl* gang_row_ = nullptr;
+    unsigned gang_capacity_ = 1;
 };
 
 }  // namespace job

@@ -47,8 +47,22 @@ class JobQueue {
 
     job::Job* top() const { return types_[pick_type()].heap.front().job; }
 
-    job::Job* pop() {
-        const size_t ti = pick_type();
+    job::Job* pop() { return pop_of(pick_type()); }
+
+    // Gang formation: takes the best queued job of `type` if `accept` says so, with the same counter
+    // arithmetic as a pop(); NULL (nothing changed) when the type has no queued job or its best is refused.
+    template <typename Pred>
+    job::Job* pop_of_type_if(JobRefId type, Pred accept) {
+        if (type >= types_.size() || types_[type].heap.empty() || !accept(types_[type].heap.front().job)) return nullptr;
+        return pop_of(type);
+    }
+
+    bool empty() const { return size_ == 0; }
+    size_t size() const { return size_; }
+    double unfairness_threshold() const { return unfairness_threshold_; }
+
+  private:
+    job::Job* pop_of(size_t ti) {
         Type& t = types_[ti];
         std::pop_heap(t.heap.begin(), t.heap.end(), worse);
         job::Job* job = t.heap.back().job;
@@ -69,11 +83,6 @@ class JobQueue {
         return job;
     }
 
-    bool empty() const { return size_ == 0; }
-    size_t size() const { return size_; }
-    double unfairness_threshold() const { return unfairness_threshold_; }
-
-  private:
     struct Entry {
         double priority;
         uint64_t seq;

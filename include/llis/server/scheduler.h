@@ -51,6 +51,7 @@ struct SchedulerConfig {
     unsigned extra_kernels = 2;       // over-subscribed ("unfit") kernels allowed in flight
     double unfairness_threshold = 1e6;
     unsigned sched_sleep = 0;
+    unsigned max_gang = 1;            // jobs of one type the scheduler may dispatch as one launch per stage (1 = never)
     SmTotals totals;
 };
 
@@ -60,6 +61,13 @@ class Scheduler {
     virtual void handle_new_job(job::Job* job) = 0;
     // Consumes one notification record (block start, block end or copy done).
     virtual void handle_record(const job::InstrumentInfo& info) = 0;
+    // Deferred scheduling (off by default = the reference's behaviour: the dispatch loop runs inside every
+    // handle_new_job / handle_record that may have made a stage runnable).  When on, those calls only update
+    // the queue and the occupancy model, and the dispatch loop runs once per flush(): the server calls it after
+    // each batch of client messages and ring records.  Fewer passes over the queue per request, and requests
+    // that arrive together are queued together, which is what lets a gang form.
+    virtual void set_deferred(bool on) { (void)on; }
+    virtual void flush() {}
     virtual unsigned num_jobs() const = 0;
     virtual uint64_t num_decisions() const = 0;
     virtual const char* name() const = 0;

@@ -158,6 +158,13 @@ typedef struct pb_op_params {
      * blocks when given at least pb_launch_info.scratch_bytes here; NULL = no split. */
     void* scratch;
     uint64_t scratch_bytes;
+    /* Images per launch (0 or 1 = one).  A batch is how a gang of requests of one model runs as one
+     * launch: x, residual and y then hold `batch` images back to back without padding ([batch][H][W][Cs]),
+     * the weights are shared.  The kernels that read the request input or write the fp32 model output
+     * take image i at offset i * (C*H*W) resp. i * K floats from x / y. */
+    int32_t batch;
+    int32_t dil_h, dil_w;     /* filter dilation (0 or 1 = dense filter); tensor-core and direct convolutions only */
+    int32_t reserved;
 } pb_op_params;
 
 /* Geometry/resources the launch of `kind` with `p` will use. */
@@ -168,6 +175,12 @@ PB_API int pb_op_launch(int kind, const pb_op_params* p, void* stream, uint32_t 
 PB_API int64_t pb_op_pack_weights(int kind, const pb_op_params* p, const float* w_oihw, void* dst_host);
 /* 1 if the tcgen05 implicit-GEMM kernel supports this convolution. */
 PB_API int pb_conv_umma_supported(const pb_op_params* p);
+/* The tensor-core convolution splits a long reduction over several thread blocks (partial tiles meet in
+ * scratch memory) when its cost model expects to save at least this many microseconds on a lone launch
+ * (default 6, or PB_CONV_SPLIT_GAIN_US from the environment; 0 = split whenever it pays at all, a large
+ * value = never; negative = back to the default).  Read at every pb_op_info / pb_op_launch, and when a model
+ * instance builds its launches for a batch size: instances built before a change keep their split. */
+PB_API void pb_set_conv_split_gain_us(double us);
 /* Tensor-core convolution for callers that must not allocate: code running inside a CUDA memory-pool
  * or allocator callback, a latency-critical thread that may not take the allocator's locks, or a host
  * that pre-partitions all device memory and leaves none to ask for.  It has no counterpart in the
@@ -230,6 +243,29 @@ PB_API int pb_model_group_stages(const pb_model* m, int group, int* first_stage,
 PB_API int pb_model_group_plan(const pb_model* m, int group, int32_t* stage_order, int32_t* launch_index, int max_stages);
 PB_API int pb_instance_launch_group(pb_instance* inst, int group, void* stream, uint32_t job_id, void* notifier,
                                     const void* io_in, void* io_out);
+/* Batches: an instance created with capacity `cap` (<= PB_MAX_GANG) runs any number nb <= cap of requests
+ * of its model as ONE set of launches - a "gang".  Its activation tensors hold cap images back to back, the
+ * tensor-core convolutions then see nb * pixels rows (fuller 128-row tiles, the weights pulled once for the
+ * gang), every other kernel puts the image on blockIdx.y, and the number of launches is that of one request.
+ * What depends on nb (descriptors, scratch, executable graphs) is built on the first use of that nb, or for
+ * every nb at creation with prepare_all != 0 (a build takes milliseconds: do it outside the serving path).
+ * pb_model_group_info_batched / pb_model_stage_info_batched give the launch geometry a stage declares for a
+ * gang of nb.  io_in[i] / io_out[i]: member i's request buffers (NULL entries or NULL arrays: the instance's
+ * own device buffers, image i).  Results are those of nb separate runs; they are bit-identical to them when
+ * the split of the reduction is the same (see pb_set_conv_split_gain_us).
+ * No counterpart in the reference, which runs one request per launch (its paper argues against batching by
+ * waiting; a gang only takes requests that are already queued). */
+#define PB_MAX_GANG 8
+PB_API int pb_instance_create_batched(pb_model* m, int capacity, int prepare_all, pb_instance** out);
+PB_API int pb_instance_capacity(const pb_instance* inst);
+PB_API int pb_model_group_info_batched(const pb_model* m, int group, int batch, pb_launch_info* out);
+PB_API int pb_model_stage_info_batched(const pb_model* m, int stage, int batch, pb_launch_info* out);
+PB_API int pb_instance_launch_group_batched(pb_instance* inst, int group, int batch, void* stream, uint32_t job_id, void* notifier,
+                                            const void* const* io_in, void* const* io_out);
+/* Convenience for tests: H2D of `batch` inputs (back to back), the model kernel by kernel (by_groups = 0) or
+ * group by group, D2H of the `batch` outputs, then synchronise. */
+PB_API int pb_instance_run_batch_sync(pb_instance* inst, int batch, int by_groups, const float* inputs_host, float* outputs_host);
+PB_API int pb_instance_time_stage_batched(pb_instance* inst, int stage, int batch, int iters, size_t flush_bytes, double* us_out);
 /* Convenience for tests: H2D, every group, D2H on one stream, then synchronise. */
 PB_API int pb_instance_run_groups_sync(pb_instance* inst, const float* input_host, float* output_host);
 /* Convenience for tests: H2D, every stage, D2H on one stream, then synchronise. */
@@ -257,6 +293,12 @@ typedef struct pb_server_config {
     uint64_t ring_capacity;      /* 0 = 1<<20 */
     const char* scheduler;       /* "full3" (default), "fifo", "fifo2" */
     int32_t device_resident;     /* 1: model jobs skip their host<->device copies (inputs already in HBM) */
+    uint32_t max_gang;           /* full3 only: up to this many queued requests of one model run as ONE launch per stage
+                                  * (a gang, <= PB_MAX_GANG); 0 or 1 = one request per launch, as in the reference */
+    uint32_t deferred_schedule;  /* 0: the dispatch loop runs inside every launch / notification, as in the reference
+                                  * (src/server/scheduler_full3.cpp:64-99,272-313).  1 (implied by max_gang > 1): launches
+                                  * and notifications only update the queue and the occupancy model; the dispatch loop runs
+                                  * once per pb_server_step batch (<= 64 records) */
 } pb_server_config;
 
 PB_API void pb_server_config_default(pb_server_config* cfg);

@@ -20,7 +20,7 @@ int main(int argc, char** argv) {
         else if (a != "--help" && i + 1 < argc) val = argv[++i];
         if (a == "--help") {
             printf("llis_server --name NAME [--sched full3|fifo|fifo2] [--num_streams 500] [--extra_kernels 2] [--unfair 1e6] "
-                   "[--sched_sleep 0] [--gpu 0]\n");
+                   "[--sched_sleep 0] [--gpu 0] [--gang 1] [--deferred 0]\n");
             return 1;
         }
         else if (a == "--name") name = val;
@@ -30,6 +30,8 @@ int main(int argc, char** argv) {
         else if (a == "--unfair") cfg.unfairness_threshold = (float)atof(val.c_str());
         else if (a == "--sched_sleep") cfg.sched_sleep = (uint32_t)atoi(val.c_str());
         else if (a == "--gpu") cfg.device = atoi(val.c_str());
+        else if (a == "--gang") cfg.max_gang = (uint32_t)atoi(val.c_str());
+        else if (a == "--deferred") cfg.deferred_schedule = (uint32_t)atoi(val.c_str());
         else { fprintf(stderr, "llis_server: unknown option %s\n", a.c_str()); return 2; }
     }
     if (name.empty()) { fprintf(stderr, "llis_server: --name is required\n"); return 2; }

@@ -31,13 +31,14 @@ class OpParams(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("dtype", "C", "H", "W", "Cs", "K", "P", "Q", "Ks", "out_c_off", "R", "S",
                                          "stride_h", "stride_w", "pad_h", "pad_w", "groups", "act", "flags", "res_Cs")] + \
                [("x", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p), ("y", C.c_void_p),
-                ("scratch", C.c_void_p), ("scratch_bytes", C.c_uint64)]
+                ("scratch", C.c_void_p), ("scratch_bytes", C.c_uint64),
+                ("batch", C.c_int32), ("dil_h", C.c_int32), ("dil_w", C.c_int32), ("reserved", C.c_int32)]
 
 
 class ServerConfig(C.Structure):
     _fields_ = [("device", C.c_int32), ("num_streams", C.c_uint32), ("extra_kernels", C.c_uint32),
                 ("unfairness_threshold", C.c_float), ("sched_sleep", C.c_uint32), ("ring_capacity", C.c_uint64),
-                ("scheduler", C.c_char_p), ("device_resident", C.c_int32)]
+                ("scheduler", C.c_char_p), ("device_resident", C.c_int32), ("max_gang", C.c_uint32), ("deferred_schedule", C.c_uint32)]
 
 
 class LoadgenConfig(C.Structure):
@@ -120,6 +121,14 @@ SIGNATURES = {
     "pb_conv_umma_supported": (_I, [C.POINTER(OpParams)]),
     "pb_conv2d_umma_noalloc": (_I, [C.POINTER(OpParams), _VP, _U32, _VP]),
     "pb_device_error_flag": (_I, [_I, C.POINTER(_U32), _I]),
+    "pb_set_conv_split_gain_us": (None, [C.c_double]),
+    "pb_instance_create_batched": (_I, [_VP, _I, _I, _PP]),
+    "pb_instance_capacity": (_I, [_VP]),
+    "pb_model_group_info_batched": (_I, [_VP, _I, _I, C.POINTER(LaunchInfo)]),
+    "pb_model_stage_info_batched": (_I, [_VP, _I, _I, C.POINTER(LaunchInfo)]),
+    "pb_instance_launch_group_batched": (_I, [_VP, _I, _I, _VP, _U32, _VP, _PP, _PP]),
+    "pb_instance_run_batch_sync": (_I, [_VP, _I, _I, _VP, _VP]),
+    "pb_instance_time_stage_batched": (_I, [_VP, _I, _I, _I, _SZ, C.POINTER(C.c_double)]),
     "pb_model_load": (_I, [C.c_char_p, _I, _I, _PP]),
     "pb_model_destroy": (None, [_VP]),
     "pb_model_input_bytes": (_SZ, [_VP]),

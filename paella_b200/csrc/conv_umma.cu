@@ -33,6 +33,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -83,7 +84,9 @@ struct ConvArgs {
     __nv_bfloat16* y;
     uint32_t* err_flag;
     int H, W, Cs;
-    int P, Q, M;          // M = P*Q
+    int P, Q, M;          // M = batch * P*Q: the images of a batch are consecutive rows of the GEMM
+    int PQ;               // output pixels per image
+    int dh, dw;           // filter dilation
     int K, Ks, out_c_off, res_Cs;
     int R, S, sh, sw, ph, pw;
     int act;
@@ -499,7 +502,7 @@ conv_umma_gather_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvAr
                 const __nv_bfloat16* xc = a.x + c;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int ih = ih0[i] + r, iw = iw0[i] + s;
+                    const int ih = ih0[i] + r * a.dh, iw = iw0[i] + s * a.dw;
                     const bool inb = tap_ok && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W;
                     const __nv_bfloat16* src = inb ? xc + ((size_t)ih * a.W + iw) * a.Cs : a.x;
                     cp_async_16(a_tile + dst_off + (uint32_t)i * 2048u, src, inb ? 16u : 0u);
@@ -634,7 +637,8 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
     } else if (warp == 4) {
         // ===== producer: one thread =====
         if (lane == 0) {
-            const int p0 = m0 / a.Q, q0 = m0 - p0 * a.Q;
+            const int img = m0 / a.PQ, rem = m0 - img * a.PQ;      // the tile may run on into the next image
+            const int p0 = rem / a.Q, q0 = rem - p0 * a.Q;
             const int w0 = q0 * a.sw - a.pw;          // filter-window origin of the tile's first pixel
             const int h0 = p0 * a.sh - a.ph;
             const int cpt = a.Cp / kBK;               // k-blocks per filter tap
@@ -651,7 +655,7 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
                 const uint32_t bar = smem_u32(&s_full[st]);
                 mbar_arrive_expect_tx(bar, (uint32_t)kATileBytes + a.b_stage_bytes);
                 if (a.a_tiled) tma_load_2d(a_tile, tmap_x, chunk * kBK, m0, bar);
-                else tma_load_im2col_4d(a_tile, tmap_x, chunk * kBK, w0, h0, 0, (uint16_t)s, (uint16_t)r, bar);
+                else tma_load_im2col_4d(a_tile, tmap_x, chunk * kBK, w0, h0, img, (uint16_t)(s * a.dw), (uint16_t)(r * a.dh), bar);
                 tma_load_2d(a_tile + kATileBytes, tmap_w, (kb_begin + kb) * kBK, n0, bar);
                 if (kb == 0) PB_T(2);
                 PB_TK(kb, 0);
@@ -846,14 +850,22 @@ int max_bn() {
 // On the serving mix (MNIST : Inception-v3 = 9 : 1, 48 Inception requests in flight): 2 -> 224k req/s,
 // 6 -> 229k, never -> 230k.  At 6 only the reductions that gain most still split (the 448 -> 384 3x3
 // convolutions on 8x8 maps of Inception-v3, the 512-channel 3x3 ones of a ResNet's last stage).
-// PB_CONV_SPLIT_GAIN_US overrides it (a large value disables splitting).
+// PB_CONV_SPLIT_GAIN_US or pb_set_conv_split_gain_us() overrides it (a large value disables splitting).
+std::atomic<double> g_split_gain_us{-1.0};      // < 0: not set yet, take PB_CONV_SPLIT_GAIN_US or the default
 double split_gain_us() {
-    static const double v = [] {
+    double v = g_split_gain_us.load(std::memory_order_relaxed);
+    if (v < 0) {
         const char* e = getenv("PB_CONV_SPLIT_GAIN_US");
-        return e ? atof(e) : 6.0;
-    }();
+        v = e ? atof(e) : 6.0;
+        if (v < 0) v = 0;
+        g_split_gain_us.store(v, std::memory_order_relaxed);
+    }
     return v;
 }
+
+int batch_of(const pb_op_params* p) { return p->batch > 1 ? p->batch : 1; }
+int dil_h(const pb_op_params* p) { return p->dil_h > 1 ? p->dil_h : 1; }
+int dil_w(const pb_op_params* p) { return p->dil_w > 1 ? p->dil_w : 1; }
 
 struct Geometry {
     int cpt, Cp;                // 64-channel k-blocks per filter tap; Cp = cpt * 64
@@ -876,7 +888,7 @@ Geometry geometry(const pb_op_params* p) {
     g.n_tiles = ceil_div(g.Kp16, use_tma_a() ? max_bn() : 128);
     g.BN = round_up(ceil_div(g.Kp16, g.n_tiles), 16);
     g.Kout_pad = g.n_tiles * g.BN;
-    g.m_tiles = ceil_div(p->P * p->Q, kBM);
+    g.m_tiles = ceil_div(batch_of(p) * p->P * p->Q, kBM);
     g.tmem_cols = 32;
     while ((int)g.tmem_cols < g.BN) g.tmem_cols <<= 1;
     g.b_stage_bytes = (uint32_t)g.BN * 128u;
@@ -946,6 +958,8 @@ struct ConvUmmaPlan {
     int device;
 };
 
+void conv_umma_set_split_gain_us(double us) { g_split_gain_us.store(us, std::memory_order_relaxed); }
+
 bool conv_umma_supported(const pb_op_params* p) {
     const int groups = p->groups > 0 ? p->groups : 1;
     return p->dtype == 1 && groups == 1 && p->Cs % 8 == 0 && p->Ks % 8 == 0 && p->out_c_off % 8 == 0 && p->K % 8 == 0 &&
@@ -973,9 +987,10 @@ int conv_umma_info(const pb_op_params* p, pb_launch_info* out) {
     out->regs_per_thread = regs;
     out->smem_per_block = g.smem_bytes + sstatic;
     out->tmem_cols_per_block = g.tmem_cols;
-    const uint64_t out_elems = (uint64_t)p->K * p->P * p->Q;
+    const uint64_t nb = (uint64_t)batch_of(p);
+    const uint64_t out_elems = nb * p->K * p->P * p->Q;
     out->flops = 2ull * out_elems * p->C * p->R * p->S;
-    out->bytes = 2ull * ((uint64_t)p->C * p->H * p->W + (uint64_t)p->K * p->C * p->R * p->S + out_elems +
+    out->bytes = 2ull * (nb * p->C * p->H * p->W + (uint64_t)p->K * p->C * p->R * p->S + out_elems +
                          (p->residual ? out_elems : 0)) + 4ull * p->K;
     return PB_OK;
 }
@@ -1020,7 +1035,7 @@ static int make_tmap(const Geometry& g, const void* w_dev, CUtensorMap* out) {
 // A 1x1, stride-1, unpadded convolution reads its input as the matrix [pixels][channels]: a tiled
 // load moves the same 128 x 64 tile with far fewer requests than the im2col mode's per-pixel walk.
 static bool pointwise(const pb_op_params* p) {
-    return p->R == 1 && p->S == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_h == 0 && p->pad_w == 0;
+    return p->R == 1 && p->S == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_h == 0 && p->pad_w == 0;      // any batch: images are contiguous
 }
 
 static int make_xmap(const pb_op_params* p, CUtensorMap* out) {
@@ -1028,7 +1043,7 @@ static int make_xmap(const pb_op_params* p, CUtensorMap* out) {
         EncodeTiledFn enc2 = encode_fn();
         PB_REQUIRE(enc2 != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
         PB_REQUIRE(((uintptr_t)p->x & 15) == 0, "conv_umma: activations must be 16-byte aligned");
-        const cuuint64_t dims2[2] = {(cuuint64_t)p->Cs, (cuuint64_t)p->H * p->W};
+        const cuuint64_t dims2[2] = {(cuuint64_t)p->Cs, (cuuint64_t)batch_of(p) * p->H * p->W};
         const cuuint64_t strides2[1] = {(cuuint64_t)p->Cs * 2};
         const cuuint32_t box2[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
         const cuuint32_t estr2[2] = {1, 1};
@@ -1044,10 +1059,10 @@ static int make_xmap(const pb_op_params* p, CUtensorMap* out) {
     EncodeIm2colFn enc = encode_im2col_fn();
     PB_REQUIRE(enc != nullptr, "cuTensorMapEncodeIm2col is not available from this driver");
     PB_REQUIRE(((uintptr_t)p->x & 15) == 0, "conv_umma: activations must be 16-byte aligned");
-    const cuuint64_t dims[4] = {(cuuint64_t)p->Cs, (cuuint64_t)p->W, (cuuint64_t)p->H, 1};
+    const cuuint64_t dims[4] = {(cuuint64_t)p->Cs, (cuuint64_t)p->W, (cuuint64_t)p->H, (cuuint64_t)batch_of(p)};
     const cuuint64_t strides[3] = {(cuuint64_t)p->Cs * 2, (cuuint64_t)p->W * p->Cs * 2, (cuuint64_t)p->H * p->W * p->Cs * 2};
     const int lower[2] = {-p->pad_w, -p->pad_h};
-    const int upper[2] = {p->pad_w - (p->S - 1), p->pad_h - (p->R - 1)};
+    const int upper[2] = {p->pad_w - (p->S - 1) * dil_w(p), p->pad_h - (p->R - 1) * dil_h(p)};
     const cuuint32_t estr[4] = {1, (cuuint32_t)p->stride_w, (cuuint32_t)p->stride_h, 1};
     const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(p->x), dims, strides, lower, upper,
                            (cuuint32_t)kBK, (cuuint32_t)kBM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1105,7 +1120,8 @@ static int fill_args(const ConvUmmaPlan* plan, const Geometry& g, const pb_op_pa
     a.y = static_cast<__nv_bfloat16*>(p->y);
     a.err_flag = err_flag ? err_flag : device_error_flag_ptr(plan->device);
     PB_REQUIRE(a.err_flag != nullptr, "conv_umma: no device error flag");
-    a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.P = p->P; a.Q = p->Q; a.M = p->P * p->Q;
+    a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.P = p->P; a.Q = p->Q; a.PQ = p->P * p->Q; a.M = batch_of(p) * a.PQ;
+    a.dh = dil_h(p); a.dw = dil_w(p);
     a.K = p->K; a.Ks = p->Ks; a.out_c_off = p->out_c_off; a.res_Cs = p->res_Cs;
     a.R = p->R; a.S = p->S; a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w;
     a.act = p->act; a.a_tiled = pointwise(p) ? 1 : 0; a.nkb = g.nkb; a.taps = p->R * p->S; a.Cp = g.Cp; a.BN = g.BN; a.idesc = g.idesc; a.tmem_cols = g.tmem_cols;
@@ -1134,8 +1150,9 @@ static cudaError_t launch_pdl(void (*kern)(Args...), dim3 grid, uint32_t smem, c
 
 int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap, const pb_op_params* p, cudaStream_t st,
                              uint32_t job_id, void* notifier, uint32_t* err_flag, bool pdl) {
-    Geometry g = plan->g;
+    Geometry g = geometry(p);       // the plan's own geometry is that of one image; tiles and split follow the batch
     if (g.splits > 1 && (p->scratch == nullptr || p->scratch_bytes < g.scratch_bytes)) drop_split(&g);
+    if (!use_tma_a()) PB_REQUIRE(batch_of(p) == 1, "conv_umma: the cp.async gather kernel (PB_CONV_GATHER=1) runs one image per launch");
     ConvArgs a;
     const int frc = fill_args(plan, g, p, err_flag, &a);
     if (frc != PB_OK) return frc;
@@ -1181,7 +1198,7 @@ int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap*
     m->n = n;
     for (int i = 0; i < n; ++i) {
         PB_REQUIRE(plans[i] && xmaps[i] && params[i], "conv_umma_multi_create: NULL entry %d", i);
-        Geometry g = plans[i]->g;
+        Geometry g = geometry(params[i]);
         if (g.splits > 1 && (params[i]->scratch == nullptr || params[i]->scratch_bytes < g.scratch_bytes)) drop_split(&g);
         SubConv& sc = table[(size_t)i];
         sc.tmap_w = plans[i]->tmap;

@@ -83,18 +83,29 @@ struct pb_model {
     std::vector<void*> allocs;
 };
 
-struct pb_instance {
-    pb_model* m = nullptr;
-    char* arena = nullptr;
-    char* scratch = nullptr;
-    float* in_dev = nullptr;
-    float* out_dev = nullptr;
-    std::vector<pb_op_params> params;   // per stage, pointers resolved
+// Everything of an instance that depends on how many images one launch carries.  An instance of
+// capacity `cap` can run any batch nb <= cap (a gang of nb requests of the model as ONE set of launches:
+// the tensor-core convolutions see nb * pixels rows, the other kernels put the image on blockIdx.y);
+// it has one variant per batch size it has been asked for.
+struct Variant {
+    int nb = 1;
+    std::vector<pb_op_params> params;       // per stage, pointers resolved
     std::vector<pb::ConvUmmaXMap*> xmaps;   // per stage: im2col descriptor of the stage's input (tensor-core convs)
-    pb::LaunchSlot* slot_host = nullptr;    // pinned mirror, filled before each graph launch
-    pb::LaunchSlot* slot_dev = nullptr;
+    std::vector<pb_launch_info> group_info; // per group, for this batch
     std::vector<cudaGraphExec_t> graphs;    // per group; NULL = single kernel, launched directly
     std::vector<std::vector<pb::ConvUmmaMulti*>> multis;   // [group][launch]: descriptor table of a grouped conv launch
+    char* scratch = nullptr;                // split-K scratch, one private slice per stage that splits at this batch
+};
+
+struct pb_instance {
+    pb_model* m = nullptr;
+    int cap = 1;                            // images the buffers hold
+    char* arena = nullptr;                  // tensor t: cap images back to back at cap * offset(t)
+    float* in_dev = nullptr;                // [cap][input floats]
+    float* out_dev = nullptr;               // [cap][output floats]
+    pb::LaunchSlot* slot_host = nullptr;    // pinned mirror, filled before each graph launch
+    pb::LaunchSlot* slot_dev = nullptr;
+    std::vector<Variant*> variants;         // [nb - 1], NULL until built
 };
 
 namespace {
@@ -131,11 +142,41 @@ bool is_mnist_topology(const std::vector<PackOp>& ops, const std::vector<TensorI
 }
 
 
+// What group `g` declares to the scheduler, from its stages' launch geometry `infos` (per stage): only the
+// LAST launch of a group reports block start/end, so the declared block count is that launch's grid; the
+// per-block resources are scaled so that blocks x per-block equals the largest footprint any launch of
+// the group has on the GPU.
+pb_launch_info group_footprint(const pb_model* m, int g, const std::vector<pb_launch_info>& infos) {
+    const pb_model::Group& grp = m->groups[(size_t)g];
+    pb_launch_info out;
+    memset(&out, 0, sizeof(out));
+    uint64_t thr = 0, smem = 0, regs = 0, tmem = 0, nb = 0;
+    for (const std::vector<int>& l : grp.launches) {
+        uint64_t lt = 0, ls = 0, lr = 0, lm = 0, lb = 0;
+        for (int i : l) {
+            const pb_launch_info& li = infos[(size_t)i];
+            lb += li.num_blocks;
+            lt += (uint64_t)li.num_blocks * li.threads_per_block;
+            ls += (uint64_t)li.num_blocks * li.smem_per_block;
+            lr += (uint64_t)li.num_blocks * li.threads_per_block * li.regs_per_thread;
+            lm += (uint64_t)li.num_blocks * li.tmem_cols_per_block;
+            out.flops += li.flops;
+            out.bytes += li.bytes;
+        }
+        thr = std::max(thr, lt); smem = std::max(smem, ls); regs = std::max(regs, lr); tmem = std::max(tmem, lm);
+        nb = lb;
+    }
+    out.kind = grp.count == 1 ? infos[(size_t)grp.first].kind : 0xFFFFu;
+    out.num_blocks = (uint32_t)nb;
+    out.threads_per_block = (uint32_t)pb::ceil_div<uint64_t>(thr, nb);
+    out.smem_per_block = (uint32_t)pb::ceil_div<uint64_t>(smem, nb);
+    out.regs_per_thread = (uint32_t)pb::ceil_div<uint64_t>(regs, (uint64_t)out.threads_per_block * nb);
+    out.tmem_cols_per_block = (uint32_t)pb::ceil_div<uint64_t>(tmem, nb);
+    return out;
+}
+
 // Splits the stage list into groups of at most PB_STAGE_GROUP kernels (default 48; 1 = one kernel per
 // scheduler stage, the reference's granularity) and derives each group's stage declaration.
-// Only the LAST kernel of a group reports block start/end, so the declared block count is that
-// kernel's grid; the per-block resources are scaled so that blocks x per-block equals the largest
-// footprint any kernel of the group has on the GPU.
 void build_groups(pb_model* m) {
     int gs = 48;      // measured on the headline mix: 24 -> 221k req/s with the host thread 94 % busy, 48 -> 225k at 79 %
     if (const char* e = getenv("PB_STAGE_GROUP")) gs = atoi(e);
@@ -180,46 +221,50 @@ void build_groups(pb_model* m) {
             }
             g.launches.push_back(std::vector<int>{s});
         }
-        // footprint of each launch; the group declares its last launch's blocks (the only ones that notify)
-        uint64_t thr = 0, smem = 0, regs = 0, tmem = 0, nb = 0;
-        for (const std::vector<int>& l : g.launches) {
-            uint64_t lt = 0, ls = 0, lr = 0, lm = 0, lb = 0;
-            for (int i : l) {
-                const pb_launch_info& li = m->stages[i].info;
-                lb += li.num_blocks;
-                lt += (uint64_t)li.num_blocks * li.threads_per_block;
-                ls += (uint64_t)li.num_blocks * li.smem_per_block;
-                lr += (uint64_t)li.num_blocks * li.threads_per_block * li.regs_per_thread;
-                lm += (uint64_t)li.num_blocks * li.tmem_cols_per_block;
-                g.info.flops += li.flops;
-                g.info.bytes += li.bytes;
-            }
-            thr = std::max(thr, lt); smem = std::max(smem, ls); regs = std::max(regs, lr); tmem = std::max(tmem, lm);
-            nb = lb;
-        }
-        g.info.kind = g.count == 1 ? m->stages[first].info.kind : 0xFFFFu;
-        g.info.num_blocks = (uint32_t)nb;
-        g.info.threads_per_block = (uint32_t)pb::ceil_div<uint64_t>(thr, nb);
-        g.info.smem_per_block = (uint32_t)pb::ceil_div<uint64_t>(smem, nb);
-        g.info.regs_per_thread = (uint32_t)pb::ceil_div<uint64_t>(regs, (uint64_t)g.info.threads_per_block * nb);
-        g.info.tmem_cols_per_block = (uint32_t)pb::ceil_div<uint64_t>(tmem, nb);
         m->groups.push_back(g);
+    }
+    for (size_t gi = 0; gi < m->groups.size(); ++gi) {
+        std::vector<pb_launch_info> infos(m->stages.size());
+        for (size_t i = 0; i < m->stages.size(); ++i) infos[i] = m->stages[i].info;
+        m->groups[gi].info = group_footprint(m, (int)gi, infos);
     }
 }
 
-int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStream_t stream, uint32_t job_id, void* notifier,
+// Launch geometry of stage `stage` when one launch carries `nb` images (scratch offered without limit).
+int stage_info_batched(const pb_model* m, int stage, int nb, pb_launch_info* out) {
+    const Stage& st = m->stages[(size_t)stage];
+    if (st.kind == PB_STAGE_MNIST_FUSED) {
+        const int rc = pb::mnist_fused_info(out);
+        out->num_blocks *= (uint32_t)nb; out->flops *= (uint64_t)nb; out->bytes *= (uint64_t)nb;
+        return rc;
+    }
+    pb_op_params p = st.p;
+    p.batch = nb;
+    p.scratch = (void*)16;
+    p.scratch_bytes = ~0ull;
+    return pb_op_info(st.kind, &p, out);
+}
+
+int launch_stage_with(pb_instance* in, const Variant& v, int stage, const pb_op_params* p, cudaStream_t stream, uint32_t job_id, void* notifier,
                       const float* mnist_x, float* mnist_y, bool pdl = false) {
     const Stage& st = in->m->stages[stage];
     switch (st.kind) {
         case PB_STAGE_MNIST_FUSED: {
             const pb_model* m = in->m;
-            return pb::mnist_fused_launch(mnist_x, m->w1, m->b1, m->w2, m->b2, m->wd, m->bd, mnist_y, stream, job_id, notifier);
+            return pb::mnist_fused_launch(mnist_x, m->w1, m->b1, m->w2, m->b2, m->wd, m->bd, mnist_y, v.nb, stream, job_id, notifier);
         }
         case PB_STAGE_CONV_UMMA:
-            return pb::conv_umma_launch_planned(st.plan, in->xmaps[stage], p, stream, job_id, notifier, nullptr, pdl);
+            return pb::conv_umma_launch_planned(st.plan, v.xmaps[stage], p, stream, job_id, notifier, nullptr, pdl);
         default:
             return pb::simple_op_launch(st.kind, p, stream, job_id, notifier, pdl);
     }
+}
+
+// A single small kernel reads the launch slot straight from the pinned host mirror (one PCIe read,
+// no copy node: about 1 us less host time per launch); larger groups get a device copy first.
+bool reads_host_slot(const pb_model* m, const pb_model::Group& grp, const Variant& v) {
+    const unsigned blocks = m->stages[grp.first].info.num_blocks;
+    return grp.count == 1 && blocks <= 4 && blocks * (unsigned)v.nb <= 16;
 }
 
 // Captures group `g` as ONE chain of launches in the group's planned order (dependence depth, then
@@ -228,12 +273,10 @@ int launch_stage_with(pb_instance* in, int stage, const pb_op_params* p, cudaStr
 // dependent of its predecessor: it waits (griddepcontrol.wait) for the completion of the kernel right
 // before it, which itself waited for its own predecessor, so the chain order is a total order.
 // The last launch is the one that notifies.
-int capture_group_chain(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed) {
+int capture_group_chain(pb_instance* in, Variant& v, int g, cudaStream_t origin, bool pdl_allowed) {
     const pb_model* m = in->m;
     const pb_model::Group& grp = m->groups[g];
-    // A single small kernel reads the launch slot straight from the pinned host mirror (one PCIe read,
-    // no copy node: about 1 us less host time per launch); larger groups get a device copy first.
-    const bool host_slot = grp.count == 1 && m->stages[grp.first].info.num_blocks <= 4;
+    const bool host_slot = reads_host_slot(m, grp, v);
     void* const slot_ptr = host_slot ? (void*)in->slot_host : (void*)in->slot_dev;
     PB_CUDA(cudaStreamBeginCapture(origin, cudaStreamCaptureModeRelaxed));
     cudaError_t e = host_slot ? cudaSuccess
@@ -244,12 +287,12 @@ int capture_group_chain(pb_instance* in, int g, cudaStream_t origin, bool pdl_al
         const std::vector<int>& l = grp.launches[li];
         const bool is_last = li + 1 == grp.launches.size();
         if (l.size() > 1) {
-            rc = pb::conv_umma_multi_launch(in->multis[(size_t)g][li], origin, is_last ? pb::kSlotNotify : 0u, is_last ? slot_ptr : nullptr,
+            rc = pb::conv_umma_multi_launch(v.multis[(size_t)g][li], origin, is_last ? pb::kSlotNotify : 0u, is_last ? slot_ptr : nullptr,
                                             pdl_allowed && after_kernel);
         } else {
             const int s = l[0];
             const Stage& st = m->stages[s];
-            pb_op_params p = in->params[s];
+            pb_op_params p = v.params[s];
             const bool reads_input = s == 0;                       // the request's input buffer
             const bool writes_output = st.y_is_output;             // the request's output buffer
             if (reads_input) p.x = nullptr;                        // NULL = take it from the launch slot
@@ -259,7 +302,7 @@ int capture_group_chain(pb_instance* in, int g, cudaStream_t origin, bool pdl_al
             if (is_last) { jid = pb::kSlotNotify; nfp = slot_ptr; }
             else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = slot_ptr; }
             const bool pdl = pdl_allowed && after_kernel && st.kind != PB_STAGE_MNIST_FUSED;
-            rc = launch_stage_with(in, s, &p, origin, jid, nfp, nullptr, nullptr, pdl);
+            rc = launch_stage_with(in, v, s, &p, origin, jid, nfp, nullptr, nullptr, pdl);
         }
         after_kernel = true;
     }
@@ -272,7 +315,7 @@ int capture_group_chain(pb_instance* in, int g, cudaStream_t origin, bool pdl_al
     const cudaError_t e3 = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
     if (e3 != cudaSuccess) return pb::cuda_fail(e3, "cudaGraphInstantiate", __FILE__, __LINE__);
-    in->graphs[g] = exec;
+    v.graphs[g] = exec;
     return PB_OK;
 }
 
@@ -282,7 +325,7 @@ int capture_group_chain(pb_instance* in, int g, cudaStream_t origin, bool pdl_al
 //   [slot copy] -> roots ...  each kernel after the producers of the tensors it reads ... -> last kernel
 // The last kernel of the group (the one that notifies) is ordered after every other kernel.
 // Kernels whose only dependence is the previous kernel on their path are programmatic dependents.
-int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed, bool parallel) {
+int capture_group(pb_instance* in, Variant& v, int g, cudaStream_t origin, bool pdl_allowed, bool parallel) {
     const pb_model* m = in->m;
     const pb_model::Group& grp = m->groups[g];
     const int first = grp.first, last = grp.first + grp.count - 1;
@@ -295,9 +338,7 @@ int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed,
     std::vector<int> lane_tail{-1};                                // last stage launched on each lane (-1: none yet)
     std::vector<std::vector<int>> writers(m->tensors.size());      // in-group stages that wrote each tensor
 
-    // A single small kernel reads the launch slot straight from the pinned host mirror (one PCIe read,
-    // no copy node: about 1 us less host time per launch); larger groups get a device copy first.
-    const bool host_slot = grp.count == 1 && m->stages[first].info.num_blocks <= 4;
+    const bool host_slot = reads_host_slot(m, grp, v);
     void* const slot_ptr = host_slot ? (void*)in->slot_host : (void*)in->slot_dev;
     PB_CUDA(cudaStreamBeginCapture(origin, cudaStreamCaptureModeRelaxed));
     cudaError_t e = host_slot ? cudaSuccess
@@ -351,7 +392,7 @@ int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed,
         }
         if (e != cudaSuccess) break;
 
-        pb_op_params p = in->params[s];
+        pb_op_params p = v.params[s];
         const bool reads_input = s == 0;                       // the request's input buffer
         const bool writes_output = st.y_is_output;             // the request's output buffer
         if (reads_input) p.x = nullptr;                        // NULL = take it from the launch slot
@@ -361,7 +402,7 @@ int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed,
         if (s == last) { jid = pb::kSlotNotify; nfp = slot_ptr; }
         else if (reads_input || writes_output) { jid = pb::kSlotQuiet; nfp = slot_ptr; }
         const bool pdl = pdl_allowed && chained && st.kind != PB_STAGE_MNIST_FUSED;
-        rc = launch_stage_with(in, s, &p, lanes[lane], jid, nfp, nullptr, nullptr, pdl);
+        rc = launch_stage_with(in, v, s, &p, lanes[lane], jid, nfp, nullptr, nullptr, pdl);
         if (rc != PB_OK) break;
         cudaEvent_t ev = new_event();
         e = cudaEventRecord(ev, lanes[lane]);
@@ -380,7 +421,112 @@ int capture_group(pb_instance* in, int g, cudaStream_t origin, bool pdl_allowed,
     const cudaError_t e3 = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
     if (e3 != cudaSuccess) return pb::cuda_fail(e3, "cudaGraphInstantiate", __FILE__, __LINE__);
-    in->graphs[g] = exec;
+    v.graphs[g] = exec;
+    return PB_OK;
+}
+
+void destroy_variant(Variant* v) {
+    if (!v) return;
+    for (pb::ConvUmmaXMap* x : v->xmaps) pb::conv_umma_xmap_destroy(x);
+    for (cudaGraphExec_t g : v->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto& l : v->multis) for (pb::ConvUmmaMulti* mu : l) pb::conv_umma_multi_destroy(mu);
+    if (v->scratch) cudaFree(v->scratch);
+    delete v;
+}
+
+// Builds (once) what the instance needs to run batches of `nb` images: resolved parameters, input
+// descriptors, scratch, grouped-launch tables and one executable graph per stage group.
+int ensure_variant(pb_instance* in, int nb, Variant** out) {
+    PB_REQUIRE(in && nb >= 1 && nb <= in->cap, "batch %d does not fit this instance (capacity %d)", nb, in ? in->cap : 0);
+    if (in->variants[(size_t)nb - 1]) { *out = in->variants[(size_t)nb - 1]; return PB_OK; }
+    pb_model* m = in->m;
+    PB_CUDA(cudaSetDevice(m->device));
+    Variant* v = new Variant();
+    v->nb = nb;
+    const size_t cap = (size_t)in->cap;
+    // launch geometry and scratch layout of every stage at this batch
+    std::vector<pb_launch_info> infos(m->stages.size());
+    std::vector<size_t> scratch_off(m->stages.size(), 0);
+    size_t scratch_bytes = 0;
+    for (size_t i = 0; i < m->stages.size(); ++i) {
+        const int rc = stage_info_batched(m, (int)i, nb, &infos[i]);
+        if (rc != PB_OK) { destroy_variant(v); return rc; }
+        if (infos[i].scratch_bytes) {
+            scratch_off[i] = scratch_bytes;
+            scratch_bytes += pb::round_up((size_t)infos[i].scratch_bytes, (size_t)256);
+        }
+    }
+    cudaError_t e = cudaSuccess;
+    if (scratch_bytes) {
+        e = cudaMalloc((void**)&v->scratch, scratch_bytes);
+        if (e == cudaSuccess) e = cudaMemset(v->scratch, 0, scratch_bytes);
+        if (e != cudaSuccess) { destroy_variant(v); return pb::cuda_fail(e, "split-K scratch", __FILE__, __LINE__); }
+    }
+    v->params.resize(m->stages.size());
+    v->xmaps.assign(m->stages.size(), nullptr);
+    for (size_t i = 0; i < m->stages.size(); ++i) {
+        const Stage& st = m->stages[i];
+        pb_op_params p = st.p;
+        p.batch = nb;
+        p.x = st.x_is_input ? (const void*)in->in_dev : (const void*)(in->arena + cap * st.x_off);
+        p.y = st.y_is_output ? (void*)in->out_dev : (void*)(in->arena + cap * st.y_off);
+        p.residual = st.has_res ? (const void*)(in->arena + cap * st.res_off) : nullptr;
+        p.scratch = infos[i].scratch_bytes ? v->scratch + scratch_off[i] : nullptr;
+        p.scratch_bytes = infos[i].scratch_bytes;
+        v->params[i] = p;
+        if (st.kind == PB_STAGE_CONV_UMMA) {
+            const int rc = pb::conv_umma_xmap_create(&p, &v->xmaps[i]);
+            if (rc != PB_OK) { destroy_variant(v); return rc; }
+        }
+    }
+    v->group_info.resize(m->groups.size());
+    for (size_t g = 0; g < m->groups.size(); ++g) v->group_info[g] = group_footprint(m, (int)g, infos);
+    v->graphs.assign(m->groups.size(), nullptr);
+    v->multis.resize(m->groups.size());
+    // PB_GRAPH_SINGLE=0: single-kernel groups are launched as plain kernels (about 3 us more host time each)
+    const bool single_graphs = env_flag("PB_GRAPH_SINGLE", true);
+    bool any_graph = single_graphs && !m->groups.empty();
+    for (const pb_model::Group& g : m->groups) any_graph = any_graph || g.count > 1;
+    if (any_graph) {
+        (void)pb::device_error_flag_ptr(m->device);      // allocate it now: nothing may allocate during capture
+        cudaStream_t cap_stream;
+        e = cudaStreamCreateWithFlags(&cap_stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) { destroy_variant(v); return pb::cuda_fail(e, "capture stream", __FILE__, __LINE__); }
+        int rc = PB_OK;
+        const bool pdl = env_flag("PB_PDL", true);
+        const bool parallel = env_flag("PB_GRAPH_BRANCHES", false);
+        for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g) {
+            const pb_model::Group& grp = m->groups[g];
+            if (grp.count <= 1 && !single_graphs) continue;
+            if (parallel && !m->fuse_branches) {
+                rc = capture_group(in, *v, (int)g, cap_stream, pdl, true);
+                if (rc == PB_OK) continue;
+                cudaGetLastError();                   // a driver that cannot capture this: the chain below
+            }
+            // descriptor tables of the grouped launches
+            v->multis[g].assign(grp.launches.size(), nullptr);
+            rc = PB_OK;
+            for (size_t li = 0; rc == PB_OK && li < grp.launches.size(); ++li) {
+                const std::vector<int>& l = grp.launches[li];
+                if (l.size() < 2) continue;
+                std::vector<const pb::ConvUmmaPlan*> plans;
+                std::vector<const pb::ConvUmmaXMap*> xm;
+                std::vector<const pb_op_params*> pp;
+                for (int s : l) { plans.push_back(m->stages[s].plan); xm.push_back(v->xmaps[s]); pp.push_back(&v->params[s]); }
+                rc = pb::conv_umma_multi_create(plans.data(), xm.data(), pp.data(), (int)l.size(), &v->multis[g][li]);
+            }
+            if (rc != PB_OK) break;
+            rc = capture_group_chain(in, *v, (int)g, cap_stream, pdl);
+            if (rc != PB_OK && pdl) {                 // a driver that cannot capture programmatic edges: plain edges
+                cudaGetLastError();
+                rc = capture_group_chain(in, *v, (int)g, cap_stream, false);
+            }
+        }
+        cudaStreamDestroy(cap_stream);
+        if (rc != PB_OK) { destroy_variant(v); return rc; }
+    }
+    in->variants[(size_t)nb - 1] = v;
+    *out = v;
     return PB_OK;
 }
 
@@ -406,6 +552,8 @@ int64_t pb_op_pack_weights(int kind, const pb_op_params* p, const float* w_oihw,
     if (kind == PB_STAGE_CONV_UMMA) return pb::conv_umma_pack_weights(p, w_oihw, dst_host);
     return pb::simple_pack_weights(kind, p, w_oihw, dst_host);
 }
+
+void pb_set_conv_split_gain_us(double us) { pb::conv_umma_set_split_gain_us(us); }
 
 int pb_conv_umma_supported(const pb_op_params* p) { return p && pb::conv_umma_supported(p) ? 1 : 0; }
 
@@ -715,101 +863,49 @@ const char* pb_model_stage_name(const pb_model* m, int stage) {
     return m->stages[stage].name.c_str();
 }
 
-int pb_instance_create(pb_model* m, pb_instance** out) {
+int pb_instance_create_batched(pb_model* m, int capacity, int prepare_all, pb_instance** out) {
     PB_REQUIRE(m && out, "pb_instance_create: NULL argument");
+    PB_REQUIRE(capacity >= 1 && capacity <= pb::kMaxGang, "pb_instance_create: capacity %d outside 1..%d", capacity, pb::kMaxGang);
     PB_CUDA(cudaSetDevice(m->device));
     pb_instance* in = new pb_instance();
     in->m = m;
-    cudaError_t e = cudaMalloc((void**)&in->arena, m->arena_bytes + 256);
-    if (e == cudaSuccess) e = cudaMemset(in->arena, 0, m->arena_bytes + 256);
-    if (e == cudaSuccess && m->scratch_bytes) e = cudaMalloc((void**)&in->scratch, m->scratch_bytes);
-    if (e == cudaSuccess && m->scratch_bytes) e = cudaMemset(in->scratch, 0, m->scratch_bytes);
-    if (e == cudaSuccess) e = cudaMalloc((void**)&in->in_dev, pb::round_up(m->in_floats * 4, (size_t)256));
-    if (e == cudaSuccess) e = cudaMalloc((void**)&in->out_dev, pb::round_up(m->out_floats * 4, (size_t)256));
-    if (e == cudaSuccess) e = cudaMemset(in->out_dev, 0, pb::round_up(m->out_floats * 4, (size_t)256));
+    in->cap = capacity;
+    in->variants.assign((size_t)capacity, nullptr);
+    const size_t cap = (size_t)capacity;
+    const size_t in_bytes = pb::round_up(cap * m->in_floats * 4, (size_t)256), out_bytes = pb::round_up(cap * m->out_floats * 4, (size_t)256);
+    cudaError_t e = cudaMalloc((void**)&in->arena, cap * m->arena_bytes + 256);
+    if (e == cudaSuccess) e = cudaMemset(in->arena, 0, cap * m->arena_bytes + 256);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&in->in_dev, in_bytes);
+    if (e == cudaSuccess) e = cudaMemset(in->in_dev, 0, in_bytes);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&in->out_dev, out_bytes);
+    if (e == cudaSuccess) e = cudaMemset(in->out_dev, 0, out_bytes);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&in->slot_host, sizeof(pb::LaunchSlot), cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&in->slot_dev, sizeof(pb::LaunchSlot));
     if (e != cudaSuccess) {
         pb_instance_destroy(in);
         return pb::cuda_fail(e, "instance buffers", __FILE__, __LINE__);
     }
-    in->params.resize(m->stages.size());
-    in->xmaps.assign(m->stages.size(), nullptr);
-    for (size_t i = 0; i < m->stages.size(); ++i) {
-        const Stage& st = m->stages[i];
-        pb_op_params p = st.p;
-        p.x = st.x_is_input ? (const void*)in->in_dev : (const void*)(in->arena + st.x_off);
-        p.y = st.y_is_output ? (void*)in->out_dev : (void*)(in->arena + st.y_off);
-        p.residual = st.has_res ? (const void*)(in->arena + st.res_off) : nullptr;
-        p.scratch = st.info.scratch_bytes ? in->scratch + st.scratch_off : nullptr;
-        p.scratch_bytes = st.info.scratch_bytes;
-        in->params[i] = p;
-        if (st.kind == PB_STAGE_CONV_UMMA) {
-            const int rc = pb::conv_umma_xmap_create(&p, &in->xmaps[i]);
-            if (rc != PB_OK) { pb_instance_destroy(in); return rc; }
-        }
-    }
-    // launch slot and one executable graph per group
-    e = cudaHostAlloc((void**)&in->slot_host, sizeof(pb::LaunchSlot), cudaHostAllocMapped);
-    if (e == cudaSuccess) e = cudaMalloc((void**)&in->slot_dev, sizeof(pb::LaunchSlot));
-    if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "launch slot", __FILE__, __LINE__); }
     memset(in->slot_host, 0, sizeof(pb::LaunchSlot));
-    in->graphs.assign(m->groups.size(), nullptr);
-    // PB_GRAPH_SINGLE=0: single-kernel groups are launched as plain kernels (about 3 us more host time each)
-    const bool single_graphs = env_flag("PB_GRAPH_SINGLE", true);
-    bool any_graph = single_graphs && !m->groups.empty();
-    for (const pb_model::Group& g : m->groups) any_graph = any_graph || g.count > 1;
-    if (any_graph) {
-        (void)pb::device_error_flag_ptr(m->device);      // allocate it now: nothing may allocate during capture
-        cudaStream_t cap;
-        e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
-        if (e != cudaSuccess) { pb_instance_destroy(in); return pb::cuda_fail(e, "capture stream", __FILE__, __LINE__); }
-        int rc = PB_OK;
-        const bool pdl = env_flag("PB_PDL", true);
-        const bool parallel = env_flag("PB_GRAPH_BRANCHES", false);
-        in->multis.resize(m->groups.size());
-        for (size_t g = 0; rc == PB_OK && g < m->groups.size(); ++g) {
-            const pb_model::Group& grp = m->groups[g];
-            if (grp.count <= 1 && !single_graphs) continue;
-            if (parallel && !m->fuse_branches) {
-                rc = capture_group(in, (int)g, cap, pdl, true);
-                if (rc == PB_OK) continue;
-                cudaGetLastError();                   // a driver that cannot capture this: the chain below
-            }
-            // descriptor tables of the grouped launches
-            in->multis[g].assign(grp.launches.size(), nullptr);
-            rc = PB_OK;
-            for (size_t li = 0; rc == PB_OK && li < grp.launches.size(); ++li) {
-                const std::vector<int>& l = grp.launches[li];
-                if (l.size() < 2) continue;
-                std::vector<const pb::ConvUmmaPlan*> plans;
-                std::vector<const pb::ConvUmmaXMap*> xm;
-                std::vector<const pb_op_params*> pp;
-                for (int s : l) { plans.push_back(m->stages[s].plan); xm.push_back(in->xmaps[s]); pp.push_back(&in->params[s]); }
-                rc = pb::conv_umma_multi_create(plans.data(), xm.data(), pp.data(), (int)l.size(), &in->multis[g][li]);
-            }
-            if (rc != PB_OK) break;
-            rc = capture_group_chain(in, (int)g, cap, pdl);
-            if (rc != PB_OK && pdl) {                 // a driver that cannot capture programmatic edges: plain edges
-                cudaGetLastError();
-                rc = capture_group_chain(in, (int)g, cap, false);
-            }
-        }
-        cudaStreamDestroy(cap);
+    for (int nb = 1; nb <= (prepare_all ? capacity : 1); ++nb) {
+        Variant* v = nullptr;
+        const int rc = ensure_variant(in, nb, &v);
         if (rc != PB_OK) { pb_instance_destroy(in); return rc; }
     }
     *out = in;
     return PB_OK;
 }
 
+int pb_instance_create(pb_model* m, pb_instance** out) { return pb_instance_create_batched(m, 1, 1, out); }
+
+int pb_instance_capacity(const pb_instance* in) { return in ? in->cap : 0; }
+
 void pb_instance_destroy(pb_instance* in) {
     if (!in) return;
     if (in->m) cudaSetDevice(in->m->device);
-    for (pb::ConvUmmaXMap* x : in->xmaps) pb::conv_umma_xmap_destroy(x);
-    for (cudaGraphExec_t g : in->graphs) if (g) cudaGraphExecDestroy(g);
-    for (auto& v : in->multis) for (pb::ConvUmmaMulti* mu : v) pb::conv_umma_multi_destroy(mu);
+    for (Variant* v : in->variants) destroy_variant(v);
     if (in->slot_host) cudaFreeHost(in->slot_host);
     if (in->slot_dev) cudaFree(in->slot_dev);
     if (in->arena) cudaFree(in->arena);
-    if (in->scratch) cudaFree(in->scratch);
     if (in->in_dev) cudaFree(in->in_dev);
     if (in->out_dev) cudaFree(in->out_dev);
     delete in;
@@ -818,9 +914,16 @@ void pb_instance_destroy(pb_instance* in) {
 void* pb_instance_input_dev(pb_instance* in) { return in ? in->in_dev : nullptr; }
 void* pb_instance_output_dev(pb_instance* in) { return in ? in->out_dev : nullptr; }
 
+static int launch_stage_batched(pb_instance* in, int stage, int nb, void* stream, uint32_t job_id, void* notifier) {
+    PB_REQUIRE(in && stage >= 0 && stage < (int)in->m->stages.size(), "pb_instance_launch_stage: bad stage %d", stage);
+    Variant* v = nullptr;
+    const int rc = ensure_variant(in, nb, &v);
+    if (rc != PB_OK) return rc;
+    return launch_stage_with(in, *v, stage, &v->params[stage], (cudaStream_t)stream, job_id, notifier, in->in_dev, in->out_dev);
+}
+
 int pb_instance_launch_stage(pb_instance* in, int stage, void* stream, uint32_t job_id, void* notifier) {
-    PB_REQUIRE(in && stage >= 0 && stage < (int)in->params.size(), "pb_instance_launch_stage: bad stage %d", stage);
-    return launch_stage_with(in, stage, &in->params[stage], (cudaStream_t)stream, job_id, notifier, in->in_dev, in->out_dev);
+    return launch_stage_batched(in, stage, 1, stream, job_id, notifier);
 }
 
 int pb_model_num_groups(const pb_model* m) { return m ? (int)m->groups.size() : 0; }
@@ -829,6 +932,25 @@ int pb_model_group_info(const pb_model* m, int group, pb_launch_info* out) {
     PB_REQUIRE(m && out && group >= 0 && group < (int)m->groups.size(), "pb_model_group_info: bad group %d", group);
     *out = m->groups[group].info;
     return PB_OK;
+}
+
+int pb_model_group_info_batched(const pb_model* m, int group, int batch, pb_launch_info* out) {
+    PB_REQUIRE(m && out && group >= 0 && group < (int)m->groups.size(), "pb_model_group_info_batched: bad group %d", group);
+    PB_REQUIRE(batch >= 1 && batch <= pb::kMaxGang, "pb_model_group_info_batched: batch %d outside 1..%d", batch, pb::kMaxGang);
+    std::vector<pb_launch_info> infos(m->stages.size());
+    const pb_model::Group& g = m->groups[(size_t)group];
+    for (int i = g.first; i < g.first + g.count; ++i) {
+        const int rc = stage_info_batched(m, i, batch, &infos[(size_t)i]);
+        if (rc != PB_OK) return rc;
+    }
+    *out = group_footprint(m, group, infos);
+    return PB_OK;
+}
+
+int pb_model_stage_info_batched(const pb_model* m, int stage, int batch, pb_launch_info* out) {
+    PB_REQUIRE(m && out && stage >= 0 && stage < (int)m->stages.size(), "pb_model_stage_info_batched: bad stage %d", stage);
+    PB_REQUIRE(batch >= 1 && batch <= pb::kMaxGang, "pb_model_stage_info_batched: batch %d outside 1..%d", batch, pb::kMaxGang);
+    return stage_info_batched(m, stage, batch, out);
 }
 
 int pb_model_group_stages(const pb_model* m, int group, int* first, int* count) {
@@ -852,61 +974,74 @@ int pb_model_group_plan(const pb_model* m, int group, int32_t* stage_order, int3
     return n;
 }
 
-int pb_instance_launch_group(pb_instance* in, int group, void* stream, uint32_t job_id, void* notifier, const void* io_in,
-                             void* io_out) {
+int pb_instance_launch_group_batched(pb_instance* in, int group, int batch, void* stream, uint32_t job_id, void* notifier,
+                                     const void* const* io_in, void* const* io_out) {
     PB_REQUIRE(in && group >= 0 && group < (int)in->m->groups.size(), "pb_instance_launch_group: bad group %d", group);
-    const pb_model::Group& g = in->m->groups[group];
-    const float* xin = io_in ? static_cast<const float*>(io_in) : in->in_dev;
-    float* yout = io_out ? static_cast<float*>(io_out) : in->out_dev;
-    if (in->graphs[group]) {
-        pb::LaunchSlot* s = in->slot_host;
-        s->nf = static_cast<llis::job::FinishedBlockNotifier*>(notifier);
-        s->job_id = job_id;
-        s->io_in = xin;
-        s->io_out = yout;
-        PB_CUDA(cudaGraphLaunch(in->graphs[group], (cudaStream_t)stream));
+    Variant* v = nullptr;
+    const int vrc = ensure_variant(in, batch, &v);
+    if (vrc != PB_OK) return vrc;
+    const pb_model* m = in->m;
+    const pb_model::Group& g = m->groups[group];
+    pb::LaunchSlot* s = in->slot_host;
+    s->nf = static_cast<llis::job::FinishedBlockNotifier*>(notifier);
+    s->job_id = job_id;
+    for (int i = 0; i < batch; ++i) {
+        s->io_in[i] = (io_in && io_in[i]) ? static_cast<const float*>(io_in[i]) : in->in_dev + (size_t)i * m->in_floats;
+        s->io_out[i] = (io_out && io_out[i]) ? static_cast<float*>(io_out[i]) : in->out_dev + (size_t)i * m->out_floats;
+    }
+    if (v->graphs[group]) {
+        PB_CUDA(cudaGraphLaunch(v->graphs[group], (cudaStream_t)stream));
         return PB_OK;
     }
-    // single kernel: direct launch with this request's buffers
+    // single kernel, no graph: a direct launch
     const int stage = g.first;
-    pb_op_params p = in->params[stage];
-    if (stage == 0) p.x = xin;
-    if (in->m->stages[stage].y_is_output) p.y = yout;
-    return launch_stage_with(in, stage, &p, (cudaStream_t)stream, job_id, notifier, xin, yout);
+    pb_op_params p = v->params[stage];
+    if (batch == 1) {
+        if (stage == 0) p.x = s->io_in[0];
+        if (m->stages[stage].y_is_output) p.y = s->io_out[0];
+        return launch_stage_with(in, *v, stage, &p, (cudaStream_t)stream, job_id, notifier, s->io_in[0], s->io_out[0]);
+    }
+    // a batch's buffers are not one array: the kernel takes them, and the notifier, from the pinned slot
+    if (stage == 0) p.x = nullptr;
+    if (m->stages[stage].y_is_output) p.y = nullptr;
+    return launch_stage_with(in, *v, stage, &p, (cudaStream_t)stream, pb::kSlotNotify, in->slot_host, nullptr, nullptr);
 }
 
-int pb_instance_run_groups_sync(pb_instance* in, const float* input_host, float* output_host) {
-    PB_REQUIRE(in && input_host && output_host, "pb_instance_run_groups_sync: NULL argument");
-    pb_model* m = in->m;
-    PB_CUDA(cudaSetDevice(m->device));
-    cudaStream_t st;
-    PB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-    int rc = PB_OK;
-    cudaError_t e = cudaMemcpyAsync(in->in_dev, input_host, m->in_floats * 4, cudaMemcpyHostToDevice, st);
-    for (int g = 0; e == cudaSuccess && rc == PB_OK && g < (int)m->groups.size(); ++g) rc = pb_instance_launch_group(in, g, st, 0, nullptr, nullptr, nullptr);
-    if (e == cudaSuccess && rc == PB_OK) e = cudaMemcpyAsync(output_host, in->out_dev, m->out_floats * 4, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess && rc == PB_OK) e = cudaStreamSynchronize(st);
-    cudaStreamDestroy(st);
-    if (rc != PB_OK) return rc;
-    if (e != cudaSuccess) return pb::cuda_fail(e, "pb_instance_run_groups_sync", __FILE__, __LINE__);
-    return PB_OK;
+int pb_instance_launch_group(pb_instance* in, int group, void* stream, uint32_t job_id, void* notifier, const void* io_in,
+                             void* io_out) {
+    const void* ins[1] = {io_in};
+    void* outs[1] = {io_out};
+    return pb_instance_launch_group_batched(in, group, 1, stream, job_id, notifier, ins, outs);
 }
 
-int pb_instance_run_sync(pb_instance* in, const float* input_host, float* output_host) {
+// H2D of `batch` inputs, the model (group by group as CUDA graphs, or kernel by kernel), D2H of the outputs.
+static int run_sync(pb_instance* in, int batch, bool by_groups, const float* input_host, float* output_host) {
     PB_REQUIRE(in && input_host && output_host, "pb_instance_run_sync: NULL argument");
+    PB_REQUIRE(batch >= 1 && batch <= in->cap, "pb_instance_run_sync: batch %d does not fit capacity %d", batch, in->cap);
     pb_model* m = in->m;
     PB_CUDA(cudaSetDevice(m->device));
     cudaStream_t st;
     PB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
     int rc = PB_OK;
-    cudaError_t e = cudaMemcpyAsync(in->in_dev, input_host, m->in_floats * 4, cudaMemcpyHostToDevice, st);
-    for (int i = 0; e == cudaSuccess && rc == PB_OK && i < (int)m->stages.size(); ++i) rc = pb_instance_launch_stage(in, i, st, 0, nullptr);
-    if (e == cudaSuccess && rc == PB_OK) e = cudaMemcpyAsync(output_host, in->out_dev, m->out_floats * 4, cudaMemcpyDeviceToHost, st);
+    cudaError_t e = cudaMemcpyAsync(in->in_dev, input_host, (size_t)batch * m->in_floats * 4, cudaMemcpyHostToDevice, st);
+    if (by_groups) {
+        for (int g = 0; e == cudaSuccess && rc == PB_OK && g < (int)m->groups.size(); ++g)
+            rc = pb_instance_launch_group_batched(in, g, batch, st, 0, nullptr, nullptr, nullptr);
+    } else {
+        for (int i = 0; e == cudaSuccess && rc == PB_OK && i < (int)m->stages.size(); ++i) rc = launch_stage_batched(in, i, batch, st, 0, nullptr);
+    }
+    if (e == cudaSuccess && rc == PB_OK) e = cudaMemcpyAsync(output_host, in->out_dev, (size_t)batch * m->out_floats * 4, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess && rc == PB_OK) e = cudaStreamSynchronize(st);
     cudaStreamDestroy(st);
     if (rc != PB_OK) return rc;
     if (e != cudaSuccess) return pb::cuda_fail(e, "pb_instance_run_sync", __FILE__, __LINE__);
     return PB_OK;
+}
+
+int pb_instance_run_groups_sync(pb_instance* in, const float* input_host, float* output_host) { return run_sync(in, 1, true, input_host, output_host); }
+int pb_instance_run_sync(pb_instance* in, const float* input_host, float* output_host) { return run_sync(in, 1, false, input_host, output_host); }
+int pb_instance_run_batch_sync(pb_instance* in, int batch, int by_groups, const float* inputs_host, float* outputs_host) {
+    return run_sync(in, batch, by_groups != 0, inputs_host, outputs_host);
 }
 
 int pb_instance_read_tensor(pb_instance* in, int tensor, float* dst, size_t dst_floats) {
@@ -924,7 +1059,7 @@ int pb_instance_read_tensor(pb_instance* in, int tensor, float* dst, size_t dst_
     if (m->mnist_fused) { pb::set_error("intermediate tensors do not exist in the fused MNIST kernel"); return PB_ERR_INVALID; }
     const size_t es = m->dtype == 0 ? 4 : 2;
     std::vector<uint8_t> raw((size_t)t.H * t.W * t.Cs * es);
-    PB_CUDA(cudaMemcpy(raw.data(), in->arena + t.offset, raw.size(), cudaMemcpyDeviceToHost));
+    PB_CUDA(cudaMemcpy(raw.data(), in->arena + (size_t)in->cap * t.offset, raw.size(), cudaMemcpyDeviceToHost));   // image 0
     for (int c = 0; c < t.C; ++c)
         for (int hw = 0; hw < t.H * t.W; ++hw) {
             const size_t s = (size_t)hw * t.Cs + c;
@@ -936,8 +1071,8 @@ int pb_instance_read_tensor(pb_instance* in, int tensor, float* dst, size_t dst_
     return PB_OK;
 }
 
-int pb_instance_time_stage(pb_instance* in, int stage, int iters, size_t flush_bytes, double* us_out) {
-    PB_REQUIRE(in && us_out && iters > 0 && stage >= 0 && stage < (int)in->params.size(), "pb_instance_time_stage: bad arguments");
+int pb_instance_time_stage_batched(pb_instance* in, int stage, int batch, int iters, size_t flush_bytes, double* us_out) {
+    PB_REQUIRE(in && us_out && iters > 0 && stage >= 0 && stage < (int)in->m->stages.size(), "pb_instance_time_stage: bad arguments");
     PB_CUDA(cudaSetDevice(in->m->device));
     cudaStream_t st;
     PB_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
@@ -948,11 +1083,11 @@ int pb_instance_time_stage(pb_instance* in, int stage, int iters, size_t flush_b
     PB_CUDA(cudaEventCreate(&e1));
     int rc = PB_OK;
     double total_ms = 0;
-    for (int i = 0; i < 3 && rc == PB_OK; ++i) rc = pb_instance_launch_stage(in, stage, st, 0, nullptr);   // warm-up
+    for (int i = 0; i < 3 && rc == PB_OK; ++i) rc = launch_stage_batched(in, stage, batch, st, 0, nullptr);   // warm-up
     for (int i = 0; i < iters && rc == PB_OK; ++i) {
         if (flush) cudaMemsetAsync(flush, i & 0xff, flush_bytes, st);
         cudaEventRecord(e0, st);
-        rc = pb_instance_launch_stage(in, stage, st, 0, nullptr);
+        rc = launch_stage_batched(in, stage, batch, st, 0, nullptr);
         cudaEventRecord(e1, st);
         if (cudaEventSynchronize(e1) != cudaSuccess) { rc = PB_ERR_CUDA; pb::set_error("timing run failed: %s", cudaGetErrorString(cudaGetLastError())); break; }
         float ms = 0;
@@ -966,6 +1101,10 @@ int pb_instance_time_stage(pb_instance* in, int stage, int iters, size_t flush_b
     if (rc != PB_OK) return rc;
     *us_out = total_ms * 1000.0 / iters;
     return PB_OK;
+}
+
+int pb_instance_time_stage(pb_instance* in, int stage, int iters, size_t flush_bytes, double* us_out) {
+    return pb_instance_time_stage_batched(in, stage, 1, iters, flush_bytes, us_out);
 }
 
 }  // extern "C"

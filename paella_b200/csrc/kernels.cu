@@ -78,12 +78,27 @@ __device__ __forceinline__ float act_fn(float v, int act) {
     if (nf) nf->start(job_id)
 #define PB_NOTIFY_END() if (nf) nf->end(job_id)
 
+// Batched launches (a gang of requests of one model): blockIdx.y is the image.  Image i of an
+// activation tensor follows image i - 1 without padding, so the tensor-core convolution sees the
+// images as one [batch * pixels][channels] matrix.
+template <typename T> __device__ __forceinline__ const T* x_img(const OpArgs& a) {
+    return static_cast<const T*>(a.x) + (size_t)blockIdx.y * a.H * a.W * a.Cs;
+}
+template <typename T> __device__ __forceinline__ T* y_img(const OpArgs& a) {
+    return static_cast<T*>(a.y) + (size_t)blockIdx.y * a.P * a.Q * a.Ks;
+}
+// fp32 model output of this image (a.flags & 2): the request's own buffer when a.y is NULL
+__device__ __forceinline__ float* out_f32_img(const OpArgs& a, const pb::LaunchSlot* slot, int n_out) {
+    return (!a.y && slot) ? slot->io_out[blockIdx.y] : static_cast<float*>(a.y) + (size_t)blockIdx.y * n_out;
+}
+
 // ---- NCHW fp32 -> channels-last T ------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) input_transform_kernel(const float* x, T* __restrict__ y, int C, int HW,
                                                               int Cs, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
-    if (!x && slot_) x = slot_->io_in;       // the request's input buffer, known only at dispatch
+    x = (!x && slot_) ? slot_->io_in[blockIdx.y] : x + (size_t)blockIdx.y * C * HW;   // the request's input buffer, known only at dispatch
+    y += (size_t)blockIdx.y * HW * Cs;
     const int pix = blockIdx.x * blockDim.x + threadIdx.x;
     if (pix < HW) {
         for (int c0 = 0; c0 < Cs; c0 += Vec<T>::N) {
@@ -105,8 +120,8 @@ __global__ void __launch_bounds__(256) input_transform_kernel(const float* x, T*
 template <typename T>
 __global__ void __launch_bounds__(256) input_patch_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
-    const float* __restrict__ x = static_cast<const float*>(a.x);
-    if (!x && slot_) x = slot_->io_in;       // the request's input buffer, known only at dispatch
+    const float* __restrict__ x = (!a.x && slot_) ? slot_->io_in[blockIdx.y]      // the request's input buffer, known only at dispatch
+                                                  : static_cast<const float*>(a.x) + (size_t)blockIdx.y * a.C * a.H * a.W;
     constexpr int N = Vec<T>::N;
     const int kv = a.Ks / N;
     const int total = a.P * a.Q * kv;
@@ -129,7 +144,7 @@ __global__ void __launch_bounds__(256) input_patch_kernel(OpArgs a, uint32_t job
             }
             o.v[j] = v;
         }
-        o.store(static_cast<T*>(a.y) + (size_t)pix * a.Ks + k0);
+        o.store(y_img<T>(a) + (size_t)pix * a.Ks + k0);
     }
     PB_NOTIFY_END();
 }
@@ -140,7 +155,7 @@ __global__ void __launch_bounds__(256) input_patch_kernel(OpArgs a, uint32_t job
 template <typename T>
 __global__ void __launch_bounds__(256) conv_simt_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
-    const T* __restrict__ x = static_cast<const T*>(a.x);
+    const T* __restrict__ x = x_img<T>(a);
     const T* __restrict__ w = static_cast<const T*>(a.w);
     const int total = a.P * a.Q * a.K;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -152,10 +167,10 @@ __global__ void __launch_bounds__(256) conv_simt_kernel(OpArgs a, uint32_t job_i
         const int g = k / (a.K / a.groups);
         float acc = 0.f;
         for (int r = 0; r < a.R; ++r) {
-            const int ih = p * a.stride_h + r - a.pad_h;
+            const int ih = p * a.stride_h + r * a.dil_h - a.pad_h;
             if (ih < 0 || ih >= a.H) continue;
             for (int s = 0; s < a.S; ++s) {
-                const int iw = q * a.stride_w + s - a.pad_w;
+                const int iw = q * a.stride_w + s * a.dil_w - a.pad_w;
                 if (iw < 0 || iw >= a.W) continue;
                 const T* xp = x + ((size_t)ih * a.W + iw) * a.Cs + g * cg;
                 const T* wp = w + ((size_t)(r * a.S + s) * cg) * a.K + k;
@@ -163,10 +178,10 @@ __global__ void __launch_bounds__(256) conv_simt_kernel(OpArgs a, uint32_t job_i
             }
         }
         if (a.bias) acc += a.bias[k];
-        if (a.residual) acc += to_f<T>(static_cast<const T*>(a.residual)[(size_t)pix * a.res_Cs + k]);
+        if (a.residual) acc += to_f<T>(static_cast<const T*>(a.residual)[((size_t)blockIdx.y * a.P * a.Q + pix) * a.res_Cs + k]);
         if (a.act == 3) acc = acc > 0.f ? acc : acc * a.bias[a.K + k];      // PReLU: slopes follow the biases
         else acc = act_fn(acc, a.act);
-        static_cast<T*>(a.y)[(size_t)pix * a.Ks + a.out_c_off + k] = from_f<T>(acc);
+        y_img<T>(a)[(size_t)pix * a.Ks + a.out_c_off + k] = from_f<T>(acc);
     }
     PB_NOTIFY_END();
 }
@@ -184,7 +199,7 @@ __global__ void __launch_bounds__(256) dwconv_kernel(OpArgs a, uint32_t job_id, 
         const int c0 = (idx % cv) * N;
         const int pix = idx / cv;
         const int q = pix % a.Q, p = pix / a.Q;
-        const T* __restrict__ x = static_cast<const T*>(a.x);
+        const T* __restrict__ x = x_img<T>(a);
         const T* __restrict__ w = static_cast<const T*>(a.w);
         float acc[N];
 #pragma unroll
@@ -207,7 +222,7 @@ __global__ void __launch_bounds__(256) dwconv_kernel(OpArgs a, uint32_t job_id, 
             float v = acc[j] + ((a.bias && c0 + j < a.K) ? a.bias[c0 + j] : 0.f);
             o.v[j] = (c0 + j < a.K) ? act_fn(v, a.act) : 0.f;
         }
-        o.store(static_cast<T*>(a.y) + (size_t)pix * a.Ks + a.out_c_off + c0);
+        o.store(y_img<T>(a) + (size_t)pix * a.Ks + a.out_c_off + c0);
     }
     PB_NOTIFY_END();
 }
@@ -224,7 +239,7 @@ __global__ void __launch_bounds__(256) pool_kernel(OpArgs a, uint32_t job_id, Fi
         const int c0 = (idx % cv) * N;
         const int pix = idx / cv;
         const int q = pix % a.Q, p = pix / a.Q;
-        const T* __restrict__ x = static_cast<const T*>(a.x);
+        const T* __restrict__ x = x_img<T>(a);
         float acc[N];
 #pragma unroll
         for (int j = 0; j < N; ++j) acc[j] = kMax ? -INFINITY : 0.f;
@@ -245,7 +260,7 @@ __global__ void __launch_bounds__(256) pool_kernel(OpArgs a, uint32_t job_id, Fi
         const float div = (a.flags & 1) ? (float)(a.R * a.S) : (float)(cnt > 0 ? cnt : 1);
 #pragma unroll
         for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.C) ? (kMax ? acc[j] : acc[j] / div) : 0.f;
-        o.store(static_cast<T*>(a.y) + (size_t)pix * a.Ks + a.out_c_off + c0);
+        o.store(y_img<T>(a) + (size_t)pix * a.Ks + a.out_c_off + c0);
     }
     PB_NOTIFY_END();
 }
@@ -370,7 +385,7 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
         const int c0 = (idx % cv) * N;
         const int rest = idx / cv;
         const int q0 = (rest % strips) * kStrip, p = rest / strips;
-        const T* __restrict__ x = static_cast<const T*>(a.x) + c0;
+        const T* __restrict__ x = x_img<T>(a) + c0;
         const T* __restrict__ w = (staged ? reinterpret_cast<const T*>(s_w3) : static_cast<const T*>(a.w)) + c0;
         f2_t acc[kStrip][NP];
         const f2_t init = (kMode == kWinMax) ? f2_pack(-INFINITY, -INFINITY) : f2_pack(0.f, 0.f);
@@ -427,7 +442,7 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
                 }
             }
         }
-        T* yrow = static_cast<T*>(a.y) + ((size_t)p * a.Q + q0) * a.Ks + a.out_c_off + c0;
+        T* yrow = y_img<T>(a) + ((size_t)p * a.Q + q0) * a.Ks + a.out_c_off + c0;
         float bias[N];
         if (kMode == kWinDw) {
 #pragma unroll
@@ -500,7 +515,7 @@ __global__ void __launch_bounds__(256) gap_kernel(OpArgs a, uint32_t job_id, Fin
 #pragma unroll
     for (int j = 0; j < N; ++j) acc[j] = 0.f;
     if (v < cv) {
-        const T* __restrict__ x = static_cast<const T*>(a.x);
+        const T* __restrict__ x = x_img<T>(a);
         for (int pix = grp; pix < HW; pix += 8) {
             const Vec<T> xv = Vec<T>::load(x + (size_t)pix * a.Cs + v * N);
 #pragma unroll
@@ -521,14 +536,14 @@ __global__ void __launch_bounds__(256) gap_kernel(OpArgs a, uint32_t job_id, Fin
             o[j] = s * inv;
         }
         if (a.flags & 2) {
-            float* y = (!a.y && slot_) ? slot_->io_out : static_cast<float*>(a.y);
+            float* y = out_f32_img(a, slot_, a.C);
 #pragma unroll
             for (int j = 0; j < N; ++j) if (v * N + j < a.C) y[v * N + j] = o[j];
         } else {
             Vec<T> ov;
 #pragma unroll
             for (int j = 0; j < N; ++j) ov.v[j] = (v * N + j < a.C) ? o[j] : 0.f;
-            ov.store(static_cast<T*>(a.y) + v * N);
+            ov.store(y_img<T>(a) + v * N);
         }
     }
     PB_NOTIFY_END();
@@ -544,7 +559,7 @@ __global__ void __launch_bounds__(256) dense_kernel(OpArgs a, uint32_t job_id, F
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp < a.K) {
-        const T* __restrict__ x = static_cast<const T*>(a.x);
+        const T* __restrict__ x = x_img<T>(a);
         const T* __restrict__ w = static_cast<const T*>(a.w) + (size_t)warp * a.C;
         float acc = 0.f;
         // A row of weights is streamed once, from HBM: four raw 128-bit loads per lane are issued before
@@ -575,8 +590,8 @@ __global__ void __launch_bounds__(256) dense_kernel(OpArgs a, uint32_t job_id, F
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (lane == 0) {
             const float v = act_fn(acc + (a.bias ? a.bias[warp] : 0.f), a.act);
-            if (a.flags & 2) ((!a.y && slot_) ? slot_->io_out : static_cast<float*>(a.y))[warp] = v;
-            else static_cast<T*>(a.y)[warp] = from_f<T>(v);
+            if (a.flags & 2) out_f32_img(a, slot_, a.K)[warp] = v;
+            else y_img<T>(a)[warp] = from_f<T>(v);
         }
     }
     PB_NOTIFY_END();
@@ -587,7 +602,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) add_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
     constexpr int N = Vec<T>::N;
-    const size_t nv = (size_t)a.H * a.W * a.Cs / N;
+    const size_t nv = (size_t)a.H * a.W * a.Cs / N;      // the host folds the images into H
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < nv) {
         const Vec<T> u = Vec<T>::load(static_cast<const T*>(a.x) + i * N);
@@ -665,7 +680,10 @@ __global__ void __launch_bounds__(256) softmax_kernel(OpArgs a, uint32_t job_id,
     __shared__ float bc;
     const int n = a.C;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    auto ld = [&](int i) { return kInF32 ? static_cast<const float*>(a.x)[i] : to_f<T>(static_cast<const T*>(a.x)[i]); };
+    // flags bit2: a bare fp32 vector per image; otherwise image i is tensor i of [H][W][Cs]
+    const float* xf = static_cast<const float*>(a.x) + (size_t)blockIdx.y * ((a.flags & 4) ? (size_t)n : (size_t)a.H * a.W * a.Cs);
+    const T* xt = x_img<T>(a);
+    auto ld = [&](int i) { return kInF32 ? xf[i] : to_f<T>(xt[i]); };
     float m = -INFINITY;
     for (int i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, ld(i));
 #pragma unroll
@@ -687,8 +705,8 @@ __global__ void __launch_bounds__(256) softmax_kernel(OpArgs a, uint32_t job_id,
     const float inv = 1.f / bc;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = __expf(ld(i) - m) * inv;
-        if (a.flags & 2) ((!a.y && slot_) ? slot_->io_out : static_cast<float*>(a.y))[i] = v;
-        else static_cast<T*>(a.y)[i] = from_f<T>(v);
+        if (a.flags & 2) out_f32_img(a, slot_, n)[i] = v;
+        else y_img<T>(a)[i] = from_f<T>(v);
     }
     PB_NOTIFY_END();
 }
@@ -709,8 +727,9 @@ struct MnistArgs {
 
 __global__ void __launch_bounds__(256) mnist_fused_kernel(MnistArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
     PB_NOTIFY_START();
-    if (!a.x && slot_) a.x = slot_->io_in;
-    if (!a.y && slot_) a.y = slot_->io_out;
+    // one block per image of the gang
+    a.x = (!a.x && slot_) ? slot_->io_in[blockIdx.x] : a.x + (size_t)blockIdx.x * 784;
+    a.y = (!a.y && slot_) ? slot_->io_out[blockIdx.x] : a.y + (size_t)blockIdx.x * 10;
     __shared__ float s_in[32][33];          // 28x28 image with a 2-pixel zero border
     __shared__ float s_w1[25 * 8];
     __shared__ float s_p1[18][18][8];       // pool1 output 14x14x8 with a 2-pixel zero border
@@ -791,11 +810,12 @@ static OpArgs to_args(const pb_op_params* p) {
     a.C = p->C; a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.K = p->K; a.P = p->P; a.Q = p->Q; a.Ks = p->Ks;
     a.out_c_off = p->out_c_off; a.R = p->R; a.S = p->S; a.stride_h = p->stride_h; a.stride_w = p->stride_w;
     a.pad_h = p->pad_h; a.pad_w = p->pad_w; a.groups = p->groups > 0 ? p->groups : 1; a.act = p->act; a.flags = p->flags;
-    a.res_Cs = p->res_Cs; a.x = p->x; a.w = p->w; a.bias = p->bias; a.residual = p->residual; a.y = p->y;
+    a.res_Cs = p->res_Cs; a.dil_h = p->dil_h > 1 ? p->dil_h : 1; a.dil_w = p->dil_w > 1 ? p->dil_w : 1; a.x = p->x; a.w = p->w; a.bias = p->bias; a.residual = p->residual; a.y = p->y;
     return a;
 }
 
 static int vec_n(int dtype) { return dtype == 0 ? 4 : 8; }
+static int batch_of(const pb_op_params* p) { return p->batch > 1 ? p->batch : 1; }
 static size_t elem_size(int dtype) { return dtype == 0 ? 4 : 2; }
 
 template <typename F>
@@ -829,7 +849,7 @@ static int strip_of(const pb_op_params* p) {
         }
     }
     const int wide = p->stride_h == 1 ? kStripWide1 : kStripWide2;
-    const size_t n = (size_t)p->P * ((p->Q + wide - 1) / wide) * (p->Cs / vec_n(p->dtype));
+    const size_t n = (size_t)batch_of(p) * p->P * ((p->Q + wide - 1) / wide) * (p->Cs / vec_n(p->dtype));
     return n >= (size_t)sms * 2048 ? wide : 1;
 }
 static size_t strip_threads(const pb_op_params* p, int strip) {
@@ -848,7 +868,8 @@ static const void* window3_fn(int kind, bool f32, int stride, int strip) {
          : kind == PB_STAGE_MAXPOOL ? window3_fn<kWinMax>(f32, stride, strip) : window3_fn<kWinAvg>(f32, stride, strip);
 }
 
-int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
+// Geometry of ONE image of the launch (blocks, algorithmic work); strip_of() alone looks at the batch.
+static int info_one_image(int kind, const pb_op_params* p, pb_launch_info* out) {
     memset(out, 0, sizeof(*out));
     out->kind = (uint32_t)kind;
     out->threads_per_block = 256;
@@ -936,6 +957,28 @@ int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
     return PB_OK;
 }
 
+// Elementwise kernels see a batch as one taller tensor (images are contiguous).
+static bool folds_batch(int kind) { return kind == PB_STAGE_ADD || kind == PB_STAGE_AFFINE; }
+
+int simple_op_info(int kind, const pb_op_params* p, pb_launch_info* out) {
+    const int nb = batch_of(p);
+    const int rc = info_one_image(kind, p, out);
+    if (rc != PB_OK || nb == 1) return rc;
+    if (folds_batch(kind)) {
+        pb_op_params q = *p;
+        q.H *= nb;
+        return info_one_image(kind, &q, out);
+    }
+    out->num_blocks *= (uint32_t)nb;
+    out->flops *= (uint64_t)nb;
+    // the weights are read once per launch whatever the batch
+    const uint64_t es = p->dtype == 0 ? 4 : 2;
+    const uint64_t wbytes = kind == PB_STAGE_DENSE ? es * (uint64_t)p->C * p->K
+                          : kind == PB_STAGE_DWCONV ? es * (uint64_t)p->K * p->R * p->S : 0;
+    out->bytes = wbytes + (out->bytes - wbytes) * (uint64_t)nb;
+    return PB_OK;
+}
+
 static thread_local size_t t_launch_smem = 0;      // dynamic shared memory of the next launch_k (reset by it)
 
 template <typename... KArgs, typename... Args>
@@ -957,14 +1000,23 @@ static void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t
 int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl) {
     FinishedBlockNotifier* nf = static_cast<FinishedBlockNotifier*>(notifier);
     pb_launch_info li;
-    int rc = simple_op_info(kind, p, &li);
+    pb_op_params folded;
+    int nb = batch_of(p);
+    if (nb > 1 && folds_batch(kind)) {
+        folded = *p;
+        folded.H *= nb;
+        folded.batch = 1;
+        p = &folded;
+        nb = 1;
+    }
+    int rc = info_one_image(kind, p, &li);
     if (rc != PB_OK) return rc;
     const OpArgs a = to_args(p);
     const bool f32 = p->dtype == 0;
     const int N = vec_n(p->dtype);
     if (kind == PB_STAGE_INPUT) PB_REQUIRE(p->Ks % N == 0, "output channel stride %d is not a multiple of the %d-element vector", p->Ks, N);
     else PB_REQUIRE(p->Cs % N == 0, "channel stride %d is not a multiple of the %d-element vector", p->Cs, N);
-    const dim3 grid(li.num_blocks), block(256);
+    const dim3 grid(li.num_blocks, (unsigned)nb), block(256);      // blockIdx.y = image
 #define PB_DISPATCH(kern_f32, kern_bf16, ...)                                           \
     do {                                                                                \
         if (f32) launch_k(kern_f32, grid, block, st, pdl, __VA_ARGS__);                 \
@@ -1028,8 +1080,8 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
             break;
         case PB_STAGE_SOFTMAX:
             // flags bit2: the input is fp32 regardless of dtype
-            if (f32 || (p->flags & 4)) launch_k(softmax_kernel<float, true>, dim3(1), block, st, pdl, a, job_id, nf);
-            else launch_k(softmax_kernel<__nv_bfloat16, false>, dim3(1), block, st, pdl, a, job_id, nf);
+            if (f32 || (p->flags & 4)) launch_k(softmax_kernel<float, true>, grid, block, st, pdl, a, job_id, nf);
+            else launch_k(softmax_kernel<__nv_bfloat16, false>, grid, block, st, pdl, a, job_id, nf);
             break;
         default:
             set_error("pb_op_launch: unknown stage kind %d", kind);
@@ -1098,9 +1150,9 @@ int mnist_fused_info(pb_launch_info* out) {
 }
 
 int mnist_fused_launch(const float* x, const float* w1, const float* b1, const float* w2, const float* b2,
-                       const float* wd, const float* bd, float* y, cudaStream_t st, uint32_t job_id, void* notifier) {
+                       const float* wd, const float* bd, float* y, int batch, cudaStream_t st, uint32_t job_id, void* notifier) {
     MnistArgs a{x, w1, b1, w2, b2, wd, bd, y};
-    mnist_fused_kernel<<<1, 256, 0, st>>>(a, job_id, static_cast<FinishedBlockNotifier*>(notifier));
+    mnist_fused_kernel<<<batch > 1 ? batch : 1, 256, 0, st>>>(a, job_id, static_cast<FinishedBlockNotifier*>(notifier));
     return launch_check("mnist_fused");
 }
 

@@ -1,6 +1,7 @@
 // Launch slot: per-instance device record through which kernels captured in a CUDA graph learn,
 // at run time, what a graph cannot bake in: the job id and notifier of this dispatch and the
-// request's input/output buffers.  The first node of every stage graph copies the slot from a
+// input/output buffers of the request, or of every request of a gang (up to kMaxGang requests of
+// one model that run as one batched launch; member i is image i of every activation tensor).  The first node of every stage graph copies the slot from a
 // pinned host mirror that the host fills right before cudaGraphLaunch.
 //
 // Kernel parameter convention (all instrumented kernels end with `uint32_t job_id, Notifier* nf`):
@@ -15,14 +16,16 @@
 
 namespace pb {
 
+constexpr int kMaxGang = 8;
+
 struct LaunchSlot {
     llis::job::FinishedBlockNotifier* nf;
     uint32_t job_id;
     uint32_t reserved;
-    const float* io_in;   // request input, NCHW fp32 (host-mapped pinned or device memory)
-    float* io_out;        // request output, fp32
+    const float* io_in[kMaxGang];   // request inputs, NCHW fp32 (host-mapped pinned or device memory), one per member
+    float* io_out[kMaxGang];        // request outputs, fp32, one per member
 };
-static_assert(sizeof(LaunchSlot) == 32, "launch slot is 32 bytes");
+static_assert(sizeof(LaunchSlot) == 16 + 16 * kMaxGang, "launch slot layout");
 
 constexpr uint32_t kSlotNotify = 0xFFFFFFFFu;
 constexpr uint32_t kSlotQuiet = 0xFFFFFFFEu;

@@ -16,6 +16,7 @@ struct OpArgs {
     int out_c_off;
     int R, S, stride_h, stride_w, pad_h, pad_w, groups;
     int act, flags, res_Cs;
+    int dil_h, dil_w;      // filter dilation (>= 1)
     const void* x;
     const void* w;
     const float* bias;
@@ -30,7 +31,7 @@ int64_t simple_pack_weights(int kind, const pb_op_params* p, const float* w_oihw
 void store_elem(void* dst, size_t i, float v, int dtype);
 int mnist_fused_info(pb_launch_info* out);
 int mnist_fused_launch(const float* x, const float* w1, const float* b1, const float* w2, const float* b2,
-                       const float* wd, const float* bd, float* y, cudaStream_t st, uint32_t job_id, void* notifier);
+                       const float* wd, const float* bd, float* y, int batch, cudaStream_t st, uint32_t job_id, void* notifier);
 
 // conv_umma.cu: tcgen05 implicit-GEMM convolution (bf16 operands, fp32 accumulation in TMEM)
 bool conv_umma_supported(const pb_op_params* p);
@@ -61,6 +62,7 @@ int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap*
 void conv_umma_multi_destroy(ConvUmmaMulti* m);
 void conv_umma_multi_info(const ConvUmmaMulti* m, pb_launch_info* out);
 int conv_umma_multi_launch(const ConvUmmaMulti* m, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl);
+void conv_umma_set_split_gain_us(double us);   // < 0: back to PB_CONV_SPLIT_GAIN_US / the default
 int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
 uint32_t* noalloc_error_flag_ptr(int device);   // NULL until the no-allocation path ran on the device
 

@@ -17,6 +17,9 @@ thread_local Job* t_current_job = nullptr;
 thread_local ipc::Gpu2SchedChannel* t_channel = nullptr;
 thread_local int t_device = 0;
 thread_local bool t_device_resident = false;
+thread_local unsigned t_max_gang = 1;
+thread_local Job* const* t_gang = nullptr;
+thread_local unsigned t_gang_n = 0;
 }  // namespace
 
 Job* Context::get_current_job() { return t_current_job; }
@@ -27,6 +30,16 @@ int Context::get_device() { return t_device; }
 void Context::set_device(int device) { t_device = device; }
 bool Context::device_resident() { return t_device_resident; }
 void Context::set_device_resident(bool v) { t_device_resident = v; }
+unsigned Context::max_gang() { return t_max_gang; }
+void Context::set_max_gang(unsigned n) { t_max_gang = n >= 1 ? n : 1; }
+Job* const* Context::get_gang(unsigned* num_followers) {
+    if (num_followers) *num_followers = t_gang_n;
+    return t_gang;
+}
+void Context::set_gang(Job* const* followers, unsigned num_followers) {
+    t_gang = num_followers ? followers : nullptr;
+    t_gang_n = followers ? num_followers : 0;
+}
 
 FinishedBlockNotifier* FinishedBlockNotifier::create_array(unsigned num, ipc::Gpu2SchedChannel* channel) {
     void* dev = nullptr;

@@ -148,6 +148,12 @@ bool ShmChannel::can_read() {
     return write_pos_->load(std::memory_order_acquire) != cached_read_;
 }
 
+size_t ShmChannel::writable_bytes() {
+    cached_read_ = read_pos_->load(std::memory_order_acquire);
+    const size_t used = cached_write_ >= cached_read_ ? cached_write_ - cached_read_ : size_ - cached_read_ + cached_write_;
+    return size_ - 1 - used;        // one byte always stays free
+}
+
 void ShmChannel::acquire_writer_lock() {
     while (lock_->test_and_set(std::memory_order_acquire)) {}
     // another writer may have moved the shared position since this endpoint last wrote

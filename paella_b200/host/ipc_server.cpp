@@ -20,12 +20,39 @@ IpcServer::IpcServer(std::string name, const pb_server_config& cfg) : name_(std:
     if (core_->init(cfg) != PB_OK) throw std::runtime_error(pb_last_error());
     c2s_channel_.connect(ipc::c2s_channel_name(name_), c2s_channel_size);
     core_->on_job_starts = [this](job::Job* job) { wake(*clients_[job->get_client_id()]); };
-    core_->on_job_ends = [this](job::Job* job) {
-        ClientConnection& c = *clients_[job->get_client_id()];
-        if (c.gone) return;             // nobody reads that ring any more
-        void* remote = job->get_remote_ptr();
-        c.s2c_channel.write(remote);
-    };
+    core_->on_job_ends = [this](job::Job* job) { complete(*clients_[job->get_client_id()], job->get_remote_ptr()); };
+}
+
+// Completion entry for one job on its client's ring.  Never waits: a client that is alive but not
+// draining (or one that died with nothing left to wake) would otherwise stall the one server thread, and
+// with it every other client.  What does not fit is kept, in order, and retried from step(); a client whose
+// ring stays full for kStallLimit is treated as gone.
+void IpcServer::complete(ClientConnection& c, void* remote_ptr) {
+    if (c.gone) return;             // nobody reads that ring any more
+    if (c.pending_done.empty() && c.s2c_channel.writable_bytes() >= sizeof(remote_ptr)) {
+        c.s2c_channel.write(remote_ptr);
+        return;
+    }
+    if (c.pending_done.empty()) c.stalled_since = std::chrono::steady_clock::now();
+    c.pending_done.push_back(remote_ptr);
+}
+
+void IpcServer::retry_completions() {
+    constexpr auto kStallLimit = std::chrono::seconds(10);
+    for (auto& cp : clients_) {
+        ClientConnection& c = *cp;
+        while (!c.gone && !c.pending_done.empty() && c.s2c_channel.writable_bytes() >= sizeof(void*)) {
+            c.s2c_channel.write(c.pending_done.front());
+            c.pending_done.pop_front();
+            c.stalled_since = std::chrono::steady_clock::now();
+        }
+        if (!c.gone && !c.pending_done.empty() && std::chrono::steady_clock::now() - c.stalled_since > kStallLimit) {
+            fprintf(stderr, "llis_server: a client has not read its completions for 10 s; dropping it\n");
+            c.gone = true;
+            c.pending_done.clear();
+            c.pending_wakeups = 0;
+        }
+    }
 }
 
 // One wake-up datagram per finishing job.  The client's receive queue is short (net.unix.max_dgram_qlen,
@@ -69,6 +96,7 @@ bool IpcServer::step() {
     // drain what the clients have queued (bounded, so that notifications are still polled in between)
     for (int i = 0; i < 32 && running_ && c2s_channel_.can_read(); ++i) handle_c2s();
     if (core_->step(64) < 0) throw std::runtime_error(pb_last_error());
+    retry_completions();
     retry_wakeups();
     return running_;
 }
@@ -133,7 +161,11 @@ void IpcServer::handle_grow_pool() {
     size_t num_new_bytes;
     c2s_channel_.read(&id);
     c2s_channel_.read(&num_new_bytes);
-    RegisteredJob& j = jobs_.at(id);
+    if (id >= jobs_.size() || jobs_[id].shm_fd < 0 || num_new_bytes == 0) {
+        fprintf(stderr, "llis_server: GROW_POOL for unknown job %u (or of 0 bytes) ignored\n", id);
+        return;
+    }
+    RegisteredJob& j = jobs_[id];
     void* p = mmap(nullptr, num_new_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, j.shm_fd, (off_t)j.pool_bytes);
     if (p == MAP_FAILED) throw std::runtime_error("mmap of the client's request pool failed");
     if (mlock(p, num_new_bytes) != 0) fprintf(stderr, "llis_server: mlock of %zu pool bytes failed (continuing)\n", num_new_bytes);
@@ -142,6 +174,7 @@ void IpcServer::handle_grow_pool() {
     if (e != cudaSuccess) throw std::runtime_error(std::string("cudaHostRegister(request pool): ") + cudaGetErrorString(e));
     j.pool_bytes += num_new_bytes;
     j.mapped.push_back(p);
+    j.mapped_bytes.push_back(num_new_bytes);
 }
 
 void IpcServer::handle_launch_job() {
@@ -153,10 +186,30 @@ void IpcServer::handle_launch_job() {
     c2s_channel_.read(&chunk);
     c2s_channel_.read(&offset);
     c2s_channel_.read(&remote_ptr);
-    RegisteredJob& j = jobs_.at(id);
-    void* io = static_cast<char*>(j.mapped.at((size_t)chunk)) + offset;
-    const int rc = core_->launch(id, io, (uint64_t)(uintptr_t)remote_ptr, j.client_id);
-    if (rc != PB_OK) fprintf(stderr, "llis_server: launch of job type %u failed: %s\n", id, pb_last_error());
+    // A malformed message must not take the server down for every other client: check what it names.
+    if (id >= jobs_.size() || jobs_[id].shm_fd < 0) {
+        fprintf(stderr, "llis_server: LAUNCH_JOB names unknown job %u; ignored (no client to answer)\n", id);
+        return;
+    }
+    RegisteredJob& j = jobs_[id];
+    int rc = PB_OK;
+    const size_t slot_bytes = core_->types[id]->slot_bytes;
+    if (chunk < 0 || (size_t)chunk >= j.mapped.size() || slot_bytes > j.mapped_bytes[(size_t)chunk] ||
+        offset > j.mapped_bytes[(size_t)chunk] - slot_bytes) {
+        fprintf(stderr, "llis_server: LAUNCH_JOB of job %u names chunk %d offset %zu outside its request pool\n", id, chunk, offset);
+        rc = PB_ERR_INVALID;
+    } else {
+        void* io = static_cast<char*>(j.mapped[(size_t)chunk]) + offset;
+        rc = core_->launch(id, io, (uint64_t)(uintptr_t)remote_ptr, j.client_id);
+        if (rc != PB_OK) fprintf(stderr, "llis_server: launch of job type %u failed: %s\n", id, pb_last_error());
+    }
+    if (rc != PB_OK && j.client_id < clients_.size() && clients_[j.client_id]->in_use) {
+        // The job never reached the scheduler, so no completion would ever come and the client's wait() would
+        // block for good: answer now with what a finished job sends (wake-up datagram, then its pointer).
+        ClientConnection& c = *clients_[j.client_id];
+        wake(c);
+        complete(c, remote_ptr);
+    }
 }
 
 }  // namespace server

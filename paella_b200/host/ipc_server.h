@@ -5,6 +5,8 @@
 #include <llis/ipc/shm_channel.h>
 #include <llis/ipc/unix_datagram_socket.h>
 
+#include <chrono>
+#include <deque>
 #include <memory>
 #include <string>
 #include <vector>
@@ -34,7 +36,11 @@ class IpcServer {
         bool in_use = false;
         bool gone = false;              // its socket vanished: the process has exited
         unsigned pending_wakeups = 0;   // datagrams that did not fit the client's receive queue yet
+        std::deque<void*> pending_done; // completions that did not fit its ring yet (a client that is not draining)
+        std::chrono::steady_clock::time_point stalled_since{};   // when pending_done became non-empty
     };
+    void complete(ClientConnection& c, void* remote_ptr);
+    void retry_completions();
     void wake(ClientConnection& c);
     void retry_wakeups();
     struct RegisteredJob {
@@ -42,7 +48,8 @@ class IpcServer {
         std::string shm_name;
         int shm_fd = -1;
         size_t pool_bytes = 0;
-        std::vector<void*> mapped;
+        std::vector<void*> mapped;            // pool chunks, in the order the client grew the pool
+        std::vector<size_t> mapped_bytes;
     };
     void handle_c2s();
     void handle_register_client();

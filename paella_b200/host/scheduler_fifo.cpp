@@ -88,7 +88,7 @@ class SchedulerFifo final : public PoolsBase {
     const char* name() const override { return "fifo"; }
 
     void handle_new_job(Job* job) override {
-        if (!job->has_next()) { host_->release_job_instance(job); return; }
+        if (!job->has_next()) { host_->notify_job_starts(job); host_->notify_job_ends(job); host_->release_job_instance(job); return; }
         admit(job);
         queue_.push_back(job);
         schedule_job();
@@ -141,8 +141,8 @@ class SchedulerFifo final : public PoolsBase {
                 ++num_decisions_;
                 host_->on_dispatch(job, is_mem, false, ss, ns);
                 run_stage(job, host_);
+                if (!job->has_error() && is_mem) host_->after_mem_stage(job);
                 if (job->has_error()) close_failed_stage(job, is_mem);
-                else if (is_mem) host_->after_mem_stage(job);
             }
         }
     }
@@ -155,7 +155,7 @@ class SchedulerFifo2 final : public PoolsBase {
     const char* name() const override { return "fifo2"; }
 
     void handle_new_job(Job* job) override {
-        if (!job->has_next()) { host_->release_job_instance(job); return; }
+        if (!job->has_next()) { host_->notify_job_starts(job); host_->notify_job_ends(job); host_->release_job_instance(job); return; }
         admit(job);
         heap_.push(job);
         schedule_job();
@@ -207,8 +207,8 @@ class SchedulerFifo2 final : public PoolsBase {
             ++num_decisions_;
             host_->on_dispatch(job, is_mem, false, ss, ns);
             run_stage(job, host_);
+            if (!job->has_error() && is_mem) host_->after_mem_stage(job);
             if (job->has_error()) close_failed_stage(job, is_mem);
-            else if (is_mem) host_->after_mem_stage(job);
         }
     }
     std::priority_queue<Job*, std::vector<Job*>, Later> heap_;

@@ -12,9 +12,19 @@
 // same ring as block notifications instead of a driver callback thread and a second ring;
 // the occupancy totals are those of the device in use (148 SMs on B200) and include tensor
 // memory; time comes from the host interface so a trace replays exactly.
+//
+// Gangs (SchedulerConfig::max_gang > 1; off by default, and off in every replay): when the job
+// about to be dispatched is at its first stage and its plugin can run several jobs per launch,
+// the queued jobs of the same type that have not started either - at most max_gang - 1 and at
+// most the plugin's capacity - are taken out of the queue with it and follow it for the rest
+// of their life: each stage of the leader is ONE dispatch (one stream, one notifier, one set
+// of records) that serves every member, and when the leader ends all members end.  Nothing
+// waits for a gang to fill: only jobs that are already queued at dispatch time join.
+#include <llis/job/context.h>
 #include <llis/server/job_queue.h>
 #include <llis/server/scheduler.h>
 
+#include <algorithm>
 #include <cstdio>
 
 namespace llis {
@@ -29,6 +39,15 @@ class SchedulerFull3 final : public Scheduler {
           max_num_outstanding_kernels_(cfg.extra_kernels) {}
 
     const char* name() const override { return "full3"; }
+    void set_deferred(bool on) override {
+        deferred_ = on;
+        if (!on) flush();
+    }
+    void flush() override {
+        if (!dirty_) return;
+        dirty_ = false;
+        dispatch_loop();
+    }
     unsigned num_jobs() const override { return num_jobs_; }
     uint64_t num_decisions() const override { return num_decisions_; }
 
@@ -45,6 +64,10 @@ class SchedulerFull3 final : public Scheduler {
 
     void handle_new_job(job::Job* job) override {
         if (!job->has_next()) {
+            // nothing to run: the client still gets its start and end messages (the reference releases such a
+            // job silently, scheduler_full3.cpp:274-278, and its client waits for ever)
+            host_->notify_job_starts(job);
+            host_->notify_job_ends(job);
             host_->release_job_instance(job);
             return;
         }
@@ -54,6 +77,7 @@ class SchedulerFull3 final : public Scheduler {
             jobs_.push_back(job);
             job_stream_slot_.push_back(0);
             job_notifier_slot_.push_back(0);
+            followers_.emplace_back();
         } else {
             id = unused_job_id_.back();
             unused_job_id_.pop_back();
@@ -104,6 +128,12 @@ class SchedulerFull3 final : public Scheduler {
         } else {
             host_->notify_job_ends(job);
             --num_jobs_;
+            // the members of its gang end with it (and share its failure, if any)
+            for (job::Job* f : followers_[job->get_id()]) {
+                if (job->has_error()) f->set_error(job->has_error());
+                host_->notify_job_ends(f);
+                --num_jobs_;
+            }
         }
     }
 
@@ -136,12 +166,37 @@ class SchedulerFull3 final : public Scheduler {
 
     void retire(job::Job* job) {
         const JobId id = job->get_id();
+        for (job::Job* f : followers_[id]) retire(f);
+        followers_[id].clear();
         unused_job_id_.push_back(id);
         jobs_[id] = nullptr;
         host_->release_job_instance(job);
     }
 
+    // Takes the queued, not yet started jobs of the leader's type out of the queue as its followers.
+    void form_gang(job::Job* leader) {
+        std::vector<job::Job*>& fol = followers_[leader->get_id()];
+        const unsigned want = std::min(cfg_.max_gang, leader->get_gang_capacity());
+        const JobRefId type = leader->get_registered_job_id();
+        while (fol.size() + 1 < want) {
+            job::Job* f = job_queue_.pop_of_type_if(type, [](const job::Job* j) { return j->get_cur_stage() == -1 && !j->is_mem(); });
+            if (!f) break;
+            f->set_started();
+            fol.push_back(f);
+        }
+        if (!fol.empty()) {
+            leader->apply_gang_size((unsigned)fol.size() + 1);
+            ++num_gangs_;
+            num_gang_members_ += fol.size() + 1;
+        }
+    }
+
     void schedule_job() {
+        if (deferred_) { dirty_ = true; return; }
+        dispatch_loop();
+    }
+
+    void dispatch_loop() {
         if (free_streams_.empty() || job_queue_.empty()) return;
         do {
             job::Job* job = job_queue_.top();
@@ -157,6 +212,7 @@ class SchedulerFull3 final : public Scheduler {
                 unfit = true;
             }
             job_queue_.pop();
+            if (cfg_.max_gang > 1 && !is_mem && job->get_cur_stage() == -1 && job->get_gang_capacity() > 1) form_gang(job);
             if (!job->has_started()) job->set_started();
 
             const unsigned sslot = free_streams_.back();
@@ -171,13 +227,19 @@ class SchedulerFull3 final : public Scheduler {
                 job->set_finished_block_notifier(all_notifiers_[nslot]);
                 gpu_resources_.acquire(job, (int)job->get_cur_num_blocks());
             }
-            if (job->is_pre_notify()) host_->notify_job_starts(job);
+            const std::vector<job::Job*>& gang = followers_[job->get_id()];
+            if (job->is_pre_notify()) {
+                host_->notify_job_starts(job);
+                for (job::Job* f : gang) host_->notify_job_starts(f);
+            }
             ++num_decisions_;
             host_->on_dispatch(job, is_mem, unfit, sslot, nslot);
 
+            job::Context::set_gang(gang.data(), (unsigned)gang.size());
             run_stage(job, host_);
+            job::Context::set_gang(nullptr, 0);
+            if (!job->has_error() && is_mem) host_->after_mem_stage(job);     // may fail too (the marker kernel's launch)
             if (job->has_error()) close_failed_stage(job, is_mem);
-            else if (is_mem) host_->after_mem_stage(job);
             if (free_streams_.empty()) break;
         } while (!job_queue_.empty());
     }
@@ -199,6 +261,9 @@ class SchedulerFull3 final : public Scheduler {
     std::vector<unsigned> free_streams_, free_notifiers_;
     std::vector<unsigned> job_stream_slot_, job_notifier_slot_;   // by JobId
     std::vector<job::Job*> jobs_;                                 // by JobId
+    std::vector<std::vector<job::Job*>> followers_;               // by JobId of the leader: the other members of its gang
+    uint64_t num_gangs_ = 0, num_gang_members_ = 0;
+    bool deferred_ = false, dirty_ = false;
     std::vector<JobId> unused_job_id_;
     unsigned num_jobs_ = 0;
     uint64_t num_decisions_ = 0;

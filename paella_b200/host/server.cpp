@@ -77,6 +77,7 @@ int pb_server::init(const pb_server_config& c) {
     sc.extra_kernels = c.extra_kernels;
     sc.unfairness_threshold = c.unfairness_threshold;
     sc.sched_sleep = c.sched_sleep;
+    sc.max_gang = c.max_gang > 1 ? (c.max_gang < PB_MAX_GANG ? c.max_gang : PB_MAX_GANG) : 1;
     int rc = llis::server::SmResources::query_device(device, &sc.totals);
     if (rc != PB_OK) return rc;
     try {
@@ -96,6 +97,7 @@ int pb_server::init(const pb_server_config& c) {
     scheduler = llis::server::Scheduler::create(c.scheduler ? c.scheduler : "full3", sc, this);
     PB_REQUIRE(scheduler != nullptr, "unknown scheduler '%s'", c.scheduler ? c.scheduler : "");
     scheduler->set_pools(streams, nfs);
+    scheduler->set_deferred(c.deferred_schedule != 0 || sc.max_gang > 1);
     return PB_OK;
 }
 
@@ -128,6 +130,7 @@ int pb_server::launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie, llis::
     PB_REQUIRE(job != nullptr, "launch: plugin could not create an instance");
     Context::set_device(device);
     Context::set_device_resident(cfg.device_resident != 0);
+    Context::set_max_gang(cfg.max_gang > 1 ? cfg.max_gang : 1);
     job->set_remote_ptr((void*)(uintptr_t)cookie);
     if (fresh) {
         job->set_client_details(client_id, t.id);
@@ -157,13 +160,17 @@ int pb_server::step(int max_records) {
     uint64_t recs[64];
     int handled = 0;
     std::vector<InstrumentInfo> made_up;
-    while (scheduler->take_synthetic(&made_up))
+    scheduler->flush();          // requests admitted since the last step
+    while (scheduler->take_synthetic(&made_up)) {
         for (const InstrumentInfo& r : made_up) scheduler->handle_record(r);
+        scheduler->flush();
+    }
     while (handled < max_records) {
         const int want = max_records - handled < 64 ? max_records - handled : 64;
         const int n = pb_ring_poll(channel.handle(), recs, want);
         if (n < 0) { last_error = n; return n; }
         for (int i = 0; i < n; ++i) scheduler->handle_record(InstrumentInfo::unpack(recs[i]));
+        scheduler->flush();
         handled += n;
         num_records += (uint64_t)n;
         if (n < want) break;
@@ -205,6 +212,7 @@ void pb_server_config_default(pb_server_config* cfg) {
     cfg->unfairness_threshold = 1e6f;
     cfg->ring_capacity = 1ull << 20;
     cfg->scheduler = "full3";
+    cfg->max_gang = 1;
 }
 
 int pb_server_create(const pb_server_config* cfg, pb_server** out) {

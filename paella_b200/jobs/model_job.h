@@ -7,6 +7,12 @@
 // and PB_STAGE_GROUP=1 its one-kernel-per-stage granularity.  Written as a stage-index state machine instead of a
 // boost coroutine; the server only sees the llis::job::Job interface.
 //
+// Gangs: when the server allows it (Context::max_gang() > 1) the adapter sizes its instance for that many
+// images and tells the scheduler, per stage, what a gang of n such jobs declares; the scheduler may then
+// dispatch this job as the LEADER of up to n - 1 queued jobs of the same model (listed in Context), and
+// each run_next() enqueues the stage once for all of them: one batched launch, every member's input read
+// from and result written to its own pinned slot.
+//
 // Differences from the reference adapters: the D2H stage copies the OUTPUT tensor (there
 // it copies from the input buffer, tvm_mnist.cpp:46); the device comes from the server
 // thread's context instead of being hard-wired to 0; CUDA failures set the job's error
@@ -43,62 +49,81 @@ class ModelJob : public llis::job::Job {
         pb_model* model = shared_model(device, path);
         if (!model) { set_error(PB_ERR_IO); return; }
         if (pb_model_input_bytes(model) != in_bytes_ || pb_model_output_bytes(model) != out_bytes_) { set_error(PB_ERR_INVALID); return; }
-        if (pb_instance_create(model, &inst_) != PB_OK) { set_error(PB_ERR_CUDA); return; }
         // PB_COPY_STAGES=1: the reference's protocol (H2D copy stage, kernels, D2H copy stage).  Default:
         // the first kernel reads the pinned request slot and the last writes the result into it, so a
         // request is nothing but its kernel stages.
         const char* cs = std::getenv("PB_COPY_STAGES");
         copy_stages_ = cs && cs[0] == '1';
+        cap_ = copy_stages_ ? 1 : (int)llis::job::Context::max_gang();
+        if (cap_ > PB_MAX_GANG) cap_ = PB_MAX_GANG;
+        if (cap_ < 1) cap_ = 1;
+        // every gang size is prepared now (descriptors, graphs): nothing is built on the serving path
+        if (pb_instance_create_batched(model, cap_, 1, &inst_) != PB_OK) { set_error(PB_ERR_CUDA); return; }
         const int n = pb_model_num_groups(model);
-        decls_.resize((size_t)n);
-        for (int i = 0; i < n; ++i) {
-            pb_launch_info li;
-            pb_model_group_info(model, i, &li);
-            llis::job::StageDecl& d = decls_[(size_t)i];
-            d.num_blocks = li.num_blocks;
-            d.num_threads_per_block = li.threads_per_block;
-            d.smem_size_per_block = li.smem_per_block;
-            d.num_registers_per_thread = li.regs_per_thread;
-            d.tmem_cols_per_block = li.tmem_cols_per_block;
-        }
+        decls_.resize((size_t)n * (size_t)cap_);          // [group][gang size - 1]
+        for (int i = 0; i < n; ++i)
+            for (int nb = 1; nb <= cap_; ++nb) {
+                pb_launch_info li;
+                if (pb_model_group_info_batched(model, i, nb, &li) != PB_OK) { set_error(PB_ERR_INVALID); return; }
+                llis::job::StageDecl& d = decls_[(size_t)i * cap_ + (nb - 1)];
+                d.num_blocks = li.num_blocks;
+                d.num_threads_per_block = li.threads_per_block;
+                d.smem_size_per_block = li.smem_per_block;
+                d.num_registers_per_thread = li.regs_per_thread;
+                d.tmem_cols_per_block = li.tmem_cols_per_block;
+            }
+        num_groups_ = n;
         init(io_ptr);
     }
 
     void init(void* io_ptr) override {
         io_ptr_ = static_cast<char*>(io_ptr);
         next_ = 0;
+        gang_n_ = 1;
         resident_ = llis::job::Context::device_resident();
         declare();
     }
 
     // Stage list: [H2D copy] group 0 .. group n-1 [D2H copy]; the copies exist only with PB_COPY_STAGES=1.
     void run_next() override {
-        const int n = (int)decls_.size();
+        const int n = num_groups_;
         const int lead = copy_stages_ ? 1 : 0;
         cudaStream_t st = get_cuda_stream();
         const int cur = next_++;
+        // the members of this dispatch: this job and, when it leads a gang, the followers the scheduler lists
+        unsigned n_follow = 0;
+        llis::job::Job* const* follow = llis::job::Context::get_gang(&n_follow);
+        if ((int)n_follow + 1 > cap_) { set_error(PB_ERR_INVALID); n_follow = 0; }
+        gang_n_ = 1 + (int)n_follow;       // a gang stays together: the following stages are declared for it
         declare();      // the stage that follows is declared before this one is enqueued
         if (!inst_) return;
         if (cur < lead) {
             if (!resident_) check(cudaMemcpyAsync(pb_instance_input_dev(inst_), io_ptr_, in_bytes_, cudaMemcpyHostToDevice, st));
         } else if (cur < lead + n) {
             const bool direct_io = !copy_stages_ && !resident_;
-            const void* in = direct_io ? io_ptr_ : nullptr;
-            // Loads issued by SMs keep few PCIe reads in flight (about 11 GB/s measured); a copy engine
-            // streams several times faster.  Large inputs therefore go through the instance's device
-            // input buffer, enqueued on the same stream right before the first kernel group.
-            if (direct_io && cur == lead && in_bytes_ >= kDmaInputBytes) {
-                check(cudaMemcpyAsync(pb_instance_input_dev(inst_), io_ptr_, in_bytes_, cudaMemcpyHostToDevice, st));
-                in = nullptr;
+            const void* ins[PB_MAX_GANG];
+            void* outs[PB_MAX_GANG];
+            for (int i = 0; i < gang_n_; ++i) {
+                char* io = i == 0 ? io_ptr_ : static_cast<ModelJob*>(follow[i - 1])->io_ptr_;     // followers are jobs of this type
+                ins[i] = direct_io ? io : nullptr;
+                // Loads issued by SMs keep few PCIe reads in flight (about 11 GB/s measured); a copy engine
+                // streams several times faster.  Large inputs therefore go through the instance's device
+                // input buffer (image i), enqueued on the same stream right before the first kernel group.
+                if (direct_io && cur == lead && in_bytes_ >= kDmaInputBytes) {
+                    check(cudaMemcpyAsync(static_cast<char*>(pb_instance_input_dev(inst_)) + (size_t)i * in_bytes_, io, in_bytes_,
+                                          cudaMemcpyHostToDevice, st));
+                    ins[i] = nullptr;
+                }
+                outs[i] = direct_io ? io + get_output_offset() : nullptr;
             }
-            void* out = direct_io ? io_ptr_ + get_output_offset() : nullptr;
-            if (pb_instance_launch_group(inst_, cur - lead, st, get_id(), get_finished_block_notifier(), in, out) != PB_OK) set_error(PB_ERR_CUDA);
+            if (pb_instance_launch_group_batched(inst_, cur - lead, gang_n_, st, get_id(), get_finished_block_notifier(), ins, outs) != PB_OK)
+                set_error(PB_ERR_CUDA);
         } else {
             if (!resident_) check(cudaMemcpyAsync(io_ptr_ + get_output_offset(), pb_instance_output_dev(inst_), out_bytes_, cudaMemcpyDeviceToHost, st));
         }
     }
 
-    bool has_next() const override { return next_ < (int)decls_.size() + (copy_stages_ ? 2 : 0); }
+    bool has_next() const override { return next_ < num_groups_ + (copy_stages_ ? 2 : 0); }
 
   private:
     static constexpr size_t kDmaInputBytes = 64 * 1024;
@@ -106,15 +131,18 @@ class ModelJob : public llis::job::Job {
 
     // Declares stage `next_` (resources, copy or compute, pre-notify on the last one).
     void declare() {
-        const int n = (int)decls_.size();
+        const int n = num_groups_;
         const int lead = copy_stages_ ? 1 : 0;
         const int total = n + 2 * lead;
         if (next_ >= total) return;
         if (next_ < lead || next_ >= lead + n) {
             set_is_mem();
+            set_gang_decls(nullptr, 1);
         } else {
             unset_is_mem();
-            set_next_stage(decls_[(size_t)(next_ - lead)]);
+            const llis::job::StageDecl* row = &decls_[(size_t)(next_ - lead) * cap_];
+            set_next_stage(row[gang_n_ - 1]);
+            set_gang_decls(row, (unsigned)cap_);
         }
         if (next_ == total - 1) set_pre_notify();
     }
@@ -137,7 +165,10 @@ class ModelJob : public llis::job::Job {
     std::string name_;
     size_t in_bytes_, out_bytes_;
     pb_instance* inst_ = nullptr;
-    std::vector<llis::job::StageDecl> decls_;
+    std::vector<llis::job::StageDecl> decls_;      // [group][gang size - 1]
+    int num_groups_ = 0;
+    int cap_ = 1;          // images the instance holds = largest gang this job can lead
+    int gang_n_ = 1;       // members of the gang this job currently leads (1 = alone)
     char* io_ptr_ = nullptr;
     int next_ = 0;
     bool resident_ = false;

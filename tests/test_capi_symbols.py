@@ -25,7 +25,7 @@ def test_header_symbols_are_exported_and_bound():
 def test_struct_sizes_match_the_header():
     import ctypes as C
     assert C.sizeof(capi.LaunchInfo) == 48
-    assert C.sizeof(capi.OpParams) == 20 * 4 + 7 * 8
+    assert C.sizeof(capi.OpParams) == 20 * 4 + 7 * 8 + 4 * 4
     assert C.sizeof(capi.ReplayEvent) == 24
     assert C.sizeof(capi.ReplayDecision) == 40
     L = capi.load()
