@@ -114,6 +114,7 @@ class Job {
         num_running_blocks_ = (int)next_.num_blocks;
         num_pending_blocks_ = (int)next_.num_blocks;
         cur_ = next_;
+        cur_is_mem_ = is_mem_;
         stage_start_time_us_ = now_us;
         ++cur_stage_;
     }
@@ -129,6 +130,10 @@ class Job {
         num_running_blocks_ -= (int)num;
         if (num_running_blocks_ <= 0) unset_running();
     }
+
+    // Blocks of the stage in flight that have not ended yet / whether that stage is a copy (watchdog).
+    unsigned running_blocks() const { return num_running_blocks_ > 0 ? (unsigned)num_running_blocks_ : 0u; }
+    bool is_mem_stage_in_flight() const { return cur_is_mem_; }
 
     void set_finished_block_notifier(FinishedBlockNotifier* n) { finished_block_notifier_ = n; }
     FinishedBlockNotifier* get_finished_block_notifier() { return finished_block_notifier_; }
@@ -196,6 +201,7 @@ class Job {
     StageDecl cur_;
     bool is_mem_ = false;
     bool is_pre_notify_ = false;
+    bool cur_is_mem_ = false;
     bool is_running_ = false;
     bool has_started_ = false;
     bool is_unfit_ = false;

@@ -52,6 +52,13 @@ struct SchedulerConfig {
     double unfairness_threshold = 1e6;
     unsigned sched_sleep = 0;
     unsigned max_gang = 1;            // jobs of one type the scheduler may dispatch as one launch per stage (1 = never)
+    // Stage watchdog (0 = off, the reference: a kernel that never reports its last block wedges the server,
+    // src/server/server.cpp:29-35 has no timeout).  A stage in flight for longer than
+    // max(watchdog_factor x the type's learned length of that stage, watchdog_floor_us) is given up:
+    // the job (and its gang) ends with PB_ERR_TIMEOUT, its occupancy is released, and its job id, stream and
+    // notifier are retired for good, because the kernel may still be running and report later.
+    double watchdog_factor = 0;
+    double watchdog_floor_us = 100000;
     SmTotals totals;
 };
 
@@ -68,6 +75,9 @@ class Scheduler {
     // that arrive together are queued together, which is what lets a gang form.
     virtual void set_deferred(bool on) { (void)on; }
     virtual void flush() {}
+    // Gives up stages that have been in flight for too long (see SchedulerConfig::watchdog_factor); returns how
+    // many jobs were failed.  The server calls it about once a millisecond.
+    virtual unsigned check_watchdog(double now_us) { (void)now_us; return 0; }
     virtual unsigned num_jobs() const = 0;
     virtual uint64_t num_decisions() const = 0;
     virtual const char* name() const = 0;

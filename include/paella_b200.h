@@ -299,6 +299,11 @@ typedef struct pb_server_config {
                                   * (src/server/scheduler_full3.cpp:64-99,272-313).  1 (implied by max_gang > 1): launches
                                   * and notifications only update the queue and the occupancy model; the dispatch loop runs
                                   * once per pb_server_step batch (<= 64 records) */
+    float watchdog_factor;       /* 0 = off (the reference: a kernel that never reports its last block wedges the server).
+                                  * > 0: a stage in flight longer than max(factor x its learned length, watchdog_floor_ms)
+                                  * is given up - the request (and its gang) ends with PB_ERR_TIMEOUT, its job id, stream
+                                  * and notifier are not reused */
+    float watchdog_floor_ms;     /* 0 = 100 ms */
 } pb_server_config;
 
 PB_API void pb_server_config_default(pb_server_config* cfg);
@@ -451,6 +456,35 @@ typedef struct pb_replay_config {
 PB_API int pb_sched_replay(const pb_replay_config* cfg, const pb_replay_type* types, uint32_t num_types,
                            const pb_replay_event* events, uint32_t num_events, pb_replay_decision* decisions,
                            uint32_t max_decisions, uint32_t* num_decisions_out, uint32_t* num_finished_out);
+
+/* Interactive form of the same (no GPU needed): the caller plays the clients and the GPU call by call - it
+ * submits jobs, is told every dispatch (with the blocks the stage declared and the size of the gang it serves)
+ * and feeds back the start / end / copy-done records, or withholds them.  For the scheduler features a recorded
+ * trace cannot express: gangs (max_gang, jobs that can lead `gang_capacity` members), deferred dispatch, plugins
+ * whose run_next() fails (stage_fails[type][stage] != 0) and the stage watchdog.  pb_sched_sim_flush runs the
+ * deferred dispatch loop and the watchdog at `now_us` and returns how many jobs the watchdog failed. */
+typedef struct pb_sched_sim pb_sched_sim;
+typedef struct pb_sim_config {
+    pb_replay_config base;
+    const char* scheduler;          /* NULL = "full3" */
+    uint32_t max_gang, gang_capacity, deferred;
+    double watchdog_factor, watchdog_floor_us;
+} pb_sim_config;
+typedef struct pb_sim_decision {
+    uint32_t job_id, type, stage, is_mem, unfit, num_blocks, gang_size;
+    uint32_t failed;                /* the plugin's run_next() raised its error flag: nothing was enqueued, no record will come */
+    uint64_t cookie;
+} pb_sim_decision;
+PB_API int pb_sched_sim_create(const pb_sim_config* cfg, const pb_replay_type* types, uint32_t num_types,
+                               const uint8_t* const* stage_fails, pb_sched_sim** out);
+PB_API void pb_sched_sim_destroy(pb_sched_sim* sim);
+PB_API int pb_sched_sim_new_job(pb_sched_sim* sim, uint32_t type, double now_us, uint64_t cookie);
+/* kind: 1 block start, 2 block end, 3 copy done */
+PB_API int pb_sched_sim_record(pb_sched_sim* sim, uint32_t kind, uint32_t job_id, uint32_t num, double now_us);
+PB_API int pb_sched_sim_flush(pb_sched_sim* sim, double now_us);
+PB_API int pb_sched_sim_take_decisions(pb_sched_sim* sim, pb_sim_decision* out, int max);
+PB_API int pb_sched_sim_take_finished(pb_sched_sim* sim, uint64_t* cookies, int32_t* errors, int max);
+PB_API uint32_t pb_sched_sim_jobs_in_flight(const pb_sched_sim* sim);
 
 #ifdef __cplusplus
 }

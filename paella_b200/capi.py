@@ -38,7 +38,8 @@ class OpParams(C.Structure):
 class ServerConfig(C.Structure):
     _fields_ = [("device", C.c_int32), ("num_streams", C.c_uint32), ("extra_kernels", C.c_uint32),
                 ("unfairness_threshold", C.c_float), ("sched_sleep", C.c_uint32), ("ring_capacity", C.c_uint64),
-                ("scheduler", C.c_char_p), ("device_resident", C.c_int32), ("max_gang", C.c_uint32), ("deferred_schedule", C.c_uint32)]
+                ("scheduler", C.c_char_p), ("device_resident", C.c_int32), ("max_gang", C.c_uint32), ("deferred_schedule", C.c_uint32),
+                ("watchdog_factor", C.c_float), ("watchdog_floor_ms", C.c_float)]
 
 
 class LoadgenConfig(C.Structure):
@@ -87,6 +88,16 @@ class ReplayConfig(C.Structure):
     _fields_ = [("num_streams", C.c_uint32), ("extra_kernels", C.c_uint32), ("unfairness_threshold", C.c_double),
                 ("total_regs", C.c_int32), ("total_smem", C.c_int32), ("total_threads", C.c_int32),
                 ("total_blocks", C.c_int32)]
+
+
+class SimConfig(C.Structure):
+    _fields_ = [("base", ReplayConfig), ("scheduler", C.c_char_p), ("max_gang", C.c_uint32), ("gang_capacity", C.c_uint32),
+                ("deferred", C.c_uint32), ("watchdog_factor", C.c_double), ("watchdog_floor_us", C.c_double)]
+
+
+class SimDecision(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("job_id", "type", "stage", "is_mem", "unfit", "num_blocks", "gang_size", "failed")] + \
+               [("cookie", C.c_uint64)]
 
 
 # name -> (restype, argtypes); every symbol include/paella_b200.h declares
@@ -181,6 +192,14 @@ SIGNATURES = {
     "pb_client_kill_server": (_I, [_VP]),
     "pb_client_profiler_cmd": (_I, [_VP, _U32, C.c_char_p]),
     "pb_server_profiler_cmd": (_I, [_VP, _U32, C.c_char_p]),
+    "pb_sched_sim_create": (_I, [C.POINTER(SimConfig), C.POINTER(ReplayType), _U32, C.POINTER(C.POINTER(C.c_uint8)), _PP]),
+    "pb_sched_sim_destroy": (None, [_VP]),
+    "pb_sched_sim_new_job": (_I, [_VP, _U32, C.c_double, _U64]),
+    "pb_sched_sim_record": (_I, [_VP, _U32, _U32, _U32, C.c_double]),
+    "pb_sched_sim_flush": (_I, [_VP, C.c_double]),
+    "pb_sched_sim_take_decisions": (_I, [_VP, C.POINTER(SimDecision), _I]),
+    "pb_sched_sim_take_finished": (_I, [_VP, C.POINTER(_U64), C.POINTER(C.c_int32), _I]),
+    "pb_sched_sim_jobs_in_flight": (_U32, [_VP]),
     "pb_sched_replay": (_I, [C.POINTER(ReplayConfig), C.POINTER(ReplayType), _U32, C.POINTER(ReplayEvent), _U32,
                              C.POINTER(ReplayDecision), _U32, C.POINTER(_U32), C.POINTER(_U32)]),
 }

@@ -164,6 +164,45 @@ class SchedulerFull3 final : public Scheduler {
         schedule_job();
     }
 
+    // Fails every stage that has been in flight longer than its limit.  The GPU may still be running it, so
+    // nothing of the dispatch is reused: the job id stays unknown to handle_record (late records count as stray),
+    // the stream and the notifier do not go back to their pools.
+    unsigned check_watchdog(double now_us) override {
+        if (cfg_.watchdog_factor <= 0) return 0;
+        unsigned failed = 0;
+        for (JobId id = 0; id < jobs_.size(); ++id) {
+            job::Job* job = jobs_[id];
+            if (!job || !job->is_running()) continue;
+            const std::vector<double>& lens = host_->get_job_stage_lengths(job);
+            const size_t st = (size_t)job->get_cur_stage();
+            const double learned = st < lens.size() ? lens[st] : 0.0;
+            const double limit = std::max(cfg_.watchdog_factor * learned, cfg_.watchdog_floor_us);
+            if (now_us - job->get_stage_start_time_us() <= limit) continue;
+            job->set_error(-5 /* PB_ERR_TIMEOUT */);
+            const bool was_mem = job->is_mem_stage_in_flight();
+            if (!was_mem) gpu_resources_.release(job, job->running_blocks());
+            job->unset_running();
+            if (job->is_unfit()) { job->unset_unfit(); --num_outstanding_kernels_; }
+            host_->notify_job_ends(job);
+            --num_jobs_;
+            for (job::Job* f : followers_[id]) {
+                f->set_error(-5);
+                host_->notify_job_ends(f);
+                --num_jobs_;
+                jobs_[f->get_id()] = nullptr;      // followers never had a dispatch of their own: their ids can be reused
+                unused_job_id_.push_back(f->get_id());
+                host_->release_job_instance(f);
+            }
+            followers_[id].clear();
+            jobs_[id] = nullptr;                   // quarantined: not pushed to unused_job_id_
+            host_->release_job_instance(job);
+            ++num_watchdog_;
+            ++failed;
+        }
+        if (failed) schedule_job();
+        return failed;
+    }
+
     void retire(job::Job* job) {
         const JobId id = job->get_id();
         for (job::Job* f : followers_[id]) retire(f);
@@ -204,6 +243,7 @@ class SchedulerFull3 final : public Scheduler {
                 for (volatile unsigned i = 0; i < cfg_.sched_sleep; ++i) {}
             }
             const bool is_mem = job->is_mem();
+            if (!is_mem && free_notifiers_.empty()) break;      // cannot happen while every kernel reports each block once
             bool unfit = false;
             if (!is_mem && !gpu_resources_.job_fits(job)) {
                 if (num_outstanding_kernels_ >= (int)max_num_outstanding_kernels_) break;
@@ -264,6 +304,7 @@ class SchedulerFull3 final : public Scheduler {
     std::vector<std::vector<job::Job*>> followers_;               // by JobId of the leader: the other members of its gang
     uint64_t num_gangs_ = 0, num_gang_members_ = 0;
     bool deferred_ = false, dirty_ = false;
+    uint64_t num_watchdog_ = 0;
     std::vector<JobId> unused_job_id_;
     unsigned num_jobs_ = 0;
     uint64_t num_decisions_ = 0;

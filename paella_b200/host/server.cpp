@@ -77,6 +77,8 @@ int pb_server::init(const pb_server_config& c) {
     sc.extra_kernels = c.extra_kernels;
     sc.unfairness_threshold = c.unfairness_threshold;
     sc.sched_sleep = c.sched_sleep;
+    sc.watchdog_factor = c.watchdog_factor;
+    if (c.watchdog_floor_ms > 0) sc.watchdog_floor_us = 1000.0 * c.watchdog_floor_ms;
     sc.max_gang = c.max_gang > 1 ? (c.max_gang < PB_MAX_GANG ? c.max_gang : PB_MAX_GANG) : 1;
     int rc = llis::server::SmResources::query_device(device, &sc.totals);
     if (rc != PB_OK) return rc;
@@ -160,6 +162,10 @@ int pb_server::step(int max_records) {
     uint64_t recs[64];
     int handled = 0;
     std::vector<InstrumentInfo> made_up;
+    if (cfg.watchdog_factor > 0) {
+        const double t = now_us();
+        if (t - last_watchdog_us > 1000.0) { last_watchdog_us = t; num_watchdog += scheduler->check_watchdog(t); }
+    }
     scheduler->flush();          // requests admitted since the last step
     while (scheduler->take_synthetic(&made_up)) {
         for (const InstrumentInfo& r : made_up) scheduler->handle_record(r);

@@ -98,4 +98,6 @@ struct pb_server final : public llis::server::SchedulerHost {
     std::vector<Done> done;
     uint64_t num_pre_notified = 0, num_kernels = 0, num_mem_stages = 0, num_records = 0;
     int last_error = 0;
+    double last_watchdog_us = 0;
+    uint64_t num_watchdog = 0;          // requests the stage watchdog gave up
 };
