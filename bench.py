@@ -137,18 +137,23 @@ def write_packs(models_dir):
 
 
 def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2, mix=None,
-             sched="full3", streams=500, gang=None, deferred=None):
+             sched="full3", streams=500, gang=None, deferred=None, samples_per_type=0, cpus=None):
+    """One load-generator run (one replica thread per entry of `devices`).  Returns the result struct and, with
+    samples_per_type > 0, the sampled request slots [(type index, slot, input float32 array, output float32 array)]."""
+    import numpy as np
     mix = mix or MIX
     cfg = capi.LoadgenConfig()
     L.pb_loadgen_config_default(C.byref(cfg))
     cfg.num_gpus = len(devices)
     for i, d in enumerate(devices):
         cfg.devices[i] = d
+        cfg.cpu_of_replica[i] = cpus[i] if cpus else -1
     cfg.num_types = len(mix)
-    for i, (job, _, prop) in enumerate(mix):
+    for i, (job, model, prop) in enumerate(mix):
         cfg.plugin_paths[i] = capi.plugin_path(job).encode()
         cfg.proportions[i] = prop
         cfg.max_outstanding[i] = caps[i]
+        cfg.input_uniform[i] = 1 if model == "mnist" else 0      # U[0,1) images for MNIST, N(0,1) for the others
     cfg.concurrency = concurrency
     cfg.mean_interarrival_us = iat_us
     cfg.num_jobs = max(1, int(batch * steps))
@@ -160,11 +165,28 @@ def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps
     cfg.server.extra_kernels = extra_kernels
     cfg.server.max_gang = GANG if gang is None else gang
     cfg.server.deferred_schedule = DEFERRED if deferred is None else deferred
+    buf = None
+    if samples_per_type and not resident:
+        buf = np.zeros(len(mix) * samples_per_type * (1 << 21) // 4, np.float32)      # <= 2 MB per sample
+        cfg.samples_per_type = samples_per_type
+        cfg.sample_buf = buf.ctypes.data
+        cfg.sample_buf_bytes = buf.nbytes
     res = capi.LoadgenResult()
     capi.check(L.pb_loadgen_run(C.byref(cfg), C.byref(res)), "pb_loadgen_run")
     if res.errors:
         raise RuntimeError(f"{res.errors} requests reported an error")
-    return res
+    if buf is None:
+        return res
+    raw, off, samples = buf.view(np.uint8), 0, []
+    for _ in range(res.samples):
+        t, slot = (int(v) for v in raw[off:off + 8].view(np.uint32))
+        nin, nout = (int(v) for v in raw[off + 8:off + 24].view(np.uint64))
+        pin, pout = (nin + 7) // 8 * 8, (nout + 7) // 8 * 8
+        x = raw[off + 24:off + 24 + nin].view(np.float32).copy()
+        y = raw[off + 24 + pin:off + 24 + pin + nout].view(np.float32).copy()
+        samples.append((t, slot, x, y))
+        off += 24 + pin + pout
+    return res, samples
 
 
 def roofline_leg(L, capi, models_dir, iters=20, only=""):

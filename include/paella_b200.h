@@ -98,6 +98,10 @@ PB_API int pb_clock_calibrate(int device, uint64_t out[3]);
  * of host->GPU visibility (the kernel's poll of host memory) and the GPU->host record; every device
  * wait is bounded.  Counterpart of the reference's tests/ipc/shm_channel/latency/shmpc_latency_gpu.cu. */
 PB_API int pb_ring_roundtrip_bench(int device, uint32_t iters, double* rtt_us_out);
+/* A device-side wait that runs out, on purpose and harmlessly: the round-trip kernel is launched with a ping that
+ * never comes and a limit of `max_polls` polls (<= 65536, i.e. well under a second); it gives up, reports status 2
+ * in *status_out (1 would mean it saw the ping) and returns.  *records_out = records it wrote (0 expected). */
+PB_API int pb_ring_wait_expiry_probe(int device, uint32_t max_polls, uint32_t* status_out, uint32_t* records_out);
 /* vec_add over n floats on private buffers, `iters` timed launches between CUDA events with an L2
  * flush (a write of flush_bytes) before each; mean microseconds per launch in *us_out. */
 PB_API int pb_vec_add_bench(int device, uint64_t n, int iters, size_t flush_bytes, double* us_out);
@@ -181,6 +185,10 @@ PB_API int pb_conv_umma_supported(const pb_op_params* p);
  * value = never; negative = back to the default).  Read at every pb_op_info / pb_op_launch, and when a model
  * instance builds its launches for a batch size: instances built before a change keep their split. */
 PB_API void pb_set_conv_split_gain_us(double us);
+/* Mean microseconds of one launch of the tensor-core convolution `p` (any batch): 3 warm-up launches, then `iters`
+ * launches on a private stream between CUDA events, a write of flush_bytes before each (0 = none).  mode 0 = the
+ * one-tile-per-CTA kernel pb_op_launch uses, 1 = the persistent kernel the model stage graphs use. */
+PB_API int pb_conv_umma_time(const pb_op_params* p, int mode, int iters, size_t flush_bytes, double* us_out);
 /* Tensor-core convolution for callers that must not allocate: code running inside a CUDA memory-pool
  * or allocator callback, a latency-critical thread that may not take the allocator's locks, or a host
  * that pre-partitions all device memory and leaves none to ask for.  It has no counterpart in the
@@ -198,7 +206,10 @@ PB_API void pb_set_conv_split_gain_us(double us);
  *    order them yourself.
  *  - Never calls cudaMalloc, cudaFree or any allocating routine, on the host heap either. */
 PB_API int pb_conv2d_umma_noalloc(const pb_op_params* p, void* stream, uint32_t job_id, void* notifier);
-/* Device-side error flag raised by bounded waits inside kernels (0 = none). */
+/* Device-side error flag raised by bounded waits inside kernels (0 = none): the OR of the library's flag and of
+ * the one pb_conv2d_umma_noalloc keeps for itself.  Reading and resetting use plain synchronous copies: synchronise
+ * the streams that may still be running kernels (pb_conv2d_umma_noalloc included) before a reset, or a flag raised
+ * in between is lost. */
 PB_API int pb_device_error_flag(int device, uint32_t* flag_out, int reset);
 
 /* ------------------------------------------------------------------------ *
@@ -354,6 +365,18 @@ typedef struct pb_loadgen_config {
     uint32_t seed;
     int32_t device_resident;       /* 1: inputs already in HBM, copy stages skipped */
     pb_server_config server;
+    /* Output check by the caller (host-buffer runs only): after the measured phase replica 0 copies, for each job
+     * type, the first `samples_per_type` request slots in which a measured request completed into sample_buf as
+     * records { u32 type, u32 slot, u64 in_bytes, u64 out_bytes, input (padded to 8), output (padded to 8) }. */
+    uint32_t samples_per_type;
+    void* sample_buf;
+    uint64_t sample_buf_bytes;
+    /* CPU placement: replica g's thread (it submits, polls and launches for GPU g) is pinned to cpu_of_replica[g]
+     * when >= 0 (sched_setaffinity on the thread only; nothing of the GPU is changed).  -1 = leave it to the OS. */
+    int32_t cpu_of_replica[PB_MAX_GPUS];
+    /* Request inputs are filled once per slot from the seed: N(0,1) floats, or U[0,1) for the types marked here
+     * (the MNIST configuration's input range). */
+    int32_t input_uniform[PB_MAX_JOB_TYPES];
 } pb_loadgen_config;
 
 typedef struct pb_latency_stats {
@@ -377,6 +400,8 @@ typedef struct pb_loadgen_result {
      * inside the plugins' run_next() (CUDA launches), inside notification handling and scheduling
      * around it, and in polls that found nothing to do (the GPU was the slower side) */
     double host_launch_us, host_sched_us, host_idle_us;
+    uint32_t samples;                /* records written to sample_buf */
+    uint64_t sample_bytes;
 } pb_loadgen_result;
 
 PB_API void pb_loadgen_config_default(pb_loadgen_config* cfg);

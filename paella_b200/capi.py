@@ -48,7 +48,9 @@ class LoadgenConfig(C.Structure):
                 ("max_outstanding", C.c_uint32 * PB_MAX_JOB_TYPES), ("concurrency", C.c_uint32),
                 ("mean_interarrival_us", C.c_double), ("lognormal_sigma", C.c_double), ("num_jobs", C.c_uint32),
                 ("warmup_jobs", C.c_uint32), ("seed", C.c_uint32), ("device_resident", C.c_int32),
-                ("server", ServerConfig)]
+                ("server", ServerConfig), ("samples_per_type", C.c_uint32), ("sample_buf", C.c_void_p),
+                ("sample_buf_bytes", C.c_uint64), ("cpu_of_replica", C.c_int32 * PB_MAX_GPUS),
+                ("input_uniform", C.c_int32 * PB_MAX_JOB_TYPES)]
 
 
 class LatencyStats(C.Structure):
@@ -64,7 +66,8 @@ class LoadgenResult(C.Structure):
                 ("per_type", LatencyStats * PB_MAX_JOB_TYPES), ("per_gpu_rps", C.c_double * PB_MAX_GPUS),
                 ("kernels_launched", C.c_uint64), ("records_consumed", C.c_uint64), ("decisions", C.c_uint64),
                 ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("errors", C.c_int32),
-                ("host_launch_us", C.c_double), ("host_sched_us", C.c_double), ("host_idle_us", C.c_double)]
+                ("host_launch_us", C.c_double), ("host_sched_us", C.c_double), ("host_idle_us", C.c_double),
+                ("samples", C.c_uint32), ("sample_bytes", C.c_uint64)]
 
 
 class ReplayType(C.Structure):
@@ -121,6 +124,7 @@ SIGNATURES = {
     "pb_launch_latency_probe": (_I, [_VP, _U32, _VP]),
     "pb_clock_calibrate": (_I, [_I, C.POINTER(_U64)]),
     "pb_ring_roundtrip_bench": (_I, [_I, _U32, C.POINTER(C.c_double)]),
+    "pb_ring_wait_expiry_probe": (_I, [_I, _U32, C.POINTER(_U32), C.POINTER(_U32)]),
     "pb_vec_add_bench": (_I, [_I, _U64, _I, _SZ, C.POINTER(C.c_double)]),
     "pb_vec_add_info": (_I, [_U64, C.POINTER(LaunchInfo)]),
     "pb_vec_add_launch": (_I, [_VP, _VP, _U64, _VP, _U32, _VP]),
@@ -133,6 +137,7 @@ SIGNATURES = {
     "pb_conv2d_umma_noalloc": (_I, [C.POINTER(OpParams), _VP, _U32, _VP]),
     "pb_device_error_flag": (_I, [_I, C.POINTER(_U32), _I]),
     "pb_set_conv_split_gain_us": (None, [C.c_double]),
+    "pb_conv_umma_time": (_I, [C.POINTER(OpParams), _I, _I, _SZ, C.POINTER(C.c_double)]),
     "pb_instance_create_batched": (_I, [_VP, _I, _I, _PP]),
     "pb_instance_capacity": (_I, [_VP]),
     "pb_model_group_info_batched": (_I, [_VP, _I, _I, C.POINTER(LaunchInfo)]),

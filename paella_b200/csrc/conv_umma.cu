@@ -127,6 +127,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase (never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false if the CTA is aborting (this wait or another ran out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* s_abort, uint32_t* err_flag,
                                           uint32_t code) {
@@ -235,6 +247,27 @@ __device__ unsigned long long g_conv_kb[8 * 64 * 3];
 #else
 #define PB_T(i) do {} while (0)
 #define PB_TK(kb, i) do {} while (0)
+#endif
+
+// Optional per-phase cycle sums over every CTA of the TMA kernels (-DPB_CONV_STATS, development builds):
+// [0] CTAs, [1] k-blocks, then clock64 differences: [2] set-up, [3] wait for the previous kernel, [4] first
+// operands, [5] main loop (first operands landed -> last MMA issued), [6] accumulator drain, [7] epilogue,
+// [8] tear-down, [9] whole CTA.
+#ifdef PB_CONV_STATS
+__device__ unsigned long long g_conv_stats[16];      // [10..15]: CTAs that found 0..5+ other conv CTAs resident on their SM
+__device__ unsigned int g_conv_resident[256];        // conv CTAs resident per SM right now
+__device__ long long g_persist_kb[64 * 6];          // CTA 0, its first tile: per k-block clock64 stamps (see PB_PK)
+#define PB_PK(kb, i) do { if (blockIdx.x == 0 && first_tile && (kb) < 64) g_persist_kb[(kb) * 6 + (i)] = clock64(); } while (0)
+__device__ unsigned int g_persist_resident;          // persistent CTAs resident GPU-wide right now
+__device__ unsigned long long g_persist_hist[16];     // [b]: CTAs that found 32*b .. 32*b+31 others resident when they started; [15]: sum of lifetimes (clk)
+__device__ long long g_persist_tile[16 * 6];        // CTA 0: per tile clock64 stamps (see PB_PT)
+#define PB_PT(ti, i) do { if (blockIdx.x == 0 && (ti) < 16) g_persist_tile[(ti) * 6 + (i)] = clock64(); } while (0)
+__device__ unsigned long long g_conv_ns;             // sum of the CTAs' lifetimes by %globaltimer (ns): cycles / ns = the SM clock
+#define PB_S(i) do { s_clk[(i)] = clock64(); } while (0)
+#else
+#define PB_S(i) do {} while (0)
+#define PB_PK(kb, i) do {} while (0)
+#define PB_PT(ti, i) do {} while (0)
 #endif
 
 // ---- the kernel -----------------------------------------------------------------------
@@ -352,12 +385,13 @@ __device__ __forceinline__ void epilogue_columns(const ConvArgs& a, uint32_t lan
 // tile in shared memory for row-contiguous stores was measured slower: the epilogue is bound by its
 // instruction count, not by the scattered 16-byte stores.)
 __device__ __forceinline__ void epilogue(const ConvArgs& a, uint32_t tmem_base, bool ok, int m0, int n0, uint32_t tile, uint32_t split,
-                                     const float* s_bias, uint64_t* s_accum_p, volatile uint32_t* s_abort_p, uint32_t* s_is_last_p) {
+                                     const float* s_bias, uint64_t* s_accum_p, volatile uint32_t* s_abort_p, uint32_t* s_is_last_p,
+                                     uint32_t accum_parity = 0u) {
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int m = m0 + tid;
     const bool row_valid = m < a.M;
-    if (ok) ok = mbar_wait(smem_u32(s_accum_p), 0u, s_abort_p, a.err_flag, 3u);
+    if (ok) ok = mbar_wait(smem_u32(s_accum_p), accum_parity, s_abort_p, a.err_flag, 3u);
     ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
     if (tid == 0) PB_T(5);
     tcgen05_fence_after();
@@ -594,6 +628,20 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+#ifdef PB_CONV_STATS
+    __shared__ long long s_clk[8];
+    __shared__ unsigned s_smid;
+    __shared__ unsigned long long s_ns0;
+    if (tid == 0) {
+        PB_S(0);
+        s_ns0 = globaltimer_ns();
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        s_smid = smid & 255u;
+        const unsigned others = atomicAdd(&g_conv_resident[s_smid], 1u);
+        atomicAdd(&g_conv_stats[10 + (others < 5 ? others : 5)], 1ull);
+    }
+#endif
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t stage_bytes = (uint32_t)kATileBytes + a.b_stage_bytes;
 
@@ -603,6 +651,9 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
     const int kb_end = min(a.nkb, kb_begin + a.kb_per_split);
     const int nkb = kb_end - kb_begin;
 
+    // the first copy of each descriptor otherwise pays its fetch into the descriptor cache
+    if (tid == 32) asm volatile("prefetch.tensormap [%0];" ::"l"(tmap_w) : "memory");
+    if (tid == 64) asm volatile("prefetch.tensormap [%0];" ::"l"(tmap_x) : "memory");
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);      // the producer's arrive.expect_tx
@@ -624,48 +675,65 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_base;
-    if (threadIdx.x == 0) PB_T(1);
+    if (threadIdx.x == 0) { PB_T(1); PB_S(1); }
     // Everything above touched only this CTA's shared/tensor memory and constant weights (bias), so it
     // may overlap the previous kernel's tail.  Activations, the residual, the output and the split-K
     // workspace may only be touched once the previous kernel has completed.
     griddep_wait();
+    if (threadIdx.x == 0) PB_S(2);
 
-    if (warp < 4) {
-        griddep_launch();      // the next kernel's blocks may be scheduled as SM resources free up
-        epilogue(a, tmem_base, true, m0, n0, (uint32_t)(by * gx + bx), (uint32_t)bz, s_bias, s_accum, s_abort, s_is_last);
-        if (tid == 0) PB_T(6);
-    } else if (warp == 4) {
-        // ===== producer: one thread =====
-        if (lane == 0) {
-            const int img = m0 / a.PQ, rem = m0 - img * a.PQ;      // the tile may run on into the next image
-            const int p0 = rem / a.Q, q0 = rem - p0 * a.Q;
-            const int w0 = q0 * a.sw - a.pw;          // filter-window origin of the tile's first pixel
-            const int h0 = p0 * a.sh - a.ph;
-            const int cpt = a.Cp / kBK;               // k-blocks per filter tap
-            int tap = kb_begin / cpt;
-            int chunk = kb_begin - tap * cpt;
-            int r = tap / a.S, s = tap - r * a.S;
-            int st = 0;
-            uint32_t parity = 1u;                     // a fresh barrier passes a wait on the "previous" phase
-            bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
+    // ===== producers: lane 0 of warp 4 and of the four epilogue warps =====
+    // A thread that issues tensor copies one after the other is slow however small the copies: measured with a
+    // copy-only kernel on tiles like these, one thread sustains one 16 KB copy per ~650 clocks (25 B/clk) at any
+    // pipeline depth, four issuing warps of the same CTA 100 B/clk, and the whole GPU saturates near 60 B/clk per
+    // SM.  The tensor cores need a k-block (two copies) every ~270 clocks, so a lone producer thread paced the
+    // whole CTA.  The epilogue warps have nothing to do until the accumulator is complete, so lane 0 of each
+    // joins warp 4: the 2 x stages (stage, operand) pairs are dealt round-robin to the kProducers threads, and a
+    // pair is always refilled by the same thread, in k order.  The thread that loads operand A also arms the
+    // stage's barrier with the byte count of both copies; operand B's bytes may land before that (the
+    // transaction count goes negative for a moment; the phase cannot complete before the arrival).
+    // (Several lanes of ONE warp would not do: they reconverge after each wait, so no copy could be issued
+    // before every stage had been drained.)
+    constexpr int kProducers = 5;
+    const int prod = warp == 4 ? 0 : warp + 1;              // producer index of this warp's lane 0
+    if (warp <= 4 && lane == 0) {
+        const int img = m0 / a.PQ, rem = m0 - img * a.PQ;      // the tile may run on into the next image
+        const int p0 = rem / a.Q, q0 = rem - p0 * a.Q;
+        const int w0 = q0 * a.sw - a.pw;          // filter-window origin of the tile's first pixel
+        const int h0 = p0 * a.sh - a.ph;
+        const int cpt = a.Cp / kBK;               // k-blocks per filter tap
+        bool ok = true;
+        int st = 0;
+        uint32_t parity = 1u;                     // a fresh barrier passes a wait on the "previous" phase
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const bool mine_a = (st * 2) % kProducers == prod, mine_b = (st * 2 + 1) % kProducers == prod;
+            if (mine_a || mine_b) {
                 ok = mbar_wait(smem_u32(&s_empty[st]), parity, s_abort, a.err_flag, 1u);
                 if (!ok) break;
                 const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
                 const uint32_t bar = smem_u32(&s_full[st]);
-                mbar_arrive_expect_tx(bar, (uint32_t)kATileBytes + a.b_stage_bytes);
-                if (a.a_tiled) tma_load_2d(a_tile, tmap_x, chunk * kBK, m0, bar);
-                else tma_load_im2col_4d(a_tile, tmap_x, chunk * kBK, w0, h0, img, (uint16_t)(s * a.dw), (uint16_t)(r * a.dh), bar);
-                tma_load_2d(a_tile + kATileBytes, tmap_w, (kb_begin + kb) * kBK, n0, bar);
-                if (kb == 0) PB_T(2);
-                PB_TK(kb, 0);
-                if (++chunk == cpt) {
-                    chunk = 0;
-                    if (++s == a.S) { s = 0; ++r; }
+                const int kbg = kb_begin + kb;
+                if (mine_a) {
+                    const int tap = kbg / cpt, chunk = kbg - tap * cpt;
+                    const int r = tap / a.S, s = tap - r * a.S;
+                    mbar_arrive_expect_tx(bar, (uint32_t)kATileBytes + a.b_stage_bytes);
+                    if (a.a_tiled) tma_load_2d(a_tile, tmap_x, chunk * kBK, m0, bar);
+                    else tma_load_im2col_4d(a_tile, tmap_x, chunk * kBK, w0, h0, img, (uint16_t)(s * a.dw), (uint16_t)(r * a.dh), bar);
+                    if (kb == 0) PB_T(2);
+                    PB_TK(kb, 0);
                 }
-                if (++st == stages) { st = 0; parity ^= 1u; }
+                if (mine_b) tma_load_2d(a_tile + kATileBytes, tmap_w, kbg * kBK, n0, bar);
             }
+            if (++st == stages) { st = 0; parity ^= 1u; }
         }
+    }
+    if (warp <= 4) __syncwarp();
+
+    if (warp < 4) {
+        griddep_launch();      // the next kernel's blocks may be scheduled as SM resources free up
+        epilogue(a, tmem_base, true, m0, n0, (uint32_t)(by * gx + bx), (uint32_t)bz, s_bias, s_accum, s_abort, s_is_last);
+        if (tid == 0) { PB_T(6); PB_S(6); }
+    } else if (warp == 4) {
         __syncwarp();
         griddep_launch();
     } else {
@@ -677,7 +745,7 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 ok = mbar_wait(smem_u32(&s_full[st]), parity, s_abort, a.err_flag, 2u);
                 if (!ok) break;
-                if (kb == 0) PB_T(3);
+                if (kb == 0) { PB_T(3); PB_S(3); }
                 PB_TK(kb, 1);
                 tcgen05_fence_after();
                 const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
@@ -691,8 +759,13 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
                 PB_TK(kb, 2);
                 if (++st == stages) { st = 0; parity ^= 1u; }
             }
+            PB_S(4);
             if (ok) tcgen05_commit(smem_u32(s_accum));
             PB_T(4);
+#ifdef PB_CONV_STATS
+            if (ok) mbar_wait(smem_u32(s_accum), 0u, s_abort, a.err_flag, 3u);
+            PB_S(5);
+#endif
         }
         __syncwarp();
         griddep_launch();
@@ -712,6 +785,19 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
         tcgen05_dealloc(tmem_base, a.tmem_cols);
     }
     if (threadIdx.x == 0) PB_T(7);
+#ifdef PB_CONV_STATS
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const long long c7 = clock64();
+        atomicAdd(&g_conv_stats[0], 1ull);
+        atomicAdd(&g_conv_stats[1], (unsigned long long)nkb);
+        for (int i = 0; i < 6; ++i) atomicAdd(&g_conv_stats[2 + i], (unsigned long long)(s_clk[i + 1] - s_clk[i]));
+        atomicAdd(&g_conv_stats[8], (unsigned long long)(c7 - s_clk[6]));
+        atomicAdd(&g_conv_stats[9], (unsigned long long)(c7 - s_clk[0]));
+        atomicSub(&g_conv_resident[s_smid], 1u);
+        atomicAdd(&g_conv_ns, globaltimer_ns() - s_ns0);
+    }
+#endif
 }
 
 __global__ void __launch_bounds__(kThreadsTma, 3)
@@ -781,6 +867,296 @@ conv_umma_multi_kernel(const SubConv* __restrict__ table, int n_sub, uint32_t jo
     if (nf) nf->end(job_id);
 }
 
+
+// ---- persistent form: a CTA walks several tiles ------------------------------------------------------------
+// What a one-tile CTA costs besides its main loop was measured under serving load (cycle stamps summed over all
+// CTAs): 1.0 us of set-up, 1.4 us until the first operands land, 0.2 us of accumulator drain, 1.4 us of epilogue,
+// 0.35 us of tear-down and about 1 us before the SM slot holds the next CTA, against 4.7 us of main loop; and the
+// GPU's throughput on these layers is what its CTA slots turn over.  Here a CTA is given several tiles of the
+// launch (tile t = blockIdx.x, + gridDim.x, ...) and pays set-up and tear-down once; the producers run on
+// into the next tile's k-blocks while the current tile finishes, so operand latency is paid once per CTA; and
+// there are TWO accumulators in tensor memory, so the epilogue of tile i (warps 0-3) runs under the MMAs of tile
+// i + 1 (warp 4).  9 warps: 0-3 epilogue, 4 TMEM allocation + MMA issue, 5-8 producers (a thread that issues
+// tensor copies back to back sustains only one copy per ~500 clocks - ~170 for the wait on the stage's barrier,
+// ~250 for the copy instruction itself - so the 2 x stages (stage, operand) pairs are dealt to four threads; a
+// pair is always refilled by the same thread).  Sized for two CTAs per SM: <= 108 KB of pipeline, 288 threads
+// of <= 112 registers, 2 x 128 tensor-memory columns.
+// Every tile comes from the launch's table of sub-problems (one entry for a lone convolution, several for the
+// independent convolutions of a grouped launch): tile index -> entry by first_block, then (m tile, n tile,
+// k split) inside it.
+constexpr int kPersistProducers = 4;
+constexpr int kThreadsPersist = 32 * (5 + kPersistProducers);
+#ifndef PB_CONV_PERSIST_SMEM_KB
+#define PB_CONV_PERSIST_SMEM_KB 108
+#endif
+constexpr uint32_t kSmemBudgetPersist = PB_CONV_PERSIST_SMEM_KB * 1024u;
+
+// A sub-problem's arguments as the CTA keeps them in shared memory (the tensor maps stay in global memory,
+// where the TMA unit reads them): decoding a tile and reading its arguments from the global table cost every
+// role a chain of dependent loads at each tile boundary, about 5 us per tile.
+struct SubArgs {
+    ConvArgs a;
+    uint32_t first_block, gx, gy, pad;
+};
+struct TileRef {
+    const SubArgs* sa;
+    const SubConv* sc;
+    int bx, by, bz;
+};
+__device__ __forceinline__ TileRef tile_ref(const SubConv* __restrict__ table, const SubArgs* s_sub, int n_sub, uint32_t t) {
+    int sub = 0;
+    while (sub + 1 < n_sub && t >= s_sub[sub + 1].first_block) ++sub;
+    TileRef r;
+    r.sa = s_sub + sub;
+    r.sc = table + sub;
+    const uint32_t local = t - r.sa->first_block;
+    const uint32_t gx = r.sa->gx, gy = r.sa->gy;
+    r.bx = (int)(local % gx);
+    const uint32_t rest = local / gx;
+    r.by = (int)(rest % gy);
+    r.bz = (int)(rest / gy);
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreadsPersist, 2)
+conv_umma_persist_kernel(const SubConv* __restrict__ table, int n_sub, uint32_t total_tiles, int stages, uint32_t stage_bytes,
+                         uint32_t acc_cols, uint32_t job_id, FinishedBlockNotifier* nf) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kMaxStages];
+    __shared__ __align__(8) uint64_t s_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t s_tfull[2];       // accumulator complete (tcgen05.commit)
+    __shared__ __align__(8) uint64_t s_tempty[2];      // accumulator read out (one arrival per epilogue warp)
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ uint32_t s_is_last;
+    __shared__ __align__(16) float s_bias[2][kMaxBN];
+    __shared__ __align__(16) SubArgs s_sub[kMaxSubConvs];
+
+    resolve_slot(job_id, nf);
+    if (nf) nf->start(job_id);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+#ifdef PB_CONV_STATS
+    __shared__ long long s_cta_t0;
+    if (tid == 0) {
+        const unsigned others = atomicAdd(&g_persist_resident, 1u);
+        atomicAdd(&g_persist_hist[others / 32u < 14u ? others / 32u : 14u], 1ull);
+        s_cta_t0 = clock64();
+    }
+#endif
+
+    // the table is constant for the life of the instance: it may be read before griddepcontrol.wait
+    {
+        static_assert(sizeof(ConvArgs) % 4 == 0 && sizeof(SubArgs) % 4 == 0, "copied word by word");
+        constexpr int kWords = (int)(sizeof(ConvArgs) / 4);
+        for (int j = tid; j < n_sub * (kWords + 3); j += kThreadsPersist) {
+            const int sub = j / (kWords + 3), w = j - sub * (kWords + 3);
+            if (w < kWords) reinterpret_cast<uint32_t*>(&s_sub[sub].a)[w] = reinterpret_cast<const uint32_t*>(&table[sub].a)[w];
+            else (&s_sub[sub].first_block)[w - kWords] = (&table[sub].first_block)[w - kWords];
+        }
+    }
+
+    if (tid == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&s_full[s]), 1);
+            mbar_init(smem_u32(&s_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&s_tfull[b]), 1);
+            mbar_init(smem_u32(&s_tempty[b]), 4);
+        }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        tcgen05_alloc(smem_u32(&s_tmem_base), 2u * acc_cols);
+        tcgen05_relinquish();
+    }
+    // the first tile's descriptors: their fetch into the descriptor cache overlaps the rest of the set-up
+    if (warp >= 5 && warp <= 6 && lane == 0) {
+        int sub = 0;
+        while (sub + 1 < n_sub && blockIdx.x >= table[sub + 1].first_block) ++sub;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(warp == 5 ? &table[sub].tmap_x : &table[sub].tmap_w) : "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    // Nothing above touched activations, the output or the split-K workspace: it may overlap the previous
+    // kernel's tail.  From here on this kernel reads what the previous one wrote.
+    griddep_wait();
+
+    if (warp < 4) {
+        // ===== epilogue warps: thread t owns accumulator lane t = tile row t =====
+        uint32_t i = 0;
+        for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++i) {
+            const uint32_t acc = i & 1u, use = i >> 1;
+            const TileRef tr = tile_ref(table, s_sub, n_sub, t);
+            const ConvArgs& a = tr.sa->a;
+            // the tile's biases, staged by these four warps for themselves
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // the tile that used this buffer before is done with it
+            const int n0 = tr.by * a.BN;
+            for (int j = tid; j < a.BN; j += 128) {
+                const int k = n0 + j;
+                s_bias[acc][j] = (a.bias && k < a.K) ? __ldg(a.bias + k) : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (tid == 0) PB_PT(i, 2);
+            epilogue(a, tmem_base + acc * acc_cols, true, tr.bx * kBM, n0, (uint32_t)(tr.by * (int)tr.sa->gx + tr.bx), (uint32_t)tr.bz,
+                     s_bias[acc], &s_tfull[acc], &s_abort, &s_is_last, use & 1u);
+            if (tid == 0) PB_PT(i, 3);
+            // this accumulator may be overwritten: every tcgen05.ld of the warp has completed (wait::ld)
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&s_tempty[acc]));
+        }
+    } else if (warp == 4) {
+        // ===== MMA issuer: one thread =====
+        // The thread's own instruction chain per k-block decides the pace of the CTA (measured: four MMA issues +
+        // commit 360 clocks, most of it the tensor cores taking the instructions; then 415 clocks until the next
+        // k-block's barrier had been looked at: a division for the stage index, a load of the error-flag pointer, and
+        // an mbarrier wait that costs ~170 clocks even when the phase is long complete).  So: stage and parity are
+        // carried, not divided; and the NEXT k-block's barrier is probed (test_wait, never blocks) before this
+        // k-block's MMAs are issued, so the probe's latency runs under them.
+        if (lane == 0) {
+            uint32_t i = 0;                         // tiles of this CTA so far
+            uint32_t st = 0, parity = 0;            // pipeline stage and phase of the next k-block
+            bool ok = true;
+            uint32_t* const err_flag = s_sub[0].a.err_flag;
+            // descriptors of stage 0; stage q is stage_bytes further on (the address field counts 16-byte units and
+            // cannot carry out of its 14 bits: shared memory ends below 256 KB)
+            const uint64_t desc_a0 = umma_desc_sw128(smem_base), desc_b0 = umma_desc_sw128(smem_base + kATileBytes);
+            const uint64_t desc_step = (uint64_t)(stage_bytes >> 4);
+            bool have_next = false;                 // the barrier of (st, parity) is already known to be complete
+            for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++i) {
+                const uint32_t acc = i & 1u, use = i >> 1;
+                const TileRef tr = tile_ref(table, s_sub, n_sub, t);
+                const ConvArgs& a = tr.sa->a;
+                const int kb_begin = tr.bz * a.kb_per_split;
+                const int nkb = min(a.nkb, kb_begin + a.kb_per_split) - kb_begin;
+                const uint32_t idesc = a.idesc;
+#ifdef PB_CONV_STATS
+                const bool first_tile = i == 0;
+#endif
+                ok = mbar_wait(smem_u32(&s_tempty[acc]), (use & 1u) ^ 1u, &s_abort, err_flag, 4u);
+                if (!ok) break;
+                PB_PT(i, 0);
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * acc_cols;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!have_next) {
+                        ok = mbar_wait(smem_u32(&s_full[st]), parity, &s_abort, err_flag, 2u);
+                        if (!ok) break;
+                    }
+                    PB_PK(kb, 4);
+                    tcgen05_fence_after();
+                    // stage of the k-block after this one (of this tile or of the CTA's next tile: the pipeline runs on)
+                    uint32_t st_n = st + 1, parity_n = parity;
+                    if (st_n == (uint32_t)stages) { st_n = 0; parity_n ^= 1u; }
+                    have_next = mbar_test_wait(smem_u32(&s_full[st_n]), parity_n);
+                    const uint64_t da = desc_a0 + (uint64_t)st * desc_step, db = desc_b0 + (uint64_t)st * desc_step;
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        tcgen05_mma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);   // +32 bytes per K=16 slice
+                    tcgen05_commit(smem_u32(&s_empty[st]));
+                    PB_PK(kb, 5);
+                    st = st_n;
+                    parity = parity_n;
+                }
+                if (ok) tcgen05_commit(smem_u32(&s_tfull[acc]));
+                PB_PT(i, 1);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ===== producers: lane 0 of warps 5-8 =====
+        if (lane == 0) {
+            const uint32_t prod = (uint32_t)(warp - 5);
+            // which (stage, operand) pairs are this thread's: bit st of mask_a / mask_b (no division in the loop)
+            uint32_t mask_a = 0, mask_b = 0;
+            for (int q = 0; q < stages; ++q) {
+                if ((uint32_t)(q * 2) % kPersistProducers == prod) mask_a |= 1u << q;
+                if ((uint32_t)(q * 2 + 1) % kPersistProducers == prod) mask_b |= 1u << q;
+            }
+            uint32_t st = 0, parity = 1u;           // a fresh barrier passes a wait on the "previous" phase
+            bool ok = true;
+            uint32_t* const err_flag = s_sub[0].a.err_flag;
+            for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+#ifdef PB_CONV_STATS
+                const bool first_tile = t == blockIdx.x;
+#endif
+                const TileRef tr = tile_ref(table, s_sub, n_sub, t);
+                const ConvArgs& a = tr.sa->a;
+                const CUtensorMap* tmap_w = &tr.sc->tmap_w;
+                const CUtensorMap* tmap_x = &tr.sc->tmap_x;
+                const int kb_begin = tr.bz * a.kb_per_split;
+                const int nkb = min(a.nkb, kb_begin + a.kb_per_split) - kb_begin;
+                const int m0 = tr.bx * kBM, n0 = tr.by * a.BN;
+                const int PQ = a.PQ, Q = a.Q;
+                const int img = m0 / PQ, rem = m0 - img * PQ;
+                const int p0 = rem / Q, q0 = rem - p0 * Q;
+                const int w0 = q0 * a.sw - a.pw, h0 = p0 * a.sh - a.ph;
+                const int cpt = a.Cp / kBK, S = a.S, dw = a.dw, dh = a.dh, a_tiled = a.a_tiled;
+                const uint32_t tx_bytes = (uint32_t)kATileBytes + a.b_stage_bytes;
+                // filter tap (r, s2) and channel chunk of the k-block, carried along
+                int tap = kb_begin / cpt, chunk = kb_begin - tap * cpt;
+                int r = tap / S, s2 = tap - r * S;
+                if (prod == 0) PB_PT((t - blockIdx.x) / gridDim.x, 4);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    const bool mine_a = (mask_a >> st) & 1u, mine_b = (mask_b >> st) & 1u;
+                    if (mine_a || mine_b) {
+                        if (mine_a) PB_PK(kb, 0);
+                        if (mine_b) PB_PK(kb, 2);
+                        ok = mbar_wait(smem_u32(&s_empty[st]), parity, &s_abort, err_flag, 1u);
+                        if (!ok) break;
+                        const uint32_t a_tile = smem_base + st * stage_bytes;
+                        const uint32_t bar = smem_u32(&s_full[st]);
+                        if (mine_a) {
+                            mbar_arrive_expect_tx(bar, tx_bytes);
+                            if (a_tiled) tma_load_2d(a_tile, tmap_x, chunk * kBK, m0, bar);
+                            else tma_load_im2col_4d(a_tile, tmap_x, chunk * kBK, w0, h0, img, (uint16_t)(s2 * dw), (uint16_t)(r * dh), bar);
+                            PB_PK(kb, 1);
+                        }
+                        if (mine_b) { tma_load_2d(a_tile + kATileBytes, tmap_w, (kb_begin + kb) * kBK, n0, bar); PB_PK(kb, 3); }
+                    }
+                    if (++chunk == cpt) {
+                        chunk = 0;
+                        if (++s2 == S) { s2 = 0; ++r; }
+                    }
+                    if (++st == (uint32_t)stages) { st = 0; parity ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // the next kernel's blocks may take SM slots from here on: this CTA is about to leave
+    griddep_launch();
+    tcgen05_fence_before();
+    __syncthreads();
+    if (s_abort) {
+        const unsigned long long t0 = globaltimer_ns();
+        for (uint32_t i = 0; i < (1u << 20); ++i) {
+            if (globaltimer_ns() - t0 > 50000ull) break;
+        }
+        __syncthreads();
+    }
+    if (warp == 4) {
+        tcgen05_fence_after();
+        tcgen05_dealloc(tmem_base, 2u * acc_cols);
+    }
+#ifdef PB_CONV_STATS
+    if (tid == 0) {
+        atomicSub(&g_persist_resident, 1u);
+        atomicAdd(&g_persist_hist[15], (unsigned long long)(clock64() - s_cta_t0));
+    }
+#endif
+    if (nf) nf->end(job_id);
+}
+
 // ---- host side ----------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -841,6 +1217,22 @@ int max_bn() {
         return n >= 256 ? 256 : 128;
     }();
     return v;
+}
+
+// Model launches run the persistent kernel (a CTA walks several tiles) unless PB_CONV_PERSIST=0.
+bool persist_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("PB_CONV_PERSIST");
+        return !(e && e[0] == '0') && use_tma_a();
+    }();
+    return v;
+}
+// Tiles a persistent CTA is given (PB_CONV_TILES_PER_CTA): more tiles per CTA spread the per-CTA costs thinner
+// and leave SM slots to the other requests in flight; fewer tiles per CTA finish a lone launch sooner.
+int tiles_per_cta() {
+    const char* e = getenv("PB_CONV_TILES_PER_CTA");      // read at every use: a model instance keeps what it was built with
+    const int n = e ? atoi(e) : 3;
+    return n < 1 ? 1 : (n > 64 ? 64 : n);
 }
 
 // A split of the reduction must save at least this much (us) of a lone launch's modelled time.
@@ -940,11 +1332,17 @@ const void* kernel_for(int stages, bool tma) {
 
 // Raises the dynamic shared-memory limit of every kernel of this file on the current device.
 cudaError_t raise_smem_limits() {
-    const void* kernels[] = {(const void*)conv_umma_tma_kernel, (const void*)conv_umma_multi_kernel,
+    const void* kernels[] = {(const void*)conv_umma_tma_kernel, (const void*)conv_umma_multi_kernel, (const void*)conv_umma_persist_kernel,
                              (const void*)conv_umma_gather_kernel<4>, (const void*)conv_umma_gather_kernel<6>,
                              (const void*)conv_umma_gather_kernel<8>};
     for (const void* k : kernels) {
-        const cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
+        if (e != cudaSuccess) return e;
+        // An SM's split between shared memory and L1 is fixed while blocks are resident.  Left to the default, the
+        // first block to land on an idle SM sizes the split for itself alone and the SM then holds one or two blocks
+        // instead of three until it has drained (measured under load: 14 % of the blocks started alone on their SM,
+        // 40 % with one other, 45 % with two).  Ask for the largest shared-memory split whenever these kernels run.
+        e = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
@@ -957,6 +1355,32 @@ struct ConvUmmaPlan {
     Geometry g;
     int device;
 };
+
+#ifdef PB_CONV_STATS
+extern "C" __attribute__((visibility("default"))) int pb_debug_persist_hist(unsigned long long* out16, int reset) {
+    if (cudaMemcpyFromSymbol(out16, g_persist_hist, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+    if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_persist_hist, z, sizeof(z)); }
+    return 0;
+}
+extern "C" __attribute__((visibility("default"))) int pb_debug_persist_tile(long long* out96) {
+    return cudaMemcpyFromSymbol(out96, g_persist_tile, sizeof(long long) * 16 * 6) == cudaSuccess ? 0 : -1;
+}
+extern "C" __attribute__((visibility("default"))) int pb_debug_persist_kb(long long* out384) {
+    return cudaMemcpyFromSymbol(out384, g_persist_kb, sizeof(long long) * 64 * 6) == cudaSuccess ? 0 : -1;
+}
+extern "C" __attribute__((visibility("default"))) int pb_debug_conv_stats(unsigned long long* out16, int reset) {
+    if (cudaMemcpyFromSymbol(out16, g_conv_stats, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+    unsigned long long ns = 0;
+    if (cudaMemcpyFromSymbol(&ns, g_conv_ns, sizeof(ns)) != cudaSuccess) return -1;
+    out16[15] = ns;          // replaces the 5+ bucket of the residency histogram
+    if (reset) { const unsigned long long z1 = 0; cudaMemcpyToSymbol(g_conv_ns, &z1, sizeof(z1)); }
+    if (reset) {
+        unsigned long long z[16] = {0};
+        if (cudaMemcpyToSymbol(g_conv_stats, z, sizeof(z)) != cudaSuccess) return -1;
+    }
+    return 0;
+}
+#endif
 
 void conv_umma_set_split_gain_us(double us) { g_split_gain_us.store(us, std::memory_order_relaxed); }
 
@@ -1100,7 +1524,13 @@ int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan
     // The shared-memory limit is a per-device function attribute: raise it once on every device used.
     static std::once_flag once[16];
     static cudaError_t attr_errs[16] = {};
-    const int dev = plan->device >= 0 && plan->device < 16 ? plan->device : 0;
+    if (plan->device < 0 || plan->device >= 16) {
+        const int bad = plan->device;
+        delete plan;
+        set_error("conv_umma: device index %d outside 0..15 (the per-device kernel attributes are kept for 16 devices)", bad);
+        return PB_ERR_INVALID;
+    }
+    const int dev = plan->device;
     std::call_once(once[dev], [dev] { attr_errs[dev] = raise_smem_limits(); });
     const cudaError_t attr_err = attr_errs[dev];
     if (attr_err != cudaSuccess) { delete plan; return cuda_fail(attr_err, "cudaFuncSetAttribute(conv_umma)", __FILE__, __LINE__); }
@@ -1182,12 +1612,22 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
 struct ConvUmmaMulti {
     SubConv* table_dev = nullptr;
     int n = 0;
-    unsigned total_blocks = 0;
+    unsigned total_blocks = 0;      // tiles of all sub-problems (= CTAs of the one-tile-per-CTA kernel)
     uint32_t smem = 0;
     uint32_t tmem_cols = 0;
+    // persistent kernel
+    bool persist = false;
+    unsigned grid = 0;
+    int stages = 0;
+    uint32_t stage_bytes = 0, persist_smem = 0;
 };
 
 bool conv_umma_multi_available() { return use_tma_a(); }
+bool conv_umma_persist_enabled() { return persist_enabled(); }
+uint32_t conv_umma_persist_grid(uint32_t total_tiles) {
+    const uint32_t g = ceil_div<uint32_t>(total_tiles, (uint32_t)tiles_per_cta());
+    return g < 1 ? 1 : g;
+}
 
 int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, int n,
                            ConvUmmaMulti** out) {
@@ -1212,7 +1652,13 @@ int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap*
         m->total_blocks += (unsigned)(g.m_tiles * g.n_tiles * g.splits);
         m->smem = std::max(m->smem, g.smem_bytes);
         m->tmem_cols = std::max(m->tmem_cols, g.tmem_cols);
+        m->stage_bytes = std::max(m->stage_bytes, (uint32_t)kATileBytes + g.b_stage_bytes);
     }
+    // persistent kernel: one pipeline for every sub-problem (stages of the widest), two accumulators
+    m->stages = (int)std::min<uint32_t>(kMaxStages, (kSmemBudgetPersist - 1024u) / m->stage_bytes);
+    m->persist_smem = (uint32_t)m->stages * m->stage_bytes + 1024u;
+    m->grid = conv_umma_persist_grid(m->total_blocks);
+    m->persist = persist_enabled() && m->stages >= 2 && 2u * m->tmem_cols <= 512u;
     cudaError_t e = cudaMalloc((void**)&m->table_dev, sizeof(SubConv) * (size_t)n);
     if (e == cudaSuccess) e = cudaMemcpy(m->table_dev, table.data(), sizeof(SubConv) * (size_t)n, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) { conv_umma_multi_destroy(m); return cuda_fail(e, "conv_umma_multi_create", __FILE__, __LINE__); }
@@ -1226,20 +1672,50 @@ void conv_umma_multi_destroy(ConvUmmaMulti* m) {
     delete m;
 }
 
+void conv_umma_persist_footprint(uint32_t total_tiles, uint32_t max_tmem_cols, pb_launch_info* out) {
+    memset(out, 0, sizeof(*out));
+    out->num_blocks = conv_umma_persist_grid(total_tiles);
+    out->threads_per_block = kThreadsPersist;
+    out->smem_per_block = kSmemBudgetPersist;
+    cudaFuncAttributes at;
+    out->regs_per_thread = 128;
+    if (cudaFuncGetAttributes(&at, (const void*)conv_umma_persist_kernel) == cudaSuccess) out->regs_per_thread = (uint32_t)at.numRegs;
+    else cudaGetLastError();
+    out->tmem_cols_per_block = 2u * max_tmem_cols;
+    out->kind = PB_STAGE_CONV_UMMA;
+}
+
 void conv_umma_multi_info(const ConvUmmaMulti* m, pb_launch_info* out) {
     memset(out, 0, sizeof(*out));
-    out->num_blocks = m->total_blocks;
-    out->threads_per_block = kThreadsTma;
-    out->smem_per_block = m->smem;
+    out->num_blocks = m->persist ? m->grid : m->total_blocks;
+    out->threads_per_block = m->persist ? kThreadsPersist : kThreadsTma;
+    out->smem_per_block = m->persist ? m->persist_smem : m->smem;
     cudaFuncAttributes at;
     out->regs_per_thread = 112;
-    if (cudaFuncGetAttributes(&at, (const void*)conv_umma_multi_kernel) == cudaSuccess) out->regs_per_thread = (uint32_t)at.numRegs;
+    if (cudaFuncGetAttributes(&at, m->persist ? (const void*)conv_umma_persist_kernel : (const void*)conv_umma_multi_kernel) == cudaSuccess)
+        out->regs_per_thread = (uint32_t)at.numRegs;
     else cudaGetLastError();
-    out->tmem_cols_per_block = m->tmem_cols;
+    out->tmem_cols_per_block = m->persist ? 2u * m->tmem_cols : m->tmem_cols;
     out->kind = PB_STAGE_CONV_UMMA;
 }
 
 int conv_umma_multi_launch(const ConvUmmaMulti* m, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl) {
+    if (m->persist) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(m->grid);
+        cfg.blockDim = dim3(kThreadsPersist);
+        cfg.dynamicSmemBytes = m->persist_smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, conv_umma_persist_kernel, (const SubConv*)m->table_dev, m->n, (uint32_t)m->total_blocks, m->stages,
+                                                 m->stage_bytes, m->tmem_cols, job_id, static_cast<FinishedBlockNotifier*>(notifier));
+        if (e != cudaSuccess) return cuda_fail(e, "launch of conv_umma_persist_kernel", __FILE__, __LINE__);
+        return PB_OK;
+    }
     const cudaError_t e = launch_pdl(conv_umma_multi_kernel, dim3(m->total_blocks), m->smem, st, pdl, (const SubConv*)m->table_dev, m->n,
                                      job_id, static_cast<FinishedBlockNotifier*>(notifier));
     if (e != cudaSuccess) return cuda_fail(e, "launch of conv_umma_multi_kernel", __FILE__, __LINE__);
@@ -1250,9 +1726,79 @@ int conv_umma_launch(const pb_op_params* p, cudaStream_t st, uint32_t job_id, vo
     ConvUmmaPlan* plan = nullptr;
     int rc = conv_umma_plan_create(p, p->w, &plan);
     if (rc != PB_OK) return rc;
+    // PB_CONV_PERSIST_OPS=1 (read at every call; for tests): a lone operator launch also runs the persistent kernel
+    // the model launches use, through a one-entry table that lives for this call only (allocates and synchronises).
+    const char* po = getenv("PB_CONV_PERSIST_OPS");
+    if (po && po[0] == '1' && persist_enabled()) {
+        ConvUmmaXMap* xm = nullptr;
+        ConvUmmaMulti* mu = nullptr;
+        rc = conv_umma_xmap_create(p, &xm);
+        if (rc == PB_OK) {
+            const ConvUmmaPlan* plans[1] = {plan};
+            const ConvUmmaXMap* xms[1] = {xm};
+            const pb_op_params* pp[1] = {p};
+            rc = conv_umma_multi_create(plans, xms, pp, 1, &mu);
+        }
+        if (rc == PB_OK && !mu->persist) { set_error("conv_umma: this shape does not fit the persistent kernel"); rc = PB_ERR_INVALID; }
+        if (rc == PB_OK) rc = conv_umma_multi_launch(mu, st, job_id, notifier, false);
+        if (rc == PB_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "persistent convolution", __FILE__, __LINE__);
+        conv_umma_multi_destroy(mu);
+        conv_umma_xmap_destroy(xm);
+        conv_umma_plan_destroy(plan);
+        return rc;
+    }
     rc = conv_umma_launch_planned(plan, nullptr, p, st, job_id, notifier, nullptr);
     conv_umma_plan_destroy(plan);   // the tensor maps were copied into the launch parameters
     return rc;
+}
+
+// Times `iters` launches of one convolution between CUDA events (after 3 warm-up launches), an L2 flush (a write
+// of flush_bytes) before each when asked: mode 0 = the one-tile-per-CTA kernel, 1 = the persistent kernel.
+int conv_umma_time(const pb_op_params* p, int mode, int iters, size_t flush_bytes, double* us_out) {
+    PB_REQUIRE(p && us_out && iters > 0, "pb_conv_umma_time: bad arguments");
+    ConvUmmaPlan* plan = nullptr;
+    ConvUmmaXMap* xm = nullptr;
+    ConvUmmaMulti* mu = nullptr;
+    void* flush = nullptr;
+    cudaStream_t st = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = conv_umma_plan_create(p, p->w, &plan);
+    if (rc == PB_OK) rc = conv_umma_xmap_create(p, &xm);
+    if (rc == PB_OK && mode == 1) {
+        const ConvUmmaPlan* plans[1] = {plan};
+        const ConvUmmaXMap* xms[1] = {xm};
+        const pb_op_params* pp[1] = {p};
+        rc = conv_umma_multi_create(plans, xms, pp, 1, &mu);
+        if (rc == PB_OK && !mu->persist) { set_error("pb_conv_umma_time: the persistent kernel is off or does not fit this shape"); rc = PB_ERR_INVALID; }
+    }
+    cudaError_t e = cudaSuccess;
+    if (rc == PB_OK) e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    if (rc == PB_OK && e == cudaSuccess && flush_bytes) e = cudaMalloc(&flush, flush_bytes);
+    if (rc == PB_OK && e == cudaSuccess) e = cudaEventCreate(&e0);
+    if (rc == PB_OK && e == cudaSuccess) e = cudaEventCreate(&e1);
+    double total_ms = 0;
+    auto launch = [&]() { return mode == 1 ? conv_umma_multi_launch(mu, st, 0, nullptr, false) : conv_umma_launch_planned(plan, xm, p, st, 0, nullptr, nullptr, false); };
+    for (int i = 0; rc == PB_OK && e == cudaSuccess && i < 3; ++i) rc = launch();
+    for (int i = 0; rc == PB_OK && e == cudaSuccess && i < iters; ++i) {
+        if (flush) cudaMemsetAsync(flush, i & 0xff, flush_bytes, st);
+        cudaEventRecord(e0, st);
+        rc = launch();
+        cudaEventRecord(e1, st);
+        e = cudaEventSynchronize(e1);
+        float ms = 0;
+        if (e == cudaSuccess) { cudaEventElapsedTime(&ms, e0, e1); total_ms += ms; }
+    }
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    if (flush) cudaFree(flush);
+    if (st) cudaStreamDestroy(st);
+    conv_umma_multi_destroy(mu);
+    conv_umma_xmap_destroy(xm);
+    conv_umma_plan_destroy(plan);
+    if (rc != PB_OK) return rc;
+    if (e != cudaSuccess) return cuda_fail(e, "pb_conv_umma_time", __FILE__, __LINE__);
+    *us_out = total_ms * 1000.0 / iters;
+    return PB_OK;
 }
 
 // ---- launch without any allocation -----------------------------------------------------------------

@@ -78,6 +78,7 @@ struct pb_model {
     struct Group { int first, count; pb_launch_info info; std::vector<std::vector<int>> launches; };
     std::vector<Group> groups;
     bool fuse_branches = false;
+    bool persist = false;       // tensor-core launches of the stage graphs run the persistent (multi-tile) kernel
     // fused MNIST weights (device)
     float *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr, *wd = nullptr, *bd = nullptr;
     std::vector<void*> allocs;
@@ -142,6 +143,13 @@ bool is_mnist_topology(const std::vector<PackOp>& ops, const std::vector<TensorI
 }
 
 
+// Launches that go through a descriptor table (ConvUmmaMulti): several tensor-core convolutions in one grid,
+// and with the persistent kernel every tensor-core convolution of a stage graph.
+bool uses_multi(const pb_model* m, const std::vector<int>& l) {
+    if (l.size() > 1) return true;
+    return m->persist && m->stages[(size_t)l[0]].kind == PB_STAGE_CONV_UMMA;
+}
+
 // What group `g` declares to the scheduler, from its stages' launch geometry `infos` (per stage): only the
 // LAST launch of a group reports block start/end, so the declared block count is that launch's grid; the
 // per-block resources are scaled so that blocks x per-block equals the largest footprint any launch of
@@ -153,6 +161,7 @@ pb_launch_info group_footprint(const pb_model* m, int g, const std::vector<pb_la
     uint64_t thr = 0, smem = 0, regs = 0, tmem = 0, nb = 0;
     for (const std::vector<int>& l : grp.launches) {
         uint64_t lt = 0, ls = 0, lr = 0, lm = 0, lb = 0;
+        uint32_t max_tmem = 0;
         for (int i : l) {
             const pb_launch_info& li = infos[(size_t)i];
             lb += li.num_blocks;
@@ -160,8 +169,21 @@ pb_launch_info group_footprint(const pb_model* m, int g, const std::vector<pb_la
             ls += (uint64_t)li.num_blocks * li.smem_per_block;
             lr += (uint64_t)li.num_blocks * li.threads_per_block * li.regs_per_thread;
             lm += (uint64_t)li.num_blocks * li.tmem_cols_per_block;
+            max_tmem = std::max(max_tmem, li.tmem_cols_per_block);
             out.flops += li.flops;
             out.bytes += li.bytes;
+        }
+        if (uses_multi(m, l)) {
+            // the launch's tiles (lb) are walked by fewer, longer-lived CTAs
+            pb_launch_info pf;
+            pb::conv_umma_persist_footprint((uint32_t)lb, max_tmem, &pf);
+            if (m->persist && 2u * max_tmem <= 512u) {
+                lb = pf.num_blocks;
+                lt = lb * pf.threads_per_block;
+                ls = lb * pf.smem_per_block;
+                lr = lt * pf.regs_per_thread;
+                lm = lb * pf.tmem_cols_per_block;
+            }
         }
         thr = std::max(thr, lt); smem = std::max(smem, ls); regs = std::max(regs, lr); tmem = std::max(tmem, lm);
         nb = lb;
@@ -184,6 +206,7 @@ void build_groups(pb_model* m) {
     // Independent tensor-core convolutions of equal dependence depth share one launch, unless the
     // graphs are captured with parallel branches (PB_GRAPH_BRANCHES=1) or PB_FUSE_BRANCHES=0.
     m->fuse_branches = env_flag("PB_FUSE_BRANCHES", true) && !env_flag("PB_GRAPH_BRANCHES", false) && pb::conv_umma_multi_available();
+    m->persist = !env_flag("PB_GRAPH_BRANCHES", false) && pb::conv_umma_multi_available() && pb::conv_umma_persist_enabled();
     const int n = (int)m->stages.size();
     std::vector<std::vector<int>> writers(m->tensors.size());
     for (int first = 0; first < n; first += gs) {
@@ -286,7 +309,7 @@ int capture_group_chain(pb_instance* in, Variant& v, int g, cudaStream_t origin,
     for (size_t li = 0; e == cudaSuccess && rc == PB_OK && li < grp.launches.size(); ++li) {
         const std::vector<int>& l = grp.launches[li];
         const bool is_last = li + 1 == grp.launches.size();
-        if (l.size() > 1) {
+        if (v.multis[(size_t)g][li]) {
             rc = pb::conv_umma_multi_launch(v.multis[(size_t)g][li], origin, is_last ? pb::kSlotNotify : 0u, is_last ? slot_ptr : nullptr,
                                             pdl_allowed && after_kernel);
         } else {
@@ -483,6 +506,22 @@ int ensure_variant(pb_instance* in, int nb, Variant** out) {
     for (size_t g = 0; g < m->groups.size(); ++g) v->group_info[g] = group_footprint(m, (int)g, infos);
     v->graphs.assign(m->groups.size(), nullptr);
     v->multis.resize(m->groups.size());
+    // descriptor tables of the launches that go through one (grouped convolutions; with the persistent kernel
+    // every tensor-core convolution)
+    for (size_t g = 0; g < m->groups.size(); ++g) {
+        const pb_model::Group& grp = m->groups[g];
+        v->multis[g].assign(grp.launches.size(), nullptr);
+        for (size_t li = 0; li < grp.launches.size(); ++li) {
+            const std::vector<int>& l = grp.launches[li];
+            if (!uses_multi(m, l)) continue;
+            std::vector<const pb::ConvUmmaPlan*> plans;
+            std::vector<const pb::ConvUmmaXMap*> xm;
+            std::vector<const pb_op_params*> pp;
+            for (int s : l) { plans.push_back(m->stages[s].plan); xm.push_back(v->xmaps[s]); pp.push_back(&v->params[s]); }
+            const int rc = pb::conv_umma_multi_create(plans.data(), xm.data(), pp.data(), (int)l.size(), &v->multis[g][li]);
+            if (rc != PB_OK) { destroy_variant(v); return rc; }
+        }
+    }
     // PB_GRAPH_SINGLE=0: single-kernel groups are launched as plain kernels (about 3 us more host time each)
     const bool single_graphs = env_flag("PB_GRAPH_SINGLE", true);
     bool any_graph = single_graphs && !m->groups.empty();
@@ -503,19 +542,6 @@ int ensure_variant(pb_instance* in, int nb, Variant** out) {
                 if (rc == PB_OK) continue;
                 cudaGetLastError();                   // a driver that cannot capture this: the chain below
             }
-            // descriptor tables of the grouped launches
-            v->multis[g].assign(grp.launches.size(), nullptr);
-            rc = PB_OK;
-            for (size_t li = 0; rc == PB_OK && li < grp.launches.size(); ++li) {
-                const std::vector<int>& l = grp.launches[li];
-                if (l.size() < 2) continue;
-                std::vector<const pb::ConvUmmaPlan*> plans;
-                std::vector<const pb::ConvUmmaXMap*> xm;
-                std::vector<const pb_op_params*> pp;
-                for (int s : l) { plans.push_back(m->stages[s].plan); xm.push_back(v->xmaps[s]); pp.push_back(&v->params[s]); }
-                rc = pb::conv_umma_multi_create(plans.data(), xm.data(), pp.data(), (int)l.size(), &v->multis[g][li]);
-            }
-            if (rc != PB_OK) break;
             rc = capture_group_chain(in, *v, (int)g, cap_stream, pdl);
             if (rc != PB_OK && pdl) {                 // a driver that cannot capture programmatic edges: plain edges
                 cudaGetLastError();
@@ -552,6 +578,8 @@ int64_t pb_op_pack_weights(int kind, const pb_op_params* p, const float* w_oihw,
     if (kind == PB_STAGE_CONV_UMMA) return pb::conv_umma_pack_weights(p, w_oihw, dst_host);
     return pb::simple_pack_weights(kind, p, w_oihw, dst_host);
 }
+
+int pb_conv_umma_time(const pb_op_params* p, int mode, int iters, size_t flush_bytes, double* us_out) { return pb::conv_umma_time(p, mode, iters, flush_bytes, us_out); }
 
 void pb_set_conv_split_gain_us(double us) { pb::conv_umma_set_split_gain_us(us); }
 
@@ -995,6 +1023,8 @@ int pb_instance_launch_group_batched(pb_instance* in, int group, int batch, void
     }
     // single kernel, no graph: a direct launch
     const int stage = g.first;
+    if (v->multis[(size_t)group][0])
+        return pb::conv_umma_multi_launch(v->multis[(size_t)group][0], (cudaStream_t)stream, job_id, notifier, false);
     pb_op_params p = v->params[stage];
     if (batch == 1) {
         if (stage == 0) p.x = s->io_in[0];

@@ -57,11 +57,19 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
 // parameters) run as ONE grid; the table of descriptors is copied to device memory here.
 struct ConvUmmaMulti;
 bool conv_umma_multi_available();
+// Model launches of tensor-core convolutions go through ConvUmmaMulti tables (one entry for a lone convolution);
+// when the persistent kernel is on (default; PB_CONV_PERSIST=0 turns it off) a launch of T tiles runs
+// conv_umma_persist_grid(T) CTAs, which is what conv_umma_multi_info reports and what notifies.
+bool conv_umma_persist_enabled();
+uint32_t conv_umma_persist_grid(uint32_t total_tiles);
+// Footprint of a persistent launch over `total_tiles` tiles whose widest accumulator has `max_tmem_cols` columns.
+void conv_umma_persist_footprint(uint32_t total_tiles, uint32_t max_tmem_cols, pb_launch_info* out);
 int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, int n,
                            ConvUmmaMulti** out);
 void conv_umma_multi_destroy(ConvUmmaMulti* m);
 void conv_umma_multi_info(const ConvUmmaMulti* m, pb_launch_info* out);
 int conv_umma_multi_launch(const ConvUmmaMulti* m, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl);
+int conv_umma_time(const pb_op_params* p, int mode, int iters, size_t flush_bytes, double* us_out);
 void conv_umma_set_split_gain_us(double us);   // < 0: back to PB_CONV_SPLIT_GAIN_US / the default
 int conv_umma_launch_noalloc(const pb_op_params* p, cudaStream_t st, uint32_t job_id, void* notifier);
 uint32_t* noalloc_error_flag_ptr(int device);   // NULL until the no-allocation path ran on the device

@@ -192,7 +192,7 @@ int pb_device_error_flag(int device, uint32_t* flag_out, int reset) {
     if (uint32_t* q = pb::noalloc_error_flag_ptr(device)) {
         uint32_t v = 0;
         PB_CUDA(cudaMemcpy(&v, q, sizeof(uint32_t), cudaMemcpyDeviceToHost));
-        if (flag_out && v) *flag_out = v;
+        if (flag_out) *flag_out |= v;      // both flags are reported: neither hides the other
         if (reset) PB_CUDA(cudaMemset(q, 0, sizeof(uint32_t)));
     }
     return PB_OK;
@@ -377,6 +377,42 @@ int pb_ring_roundtrip_bench(int device, uint32_t iters, double* rtt_us_out) {
     cudaStreamDestroy(st);
     cudaFreeHost((void*)ping);
     cudaFreeHost(status);
+    pb_notifier_free_array(nf);
+    pb_ring_destroy(ring);
+    return rc;
+}
+
+// The same one-thread kernel with a ping that never comes: its wait runs out after `max_polls` polls of host
+// memory, it records status 2 and returns; the context stays usable.  This is how a device-side wait is
+// expected to fail everywhere in this library, and the test of that.
+int pb_ring_wait_expiry_probe(int device, uint32_t max_polls, uint32_t* status_out, uint32_t* records_out) {
+    PB_REQUIRE(status_out && max_polls >= 1 && max_polls <= (1u << 16), "pb_ring_wait_expiry_probe: max_polls outside 1..65536");
+    PB_CUDA(cudaSetDevice(device));
+    pb_ring* ring = nullptr;
+    void* nf = nullptr;
+    int rc = pb_ring_create(device, 1 << 8, &ring);
+    if (rc != PB_OK) return rc;
+    rc = pb_notifier_create_array(ring, 1, &nf);
+    if (rc != PB_OK) { pb_ring_destroy(ring); return rc; }
+    volatile uint32_t* ping = nullptr;
+    uint32_t* status = nullptr;
+    cudaError_t e = cudaHostAlloc((void**)&ping, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&status, 64, cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        *ping = 0;          // the kernel waits for 1
+        *status = 0;
+        ring_pingpong_kernel<<<1, 32>>>(ping, 1, max_polls, (FinishedBlockNotifier*)nf, status);
+        rc = pb::launch_check("ring_pingpong");
+        e = cudaDeviceSynchronize();
+    }
+    if (e != cudaSuccess && rc == PB_OK) rc = pb::cuda_fail(e, "wait-expiry probe", __FILE__, __LINE__);
+    if (rc == PB_OK) {
+        *status_out = *status;
+        uint64_t rec = 0;
+        if (records_out) *records_out = pb_ring_poll(ring, &rec, 1) == 1 ? 1u : 0u;
+    }
+    if (ping) cudaFreeHost((void*)ping);
+    if (status) cudaFreeHost(status);
     pb_notifier_free_array(nf);
     pb_ring_destroy(ring);
     return rc;

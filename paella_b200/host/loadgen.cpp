@@ -14,6 +14,8 @@
 // server's poll/dispatch loop, so no queue or lock sits between "client" and scheduler.
 #include <cuda_runtime.h>
 #include <llis/job/context.h>
+#include <pthread.h>
+#include <sched.h>
 
 #include <algorithm>
 #include <atomic>
@@ -43,6 +45,7 @@ struct Request {
 struct Slot {
     void* io = nullptr;
     int type = 0;
+    bool measured = false;      // a measured request has completed in this slot
 };
 
 struct GpuResult {
@@ -52,6 +55,8 @@ struct GpuResult {
     uint64_t measured = 0, kernels = 0, records = 0, decisions = 0, h2d = 0, d2h = 0;
     double host_launch_us = 0, host_busy_us = 0, host_idle_us = 0;
     int errors = 0;
+    uint32_t samples = 0;
+    uint64_t sample_bytes = 0;
     int rc = PB_OK;
     char err[256] = "";
 };
@@ -109,6 +114,16 @@ std::vector<std::vector<Request>> plan_requests(const pb_loadgen_config* cfg) {
 void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<Request>* reqs, std::atomic<int>* ready,
                  std::atomic<int>* go, std::atomic<int>* phase2_ready, GpuResult* out) {
     const int device = cfg->devices[gpu_index];
+    // This thread submits, polls the ring and makes every CUDA launch call of its GPU: keep it on one core
+    // (the reference pins its server loop with taskset, sosp23_artifact/gen_data_fig11_paella.sh:63), and
+    // allocate the request slots after that so that their pages are first touched from there.
+    if (cfg->cpu_of_replica[gpu_index] >= 0) {
+        cpu_set_t set;
+        CPU_ZERO(&set);
+        CPU_SET(cfg->cpu_of_replica[gpu_index], &set);
+        if (pthread_setaffinity_np(pthread_self(), sizeof(set), &set) != 0)
+            fprintf(stderr, "paella_b200: could not pin replica %d to cpu %d (continuing unpinned)\n", gpu_index, cfg->cpu_of_replica[gpu_index]);
+    }
     auto fail = [&](int rc) {
         out->rc = rc;
         snprintf(out->err, sizeof(out->err), "%s", pb_last_error());
@@ -130,6 +145,7 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
     std::vector<void*> pinned;
     std::mt19937 fill_rng(cfg->seed + 977u * (unsigned)gpu_index);
     std::normal_distribution<float> nd(0.f, 1.f);
+    std::uniform_real_distribution<float> ud(0.f, 1.f);
     for (int t = 0; t < nt; ++t) {
         rc = pb_server_register_job(srv, cfg->plugin_paths[t], &type_id[t]);
         if (rc != PB_OK) { pb_server_destroy(srv); return fail(rc); }
@@ -147,7 +163,7 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
             s.io = (char*)base + slot_b[t] * i;
             s.type = t;
             float* f = (float*)s.io;
-            for (size_t k = 0; k < in_b[t] / 4; ++k) f[k] = nd(fill_rng);
+            for (size_t k = 0; k < in_b[t] / 4; ++k) f[k] = cfg->input_uniform[t] ? ud(fill_rng) : nd(fill_rng);
             free_slots[t].push_back((int)slots.size());
             slots.push_back(s);
         }
@@ -230,6 +246,7 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
                     if (!have_first || t_arr < out->first_arrival_us) { out->first_arrival_us = t_arr; have_first = true; }
                     out->last_done_us = std::max(out->last_done_us, now);
                     ++out->measured;
+                    slots[(size_t)slot].measured = true;
                 }
                 free_slots[r.type].push_back(slot);
                 --outstanding;
@@ -285,6 +302,31 @@ void run_replica(const pb_loadgen_config* cfg, int gpu_index, const std::vector<
         out->rc = loop_rc;
         snprintf(out->err, sizeof(out->err), "%s", pb_last_error());
     }
+    // Samples for an output check by the caller: replica 0 copies out, per job type, the first slots in which a
+    // measured request completed - the slot's input and the result the serving path left beside it.
+    if (gpu_index == 0 && cfg->sample_buf && cfg->samples_per_type > 0 && !cfg->device_resident) {
+        char* dst = static_cast<char*>(cfg->sample_buf);
+        uint64_t used = 0;
+        std::vector<uint32_t> taken(nt, 0);
+        for (size_t i = 0; i < slots.size(); ++i) {
+            const Slot& sl = slots[i];
+            const int t = sl.type;
+            if (!sl.measured || taken[t] >= cfg->samples_per_type) continue;
+            const uint64_t in_pad = (in_b[t] + 7) / 8 * 8, out_pad = (out_b[t] + 7) / 8 * 8;
+            const uint64_t need = 24 + in_pad + out_pad;
+            if (used + need > cfg->sample_buf_bytes) break;
+            const uint32_t hdr32[2] = {(uint32_t)t, (uint32_t)i};
+            const uint64_t hdr64[2] = {(uint64_t)in_b[t], (uint64_t)out_b[t]};
+            memcpy(dst + used, hdr32, 8);
+            memcpy(dst + used + 8, hdr64, 16);
+            memcpy(dst + used + 24, sl.io, in_b[t]);
+            memcpy(dst + used + 24 + in_pad, (const char*)sl.io + in_pad, out_b[t]);
+            used += need;
+            ++taken[t];
+            ++out->samples;
+        }
+        out->sample_bytes = used;
+    }
     pb_server_destroy(srv);
     for (void* p : pinned) cudaFreeHost(p);
 }
@@ -302,6 +344,7 @@ void pb_loadgen_config_default(pb_loadgen_config* cfg) {
     cfg->num_jobs = 1000;
     cfg->warmup_jobs = 100;
     cfg->seed = 1;
+    for (int i = 0; i < PB_MAX_GPUS; ++i) cfg->cpu_of_replica[i] = -1;
     pb_server_config_default(&cfg->server);
 }
 
@@ -347,6 +390,8 @@ int pb_loadgen_run(const pb_loadgen_config* cfg, pb_loadgen_result* out) {
         out->h2d_bytes += res[g].h2d;
         out->d2h_bytes += res[g].d2h;
         out->errors += res[g].errors;
+        out->samples += res[g].samples;
+        out->sample_bytes += res[g].sample_bytes;
         out->elapsed_event_ms = std::max(out->elapsed_event_ms, res[g].event_ms);
     }
     if (rc != PB_OK) return rc;

@@ -128,6 +128,27 @@ def test_conv_umma(case):
     _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=False)
 
 
+@pytest.mark.parametrize("tiles_per_cta", ["1", "3"])
+@pytest.mark.parametrize("case", UMMA_CASES)
+def test_conv_umma_persistent_kernel(case, monkeypatch, tiles_per_cta):
+    """The kernel the model launches use (a CTA walks several tiles, two accumulators in tensor memory, three
+    producer threads), on the same shapes, alone and with the split reduction where the shape splits."""
+    monkeypatch.setenv("PB_CONV_PERSIST_OPS", "1")
+    monkeypatch.setenv("PB_CONV_TILES_PER_CTA", tiles_per_cta)
+    _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=(case[3] % 64 == 0))
+    L = capi.load()
+    L.pb_set_conv_split_gain_us(0.0)
+    try:
+        C_, H, W, K, R, S, sh, sw, ph, pw = case
+        p = _params(1, (C_, H, W), K, (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1, K, R, S, sh, sw, ph, pw)
+        li = capi.LaunchInfo()
+        capi.check(L.pb_op_info(capi.STAGE_CONV_UMMA, C.byref(p), C.byref(li)), "pb_op_info")
+        if li.scratch_bytes:
+            _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=2, residual=False, scratch=True)
+    finally:
+        L.pb_set_conv_split_gain_us(-1.0)
+
+
 SPLIT_CASES = [c for c in UMMA_CASES if c[4] * c[5] * c[0] >= 256 and ((c[1] + 2 * c[8] - c[4]) // c[6] + 1) ** 2 <= 2048]
 
 
@@ -136,7 +157,12 @@ def test_conv_umma_split_reduction(case):
     """Same cases with scratch memory supplied: the reduction is split over blockIdx.z and the last
     block to arrive on a tile adds the partial tiles.  fp32 partial sums in a different order:
     same tolerance as the unsplit kernel."""
-    _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=(case[3] % 64 == 0), scratch=True)
+    L = capi.load()
+    L.pb_set_conv_split_gain_us(0.0)        # split whenever the cost model sees any gain (the default asks for 6 us)
+    try:
+        _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=(case[3] % 64 == 0), scratch=True)
+    finally:
+        L.pb_set_conv_split_gain_us(-1.0)
 
 
 @pytest.mark.parametrize("case,residual", [((448, 8, 8, 384, 3, 3, 1, 1, 1, 1), False), ((512, 7, 7, 512, 3, 3, 1, 1, 1, 1), True),

@@ -162,3 +162,16 @@ def test_ring_latency_probe_and_clock_calibration(ring_env):
     assert cal[2] >= cal[0] and cal[1] > 0
     capi.check(L.pb_launch_latency_probe(None, 8, nf), "latency probe")
     assert len(_drain(L, ring, 8)) == 8
+
+
+def test_a_device_wait_that_runs_out_reports_status_and_leaves_the_context_usable():
+    """The bounded-wait rule, checked on the kernel that waits for the host: with a ping that never comes it gives
+    up after its poll limit, reports status 2 and returns; nothing faults and the next kernel runs normally."""
+    L = capi.load()
+    status, recs = C.c_uint32(0), C.c_uint32(7)
+    capi.check(L.pb_ring_wait_expiry_probe(0, 2000, C.byref(status), C.byref(recs)), "pb_ring_wait_expiry_probe")
+    assert status.value == 2 and recs.value == 0
+    n = 200
+    rtt = (C.c_double * n)()
+    capi.check(L.pb_ring_roundtrip_bench(0, n, rtt), "round trip after the expired wait")
+    assert all(0 < rtt[i] < 1e5 for i in range(n))

@@ -76,11 +76,15 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row():
         assert _close(got, want), f"call {call}: differs from the ordinary entry point by {float(np.abs(got - want).max())}"
         assert _close(got, ref)
 
-    # a different shape right after, through the same built-in buffer (stale partial tiles must not leak)
-    p2, yd2, keep2, (x2, w2, b2, pad2) = _problem(2048, 8, 8, 320, 1, 1, 0, seed=42)
+    # a different shape that splits too, right after, through the same built-in buffer: the partial tiles the
+    # first shape left behind must not leak into it
+    p2, yd2, keep2, (x2, w2, b2, pad2) = _problem(512, 7, 7, 512, 3, 3, 1, seed=42)
+    capi.check(L.pb_op_info(capi.STAGE_CONV_UMMA, C.byref(p2), C.byref(li)), "pb_op_info")
+    assert 0 < li.scratch_bytes <= (4 << 20), "the second shape must split as well"
     capi.check(L.pb_conv2d_umma_noalloc(C.byref(p2), None, 0, None), "second shape")
     gu.sync()
-    assert _close(gu.from_device_cl(yd2, 320), og.conv2d(x2, w2, b2, (1, 1), (0, 0), 1, 1, None))
+    assert gu.error_flag() == 0
+    assert _close(gu.from_device_cl(yd2, 512), og.conv2d(x2, w2, b2, (1, 1), (1, 1), 1, 1, None))
 
 
 def test_noalloc_refuses_what_does_not_fit():
