@@ -189,39 +189,52 @@ def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps
     return res, samples
 
 
-def roofline_leg(L, capi, models_dir, iters=20, only=""):
-    """Times every stage of Inception-v3 alone; returns the tensor-core convolution aggregate and a
-    per-kind table (time share of one request)."""
+def roofline_leg(L, capi, models_dir, iters=20, only="", batch=1):
+    """Times every stage of Inception-v3 alone, at the batch the serving path runs it with (a gang of `batch`
+    requests per launch), L2 flushed before every launch.  The tensor-core convolutions are timed through
+    pb_conv_umma_time on the kernel the stage graphs use (the persistent one); the other kinds through the
+    instance.  Returns the convolution aggregate and a per-kind table."""
     from paella_b200 import packer
     hbm, tf, how = measured_peaks()
     model, inst = C.c_void_p(), C.c_void_p()
     path = os.path.join(models_dir, packer.pack_file_name("inception_v3"))
     capi.check(L.pb_model_load(path.encode(), 0, 1, C.byref(model)), "pb_model_load")
-    capi.check(L.pb_instance_create(model, C.byref(inst)), "pb_instance_create")
+    capi.check(L.pb_instance_create_batched(model, batch, 0, C.byref(inst)), "pb_instance_create_batched")
     li, us = capi.LaunchInfo(), C.c_double()
     per_kind = {}
     layers = []
+    persist = os.environ.get("PB_CONV_PERSIST", "0") == "1"
     for s in range(L.pb_model_num_stages(model)):
-        L.pb_model_stage_info(model, s, C.byref(li))
-        if only and only not in L.pb_model_stage_name(model, s).decode():
+        capi.check(L.pb_model_stage_info_batched(model, s, batch, C.byref(li)), "pb_model_stage_info_batched")
+        name = L.pb_model_stage_name(model, s).decode()
+        if only and only not in name:
             continue
-        capi.check(L.pb_instance_time_stage(inst, s, iters, 192 << 20, C.byref(us)), "pb_instance_time_stage")
         k = capi.STAGE_NAMES[li.kind]
+        if li.kind == capi.STAGE_CONV_UMMA:
+            p = capi.OpParams()
+            capi.check(L.pb_instance_stage_params(inst, s, batch, C.byref(p)), "pb_instance_stage_params")
+            capi.check(L.pb_conv_umma_time(C.byref(p), 1 if persist else 0, iters, 192 << 20, C.byref(us)), "pb_conv_umma_time")
+        else:
+            capi.check(L.pb_instance_time_stage_batched(inst, s, batch, iters, 192 << 20, C.byref(us)), "pb_instance_time_stage_batched")
         d = per_kind.setdefault(k, {"launches": 0, "us": 0.0, "flops": 0, "bytes": 0})
         d["launches"] += 1; d["us"] += us.value; d["flops"] += li.flops; d["bytes"] += li.bytes
-        layers.append((L.pb_model_stage_name(model, s).decode(), k, us.value, li.flops, li.bytes, li.num_blocks))
+        layers.append((name, k, us.value, li.flops, li.bytes, li.num_blocks))
     L.pb_instance_destroy(inst)
     L.pb_model_destroy(model)
     conv = per_kind.get("conv_umma", {"launches": 0, "us": 1.0, "flops": 0, "bytes": 0})
     achieved = conv["flops"] / (conv["us"] * 1e-6) / 1e12 if conv["launches"] else 0.0
     total_us = sum(d["us"] for d in per_kind.values())
-    # DRAM bytes per launch of this kernel, from the ncu capture summarised in
-    # profiles/conv_umma_tma_kernel__inception_v3_layers.md (mean over the 89 Mixed_* layers)
-    traffic = 818185 if not only else None
-    roof = {"bound": "tensor", "kernel": "conv_umma_tma_kernel (tcgen05 implicit GEMM, TMA im2col), every Inception-v3 conv layer launched alone, batch 1, L2 flushed",
+    # DRAM bytes per launch of this kernel at batch 1, from the ncu capture summarised in
+    # profiles/conv_umma_kernels__inception_v3_layers.md (mean over the Mixed_* layers), scaled by the batch for the
+    # activation part is not attempted: reported for batch 1 only
+    traffic = 818185 if (not only and batch == 1) else None
+    kern = ("conv_umma_persist_kernel (tcgen05 implicit GEMM, TMA im2col, several tiles per CTA, two TMEM accumulators)" if persist
+            else "conv_umma_tma_kernel (tcgen05 implicit GEMM, TMA im2col, one tile per CTA)")
+    roof = {"bound": "tensor", "kernel": f"{kern}: every Inception-v3 conv layer launched alone, {batch} image(s) per launch as served, L2 flushed",
             "achieved": round(achieved, 3), "peak": tf, "unit": "TFLOP/s", "frac": round(achieved / tf, 5), "of": how,
             "traffic": traffic, "algorithmic_bytes_per_launch": int(conv["bytes"] / max(conv["launches"], 1)),
             "launches": conv["launches"], "avg_launch_us": round(conv["us"] / max(conv["launches"], 1), 3),
+            "images_per_launch": batch,
             "hbm_gbs_same_kernel": round(conv["bytes"] / (conv["us"] * 1e-6) / 1e9, 1),
             "time_share_of_request": round(conv["us"] / total_us, 4) if total_us else None}
     table = {k: {"launches": d["launches"], "us": round(d["us"], 2), "share": round(d["us"] / total_us, 4),
@@ -230,12 +243,12 @@ def roofline_leg(L, capi, models_dir, iters=20, only=""):
     return roof, table, layers
 
 
-def fairness_leg(L, capi, device, mix, mixed_result):
+def fairness_leg(L, capi, device, mix, mixed_result, cpus=None):
     """Jain's index over per-model slowdowns (mean latency in the mix / mean latency alone, one client):
     tools/calculate_jains_fairness_index.py:17-21 of the reference."""
     iso, slow = {}, []
     for i, (job, model, _) in enumerate(mix):
-        r = run_load(L, capi, [device], 60 if model != "mnist" else 300, 1, 0.2, False, 1, [1], mix=[(job, model, 1.0)])
+        r = run_load(L, capi, [device], 60 if model != "mnist" else 300, 1, 0.2, False, 1, [1], mix=[(job, model, 1.0)], gang=1, cpus=cpus)
         iso[model or job] = r.all.mean_us
         slow.append(mixed_result.per_type[i].mean_us / r.all.mean_us)
     jain = (sum(slow) ** 2) / (len(slow) * sum(x * x for x in slow))
@@ -394,27 +407,109 @@ def ipc_leg(capi, models_dir, rates=(50000, 75000, 100000)):
     return {"what": "llis_server process + llis_app_client process (open loop, Poisson), 9:1 MNIST : Inception-v3, one GPU", "points": out}
 
 
-def cpu_sample(graphs, n_mnist=9, n_inception=1, repeats=1):
-    """Oracle (CPU fp32, OpenMP over all cores) on a bounded sample of the mix; returns req/s."""
+def cpu_sample(graphs, samples=None, names=None, repeats=3):
+    """Oracle (CPU fp32, OpenMP over all cores) on a bounded sample of the mix; returns req/s of the 9:1 mix, the
+    seconds spent, the requests run and - when `samples` (sampled request slots of the GPU run) are given - the
+    comparison of the serving path's outputs with the oracle's on the same inputs."""
     # torchrun pins OMP_NUM_THREADS=1 in its workers; the CPU leg is meant to use every host core
     os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import numpy as np
     from oracle import graph as og
     og.build()
     packs = {m: og.Pack(g.to_bytes()) for m, g in graphs.items()}
+    shapes = {"mnist": (1, 28, 28), "inception_v3": (3, 299, 299)}
     rng = np.random.default_rng(0)
-    xm = rng.random((1, 28, 28), dtype=np.float32)
-    xi = rng.standard_normal((3, 299, 299), dtype=np.float32)
-    og.run(packs["mnist"], xm)
-    t0 = time.perf_counter()
-    n = 0
-    for _ in range(repeats):
-        for _ in range(n_mnist):
-            og.run(packs["mnist"], xm); n += 1
-        for _ in range(n_inception):
-            og.run(packs["inception_v3"], xi); n += 1
-    dt = time.perf_counter() - t0
-    return n / dt, dt, n
+    inputs = {"mnist": [], "inception_v3": []}
+    gpu_out = {"mnist": [], "inception_v3": []}
+    for (t, slot, x, y) in (samples or []):
+        m = names[t]
+        if m in inputs:
+            inputs[m].append(x.reshape(shapes[m])); gpu_out[m].append(y)
+    have_samples = all(len(v) > 0 for v in inputs.values())
+    if not have_samples:
+        inputs = {"mnist": [rng.random((1, 28, 28), dtype=np.float32)], "inception_v3": [rng.standard_normal((3, 299, 299), dtype=np.float32)]}
+    og.run(packs["mnist"], inputs["mnist"][0])
+    t_model, n = {}, 0
+    refs = {"mnist": [], "inception_v3": []}
+    t_all0 = time.perf_counter()
+    for m in ("mnist", "inception_v3"):
+        reps = repeats * (9 if m == "mnist" else 1)
+        t0 = time.perf_counter()
+        for r in range(reps):
+            for x in inputs[m]:
+                y = og.run(packs[m], x); n += 1
+                if r == 0:
+                    refs[m].append(y)
+        t_model[m] = (time.perf_counter() - t0) / (reps * len(inputs[m]))
+    dt = time.perf_counter() - t_all0
+    rps = 10.0 / (9 * t_model["mnist"] + t_model["inception_v3"])
+    parity = {}
+    if have_samples:
+        rel, same = {}, True
+        for m in refs:
+            worst = 0.0
+            for y, ref in zip(gpu_out[m], refs[m]):
+                worst = max(worst, float(np.abs(y - ref).max() / max(float(np.abs(ref).max()), 1e-30)))
+                same = same and int(y.argmax()) == int(ref.argmax())
+            rel[m] = worst
+        tol = {"mnist": 1e-5, "inception_v3": 1e-2}
+        parity = {"parity_checked": sum(len(v) for v in refs.values()),
+                  "parity_max_rel": {m: float(f"{v:.3g}") for m, v in rel.items()},
+                  "parity_argmax_equal": bool(same),
+                  "parity_ok": bool(same and all(rel[m] <= tol[m] for m in rel)),
+                  "parity_what": "outputs left in sampled request slots by the timed closed-loop host-buffer run vs the CPU oracle on the same "
+                                 "slot inputs; tolerance 1e-5 (MNIST, fp32) / 1e-2 of the largest logit and same argmax (Inception-v3, bf16)"}
+    return rps, dt, n, parity
+
+
+def pick_cpu(device, index):
+    """A CPU of the GPU's NUMA node for replica `index` (reads sysfs only): the i-th allowed CPU of the node's list, skipping
+    its first one.  -1 (no pinning) when the topology cannot be read."""
+    try:
+        out = subprocess.run(["nvidia-smi", "--query-gpu=index,pci.bus_id", "--format=csv,noheader"], capture_output=True, text=True, timeout=20).stdout
+        bdf = None
+        for ln in out.splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) == 2 and f[0].isdigit() and int(f[0]) == device:
+                bdf = f[1].lower()
+        if bdf is None:
+            return -1
+        if bdf.startswith("00000000:"):
+            bdf = bdf[4:]
+        txt = open(f"/sys/bus/pci/devices/{bdf}/local_cpulist").read().strip()
+        local = []
+        for part in txt.split(","):
+            a, _, b = part.partition("-")
+            local += list(range(int(a), int(b or a) + 1))
+        allowed = sorted(set(local) & set(os.sched_getaffinity(0))) or sorted(os.sched_getaffinity(0))
+        if len(allowed) < 2:
+            return -1
+        # ranks that share a node must not share a core: spread by the GPU index as well
+        return allowed[(1 + 2 * (device + index)) % len(allowed)]
+    except Exception:
+        return -1
+
+
+def granularity_sweep(args):
+    """Scheduling granularity on the same kernels: layers per scheduler stage (PB_STAGE_GROUP), one child process per
+    point because the grouping is fixed when a model is loaded.  1 = one kernel per stage with H2D / D2H copy stages,
+    the reference's protocol."""
+    pts = []
+    for g in (1, 4, 12, 24, 48):
+        env = dict(os.environ, PB_STAGE_GROUP=str(g))
+        if g == 1:
+            env["PB_COPY_STAGES"] = "1"
+        cmd = [sys.executable, os.path.abspath(__file__), "--granularity-child", str(g), "--steps", "3", "--warmup", "3",
+               "--batch", str(1000 if g == 1 else 4000), "--gang", str(1 if g == 1 else args.gang), "--concurrency", str(args.concurrency),
+               "--inception-instances", str(args.inception_instances), "--extra-kernels", str(args.extra_kernels), "--sched", args.sched]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=env)
+            pts.append(json.loads(r.stdout.strip().splitlines()[-1]) if r.returncode == 0 and r.stdout.strip() else
+                       {"layers_per_stage": g, "error": (r.stderr or "no output")[-200:]})
+        except Exception as e:      # a point that fails does not take the headline down with it
+            pts.append({"layers_per_stage": g, "error": str(e)[:200]})
+    return {"what": "closed loop, host buffers, same mix and clients; layers_per_stage = 1 also restores the H2D / D2H copy stages "
+                    "(the reference's protocol: one scheduler decision and one set of block records per kernel)", "points": pts}
 
 
 def main():
@@ -422,16 +517,16 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--batch", type=int, default=1000, help="requests per GPU per step")
-    ap.add_argument("--concurrency", type=int, default=96, help="closed-loop clients per replica")
-    ap.add_argument("--inception-instances", type=int, default=48, help="Inception-v3 instances (max outstanding) per replica")
+    ap.add_argument("--batch", type=int, default=0, help="requests per GPU per step (default 12000 for the mix, so that 20 steps last about a second)")
+    ap.add_argument("--concurrency", type=int, default=192, help="clients per replica: requests in flight at most (closed loop: always)")
+    ap.add_argument("--inception-instances", type=int, default=96, help="Inception-v3 instances (max outstanding) per replica")
     ap.add_argument("--replicas-per-gpu", type=int, default=1,
                     help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU")
     ap.add_argument("--extra-kernels", type=int, default=64, help="scheduler: over-subscribed stages allowed in flight (--extra_kernels)")
     ap.add_argument("--sched", default="full3", choices=["full3", "fifo", "fifo2"],
                     help="full3 = the kernel-level scheduler; fifo (job by job) and fifo2 (stage by stage, arrival order) are the ablations")
     ap.add_argument("--streams", type=int, default=500, help="scheduler stream pool (--num_streams); 1 with --sched fifo = single-stream baseline")
-    ap.add_argument("--gang", type=int, default=1, help="scheduler: up to this many queued requests of one model run as one launch per stage")
+    ap.add_argument("--gang", type=int, default=8, help="scheduler: up to this many queued requests of one model run as one launch per stage (1 = never)")
     ap.add_argument("--deferred", type=int, default=0, help="scheduler: 1 = dispatch loop once per batch of notifications (implied by --gang > 1)")
     ap.add_argument("--workload", default="mix", choices=sorted(WORKLOADS), help="mix = the headline (MNIST : Inception-v3 = 9 : 1)")
     ap.add_argument("--extras", action="store_true", help="also measure ring round trip and vec_add bandwidth")
@@ -439,7 +534,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--no-fairness", action="store_true", help="skip the isolated runs behind Jain's index")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the open-loop Poisson rate sweep of the mix")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the open-loop Poisson rate sweep of the mix (headline = closed loop)")
+    ap.add_argument("--no-granularity", action="store_true", help="skip the layers-per-scheduler-stage sweep (child processes)")
+    ap.add_argument("--no-membound", action="store_true", help="skip the memory-bound operator kernels on tensors larger than L2")
+    ap.add_argument("--no-pin", dest="pin", action="store_false", help="do not pin the replica threads to CPUs of their GPU's NUMA node")
+    ap.add_argument("--parity-samples", type=int, default=4, help="request slots per model whose outputs are compared with the CPU oracle")
+    ap.add_argument("--granularity-child", type=int, default=None, help=argparse.SUPPRESS)
     ap.add_argument("--layers", default="", help="write the per-layer timing table to this file")
     ap.add_argument("--only-roofline", default=None, metavar="SUBSTR",
                     help="skip the serving legs; time only the Inception-v3 stages whose name contains SUBSTR "
@@ -450,6 +550,8 @@ def main():
                          "(large: 256 MB per tensor; small: 144 MB per tensor, 3 launches each, for an ncu capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.batch <= 0:
+        args.batch = {"mix": 12000, "mnist": 20000}.get(args.workload, 1500)
     global MIX, GANG, DEFERRED
     MIX = WORKLOADS[args.workload]
     GANG, DEFERRED = args.gang, args.deferred
@@ -470,7 +572,7 @@ def main():
                "arcfaceresnet100": "ArcFace LResNet100E-IR alone, batch 1, 112x112, random He-normal weights",
                "mobilenet_resnet50": "MobileNetV2 : ResNet-50 = 1:1, batch 1, 224x224",
                "stress": "vec_add : dummy_short : dummy_long = 1:1:1 synthetic scheduler stress"}[args.workload]
-    config = {"workload": wl_text + ("; closed loop" if args.iat_us <= 0 else f"; open loop, Poisson, mean inter-arrival {args.iat_us} us per replica"),
+    config = {"workload": wl_text,
               "batch_per_step_per_replica": args.batch, "clients_per_replica": args.concurrency,
               "instances_per_replica": {names[0]: args.concurrency, **({names[-1]: args.inception_instances} if len(names) > 1 else {})},
               "scheduler": args.sched, "max_gang": args.gang, "deferred_schedule": int(args.deferred or args.gang > 1), "num_streams": args.streams, "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu,
@@ -488,9 +590,9 @@ def main():
             graphs = write_packs(d)
         times, n_per = [], 10
         for _ in range(args.warmup):
-            cpu_sample(graphs)
+            cpu_sample(graphs, repeats=1)
         for _ in range(args.steps):
-            rps, dt, n_per = cpu_sample(graphs, repeats=3)
+            rps, dt, n_per, _ = cpu_sample(graphs, repeats=3)
             times.append(dt)
         total = sum(times)
         value = n_per * len(times) / total
@@ -536,38 +638,140 @@ def main():
         print(json.dumps({"membound": membound_leg(L, capi, devices[0], args.only_membound,
                                                    10 if args.only_membound == "large" else 3)}))
         return
+    if args.granularity_child is not None:
+        # one point of the granularity sweep: closed loop through host buffers, this process's PB_STAGE_GROUP
+        r = run_load(L, capi, devices[:1], args.batch, args.steps, args.warmup, False, args.concurrency, caps,
+                     extra_kernels=args.extra_kernels, sched=args.sched, streams=args.streams, cpus=[pick_cpu(devices[0], 0)] if args.pin else None)
+        t = max(r.host_launch_us + r.host_sched_us + r.host_idle_us, 1e-9)
+        sec = r.elapsed_event_ms * 1e-3
+        mh = C.c_void_p()
+        capi.check(L.pb_model_load(os.path.join(tmp.name, packer_name("inception_v3")).encode(), devices[0], -1, C.byref(mh)), "pb_model_load")
+        stages = L.pb_model_num_groups(mh) + (2 if os.environ.get("PB_COPY_STAGES") == "1" else 0)
+        L.pb_model_destroy(mh)
+        print(json.dumps({"layers_per_stage": args.granularity_child, "inception_v3_scheduler_stages": stages, "max_gang": args.gang,
+                          "rps": round(r.all.count / sec),
+                          "mnist_p50_p99_us": [round(r.per_type[0].p50_us), round(r.per_type[0].p99_us)],
+                          "inception_v3_p50_p99_us": [round(r.per_type[1].p50_us), round(r.per_type[1].p99_us)],
+                          "decisions_per_s": round(r.decisions / sec), "records_per_s": round(r.records_consumed / sec),
+                          "host_time_share": {"launch": round(r.host_launch_us / t, 3), "sched": round(r.host_sched_us / t, 3),
+                                              "idle": round(r.host_idle_us / t, 3)}}))
+        return
     if args.only_roofline is not None:
-        roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters, args.only_roofline)
+        roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters, args.only_roofline, batch=max(1, args.gang))
         print(json.dumps({"roofline": roof, "kernel_table_inception_v3": table,
                           "layers": [(n, k, round(u, 2), nb) for (n, k, u, _, _, nb) in layers]}))
         return
 
+    cpus = None
+    if args.pin:
+        cpus = [pick_cpu(d, i) for i, d in enumerate(devices)]
+        config["replica_cpus"] = cpus
     sampler = ClockSampler()
+    load_kw = dict(extra_kernels=args.extra_kernels, sched=args.sched, streams=args.streams, cpus=cpus)
+    leg_seconds = {}
 
-    def timed(resident):
+    def leg(name, resident, iat_us, steps, seed=1, samples=0, warmup=None):
+        """One load run on every rank (barrier first); returns rank-reduced numbers."""
+        import numpy as np
         if dist:
             dist.barrier()
-        r = run_load(L, capi, devices, args.batch, args.steps, args.warmup, resident, args.concurrency, caps,
-                     iat_us=args.iat_us, extra_kernels=args.extra_kernels, sched=args.sched, streams=args.streams)
-        sums = [float(r.all.count), float(r.h2d_bytes), float(r.d2h_bytes)] + [float(r.per_type[i].count) for i in range(len(MIX))]
+        t0 = time.time()
+        out = run_load(L, capi, devices, args.batch, steps, args.warmup if warmup is None else warmup, resident, args.concurrency, caps,
+                       iat_us=iat_us, seed=seed, samples_per_type=samples, **load_kw)
+        r, smp = out if isinstance(out, tuple) else (out, [])
+        leg_seconds[name] = round(time.time() - t0, 1)
+        nt = len(MIX)
+        sums = [float(r.all.count), float(r.h2d_bytes), float(r.d2h_bytes), float(r.records_consumed), float(r.decisions)] + \
+               [float(r.per_type[i].count) for i in range(nt)]
         ms, sums = reduce_over_ranks(dist, r.elapsed_event_ms, sums)
-        return r, sums[0], ms, sums[3:], sums[1], sums[2]
+        # per-model tails: the worst rank's (an SLO has to hold on every GPU)
+        p99 = [r.per_type[i].p99_us for i in range(nt)]
+        p50 = [r.per_type[i].p50_us for i in range(nt)]
+        mean = [r.per_type[i].mean_us for i in range(nt)]
+        per_rank = None
+        if dist:
+            import torch
+            t = torch.tensor(p99 + p50, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            p99, p50 = [float(v) for v in t[:nt]], [float(v) for v in t[nt:]]
+            tt = max(r.host_launch_us + r.host_sched_us + r.host_idle_us, 1e-9)
+            mine = torch.tensor([r.all.count / (r.elapsed_event_ms * 1e-3), r.host_launch_us / tt, r.host_sched_us / tt, r.host_idle_us / tt],
+                                dtype=torch.float64)
+            allr = [torch.zeros(4, dtype=torch.float64) for _ in range(world)]
+            dist.all_gather(allr, mine)
+            per_rank = [{"rps": round(float(a[0])), "launch": round(float(a[1]), 3), "sched": round(float(a[2]), 3), "idle": round(float(a[3]), 3)}
+                        for a in allr]
+        return {"r": r, "n": sums[0], "ms": ms, "rps": sums[0] / (ms * 1e-3), "h2d": sums[1], "d2h": sums[2], "records": sums[3],
+                "decisions": sums[4], "counts": sums[5:], "p99": p99, "p50": p50, "mean": mean, "samples": smp, "per_rank": per_rank}
+
+    slo = {"inception_v3_p99_ms": 5.0, "mnist_p99_ms": 1.0}
+    is_mix = args.workload == "mix"
+
+    def meets_slo(x):
+        return (not is_mix) or (x["p99"][1] <= slo["inception_v3_p99_ms"] * 1e3 and x["p99"][0] <= slo["mnist_p99_ms"] * 1e3)
+
+    def point(x, offered=None):
+        d = {"achieved_rps": round(x["rps"]), "slo_met": bool(meets_slo(x))}
+        if offered is not None:
+            d["offered_rps"] = round(offered)
+        for i, nm in enumerate(names):
+            d[f"{nm}_p50_p99_us"] = [round(x["p50"][i]), round(x["p99"][i])]
+        return d
 
     if rank == 0:
         sampler.start()
-    r_dev, n_dev, ms_dev, k_dev, _, _ = timed(resident=True)
-    r_e2e, n_e2e, ms_e2e, k_e2e, h2d, d2h = timed(resident=False)
+    # ---- closed loop: the capacity of the serving path, inputs resident in HBM and through host buffers ----
+    closed_dev = leg("closed_resident", True, 0.0, args.steps)
+    closed_e2e = leg("closed_e2e", False, 0.0, args.steps, samples=args.parity_samples if rank == 0 else 0)
+    open_loop = args.iat_us > 0 or (is_mix and not args.no_sweep)
+    sweep_pts = []
+    head_dev, head_e2e = closed_dev, closed_e2e
+    if args.iat_us > 0:
+        head_dev = leg("poisson_resident", True, args.iat_us, args.steps, seed=7)
+        head_e2e = leg("poisson_e2e", False, args.iat_us, args.steps, seed=7)
+    elif open_loop:
+        # ---- open loop (the configuration's arrivals): Poisson at fractions of the closed-loop rate, highest first; the
+        # headline is the highest offered rate whose per-model p99s stay inside the SLO (the first failing point
+        # above it brackets the knee).  Every point is a full K-step run timed like the others. ----
+        def sweep(resident, cap_rps, tag):
+            best = None
+            for frac in (1.05, 1.0, 0.95, 0.9, 0.8, 0.7, 0.5):
+                offered = frac * cap_rps
+                x = leg(f"poisson_{tag}_{frac}", resident, 1e6 * n_gpus * args.replicas_per_gpu / offered, args.steps, seed=7)
+                sweep_pts.append(dict(point(x, offered), inputs=tag, fraction_of_closed_loop=frac))
+                if meets_slo(x) and x["rps"] >= 0.97 * offered:
+                    best = x
+                    break
+            return best
+        b = sweep(False, closed_e2e["rps"], "host_buffers")
+        if b is not None:
+            head_e2e = b
+        b = sweep(True, closed_dev["rps"], "resident")
+        if b is not None:
+            head_dev = b
     clocks = sampler.stop(set(range(n_gpus))) if rank == 0 else None
+
+    fairness = None
+    if args.workload in ("mix", "mobilenet_resnet50") and not args.no_fairness:
+        # every rank measures its own GPU: isolated mean latency per model, then Jain's index over the slowdowns
+        t0 = time.time()
+        f = fairness_leg(L, capi, devices[0], MIX, head_e2e["r"], cpus=cpus[:1] if cpus else None)
+        leg_seconds["fairness"] = round(time.time() - t0, 1)
+        if dist:
+            import torch
+            allj = [torch.zeros(1, dtype=torch.float64) for _ in range(world)]
+            dist.all_gather(allj, torch.tensor([f["jain_index"]], dtype=torch.float64))
+            f["jain_index_per_gpu"] = [round(float(a[0]), 4) for a in allj]
+            f["jain_index"] = round(min(f["jain_index_per_gpu"]), 4)
+        fairness = f
 
     if rank != 0:
         dist.barrier()
         return
 
-    value = n_dev / (ms_dev * 1e-3)
-    e2e = n_e2e / (ms_e2e * 1e-3)
     # kernels of ours inside the timed region: every measured request runs all launches of its model's plan
     # (a stage group replayed as a CUDA graph still launches each of its kernels on the device; independent
-    # tensor-core convolutions that share a launch count once)
+    # tensor-core convolutions that share a launch count once; the requests of a gang share their launches)
     kernels_per_request = {}
     layers_per_request = {}
     for job, model, _ in MIX:
@@ -584,70 +788,69 @@ def main():
         kernels_per_request[model] = (n_launches, n_groups)
         layers_per_request[model] = n_stages
         L.pb_model_destroy(mh)
-    counts = k_dev          # measured requests per model, summed over GPUs
-    gpu_launches = int(sum(c * kernels_per_request[m or j][0] for c, (j, m, _) in zip(counts, MIX)))
+    counts = head_dev["counts"]          # measured requests per model, summed over GPUs
+    # dispatches the schedulers made = stage launches; launches per stage from the plan (gangs make fewer dispatches)
+    stages_if_alone = sum(c * kernels_per_request[m or j][1] for c, (j, m, _) in zip(counts, MIX))
+    launches_if_alone = sum(c * kernels_per_request[m or j][0] for c, (j, m, _) in zip(counts, MIX))
+    gpu_launches = int(launches_if_alone * head_dev["decisions"] / max(stages_if_alone, 1))
     config["kernels_per_request"] = {m: k[0] for m, k in kernels_per_request.items()}
     config["layers_per_request"] = layers_per_request
     config["scheduler_stages_per_request"] = {m: k[1] for m, k in kernels_per_request.items()}
+    config["mean_gang_size"] = round(stages_if_alone / max(head_dev["decisions"], 1), 2)
+    config["slo"] = slo
+    config["arrivals"] = ("closed loop" if head_e2e is closed_e2e else "Poisson (exponential inter-arrival), latency = completion - scheduled arrival; "
+                          "headline = highest offered rate of the sweep whose per-model p99s meet the SLO")
 
-    def lat(r):
+    def lat(x):
+        r = x["r"]
         d = {"all": r.all.as_dict()}
         for i, nm in enumerate(names):
             d[nm] = r.per_type[i].as_dict()
         return d
 
-    slo = {"inception_v3_p99_ms": 5.0, "mnist_p99_ms": 1.0}
-    config["slo"] = slo
-    slo_met = args.workload != "mix" or (r_e2e.per_type[1].p99_us <= slo["inception_v3_p99_ms"] * 1e3 and
-                                         r_e2e.per_type[0].p99_us <= slo["mnist_p99_ms"] * 1e3)
-    line = {"metric": METRIC if args.workload == "mix" else f"requests/s, {args.workload}", "slo_met": bool(slo_met),
-            "value": round(value, 2), "unit": "req/s",
-            "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3),
+    r_e2e = head_e2e["r"]
+    host_t = max(r_e2e.host_launch_us + r_e2e.host_sched_us + r_e2e.host_idle_us, 1e-9)
+    line = {"metric": METRIC if is_mix else f"requests/s, {args.workload}", "slo_met": bool(meets_slo(head_e2e)),
+            "value": round(head_dev["rps"], 2), "unit": "req/s",
+            "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(head_dev["ms"] / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config, "clocks": clocks, "gpu_launches": gpu_launches,
-            "e2e": {"value": round(e2e, 2), "unit": "req/s", "h2d_bytes_per_step": int(h2d / args.steps),
-                    "d2h_bytes_per_step": int(d2h / args.steps), "ms_per_step": round(ms_e2e / args.steps, 3),
-                    "latency_us": lat(r_e2e)},
-            "latency_us": lat(r_dev),
+            "e2e": {"value": round(head_e2e["rps"], 2), "unit": "req/s", "h2d_bytes_per_step": int(head_e2e["h2d"] / args.steps),
+                    "d2h_bytes_per_step": int(head_e2e["d2h"] / args.steps), "ms_per_step": round(head_e2e["ms"] / args.steps, 3),
+                    "latency_us": lat(head_e2e)},
+            "latency_us": lat(head_dev),
+            "closed_loop": {"resident": point(closed_dev), "host_buffers": point(closed_e2e)},
             "timing": "CUDA events on each GPU around the measured requests (device idle on both sides), max over GPUs",
-            "records_consumed": int(r_dev.records_consumed), "decisions": int(r_dev.decisions),
-            "scheduler_decisions_per_s": round(r_dev.decisions / (ms_dev * 1e-3)),
-            "notification_records_per_s": round(r_dev.records_consumed / (ms_dev * 1e-3)),
-            # this rank's replica threads during the e2e leg: share of their time inside CUDA launch calls, in
+            "records_consumed": int(head_dev["records"]), "decisions": int(head_dev["decisions"]),
+            "scheduler_decisions_per_s": round(head_dev["decisions"] / (head_dev["ms"] * 1e-3)),
+            "notification_records_per_s": round(head_dev["records"] / (head_dev["ms"] * 1e-3)),
+            # rank 0's replica threads during the e2e leg: share of their time inside CUDA launch calls, in
             # notification handling + scheduling, and polling with nothing to do (GPU-bound when large)
-            "host_time_share": (lambda t: {"launch": round(r_e2e.host_launch_us / t, 3), "sched": round(r_e2e.host_sched_us / t, 3),
-                                           "idle": round(r_e2e.host_idle_us / t, 3)})(
-                max(r_e2e.host_launch_us + r_e2e.host_sched_us + r_e2e.host_idle_us, 1e-9)),
-            "per_replica_rps": {"resident": [round(r_dev.per_gpu_rps[i]) for i in range(len(devices))],
-                                "e2e": [round(r_e2e.per_gpu_rps[i]) for i in range(len(devices))]}}
+            "host_time_share": {"launch": round(r_e2e.host_launch_us / host_t, 3), "sched": round(r_e2e.host_sched_us / host_t, 3),
+                                "idle": round(r_e2e.host_idle_us / host_t, 3)},
+            "leg_seconds": leg_seconds}
+    if head_e2e["per_rank"]:
+        line["per_rank_e2e"] = head_e2e["per_rank"]
+    if sweep_pts:
+        line["poisson_sweep"] = {"arrivals": "Poisson, exponential inter-arrival, latency = completion - scheduled arrival; points in the order run "
+                                             "(highest offered rate first, stopping at the first that meets the SLO and keeps up)",
+                                 "points": sweep_pts}
+    if fairness:
+        line["fairness"] = fairness
 
-    if args.workload in ("mix", "mobilenet_resnet50") and not dist and not args.no_fairness:
-        line["fairness"] = fairness_leg(L, capi, devices[0], MIX, r_e2e)
-    if args.workload == "mix" and not dist and args.iat_us <= 0 and not args.no_sweep:
-        # Open loop: Poisson arrivals at fractions of the closed-loop rate, through host buffers; the highest
-        # offered rate whose p99s stay inside the SLO is the "requests/s at p99 SLO" of an open system.
-        sweep, best = [], None
-        for frac in (0.5, 0.7, 0.8, 0.9):
-            rate = frac * e2e
-            r = run_load(L, capi, devices, args.batch, max(2, args.steps // 2), 1, False, args.concurrency, caps,
-                         iat_us=1e6 * len(devices) / rate, extra_kernels=args.extra_kernels, sched=args.sched, streams=args.streams, seed=7)
-            ok = r.per_type[1].p99_us <= slo["inception_v3_p99_ms"] * 1e3 and r.per_type[0].p99_us <= slo["mnist_p99_ms"] * 1e3
-            sweep.append({"offered_rps": round(rate), "achieved_rps": round(r.throughput_rps), "slo_met": bool(ok),
-                          "mnist_p50_p99_us": [round(r.per_type[0].p50_us), round(r.per_type[0].p99_us)],
-                          "inception_v3_p50_p99_us": [round(r.per_type[1].p50_us), round(r.per_type[1].p99_us)]})
-            if ok:
-                best = round(rate)
-        line["poisson_sweep"] = {"arrivals": "Poisson, exponential inter-arrival, latency = completion - scheduled arrival",
-                                 "points": sweep, "max_offered_rps_meeting_slo": best}
-    if args.extras and not dist and args.workload == "mix":
+    if is_mix and not dist and not args.no_granularity:
+        # ---- scheduling granularity: layers per scheduler stage (1 = the reference's kernel-by-kernel release) ----
+        t0 = time.time()
+        line["granularity_sweep"] = granularity_sweep(args)
+        leg_seconds["granularity_sweep"] = round(time.time() - t0, 1)
+    if args.extras and not dist and is_mix:
         # Job-event timeline of a short e2e run (the server records it when PB_PROFILE_PREFIX is set) and the
         # reference's overhead stack computed from it, per model (MNIST = 1 scheduler stage per request).
         from paella_b200 import overhead_stack as ost
         prefix = os.path.join(tmp.name, "timeline")
         os.environ["PB_PROFILE_PREFIX"] = prefix
         try:
-            run_load(L, capi, devices[:1], 4000, 1, 0.25, False, args.concurrency, caps, extra_kernels=args.extra_kernels,
-                     sched=args.sched, streams=args.streams, seed=11)
+            run_load(L, capi, devices[:1], 4000, 1, 0.25, False, args.concurrency, caps, seed=11, **load_kw)
         finally:
             del os.environ["PB_PROFILE_PREFIX"]
         jobs = ost.read_job_events(prefix + "_job_events.txt")
@@ -662,29 +865,39 @@ def main():
                                   "mnist": ost.overhead_stack(jobs, stages=1), "inception_v3": ost.overhead_stack(jobs, stages=n_inc_stages)}
     if args.extras and not dist:
         line["extras"] = extras_leg(L, capi, devices[0])
-        line["extras"]["membound"] = membound_leg(L, capi, devices[0])
-        if args.workload == "mix":
+        if is_mix:
             line["extras"]["ipc"] = ipc_leg(capi, tmp.name)
-    if n_gpus == 1 and not args.no_roofline and args.workload == "mix":
-        roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters)
+    if n_gpus == 1 and not dist and not args.no_membound:
+        t0 = time.time()
+        line["membound"] = membound_leg(L, capi, devices[0], "large", 5)
+        leg_seconds["membound"] = round(time.time() - t0, 1)
+    if n_gpus == 1 and not args.no_roofline and is_mix:
+        t0 = time.time()
+        roof, table, layers = roofline_leg(L, capi, tmp.name, args.iters, batch=max(1, args.gang))
         # The same kernel while the GPU serves the whole mix: tensor-core convolution FLOPs retired per second of
         # the timed region (many launches of many requests overlap, so there is no per-launch duration here).
-        conv_flops = sum(fl for (_, k, _, fl, _, _) in layers if k == "conv_umma")
-        inc_rps = counts[1] / (ms_dev * 1e-3)
+        conv_flops = sum(fl for (_, k, _, fl, _, _) in layers if k == "conv_umma") / max(1, args.gang)
+        inc_rps = closed_dev["counts"][1] / (closed_dev["ms"] * 1e-3)
         roof["under_load"] = {"achieved": round(conv_flops * inc_rps / 1e12, 2), "unit": "TFLOP/s",
                               "frac": round(conv_flops * inc_rps / 1e12 / roof["peak"], 4),
-                              "inception_v3_per_s": round(inc_rps, 1), "conv_flops_per_request": int(conv_flops)}
+                              "inception_v3_per_s": round(inc_rps, 1), "conv_flops_per_request": int(conv_flops),
+                              "leg": "closed loop, inputs resident"}
         line["roofline"] = roof
         line["kernel_table_inception_v3"] = table
+        leg_seconds["roofline"] = round(time.time() - t0, 1)
         if args.layers:
             with open(args.layers, "w") as f:
                 f.write("stage\tkind\tus\tflops\tbytes\tblocks\tTFLOP/s\tGB/s\n")
                 for (nm, k, us, fl, by, nb) in layers:
                     f.write(f"{nm}\t{k}\t{us:.2f}\t{fl}\t{by}\t{nb}\t{fl / us / 1e6:.3f}\t{by / us / 1e3:.1f}\n")
-        rps, dt, n = cpu_sample(graphs, repeats=12)
+        # ---- CPU baseline + output check: the oracle runs the sampled request slots' own inputs ----
+        t0 = time.time()
+        rps, dt, n, parity = cpu_sample(graphs, closed_e2e["samples"], names)
+        leg_seconds["cpu_baseline"] = round(time.time() - t0, 1)
         line["cpu_baseline"] = {"value": round(rps, 3), "unit": "req/s", "cores": os.cpu_count(), "kind": "port",
-                                "sample": f"{n} requests (9:1 MNIST : Inception-v3) by the CPU oracle, fp32, OpenMP on all "
-                                          f"host cores, {dt:.1f} s"}
+                                "sample": f"{n} requests (9:1 MNIST : Inception-v3, the inputs of request slots of the timed host-buffer run) "
+                                          f"by the CPU oracle, fp32, OpenMP on all host cores, {dt:.1f} s"}
+        line.update(parity)
     print(json.dumps(line))
     if dist:
         dist.barrier()

@@ -276,6 +276,9 @@ PB_API int pb_instance_launch_group_batched(pb_instance* inst, int group, int ba
 /* Convenience for tests: H2D of `batch` inputs (back to back), the model kernel by kernel (by_groups = 0) or
  * group by group, D2H of the `batch` outputs, then synchronise. */
 PB_API int pb_instance_run_batch_sync(pb_instance* inst, int batch, int by_groups, const float* inputs_host, float* outputs_host);
+/* The operator parameters (device pointers resolved, batch set) stage `stage` of the instance is launched with for a
+ * gang of `batch`: what pb_op_launch / pb_conv_umma_time take, for layer-by-layer measurements. */
+PB_API int pb_instance_stage_params(pb_instance* inst, int stage, int batch, pb_op_params* out);
 PB_API int pb_instance_time_stage_batched(pb_instance* inst, int stage, int batch, int iters, size_t flush_bytes, double* us_out);
 /* Convenience for tests: H2D, every group, D2H on one stream, then synchronise. */
 PB_API int pb_instance_run_groups_sync(pb_instance* inst, const float* input_host, float* output_host);

@@ -144,6 +144,7 @@ SIGNATURES = {
     "pb_model_stage_info_batched": (_I, [_VP, _I, _I, C.POINTER(LaunchInfo)]),
     "pb_instance_launch_group_batched": (_I, [_VP, _I, _I, _VP, _U32, _VP, _PP, _PP]),
     "pb_instance_run_batch_sync": (_I, [_VP, _I, _I, _VP, _VP]),
+    "pb_instance_stage_params": (_I, [_VP, _I, _I, C.POINTER(OpParams)]),
     "pb_instance_time_stage_batched": (_I, [_VP, _I, _I, _I, _SZ, C.POINTER(C.c_double)]),
     "pb_model_load": (_I, [C.c_char_p, _I, _I, _PP]),
     "pb_model_destroy": (None, [_VP]),

@@ -705,17 +705,25 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
         bool ok = true;
         int st = 0;
         uint32_t parity = 1u;                     // a fresh barrier passes a wait on the "previous" phase
+        // which (stage, operand) pairs are this thread's (bit st), and the filter tap / channel chunk of the k-block,
+        // carried along: a division per k-block is a tenth of what the thread has per copy
+        uint32_t mask_a = 0, mask_b = 0;
+        for (int q = 0; q < stages; ++q) {
+            if ((q * 2) % kProducers == prod) mask_a |= 1u << q;
+            if ((q * 2 + 1) % kProducers == prod) mask_b |= 1u << q;
+        }
+        int tap = kb_begin / cpt, chunk = kb_begin - tap * cpt;
+        int r = tap / a.S, s = tap - r * a.S;
+        uint32_t* const err_flag = a.err_flag;
         for (int kb = 0; kb < nkb && ok; ++kb) {
-            const bool mine_a = (st * 2) % kProducers == prod, mine_b = (st * 2 + 1) % kProducers == prod;
+            const bool mine_a = (mask_a >> st) & 1u, mine_b = (mask_b >> st) & 1u;
             if (mine_a || mine_b) {
-                ok = mbar_wait(smem_u32(&s_empty[st]), parity, s_abort, a.err_flag, 1u);
+                ok = mbar_wait(smem_u32(&s_empty[st]), parity, s_abort, err_flag, 1u);
                 if (!ok) break;
                 const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
                 const uint32_t bar = smem_u32(&s_full[st]);
                 const int kbg = kb_begin + kb;
                 if (mine_a) {
-                    const int tap = kbg / cpt, chunk = kbg - tap * cpt;
-                    const int r = tap / a.S, s = tap - r * a.S;
                     mbar_arrive_expect_tx(bar, (uint32_t)kATileBytes + a.b_stage_bytes);
                     if (a.a_tiled) tma_load_2d(a_tile, tmap_x, chunk * kBK, m0, bar);
                     else tma_load_im2col_4d(a_tile, tmap_x, chunk * kBK, w0, h0, img, (uint16_t)(s * a.dw), (uint16_t)(r * a.dh), bar);
@@ -723,6 +731,10 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
                     PB_TK(kb, 0);
                 }
                 if (mine_b) tma_load_2d(a_tile + kATileBytes, tmap_w, kbg * kBK, n0, bar);
+            }
+            if (++chunk == cpt) {
+                chunk = 0;
+                if (++s == a.S) { s = 0; ++r; }
             }
             if (++st == stages) { st = 0; parity ^= 1u; }
         }
@@ -738,26 +750,37 @@ __device__ __forceinline__ void conv_tile_tma(const CUtensorMap* tmap_w, const C
         griddep_launch();
     } else {
         // ===== MMA issuer: one thread =====
+        // This thread's own instruction chain per k-block paces the CTA (measured: four MMA issues + commit ~320
+        // clocks, most of it the tensor cores taking the instructions, then ~400 clocks until the next k-block's
+        // barrier had been looked at; an mbarrier wait costs ~170 clocks even when its phase is long complete).
+        // So the NEXT k-block's barrier is probed (test_wait, never blocks) before this k-block's MMAs are issued:
+        // the probe's latency runs under them; and the descriptors are stage 0's plus a stride.
         if (lane == 0) {
-            int st = 0;
-            uint32_t parity = 0u;
-            bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                ok = mbar_wait(smem_u32(&s_full[st]), parity, s_abort, a.err_flag, 2u);
-                if (!ok) break;
+            uint32_t st = 0, parity = 0u;
+            bool ok = true, have_next = false;
+            uint32_t* const err_flag = a.err_flag;
+            const uint32_t idesc = a.idesc;
+            const uint64_t desc_a0 = umma_desc_sw128(smem_base), desc_b0 = umma_desc_sw128(smem_base + kATileBytes);
+            const uint64_t desc_step = (uint64_t)(stage_bytes >> 4);      // address field counts 16-byte units; no carry out of its 14 bits
+            for (int kb = 0; kb < nkb; ++kb) {
+                if (!have_next) {
+                    ok = mbar_wait(smem_u32(&s_full[st]), parity, s_abort, err_flag, 2u);
+                    if (!ok) break;
+                }
                 if (kb == 0) { PB_T(3); PB_S(3); }
                 PB_TK(kb, 1);
                 tcgen05_fence_after();
-                const uint32_t a_tile = smem_base + (uint32_t)st * stage_bytes;
-                const uint32_t b_tile = a_tile + kATileBytes;
+                uint32_t st_n = st + 1, parity_n = parity;
+                if (st_n == (uint32_t)stages) { st_n = 0; parity_n ^= 1u; }
+                have_next = kb + 1 < nkb && mbar_test_wait(smem_u32(&s_full[st_n]), parity_n);
+                const uint64_t da = desc_a0 + (uint64_t)st * desc_step, db = desc_b0 + (uint64_t)st * desc_step;
 #pragma unroll
-                for (int k = 0; k < kBK / 16; ++k) {
-                    tcgen05_mma_bf16(tmem_base, umma_desc_sw128(a_tile + k * 32), umma_desc_sw128(b_tile + k * 32), a.idesc,
-                                     (kb > 0 || k > 0) ? 1u : 0u);
-                }
+                for (int k = 0; k < kBK / 16; ++k)
+                    tcgen05_mma_bf16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);   // +32 bytes per K=16 slice
                 tcgen05_commit(smem_u32(&s_empty[st]));
                 PB_TK(kb, 2);
-                if (++st == stages) { st = 0; parity ^= 1u; }
+                st = st_n;
+                parity = parity_n;
             }
             PB_S(4);
             if (ok) tcgen05_commit(smem_u32(s_accum));
@@ -1219,13 +1242,14 @@ int max_bn() {
     return v;
 }
 
-// Model launches run the persistent kernel (a CTA walks several tiles) unless PB_CONV_PERSIST=0.
+// PB_CONV_PERSIST=1: model launches run the persistent kernel (a CTA walks several tiles).  Off by default.
+// Measured on B200: a lone Inception-v3 request 723 -> 604 us (3 tiles per CTA: 868 us), Inception-v3 alone with 96
+// requests in flight 26.5k -> 27.4k req/s, but the headline mix (MNIST : Inception-v3 = 9 : 1, 96 clients, gangs of 4)
+// 242k -> 221k req/s: its 108 KB CTAs leave an SM no room for anything else, and fewer, longer CTAs per launch lengthen
+// every request's chain of launches, which is what the mix runs out of first.
 bool persist_enabled() {
-    static const bool v = [] {
-        const char* e = getenv("PB_CONV_PERSIST");
-        return !(e && e[0] == '0') && use_tma_a();
-    }();
-    return v;
+    const char* e = getenv("PB_CONV_PERSIST");      // read at every use: a model keeps what it was loaded with
+    return e && e[0] == '1' && use_tma_a();
 }
 // Tiles a persistent CTA is given (PB_CONV_TILES_PER_CTA): more tiles per CTA spread the per-CTA costs thinner
 // and leave SM slots to the other requests in flight; fewer tiles per CTA finish a lone launch sooner.

@@ -1101,6 +1101,15 @@ int pb_instance_read_tensor(pb_instance* in, int tensor, float* dst, size_t dst_
     return PB_OK;
 }
 
+int pb_instance_stage_params(pb_instance* in, int stage, int batch, pb_op_params* out) {
+    PB_REQUIRE(in && out && stage >= 0 && stage < (int)in->m->stages.size(), "pb_instance_stage_params: bad stage %d", stage);
+    Variant* v = nullptr;
+    const int rc = ensure_variant(in, batch, &v);
+    if (rc != PB_OK) return rc;
+    *out = v->params[(size_t)stage];
+    return PB_OK;
+}
+
 int pb_instance_time_stage_batched(pb_instance* in, int stage, int batch, int iters, size_t flush_bytes, double* us_out) {
     PB_REQUIRE(in && us_out && iters > 0 && stage >= 0 && stage < (int)in->m->stages.size(), "pb_instance_time_stage: bad arguments");
     PB_CUDA(cudaSetDevice(in->m->device));

@@ -58,7 +58,7 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
 struct ConvUmmaMulti;
 bool conv_umma_multi_available();
 // Model launches of tensor-core convolutions go through ConvUmmaMulti tables (one entry for a lone convolution);
-// when the persistent kernel is on (default; PB_CONV_PERSIST=0 turns it off) a launch of T tiles runs
+// when the persistent kernel is on (PB_CONV_PERSIST=1 when the model is loaded; off by default) a launch of T tiles runs
 // conv_umma_persist_grid(T) CTAs, which is what conv_umma_multi_info reports and what notifies.
 bool conv_umma_persist_enabled();
 uint32_t conv_umma_persist_grid(uint32_t total_tiles);

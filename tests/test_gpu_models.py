@@ -266,11 +266,7 @@ def test_stage_groups_replayed_as_graphs_give_the_same_bits(models_dir, model, p
                 assert len([x for x in launch if x == l_idx]) == 1 or si.kind == 2  # PB_STAGE_CONV_UMMA
                 last_blocks += si.num_blocks
                 last_kinds.add(si.kind)
-        if last_kinds == {capi.STAGE_CONV_UMMA}:
-            # tensor-core launches of a stage graph run the persistent kernel: three tiles per CTA by default
-            assert li.num_blocks == -(-last_blocks // 3)
-        else:
-            assert li.num_blocks == last_blocks
+        assert li.num_blocks == last_blocks
     assert covered == n_stages
     if model == "inception_v3":
         assert n_fused >= 40        # the branches of every Inception block share launches
@@ -280,3 +276,47 @@ def test_stage_groups_replayed_as_graphs_give_the_same_bits(models_dir, model, p
         np.testing.assert_array_equal(m.run_groups(x), ref)
         np.testing.assert_array_equal(m.run_groups(x), ref)
     m.close()
+
+
+def test_persistent_convolution_kernel_in_the_stage_graphs(tmp_path, monkeypatch):
+    """PB_CONV_PERSIST=1 when the model is loaded: every tensor-core launch of the stage graphs runs the persistent kernel
+    (a CTA walks three tiles, two accumulators in tensor memory).  Same arithmetic per output element, so with the
+    reduction split switched off the logits are the bits of the kernel-by-kernel run (which uses the one-tile kernel),
+    for one request and for a gang; the last group declares a third of the tiles as blocks."""
+    d = tmp_path / "models_persist"           # own directory and load: the choice is made when a model is loaded
+    d.mkdir()
+    packer.write_all(str(d), ["inception_v3"])
+    path = os.path.join(str(d), packer.pack_file_name("inception_v3"))
+    L = capi.load()
+    L.pb_set_conv_split_gain_us(1e9)
+    try:
+        plain = Model(path, 1)
+        x = make_input("inception_v3")
+        want = plain.run(x)
+        li0 = capi.LaunchInfo()
+        g_mid = 1                                  # a group that ends in a tensor-core convolution
+        capi.check(L.pb_model_group_info(plain.m, g_mid, C.byref(li0)), "group info")
+        plain.close()
+        monkeypatch.setenv("PB_CONV_PERSIST", "1")
+        m, inst = C.c_void_p(), C.c_void_p()
+        capi.check(L.pb_model_load(path.encode(), 0, 1, C.byref(m)), "pb_model_load")
+        capi.check(L.pb_instance_create_batched(m, 3, 0, C.byref(inst)), "pb_instance_create_batched")
+        li1 = capi.LaunchInfo()
+        capi.check(L.pb_model_group_info(m, g_mid, C.byref(li1)), "group info")
+        assert li1.num_blocks == -(-li0.num_blocks // 3)       # a third of the tiles as CTAs: that many blocks notify
+        xs = np.stack([x, make_input("inception_v3", 6), make_input("inception_v3", 7)]).astype(np.float32)
+        y = np.zeros((3, 1000), np.float32)
+        capi.check(L.pb_instance_run_batch_sync(inst, 1, 1, xs.ctypes.data, y.ctypes.data), "one request, graphs")
+        assert gu.error_flag() == 0
+        np.testing.assert_array_equal(y[0], want)
+        y3 = np.zeros((3, 1000), np.float32)
+        capi.check(L.pb_instance_run_batch_sync(inst, 3, 1, xs.ctypes.data, y3.ctypes.data), "gang of three, graphs")
+        assert gu.error_flag() == 0
+        np.testing.assert_array_equal(y3[0], want)
+        ref = GOLDEN["inception_v3"]
+        assert float(np.abs(y3[0] - ref).max()) <= 1e-2 * float(np.abs(ref).max())
+        assert not np.array_equal(y3[1], y3[0])
+        L.pb_instance_destroy(inst)
+        L.pb_model_destroy(m)
+    finally:
+        L.pb_set_conv_split_gain_us(-1.0)

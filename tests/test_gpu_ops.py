@@ -133,6 +133,7 @@ def test_conv_umma(case):
 def test_conv_umma_persistent_kernel(case, monkeypatch, tiles_per_cta):
     """The kernel the model launches use (a CTA walks several tiles, two accumulators in tensor memory, three
     producer threads), on the same shapes, alone and with the split reduction where the shape splits."""
+    monkeypatch.setenv("PB_CONV_PERSIST", "1")
     monkeypatch.setenv("PB_CONV_PERSIST_OPS", "1")
     monkeypatch.setenv("PB_CONV_TILES_PER_CTA", tiles_per_cta)
     _run_conv(capi.STAGE_CONV_UMMA, 1, *case, act=1, residual=(case[3] % 64 == 0))
