@@ -28,6 +28,11 @@ class Context {
     // Gangs.  max_gang: how many jobs of one type the server's scheduler may run as one launch per stage
     // (1 = never; a plugin sizes its buffers for it at full_init).  get_gang: during run_next() of a gang's
     // leader, the other members (same type, same stage, their io_ptr given at init()); NULL / 0 otherwise.
+    // The server on whose behalf the plugin is being called (an opaque token; NULL outside a server).  A plugin that
+    // exports `extern "C" void pb_plugin_release(void* owner)` is called with it when that server is destroyed and
+    // may free what its jobs of that server hold on the device.
+    static void* get_owner();
+    static void set_owner(void* owner);
     static unsigned max_gang();
     static void set_max_gang(unsigned n);
     static Job* const* get_gang(unsigned* num_followers);

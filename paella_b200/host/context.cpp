@@ -17,6 +17,7 @@ thread_local Job* t_current_job = nullptr;
 thread_local ipc::Gpu2SchedChannel* t_channel = nullptr;
 thread_local int t_device = 0;
 thread_local bool t_device_resident = false;
+thread_local void* t_owner = nullptr;
 thread_local unsigned t_max_gang = 1;
 thread_local Job* const* t_gang = nullptr;
 thread_local unsigned t_gang_n = 0;
@@ -30,6 +31,8 @@ int Context::get_device() { return t_device; }
 void Context::set_device(int device) { t_device = device; }
 bool Context::device_resident() { return t_device_resident; }
 void Context::set_device_resident(bool v) { t_device_resident = v; }
+void* Context::get_owner() { return t_owner; }
+void Context::set_owner(void* owner) { t_owner = owner; }
 unsigned Context::max_gang() { return t_max_gang; }
 void Context::set_max_gang(unsigned n) { t_max_gang = n >= 1 ? n : 1; }
 Job* const* Context::get_gang(unsigned* num_followers) {

@@ -18,6 +18,12 @@ pb_server::~pb_server() {
     cudaSetDevice(device);
     cudaDeviceSynchronize();
     if (!profile_prefix.empty()) profiler_save(profile_prefix);
+    // plugins that can give back what their instances of this server hold on the device
+    for (auto& t : types) {
+        if (!t->dl_handle) continue;
+        typedef void (*release_t)(void*);
+        if (release_t fn = (release_t)dlsym(t->dl_handle, "pb_plugin_release")) fn(this);
+    }
     for (cudaStream_t s : streams) cudaStreamDestroy(s);
     if (notifiers_raw) llis::job::FinishedBlockNotifier::free_array(notifiers_raw);
     // Plugin instances are never destroyed (their class has no virtual destructor in the
@@ -133,6 +139,7 @@ int pb_server::launch(uint32_t job_ref_id, void* io_ptr, uint64_t cookie, llis::
     Context::set_device(device);
     Context::set_device_resident(cfg.device_resident != 0);
     Context::set_max_gang(cfg.max_gang > 1 ? cfg.max_gang : 1);
+    Context::set_owner(this);
     job->set_remote_ptr((void*)(uintptr_t)cookie);
     if (fresh) {
         job->set_client_details(client_id, t.id);

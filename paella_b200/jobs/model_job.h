@@ -59,6 +59,7 @@ class ModelJob : public llis::job::Job {
         if (cap_ < 1) cap_ = 1;
         // every gang size is prepared now (descriptors, graphs): nothing is built on the serving path
         if (pb_instance_create_batched(model, cap_, 1, &inst_) != PB_OK) { set_error(PB_ERR_CUDA); return; }
+        remember(llis::job::Context::get_owner(), inst_);
         const int n = pb_model_num_groups(model);
         decls_.resize((size_t)n * (size_t)cap_);          // [group][gang size - 1]
         for (int i = 0; i < n; ++i)
@@ -147,6 +148,36 @@ class ModelJob : public llis::job::Job {
         if (next_ == total - 1) set_pre_notify();
     }
 
+    // Instances by the server that owns them: the job objects themselves are never destroyed (the plugin ABI has no
+    // virtual destructor and the reference pools instances for ever, src/server/registered_job.cpp:91-93), but a
+    // server that goes away gives the device memory of its instances back through pb_plugin_release().
+    static std::map<void*, std::vector<pb_instance*>>& registry() {
+        static std::map<void*, std::vector<pb_instance*>> r;
+        return r;
+    }
+    static std::mutex& registry_mu() {
+        static std::mutex mu;
+        return mu;
+    }
+    static void remember(void* owner, pb_instance* inst) {
+        std::lock_guard<std::mutex> lk(registry_mu());
+        registry()[owner].push_back(inst);
+    }
+
+  public:
+    static void release_all(void* owner) {
+        std::vector<pb_instance*> mine;
+        {
+            std::lock_guard<std::mutex> lk(registry_mu());
+            auto it = registry().find(owner);
+            if (it == registry().end()) return;
+            mine.swap(it->second);
+            registry().erase(it);
+        }
+        for (pb_instance* i : mine) pb_instance_destroy(i);
+    }
+
+  private:
     static pb_model* shared_model(int device, const std::string& path) {
         static std::mutex mu;
         static std::map<std::pair<int, std::string>, pb_model*> cache;
@@ -180,4 +211,8 @@ class ModelJob : public llis::job::Job {
 #define PB_DEFINE_MODEL_JOB(NAME, IN_FLOATS, OUT_FLOATS)                                             \
     extern "C" __attribute__((visibility("default"))) llis::job::Job* init_job() {                  \
         return new pbjobs::ModelJob(NAME, IN_FLOATS, OUT_FLOATS);                                    \
+    }                                                                                                \
+    /* optional: a server that is being destroyed hands back the device memory of its instances */  \
+    extern "C" __attribute__((visibility("default"))) void pb_plugin_release(void* owner) {         \
+        pbjobs::ModelJob::release_all(owner);                                                        \
     }
