@@ -1,0 +1,2 @@
+#pragma once
+namespace llis { namespace server { class SmResources {}; } }
