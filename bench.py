@@ -48,11 +48,24 @@ WORKLOADS = {
     "squeezenet1_1": [("tvm_squeezenet1_1", "squeezenet1_1", 1.0)],
     "densenet121": [("tvm_densenet121", "densenet121", 1.0)],
     "arcfaceresnet100": [("tvm_arcfaceresnet100", "arcfaceresnet100", 1.0)],
+    "ultraface320": [("tvm_ultraface320", "ultraface320", 1.0)],
+    # the reference's face pipeline mix (tools/run_ultraface_arcface.sh:27): detector 0.7, embedding 0.3
+    "ultraface_arcface": [("tvm_ultraface320", "ultraface320", 0.7), ("tvm_arcfaceresnet100", "arcfaceresnet100", 0.3)],
     # depthwise + bottleneck mix
     "mobilenet_resnet50": [("tvm_mobilenet", "mobilenet", 0.5), ("tvm_resnet50", "resnet50", 0.5)],
+    # the reference's eight-model mix (sosp23_artifact/gen_data_fig11_paella.sh:81-90) and its ResNet-18 : Inception-v3
+    # pair (gen_data_fig12_paella.sh:82-84): proportions here, per-model instance caps and client count in PAPER_MIXES
+    "fig11": [("tvm_mobilenet", "mobilenet", 0.257), ("tvm_densenet121", "densenet121", 0.0706), ("tvm_googlenet", "googlenet", 0.0546),
+              ("tvm_inception_v3", "inception_v3", 0.0138), ("tvm_resnet18", "resnet18", 0.272), ("tvm_resnet34", "resnet34", 0.168),
+              ("tvm_resnet50", "resnet50", 0.0745), ("tvm_squeezenet1_1", "squeezenet1_1", 0.0895)],
+    "fig12": [("tvm_resnet18", "resnet18", 0.952), ("tvm_inception_v3", "inception_v3", 0.048)],
     # scheduler stress (vec_add of 2^22 floats x 10 launches, 148-block spin kernels of 10 us / 1 ms)
     "stress": [("vec_add", None, 1 / 3), ("dummy_short", None, 1 / 3), ("dummy_long", None, 1 / 3)],
 }
+# instances (max outstanding) per model in the order of WORKLOADS, clients in flight, and the lognormal sigmas of the
+# arrival process, as the reference's scripts give them
+PAPER_MIXES = {"fig11": {"caps": [36, 10, 8, 2, 38, 24, 10, 13], "concurrency": 141, "ln_sigma": (1.5, 2.0)},
+               "fig12": {"caps": [119, 6], "concurrency": 125, "ln_sigma": (1.5, 2.0)}}
 MIX = WORKLOADS["mix"]
 GANG, DEFERRED = 1, 0      # set from the command line
 
@@ -137,7 +150,7 @@ def write_packs(models_dir):
 
 
 def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps, iat_us=0.0, seed=1, extra_kernels=2, mix=None,
-             sched="full3", streams=500, gang=None, deferred=None, samples_per_type=0, cpus=None):
+             sched="full3", streams=500, gang=None, deferred=None, samples_per_type=0, cpus=None, ln_sigma=0.0):
     """One load-generator run (one replica thread per entry of `devices`).  Returns the result struct and, with
     samples_per_type > 0, the sampled request slots [(type index, slot, input float32 array, output float32 array)]."""
     import numpy as np
@@ -156,6 +169,7 @@ def run_load(L, capi, devices, batch, steps, warmup, resident, concurrency, caps
         cfg.input_uniform[i] = 1 if model == "mnist" else 0      # U[0,1) images for MNIST, N(0,1) for the others
     cfg.concurrency = concurrency
     cfg.mean_interarrival_us = iat_us
+    cfg.lognormal_sigma = ln_sigma
     cfg.num_jobs = max(1, int(batch * steps))
     cfg.warmup_jobs = int(batch * warmup)
     cfg.seed = seed
@@ -518,7 +532,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=0, help="requests per GPU per step (default 12000 for the mix, so that 20 steps last about a second)")
-    ap.add_argument("--concurrency", type=int, default=192, help="clients per replica: requests in flight at most (closed loop: always)")
+    ap.add_argument("--concurrency", type=int, default=0, help="clients per replica: requests in flight at most (closed loop: always); default 192 "
+                                                                 "(fig11: 141, fig12: 125, the reference's)")
     ap.add_argument("--inception-instances", type=int, default=96, help="Inception-v3 instances (max outstanding) per replica")
     ap.add_argument("--replicas-per-gpu", type=int, default=1,
                     help="independent scheduler+pool replicas (one busy-polling host thread each) sharing every GPU")
@@ -551,7 +566,10 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.batch <= 0:
-        args.batch = {"mix": 12000, "mnist": 20000}.get(args.workload, 1500)
+        args.batch = {"mix": 12000, "mnist": 20000, "fig11": 6000, "fig12": 6000}.get(args.workload, 1500)
+    paper = PAPER_MIXES.get(args.workload)
+    if args.concurrency <= 0:
+        args.concurrency = paper["concurrency"] if paper else 192
     global MIX, GANG, DEFERRED
     MIX = WORKLOADS[args.workload]
     GANG, DEFERRED = args.gang, args.deferred
@@ -570,11 +588,17 @@ def main():
                "squeezenet1_1": "SqueezeNet 1.1 alone, batch 1, 224x224, random He-normal weights",
                "densenet121": "DenseNet-121 alone, batch 1, 224x224, random He-normal weights",
                "arcfaceresnet100": "ArcFace LResNet100E-IR alone, batch 1, 112x112, random He-normal weights",
+               "ultraface320": "320x240 receptive-field-block face detector alone, batch 1, random He-normal weights",
+               "ultraface_arcface": "face detector : ArcFace LResNet100E-IR = 0.7 : 0.3, batch 1",
                "mobilenet_resnet50": "MobileNetV2 : ResNet-50 = 1:1, batch 1, 224x224",
+               "fig11": "the reference's eight-model mix by its proportions and per-model instance caps: MobileNetV2 .257, DenseNet-121 .0706, "
+                        "GoogLeNet .0546, Inception-v3 .0138, ResNet-18 .272, ResNet-34 .168, ResNet-50 .0745, SqueezeNet 1.1 .0895; batch 1",
+               "fig12": "ResNet-18 : Inception-v3 = 0.952 : 0.048 with the reference's instance caps (119 / 6), batch 1",
                "stress": "vec_add : dummy_short : dummy_long = 1:1:1 synthetic scheduler stress"}[args.workload]
     config = {"workload": wl_text,
               "batch_per_step_per_replica": args.batch, "clients_per_replica": args.concurrency,
-              "instances_per_replica": {names[0]: args.concurrency, **({names[-1]: args.inception_instances} if len(names) > 1 else {})},
+              "instances_per_replica": dict(zip(names, paper["caps"])) if paper else
+                                       {names[0]: args.concurrency, **({names[-1]: args.inception_instances} if len(names) > 1 else {})},
               "scheduler": args.sched, "max_gang": args.gang, "deferred_schedule": int(args.deferred or args.gang > 1), "num_streams": args.streams, "extra_kernels": args.extra_kernels, "replicas_per_gpu": args.replicas_per_gpu,
               "precision": "MNIST fp32; other models bf16 x bf16 -> fp32 (tcgen05)",
               "replicas": "one scheduler+pools per GPU, requests dealt round-robin, no collective",
@@ -619,6 +643,8 @@ def main():
     os.environ["LLIS_MODELS_DIR"] = tmp.name
     graphs = write_packs(tmp.name)
     caps = [args.concurrency] * (len(MIX) - 1) + [args.inception_instances] if len(MIX) > 1 else [args.concurrency]
+    if paper:
+        caps = list(paper["caps"])
     if args.workload == "stress":
         os.environ.setdefault("PB_VEC_ADD_N", str(1 << 22))
         caps = [args.inception_instances] * 3
@@ -670,14 +696,14 @@ def main():
     load_kw = dict(extra_kernels=args.extra_kernels, sched=args.sched, streams=args.streams, cpus=cpus)
     leg_seconds = {}
 
-    def leg(name, resident, iat_us, steps, seed=1, samples=0, warmup=None):
+    def leg(name, resident, iat_us, steps, seed=1, samples=0, warmup=None, ln_sigma=0.0):
         """One load run on every rank (barrier first); returns rank-reduced numbers."""
         import numpy as np
         if dist:
             dist.barrier()
         t0 = time.time()
         out = run_load(L, capi, devices, args.batch, steps, args.warmup if warmup is None else warmup, resident, args.concurrency, caps,
-                       iat_us=iat_us, seed=seed, samples_per_type=samples, **load_kw)
+                       iat_us=iat_us, seed=seed, samples_per_type=samples, ln_sigma=ln_sigma, **load_kw)
         r, smp = out if isinstance(out, tuple) else (out, [])
         leg_seconds[name] = round(time.time() - t0, 1)
         nt = len(MIX)
@@ -749,6 +775,18 @@ def main():
         b = sweep(True, closed_dev["rps"], "resident")
         if b is not None:
             head_dev = b
+    lognormal_pts = []
+    if paper and args.iat_us <= 0:
+        # ---- the reference's arrival process for these mixes: lognormal inter-arrival times (sigma 1.5 and 2) at two
+        # offered rates below the closed-loop capacity; per-model mean and tail latency at each ----
+        for sigma in paper["ln_sigma"]:
+            for frac in (0.5, 0.8):
+                offered = frac * closed_e2e["rps"]
+                x = leg(f"lognormal_{sigma}_{frac}", False, 1e6 * n_gpus * args.replicas_per_gpu / offered, args.steps, seed=7, ln_sigma=sigma)
+                d = dict(point(x, offered), ln_sigma=sigma, fraction_of_closed_loop=frac, inputs="host_buffers")
+                for i, nm in enumerate(names):
+                    d[f"{nm}_mean_us"] = round(x["mean"][i])
+                lognormal_pts.append(d)
     clocks = sampler.stop(set(range(n_gpus))) if rank == 0 else None
 
     fairness = None
@@ -837,6 +875,10 @@ def main():
                                  "points": sweep_pts}
     if fairness:
         line["fairness"] = fairness
+    if lognormal_pts:
+        line["lognormal_arrivals"] = {"what": "open loop, lognormal inter-arrival times with the mean of the offered rate (mu = ln(mean) - sigma^2/2), "
+                                              "latency = completion - scheduled arrival, host buffers",
+                                      "points": lognormal_pts}
 
     if is_mix and not dist and not args.no_granularity:
         # ---- scheduling granularity: layers per scheduler stage (1 = the reference's kernel-by-kernel release) ----

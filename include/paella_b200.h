@@ -139,7 +139,11 @@ typedef enum pb_stage_kind {
     PB_STAGE_ADD = 8,
     PB_STAGE_SOFTMAX = 9,
     PB_STAGE_MNIST_FUSED = 10,
-    PB_STAGE_AFFINE = 11     /* per-channel scale + bias (+ activation): a batch-norm that precedes its convolution (DenseNet) */
+    PB_STAGE_AFFINE = 11,    /* per-channel scale + bias (+ activation): a batch-norm that precedes its convolution (DenseNet) */
+    PB_STAGE_DETECT = 12     /* detection head over one feature map: x = [H][W][6A] (2A class logits, then 4A box regressions),
+                              * w = fp32 priors [H*W*A][4] (cx, cy, w, h), bias = {centre variance, size variance}, K = priors of
+                              * the whole model, out_c_off = first prior of this map; writes softmax scores to y[(first+i)*2..]
+                              * and corner-form boxes to y[K*2 + (first+i)*4..] of the fp32 model output (K*6 floats) */
 } pb_stage_kind;
 
 typedef struct pb_op_params {

@@ -20,7 +20,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
-OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE = 1, 2, 3, 4, 5, 6, 7, 8
+OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE, OP_DETECT = 1, 2, 3, 4, 5, 6, 7, 8, 9
 NONE = 0xFFFFFFFF
 _f = ctypes.POINTER(ctypes.c_float)
 _i = ctypes.c_int
@@ -38,6 +38,8 @@ def lib():
             build()
         L = ctypes.CDLL(path)
         L.orc_conv2d.argtypes = [_f, _i, _i, _i, _f, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i]
+        L.orc_conv2d_dil.argtypes = [_f, _i, _i, _i, _f, _f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i]
+        L.orc_detect.argtypes = [_f, _i, _i, _i, _f, ctypes.c_float, ctypes.c_float, _i, _i, _f]
         L.orc_dense.argtypes = [_f, _i, _f, _f, _i, _i, _f]
         L.orc_maxpool.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
         L.orc_maxpool_pq.argtypes = [_f, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i]
@@ -63,17 +65,27 @@ def round_bf16(a):
     return a
 
 
-def conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0), groups=1, act=0, residual=None, out=None, out_c_off=0):
+def conv2d(x, w, b=None, stride=(1, 1), pad=(0, 0), groups=1, act=0, residual=None, out=None, out_c_off=0, dilation=(1, 1)):
     c, h, wd = x.shape
     k, _, r, s = w.shape
-    p = (h + 2 * pad[0] - r) // stride[0] + 1
-    q = (wd + 2 * pad[1] - s) // stride[1] + 1
+    p = (h + 2 * pad[0] - dilation[0] * (r - 1) - 1) // stride[0] + 1
+    q = (wd + 2 * pad[1] - dilation[1] * (s - 1) - 1) // stride[1] + 1
     if out is None:
         out = np.zeros((k, p, q), np.float32)
     x = np.ascontiguousarray(x, np.float32)
     w = np.ascontiguousarray(w, np.float32)
-    lib().orc_conv2d(_p(x), c, h, wd, _p(w), _p(b), k, r, s, stride[0], stride[1], pad[0], pad[1],
-                     groups, act, _p(residual), _p(out), out.shape[0], out_c_off)
+    lib().orc_conv2d_dil(_p(x), c, h, wd, _p(w), _p(b), k, r, s, stride[0], stride[1], pad[0], pad[1], dilation[0], dilation[1],
+                         groups, act, _p(residual), _p(out), out.shape[0], out_c_off)
+    return out
+
+
+def detect(head, anchors, priors, center_var, size_var, first, n_total, out):
+    """Detection head over one feature map (orc_detect): writes this map's scores and boxes into `out`
+    ([n_total*2 scores | n_total*4 boxes])."""
+    head = np.ascontiguousarray(head, np.float32)
+    priors = np.ascontiguousarray(priors, np.float32)
+    assert head.shape[0] == 6 * anchors and priors.size == head.shape[1] * head.shape[2] * anchors * 4 and out.size == n_total * 6
+    lib().orc_detect(_p(head), anchors, head.shape[1], head.shape[2], _p(priors), float(center_var), float(size_var), first, n_total, _p(out))
     return out
 
 
@@ -192,7 +204,8 @@ def run(pack: Pack, x: np.ndarray, emulate_bf16: bool = False, keep_all: bool = 
     bufs[pack.input] = rb(np.ascontiguousarray(x, np.float32).reshape(pack.tensors[pack.input]))
     for rec in pack.ops:
         (typ, in0, in1, out, _, ooff, cin, cout, r, s, sh, sw, ph, pw, groups, act, flags, _,
-         wlo, whi, blo, bhi, _, _) = rec
+         wlo, whi, blo, bhi, dh, dw) = rec
+        dil = (max(dh, 1), max(dw, 1))        # 0 in packs written before dilation existed
         woff, boff = wlo | (whi << 32), blo | (bhi << 32)
         oc, oh, ow = pack.tensors[out]
         if bufs[out] is None:
@@ -203,12 +216,12 @@ def run(pack: Pack, x: np.ndarray, emulate_bf16: bool = False, keep_all: bool = 
             b = np.ascontiguousarray(W[boff: boff + cout])
             res = None if in1 == NONE else np.ascontiguousarray(bufs[in1])
             if act == 3:     # PReLU: slopes follow the biases; y = v if v > 0 else slope[c] * v
-                conv2d(xin, w, b, (sh, sw), (ph, pw), groups, 0, res, bufs[out], ooff)
+                conv2d(xin, w, b, (sh, sw), (ph, pw), groups, 0, res, bufs[out], ooff, dil)
                 v = bufs[out][ooff: ooff + cout]
                 slope = W[boff + cout: boff + 2 * cout].reshape(-1, 1, 1)
                 bufs[out][ooff: ooff + cout] = np.where(v > 0, v, v * slope).astype(np.float32)
             else:
-                conv2d(xin, w, b, (sh, sw), (ph, pw), groups, act, res, bufs[out], ooff)
+                conv2d(xin, w, b, (sh, sw), (ph, pw), groups, act, res, bufs[out], ooff, dil)
         elif typ == OP_DENSE:
             w = rb(W[woff: woff + cout * cin].reshape(cout, cin))
             b = np.ascontiguousarray(W[boff: boff + cout])
@@ -225,8 +238,13 @@ def run(pack: Pack, x: np.ndarray, emulate_bf16: bool = False, keep_all: bool = 
             bufs[out][ooff: ooff + cin] = affine(xin[:cin], W[woff: woff + cin], W[boff: boff + cin], act)
         elif typ == OP_SOFTMAX:
             bufs[out][:] = softmax(xin).reshape(oc, oh, ow)
+        elif typ == OP_DETECT:   # cin = anchors per position, cout = priors of the whole model, out_c_off = this map's first prior
+            n_here = xin.shape[1] * xin.shape[2] * cin
+            detect(xin, cin, W[woff: woff + 4 * n_here], W[boff], W[boff + 1], ooff, cout, bufs[out].reshape(-1))
         else:
             raise ValueError(f"unknown op type {typ}")
+        if typ == OP_DETECT:
+            continue
         if emulate_bf16 and out != pack.output:
             sl = bufs[out][ooff: ooff + cout] if typ in (OP_CONV, OP_MAXPOOL, OP_AVGPOOL, OP_AFFINE) else bufs[out]
             sl[...] = round_bf16(sl)

@@ -27,10 +27,11 @@ struct Handle {
 };
 }  // namespace
 
+#define JQ_API __attribute__((visibility("default")))
 extern "C" {
-void* jq_create(double unfairness_threshold) { return new Handle(unfairness_threshold); }
-void jq_destroy(void* h) { delete static_cast<Handle*>(h); }
-void jq_push(void* h, uint32_t type, double priority, uint64_t tag) {
+JQ_API void* jq_create(double unfairness_threshold) { return new Handle(unfairness_threshold); }
+JQ_API void jq_destroy(void* h) { delete static_cast<Handle*>(h); }
+JQ_API void jq_push(void* h, uint32_t type, double priority, uint64_t tag) {
     Handle* s = static_cast<Handle*>(h);
     s->jobs.emplace_back(tag);
     TagJob* j = &s->jobs.back();
@@ -38,7 +39,7 @@ void jq_push(void* h, uint32_t type, double priority, uint64_t tag) {
     j->set_priority(priority);
     s->q.push(j);
 }
-uint64_t jq_top(void* h) { return static_cast<TagJob*>(static_cast<Handle*>(h)->q.top())->tag(); }
-uint64_t jq_pop(void* h) { return static_cast<TagJob*>(static_cast<Handle*>(h)->q.pop())->tag(); }
-uint64_t jq_size(void* h) { return static_cast<Handle*>(h)->q.size(); }
+JQ_API uint64_t jq_top(void* h) { return static_cast<TagJob*>(static_cast<Handle*>(h)->q.top())->tag(); }
+JQ_API uint64_t jq_pop(void* h) { return static_cast<TagJob*>(static_cast<Handle*>(h)->q.pop())->tag(); }
+JQ_API uint64_t jq_size(void* h) { return static_cast<Handle*>(h)->q.size(); }
 }

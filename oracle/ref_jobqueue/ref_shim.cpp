@@ -15,15 +15,16 @@ struct Handle {
 };
 }  // namespace
 
+#define JQ_API __attribute__((visibility("default")))
 extern "C" {
-void* jq_create(double unfairness_threshold) { return new Handle(unfairness_threshold); }
-void jq_destroy(void* h) { delete static_cast<Handle*>(h); }
-void jq_push(void* h, uint32_t type, double priority, uint64_t tag) {
+JQ_API void* jq_create(double unfairness_threshold) { return new Handle(unfairness_threshold); }
+JQ_API void jq_destroy(void* h) { delete static_cast<Handle*>(h); }
+JQ_API void jq_push(void* h, uint32_t type, double priority, uint64_t tag) {
     Handle* s = static_cast<Handle*>(h);
     s->jobs.emplace_back(type, priority, tag);
     s->q.push(&s->jobs.back());
 }
-uint64_t jq_top(void* h) { return static_cast<Handle*>(h)->q.top()->tag(); }
-uint64_t jq_pop(void* h) { return static_cast<Handle*>(h)->q.pop()->tag(); }
-uint64_t jq_size(void* h) { return static_cast<Handle*>(h)->q.size(); }
+JQ_API uint64_t jq_top(void* h) { return static_cast<Handle*>(h)->q.top()->tag(); }
+JQ_API uint64_t jq_pop(void* h) { return static_cast<Handle*>(h)->q.pop()->tag(); }
+JQ_API uint64_t jq_size(void* h) { return static_cast<Handle*>(h)->q.size(); }
 }

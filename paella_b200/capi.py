@@ -12,9 +12,9 @@ PB_MAX_JOB_TYPES = 8
 PB_MAX_GPUS = 8
 
 (STAGE_INPUT, STAGE_CONV_SIMT, STAGE_CONV_UMMA, STAGE_DWCONV, STAGE_DENSE, STAGE_MAXPOOL, STAGE_AVGPOOL,
- STAGE_GAP, STAGE_ADD, STAGE_SOFTMAX, STAGE_MNIST_FUSED, STAGE_AFFINE) = range(12)
+ STAGE_GAP, STAGE_ADD, STAGE_SOFTMAX, STAGE_MNIST_FUSED, STAGE_AFFINE, STAGE_DETECT) = range(13)
 STAGE_NAMES = ["input", "conv_simt", "conv_umma", "dwconv", "dense", "maxpool", "avgpool", "gap", "add", "softmax",
-               "mnist_fused", "affine"]
+               "mnist_fused", "affine", "detect"]
 
 
 class PbError(RuntimeError):

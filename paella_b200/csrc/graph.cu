@@ -28,11 +28,11 @@
 namespace {
 
 constexpr uint32_t kNone = 0xFFFFFFFFu;
-enum { OP_CONV = 1, OP_DENSE = 2, OP_MAXPOOL = 3, OP_AVGPOOL = 4, OP_GAP = 5, OP_ADD = 6, OP_SOFTMAX = 7, OP_AFFINE = 8 };
+enum { OP_CONV = 1, OP_DENSE = 2, OP_MAXPOOL = 3, OP_AVGPOOL = 4, OP_GAP = 5, OP_ADD = 6, OP_SOFTMAX = 7, OP_AFFINE = 8, OP_DETECT = 9 };
 
 struct PackOp {
     uint32_t type, in0, in1, out, rsv0, out_c_off, cin, cout, r, s, stride_h, stride_w, pad_h, pad_w, groups, act, flags,
-        rsv1, w_off_lo, w_off_hi, b_off_lo, b_off_hi, rsv2, rsv3;
+        rsv1, w_off_lo, w_off_hi, b_off_lo, b_off_hi, dil_h, dil_w;     // dilation 0 reads as 1
 };
 static_assert(sizeof(PackOp) == 96, "pack op record is 96 bytes");
 
@@ -697,6 +697,7 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         }
         if (readers == 1 && ops[first].type == OP_CONV && ops[first].in0 == t_in && ops[first].in1 == kNone &&
             (ops[first].groups == 0 || ops[first].groups == 1) && ops[first].r * ops[first].s > 1 && ops[first].out < nt &&
+            ops[first].dil_h <= 1 && ops[first].dil_w <= 1 &&
             ops[first].cout % 8 == 0 && ops[first].out_c_off % 8 == 0 && (int)ops[first].out != m->t_out) {   // = what the tensor-core path needs
             patch_op = first;
             const PackOp& o = ops[first];
@@ -763,6 +764,7 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
         p.R = (int)o.r; p.S = (int)o.s; p.stride_h = (int)o.stride_h; p.stride_w = (int)o.stride_w;
         p.pad_h = (int)o.pad_h; p.pad_w = (int)o.pad_w; p.groups = (int)(o.groups ? o.groups : 1);
         p.act = (int)o.act; p.flags = (int)(o.flags & 1);
+        p.dil_h = o.dil_h > 1 ? (int)o.dil_h : 1; p.dil_w = o.dil_w > 1 ? (int)o.dil_w : 1;
         st.x_is_input = false;
         st.x_off = tx.offset;
         st.y_is_output = (int)o.out == m->t_out;
@@ -794,6 +796,7 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
                     st.in_tensor = patch_tensor;
                 }
                 const bool dw = p.groups > 1 && p.groups == p.C && p.K == p.C;
+                if (dw && (p.dil_h > 1 || p.dil_w > 1)) { pb::set_error("%s: dilated depthwise convolution is not supported", pack_path); PB_FAIL_LOAD(PB_ERR_INVALID); }
                 if (dw) st.kind = PB_STAGE_DWCONV;
                 else if (use_umma && pb::conv_umma_supported(&p)) st.kind = PB_STAGE_CONV_UMMA;
                 else st.kind = PB_STAGE_CONV_SIMT;
@@ -841,11 +844,25 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
                 break;
             }
             case OP_SOFTMAX: st.kind = PB_STAGE_SOFTMAX; p.C = tx.C * tx.H * tx.W; break;
+            case OP_DETECT: {
+                // cin = anchors per cell, cout = priors of the whole model, out_c_off = first prior of this map;
+                // weights = this map's priors [H*W*anchors][4], bias block = {centre variance, size variance}
+                const uint64_t n_here = (uint64_t)tx.H * tx.W * o.cin;
+                if (o.cin == 0 || tx.C != (int)(6 * o.cin) || !st.y_is_output || (uint64_t)ty.C * ty.H * ty.W != 6ull * o.cout ||
+                    (uint64_t)o.out_c_off + n_here > o.cout || w_off + 4 * n_here > n_floats || b_off + 2 > n_floats) {
+                    pb::set_error("%s: detection head %u does not fit its tensors", pack_path, i);
+                    PB_FAIL_LOAD(PB_ERR_INVALID);
+                }
+                st.kind = PB_STAGE_DETECT;
+                PB_FAIL_LOAD(upload(m, W + w_off, (size_t)n_here * 16, &st.w_dev));
+                PB_FAIL_LOAD(upload(m, W + b_off, 8, (void**)&st.bias_dev));
+                break;
+            }
             default:
                 pb::set_error("%s: unknown operator type %u", pack_path, o.type);
                 PB_FAIL_LOAD(PB_ERR_IO);
         }
-        if (st.y_is_output && !(st.kind == PB_STAGE_DENSE || st.kind == PB_STAGE_GAP || st.kind == PB_STAGE_SOFTMAX)) {
+        if (st.y_is_output && !(st.kind == PB_STAGE_DENSE || st.kind == PB_STAGE_GAP || st.kind == PB_STAGE_SOFTMAX || st.kind == PB_STAGE_DETECT)) {
             pb::set_error("stage kind %d cannot write the fp32 model output", st.kind);
             PB_FAIL_LOAD(PB_ERR_INVALID);
         }

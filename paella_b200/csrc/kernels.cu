@@ -712,6 +712,38 @@ __global__ void __launch_bounds__(256) softmax_kernel(OpArgs a, uint32_t job_id,
     PB_NOTIFY_END();
 }
 
+// ---- detection head over one feature map ----------------------------------------------
+// One thread per prior (cell, anchor) of the map.  x is [H][W][Cs] with C = 6A channels: 2A class logits
+// (anchor, class), then 4A box regressions (anchor, coordinate).  a.w = fp32 priors [H*W*A][4] = (cx, cy, w, h),
+// a.bias = {centre variance, size variance}, a.K = priors of the whole model, a.out_c_off = this map's first
+// prior.  The fp32 model output is [K*2 scores | K*4 corner-form boxes].
+template <typename T>
+__global__ void __launch_bounds__(256) detect_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    const int A = a.C / 6;
+    const int n = a.H * a.W * A;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const int cell = i / A, an = i - cell * A;
+        const T* __restrict__ x = x_img<T>(a) + (size_t)cell * a.Cs;
+        const float c0 = to_f<T>(x[an * 2]), c1 = to_f<T>(x[an * 2 + 1]);
+        const float m = fmaxf(c0, c1);
+        const float e0 = expf(c0 - m), e1 = expf(c1 - m);
+        const float inv = 1.f / (e0 + e1);
+        float* out = out_f32_img(a, slot_, a.K * 6);
+        float* sc = out + (size_t)(a.out_c_off + i) * 2;       // scalar stores: a request's buffer need not be 16-byte aligned
+        sc[0] = e0 * inv; sc[1] = e1 * inv;
+        const float4 pr = __ldg(reinterpret_cast<const float4*>(a.w) + i);
+        const float cv = __ldg(a.bias), sv = __ldg(a.bias + 1);
+        const T* l = x + 2 * A + an * 4;
+        const float cx = to_f<T>(l[0]) * cv * pr.z + pr.x, cy = to_f<T>(l[1]) * cv * pr.w + pr.y;
+        const float bw = expf(to_f<T>(l[2]) * sv) * pr.z, bh = expf(to_f<T>(l[3]) * sv) * pr.w;
+        float* bo = out + (size_t)a.K * 2 + (size_t)(a.out_c_off + i) * 4;
+        bo[0] = cx - bw * 0.5f; bo[1] = cy - bh * 0.5f; bo[2] = cx + bw * 0.5f; bo[3] = cy + bh * 0.5f;
+    }
+    PB_NOTIFY_END();
+}
+
 // ---- whole MNIST-CNN in one launch ---------------------------------------------------
 // conv5x5(1->8)+ReLU, maxpool2, conv5x5(8->16)+ReLU, maxpool3, dense 256->10 for one
 // 28x28 image, fp32, activations in shared memory.  One block of 256 threads: the network
@@ -955,6 +987,12 @@ static int info_one_image(int kind, const pb_op_params* p, pb_launch_info* out) 
             out->smem_per_block = static_smem_of(softmax_kernel<float, true>);
             out->bytes = 8ull * p->C;
             break;
+        case PB_STAGE_DETECT:
+            out->num_blocks = blocks_for((size_t)p->H * p->W * (p->C / 6));
+            out->regs_per_thread = f32 ? regs_of(detect_kernel<float>) : regs_of(detect_kernel<__nv_bfloat16>);
+            out->flops = 20ull * p->H * p->W * (p->C / 6);
+            out->bytes = es * (uint64_t)p->H * p->W * p->C + (16ull + 24ull) * p->H * p->W * (p->C / 6);
+            break;
         default:
             set_error("pb_op_info: unknown stage kind %d", kind);
             return PB_ERR_INVALID;
@@ -1096,6 +1134,12 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
             // flags bit2: the input is fp32 regardless of dtype
             if (f32 || (p->flags & 4)) launch_k(softmax_kernel<float, true>, grid, block, st, pdl, a, job_id, nf);
             else launch_k(softmax_kernel<__nv_bfloat16, false>, grid, block, st, pdl, a, job_id, nf);
+            break;
+        case PB_STAGE_DETECT:
+            PB_REQUIRE(a.w != nullptr && a.bias != nullptr && a.C % 6 == 0 && a.C > 0, "detect: priors, variances and 6 channels per anchor are required");
+            PB_REQUIRE((p->flags & 2) != 0, "detect: writes the fp32 model output only");
+            PB_REQUIRE((size_t)a.out_c_off + (size_t)a.H * a.W * (a.C / 6) <= (size_t)a.K, "detect: priors of this map exceed the model's count");
+            PB_DISPATCH(detect_kernel<float>, detect_kernel<__nv_bfloat16>, a, job_id, nf);
             break;
         default:
             set_error("pb_op_launch: unknown stage kind %d", kind);

@@ -35,14 +35,14 @@ MAGIC = b"PB2PACK\0"
 VERSION = 1
 NONE = 0xFFFFFFFF
 
-OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE = 1, 2, 3, 4, 5, 6, 7, 8
+OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE, OP_DETECT = 1, 2, 3, 4, 5, 6, 7, 8, 9
 ACT_NONE, ACT_RELU, ACT_RELU6, ACT_PRELU = 0, 1, 2, 3   # PReLU: the conv's bias block is [bias | per-channel slope]
 FLAG_COUNT_INCLUDE_PAD = 1
 FLAG_CEIL_MODE = 4          # informational: the output tensor's extent already says it
 
 OP_FIELDS = ("type", "in0", "in1", "out", "rsv0", "out_c_off", "cin", "cout", "r", "s",
              "stride_h", "stride_w", "pad_h", "pad_w", "groups", "act", "flags", "rsv1",
-             "w_off_lo", "w_off_hi", "b_off_lo", "b_off_hi", "rsv2", "rsv3")
+             "w_off_lo", "w_off_hi", "b_off_lo", "b_off_hi", "dil_h", "dil_w")   # dilation 0 reads as 1
 
 
 @dataclass
@@ -66,13 +66,15 @@ class Op:
     w_off: int = 0
     b_off: int = 0
     name: str = ""
+    dil_h: int = 1
+    dil_w: int = 1
 
     def record(self) -> bytes:
         return struct.pack(
             "<24I", self.type, self.in0, self.in1, self.out, 0, self.out_c_off, self.cin,
             self.cout, self.r, self.s, self.stride_h, self.stride_w, self.pad_h, self.pad_w,
             self.groups, self.act, self.flags, 0, self.w_off & 0xFFFFFFFF, self.w_off >> 32,
-            self.b_off & 0xFFFFFFFF, self.b_off >> 32, 0, 0)
+            self.b_off & 0xFFFFFFFF, self.b_off >> 32, self.dil_h, self.dil_w)
 
 
 def _pool_extent(n, k, stride, pad, ceil_mode):
@@ -141,13 +143,14 @@ class Graph:
 
     # -- operators -----------------------------------------------------------
     def conv(self, x, cout, k, stride=1, pad=0, groups=1, act=ACT_RELU, residual=None,
-             out=None, out_c_off=0, bn_eps=None, name="", w_scale=1.0):
+             out=None, out_c_off=0, bn_eps=None, name="", w_scale=1.0, dilation=1):
         c, h, w = self.shape(x)
         r, s = _pair(k)
         sh, sw = _pair(stride)
         ph, pw = _pair(pad)
-        p = (h + 2 * ph - r) // sh + 1
-        q = (w + 2 * pw - s) // sw + 1
+        dh, dw = _pair(dilation)
+        p = (h + 2 * ph - dh * (r - 1) - 1) // sh + 1
+        q = (w + 2 * pw - dw * (s - 1) - 1) // sw + 1
         if out is None:
             out = self.tensor(cout, p, q)
         else:
@@ -159,7 +162,7 @@ class Graph:
         if act == ACT_PRELU:     # slopes right behind the biases: 0.25 (the usual initial value) +- 0.1
             self._push((0.25 + 0.2 * (self.rng.random(cout, dtype=np.float32) - 0.5)).astype(np.float32))
         self.ops.append(Op(OP_CONV, x, out, NONE if residual is None else residual, out_c_off,
-                           c, cout, r, s, sh, sw, ph, pw, groups, act, 0, w_off, b_off, name))
+                           c, cout, r, s, sh, sw, ph, pw, groups, act, 0, w_off, b_off, name, dh, dw))
         self.output = out
         return out
 
@@ -239,6 +242,23 @@ class Graph:
         c, h, w = self.shape(x)
         out = self.tensor(c, h, w)
         self.ops.append(Op(OP_SOFTMAX, x, out, cin=c * h * w, cout=c * h * w, name=name))
+        self.output = out
+        return out
+
+    def detect(self, head, anchors, priors, first, n_total, out=None, center_variance=0.1, size_variance=0.2, name=""):
+        """Detection head of a single-shot detector over one feature map.  `head` has 6*anchors channels: class
+        logits (anchor, class) then box regressions (anchor, coordinate); `priors` is [H*W*anchors][4] = (cx, cy,
+        w, h) in (row, column, anchor) order.  Writes the softmax scores of this map's priors to
+        out[(first+i)*2 ..] and their corner-form boxes to out[n_total*2 + (first+i)*4 ..]; `out` is the fp32
+        model output of n_total*6 floats that all maps of the model share."""
+        c, h, w = self.shape(head)
+        assert c == 6 * anchors
+        priors = np.asarray(priors, np.float32).reshape(h * w * anchors, 4)
+        if out is None:
+            out = self.tensor(n_total * 6, 1, 1)
+        w_off = self._push(priors)
+        b_off = self._push(np.array([center_variance, size_variance], np.float32))
+        self.ops.append(Op(OP_DETECT, head, out, out_c_off=first, cin=anchors, cout=n_total, w_off=w_off, b_off=b_off, name=name))
         self.output = out
         return out
 
@@ -586,6 +606,99 @@ def arcface_r100(seed=1234, precision=1, **kw) -> Graph:
     return g
 
 
+def ultraface_priors(image_wh=(320, 240), min_boxes=((10, 16, 24), (32, 48), (64, 96), (128, 192, 256)), strides=(8, 16, 32, 64)):
+    """Prior boxes of the single-shot face detector, one list per feature map: for every cell (row, column) and
+    every min box size, (cx, cy, w, h) relative to the image, clipped to [0, 1].  The feature map of stride s has
+    ceil(W/s) x ceil(H/s) cells and its cell pitch is the image extent divided by that count."""
+    iw, ih = image_wh
+    maps = []
+    for boxes, st in zip(min_boxes, strides):
+        fw, fh = -(-iw // st), -(-ih // st)
+        scale_w, scale_h = iw / (iw / fw), ih / (ih / fh)
+        pri = []
+        for j in range(fh):
+            for i in range(fw):
+                for mb in boxes:
+                    pri.append(((i + 0.5) / scale_w, (j + 0.5) / scale_h, mb / iw, mb / ih))
+        maps.append(np.clip(np.asarray(pri, np.float32), 0.0, 1.0))
+    return maps
+
+
+def ultraface_rfb320(seed=1234, precision=1, **kw) -> Graph:
+    """The 320x240 face detector with receptive-field blocks (jobs/tvm_ultraface320 of the reference: 3x240x320 in,
+    4420 priors out).  Backbone of depthwise-separable units (3x3 depthwise + 1x1, batch-norm + ReLU after each,
+    folded), 16-32-32-32-64-64-64 channels down to stride 8, one receptive-field block there (three branches of
+    1x1 -> 3x3 (-> 3x3) -> 3x3 dilated by 2 / 3 / 5, concatenated, 1x1, plus a 1x1 shortcut, ReLU), 128 x3 at stride
+    16, 256 x2 at stride 32 and an extra 1x1 -> separable 3x3 stride 2 at stride 64.  Each of the four maps feeds a
+    class head and a box head (separable 3x3; plain 3x3 on the last map) with 3, 2, 2, 3 anchors per cell.
+    Output: [4420 x 2 softmax scores | 4420 x 4 corner-form boxes]; the reference's adapter returns the first
+    4420 x 2 floats (tvm_ultraface320.cpp:15-17), which are the first 4420 x 2 floats here."""
+    eps = 1e-5
+    g = Graph("ultraface320", (3, 240, 320), seed, precision, **kw)
+
+    def dw_unit(x, cout, stride, n):
+        c = g.shape(x)[0]
+        y = g.conv(x, c, 3, stride, 1, groups=c, bn_eps=eps, name=n + "_dw")
+        return g.conv(y, cout, 1, 1, 0, bn_eps=eps, name=n + "_pw")
+
+    def bconv(x, cout, k, stride=1, pad=0, dilation=1, relu=True, n="", **k2):
+        return g.conv(x, cout, k, stride, pad, act=ACT_RELU if relu else ACT_NONE, bn_eps=eps, dilation=dilation, name=n, **k2)
+
+    def rfb(x, cout, n, reduce=8):
+        c, h, w = g.shape(x)
+        inter = c // reduce
+        cat = g.tensor(6 * inter, h, w)
+        b = bconv(x, inter, 1, relu=False, n=n + "_b0_0")
+        b = bconv(b, 2 * inter, 3, 1, 1, n=n + "_b0_1")
+        bconv(b, 2 * inter, 3, 1, 2, dilation=2, relu=False, n=n + "_b0_2", out=cat, out_c_off=0)
+        b = bconv(x, inter, 1, relu=False, n=n + "_b1_0")
+        b = bconv(b, 2 * inter, 3, 1, 1, n=n + "_b1_1")
+        bconv(b, 2 * inter, 3, 1, 3, dilation=3, relu=False, n=n + "_b1_2", out=cat, out_c_off=2 * inter)
+        b = bconv(x, inter, 1, relu=False, n=n + "_b2_0")
+        b = bconv(b, inter // 2 * 3, 3, 1, 1, n=n + "_b2_1")
+        b = bconv(b, 2 * inter, 3, 1, 1, n=n + "_b2_2")
+        bconv(b, 2 * inter, 3, 1, 5, dilation=5, relu=False, n=n + "_b2_3", out=cat, out_c_off=4 * inter)
+        short = bconv(x, cout, 1, relu=False, n=n + "_shortcut")
+        return bconv(cat, cout, 1, relu=True, n=n + "_linear", residual=short)      # relu(linear(cat) + shortcut)
+
+    x = g.conv(g.input, 16, 3, 2, 1, bn_eps=eps, name="base_0")
+    for i, (cout, stride) in enumerate([(32, 1), (32, 2), (32, 1), (64, 2), (64, 1), (64, 1)]):
+        x = dw_unit(x, cout, stride, f"base_{i + 1}")
+    f0 = rfb(x, 64, "base_7")
+    x = dw_unit(f0, 128, 2, "base_8")
+    x = dw_unit(x, 128, 1, "base_9")
+    f1 = dw_unit(x, 128, 1, "base_10")
+    x = dw_unit(f1, 256, 2, "base_11")
+    f2 = dw_unit(x, 256, 1, "base_12")
+    x = g.conv(f2, 64, 1, 1, 0, name="extras_0")
+    x = g.conv(x, 64, 3, 2, 1, groups=64, name="extras_1_dw")
+    f3 = g.conv(x, 256, 1, 1, 0, name="extras_1_pw")
+
+    anchors = (3, 2, 2, 3)
+    priors = ultraface_priors()
+    n_total = sum(len(p) for p in priors)
+    out = g.tensor(n_total * 6, 1, 1)
+    first = 0
+    saved_bias = g.bias_std
+    g.bias_std = max(g.bias_std, 0.5)          # head biases: spread the class logits so that scores are not all 0.5
+    for i, (f, a) in enumerate(zip((f0, f1, f2, f3), anchors)):
+        c, h, w = g.shape(f)
+        assert h * w * a == len(priors[i])
+        head = g.tensor(6 * a, h, w)
+        if i < 3:
+            y = g.conv(f, c, 3, 1, 1, groups=c, name=f"cls_{i}_dw")
+            g.conv(y, 2 * a, 1, 1, 0, act=ACT_NONE, name=f"cls_{i}_pw", out=head, out_c_off=0)
+            y = g.conv(f, c, 3, 1, 1, groups=c, name=f"reg_{i}_dw")
+            g.conv(y, 4 * a, 1, 1, 0, act=ACT_NONE, name=f"reg_{i}_pw", out=head, out_c_off=2 * a)
+        else:
+            g.conv(f, 2 * a, 3, 1, 1, act=ACT_NONE, name=f"cls_{i}", out=head, out_c_off=0)
+            g.conv(f, 4 * a, 3, 1, 1, act=ACT_NONE, name=f"reg_{i}", out=head, out_c_off=2 * a)
+        g.detect(head, a, priors[i], first, n_total, out=out, name=f"detect_{i}")
+        first += len(priors[i])
+    g.bias_std = saved_bias
+    return g
+
+
 def googlenet(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
     """GoogLeNet / Inception-v1 (jobs/tvm_googlenet of the reference) in torchvision's form: batch-norm
     (eps 1e-3) folded, no auxiliary heads, 3x3 in the "5x5" branch, ceil-mode max pooling."""
@@ -639,6 +752,7 @@ MODELS = {
     "googlenet": googlenet,
     "densenet121": densenet121,
     "arcfaceresnet100": arcface_r100,
+    "ultraface320": ultraface_rfb320,
 }
 
 

@@ -16,7 +16,7 @@ from paella_b200 import packer  # noqa: E402
 INPUTS = {"mnist": ((1, 28, 28), "uniform"), "resnet18": ((3, 224, 224), "normal"), "inception_v3": ((3, 299, 299), "normal"),
           "resnet50": ((3, 224, 224), "normal"), "mobilenet": ((3, 224, 224), "normal"), "resnet34": ((3, 224, 224), "normal"),
           "squeezenet1_1": ((3, 224, 224), "normal"), "googlenet": ((3, 224, 224), "normal"), "densenet121": ((3, 224, 224), "normal"),
-          "arcfaceresnet100": ((3, 112, 112), "normal")}
+          "arcfaceresnet100": ((3, 112, 112), "normal"), "ultraface320": ((3, 240, 320), "normal")}
 
 
 def make_input(model, seed=5):

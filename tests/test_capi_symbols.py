@@ -37,7 +37,7 @@ def test_plugins_export_init_job_and_load_without_cuda_context():
     """Clients dlopen a plugin only to read its I/O sizes (src/client/client.cpp:64-76)."""
     import ctypes as C
     capi.load()
-    for job in ["tvm_mnist", "tvm_resnet18", "tvm_resnet34", "tvm_resnet50", "tvm_mobilenet", "tvm_inception_v3", "tvm_squeezenet1_1", "tvm_googlenet", "tvm_densenet121", "tvm_arcfaceresnet100", "vec_add",
+    for job in ["tvm_mnist", "tvm_resnet18", "tvm_resnet34", "tvm_resnet50", "tvm_mobilenet", "tvm_inception_v3", "tvm_squeezenet1_1", "tvm_googlenet", "tvm_densenet121", "tvm_arcfaceresnet100", "tvm_ultraface320", "vec_add",
                 "dummy_short", "dummy_long"]:
         lib = C.CDLL(capi.plugin_path(job))
         assert hasattr(lib, "init_job")

@@ -151,7 +151,7 @@ class Batched:
 
 
 @pytest.mark.parametrize("model,precision,shape", [("mnist", 0, (1, 28, 28)), ("resnet18", 1, (3, 224, 224)), ("inception_v3", 1, (3, 299, 299)),
-                                                   ("mobilenet", 1, (3, 224, 224))])
+                                                   ("mobilenet", 1, (3, 224, 224)), ("ultraface320", 1, (3, 240, 320))])
 def test_gang_of_four_equals_four_single_runs_bit_for_bit(models_dir, model, precision, shape):
     """With the reduction split switched off on both sides, a gang's logits are the bits of the single runs,
     kernel by kernel and as stage-group graphs, for every gang size up to the capacity."""

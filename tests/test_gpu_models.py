@@ -225,6 +225,35 @@ def test_arcface_embedding(models_dir):
     m.close()
 
 
+def test_ultraface_detector(models_dir):
+    """The 320x240 face detector: dilated convolutions in its receptive-field block, four detection heads writing
+    one output block [4420 x 2 scores | 4420 x 4 boxes].  fp32 path: 1e-4 of the output range against the
+    committed oracle output.  bf16 path: scores and boxes within 3e-2 absolute of the bf16-emulating oracle
+    (scores lie in [0, 1], boxes are relative to the image), and the face / background decision of a prior equals
+    the fp32 oracle's wherever that oracle's score is at least 0.1 away from 0.5."""
+    ref = GOLDEN["ultraface320"]
+    x = make_input("ultraface320")
+    m = Model(os.path.join(models_dir, packer.pack_file_name("ultraface320")), 0)
+    assert m.L.pb_model_output_bytes(m.m) == 4420 * 6 * 4 and m.L.pb_model_input_bytes(m.m) == 240 * 320 * 3 * 4
+    assert m.kinds().count(capi.STAGE_DETECT) == 4
+    y32 = m.run(x)
+    assert float(np.abs(y32 - ref).max()) <= 1e-4 * float(np.abs(ref).max())
+    np.testing.assert_array_equal(m.run_groups(x), y32)
+    m.close()
+    m = Model(os.path.join(models_dir, packer.pack_file_name("ultraface320")), 1)
+    kinds = m.kinds()
+    assert kinds.count(capi.STAGE_DETECT) == 4 and kinds.count(capi.STAGE_CONV_UMMA) >= 25 and kinds.count(capi.STAGE_DWCONV) == 18
+    y = m.run(x)
+    emu = og.run(og.Pack(packer.ultraface_rfb320(seed=1234).to_bytes()), x, emulate_bf16=True)
+    assert float(np.abs(y - emu).max()) <= 3e-2, float(np.abs(y - emu).max())
+    face_ref, face = ref[1:8840:2], y[1:8840:2]
+    sure = np.abs(face_ref - 0.5) >= 0.1
+    assert sure.sum() > 3000 and ((face[sure] > 0.5) == (face_ref[sure] > 0.5)).all()
+    np.testing.assert_allclose(y[:8840:2] + y[1:8840:2], 1.0, atol=1e-6)
+    np.testing.assert_array_equal(m.run_groups(x), y)
+    m.close()
+
+
 def test_same_input_same_output_and_instances_are_independent(models_dir):
     m = Model(os.path.join(models_dir, packer.pack_file_name("resnet18")), 1)
     i2 = C.c_void_p()

@@ -38,14 +38,14 @@ def _assert_close(got, ref, dtype):
 
 
 def _run_conv(kind, dtype, C_, H, W, K, R, S, sh, sw, ph, pw, groups=1, act=1, residual=False, out_total=None, off=0, bias=True,
-              scratch=False):
+              scratch=False, dilation=(1, 1)):
     import torch
     L = capi.load()
     x = RNG.standard_normal((C_, H, W), dtype=np.float32)
     w = (RNG.standard_normal((K, C_ // groups, R, S), dtype=np.float32) * np.float32(np.sqrt(2.0 / (C_ // groups * R * S))))
     b = RNG.standard_normal(K, dtype=np.float32) * np.float32(0.1) if bias else np.zeros(K, np.float32)
-    P = (H + 2 * ph - R) // sh + 1
-    Q = (W + 2 * pw - S) // sw + 1
+    P = (H + 2 * ph - dilation[0] * (R - 1) - 1) // sh + 1
+    Q = (W + 2 * pw - dilation[1] * (S - 1) - 1) // sw + 1
     res = RNG.standard_normal((K, P, Q), dtype=np.float32) if residual else None
     if dtype == 1:
         x, w = og.round_bf16(x), og.round_bf16(w)
@@ -54,6 +54,7 @@ def _run_conv(kind, dtype, C_, H, W, K, R, S, sh, sw, ph, pw, groups=1, act=1, r
     xd, cs = gu.to_device_cl(x, dtype)
     yd, ks = gu.empty_cl(P, Q, out_total, dtype, fill=7.0)
     p = _params(dtype, (C_, H, W), K, P, Q, ks, R, S, sh, sw, ph, pw, groups, act, 0, off, cs)
+    p.dil_h, p.dil_w = dilation
     if residual:
         rd, rcs = gu.to_device_cl(res, dtype)
         p.residual, p.res_Cs = rd.data_ptr(), rcs
@@ -73,7 +74,7 @@ def _run_conv(kind, dtype, C_, H, W, K, R, S, sh, sw, ph, pw, groups=1, act=1, r
         capi.check(L.pb_op_info(kind, C.byref(p), C.byref(li)), "pb_op_info")
         assert li.num_blocks > unsplit_blocks
         launches = 3          # the tile counters must be back at zero after every launch
-    ref = og.conv2d(x, w, b, (sh, sw), (ph, pw), groups, act, res)
+    ref = og.conv2d(x, w, b, (sh, sw), (ph, pw), groups, act, res, dilation=dilation)
     for _ in range(launches):
         yd.fill_(7.0)
         capi.check(L.pb_op_launch(kind, C.byref(p), None, 0, None), "pb_op_launch")
@@ -99,6 +100,25 @@ SIMT_CASES = [
 @pytest.mark.parametrize("case", SIMT_CASES)
 def test_conv_simt(case, dtype):
     _run_conv(capi.STAGE_CONV_SIMT, dtype, *case, act=1, residual=(case[3] % 8 == 0))
+
+
+# dilated filters (the receptive-field block of the face detector: 3x3 dilated by 2, 3 and 5 with equal padding)
+DILATED_CASES = [
+    # C, H, W, K, R, S, sh, sw, ph, pw, (dil_h, dil_w)
+    (16, 30, 40, 16, 3, 3, 1, 1, 2, 2, (2, 2)), (16, 30, 40, 16, 3, 3, 1, 1, 3, 3, (3, 3)), (16, 30, 40, 16, 3, 3, 1, 1, 5, 5, (5, 5)),
+    (24, 19, 23, 32, 3, 3, 2, 2, 2, 1, (2, 1)), (64, 14, 14, 64, 3, 3, 1, 1, 0, 0, (2, 3)), (8, 9, 9, 8, 2, 2, 1, 1, 0, 0, (4, 4)),
+]
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("case", DILATED_CASES)
+def test_conv_simt_dilated(case, dtype):
+    _run_conv(capi.STAGE_CONV_SIMT, dtype, *case[:10], act=1, dilation=case[10])
+
+
+@pytest.mark.parametrize("case", DILATED_CASES)
+def test_conv_umma_dilated(case):
+    _run_conv(capi.STAGE_CONV_UMMA, 1, *case[:10], act=0, residual=True, dilation=case[10])
 
 
 def test_conv_simt_grouped_and_slice():

@@ -29,6 +29,9 @@ def _load_into_torch(model, g, bn_eps, folded=lambda name: True):
                     mods[name + "_prelu"].weight.copy_(torch.from_numpy(pack.weights[boff + cout: boff + 2 * cout]))
                 if m.bias is None:           # conv + batch-norm: the pack holds the folded weight
                     m.weight.copy_(torch.from_numpy(w * np.float32(scale if folded(name) else 1.0)))
+                    if name + "_bn" in mods:     # a non-zero folded bias is the batch-norm's beta (mean 0)
+                        mods[name + "_bn"].bias.copy_(torch.from_numpy(pack.weights[boff: boff + cout]))
+                        loaded_bn.add(name + "_bn")
                 else:                        # plain biased convolution
                     m.weight.copy_(torch.from_numpy(w))
                     m.bias.copy_(torch.from_numpy(pack.weights[boff: boff + cout]))
@@ -98,7 +101,92 @@ class ArcFaceR100(nn.Module):
         return self.pre_fc1(torch.flatten(self.bn1(x), 1))
 
 
+class UltraFaceRFB320(nn.Module):
+    """The 320x240 receptive-field-block face detector written out in torch, modules named after the pack's
+    operators; its post-processing (softmax scores, prior decoding to corner-form boxes) as torch tensor code with
+    priors generated here.  Returns [4420*2 scores | 4420*4 boxes] flattened."""
+
+    def __init__(self):
+        super().__init__()
+        eps = 1e-5
+        self.relu_of = {}
+
+        def cb(name, cin, cout, k, stride=1, pad=0, dil=1, groups=1, relu=True):
+            setattr(self, name, nn.Conv2d(cin, cout, k, stride, pad, dilation=dil, groups=groups, bias=False))
+            setattr(self, name + "_bn", nn.BatchNorm2d(cout, eps=eps))
+            self.relu_of[name] = relu
+
+        def dw(name, cin, cout, stride):
+            cb(name + "_dw", cin, cin, 3, stride, 1, groups=cin)
+            cb(name + "_pw", cin, cout, 1)
+
+        cb("base_0", 3, 16, 3, 2, 1)
+        chans = [(16, 32, 1), (32, 32, 2), (32, 32, 1), (32, 64, 2), (64, 64, 1), (64, 64, 1)]
+        for i, (ci, co, st) in enumerate(chans):
+            dw(f"base_{i + 1}", ci, co, st)
+        n, inter = "base_7", 8
+        cb(n + "_b0_0", 64, inter, 1, relu=False); cb(n + "_b0_1", inter, 16, 3, 1, 1); cb(n + "_b0_2", 16, 16, 3, 1, 2, 2, relu=False)
+        cb(n + "_b1_0", 64, inter, 1, relu=False); cb(n + "_b1_1", inter, 16, 3, 1, 1); cb(n + "_b1_2", 16, 16, 3, 1, 3, 3, relu=False)
+        cb(n + "_b2_0", 64, inter, 1, relu=False); cb(n + "_b2_1", inter, 12, 3, 1, 1); cb(n + "_b2_2", 12, 16, 3, 1, 1)
+        cb(n + "_b2_3", 16, 16, 3, 1, 5, 5, relu=False)
+        cb(n + "_shortcut", 64, 64, 1, relu=False); cb(n + "_linear", 48, 64, 1, relu=False)
+        dw("base_8", 64, 128, 2); dw("base_9", 128, 128, 1); dw("base_10", 128, 128, 1)
+        dw("base_11", 128, 256, 2); dw("base_12", 256, 256, 1)
+        self.extras_0 = nn.Conv2d(256, 64, 1)
+        self.extras_1_dw = nn.Conv2d(64, 64, 3, 2, 1, groups=64)
+        self.extras_1_pw = nn.Conv2d(64, 256, 1)
+        for i, (c, a) in enumerate(zip((64, 128, 256), (3, 2, 2))):
+            for kind, per in (("cls", 2), ("reg", 4)):
+                setattr(self, f"{kind}_{i}_dw", nn.Conv2d(c, c, 3, 1, 1, groups=c))
+                setattr(self, f"{kind}_{i}_pw", nn.Conv2d(c, a * per, 1))
+        self.cls_3 = nn.Conv2d(256, 3 * 2, 3, 1, 1)
+        self.reg_3 = nn.Conv2d(256, 3 * 4, 3, 1, 1)
+        # priors: per feature map, rows then columns then box sizes; (cx, cy, w, h) relative to 320 x 240
+        pri = []
+        for (fw, fh), boxes in zip(((40, 30), (20, 15), (10, 8), (5, 4)), ((10, 16, 24), (32, 48), (64, 96), (128, 192, 256))):
+            for j in range(fh):
+                for i in range(fw):
+                    for mb in boxes:
+                        pri.append([(i + 0.5) / fw, (j + 0.5) / fh, mb / 320.0, mb / 240.0])
+        self.register_buffer("priors", torch.tensor(pri, dtype=torch.float32).clamp(0.0, 1.0))
+
+    def _c(self, name, x):
+        x = getattr(self, name + "_bn")(getattr(self, name)(x))
+        return torch.relu(x) if self.relu_of[name] else x
+
+    def _dw(self, name, x):
+        return self._c(name + "_pw", self._c(name + "_dw", x))
+
+    def forward(self, x):
+        x = self._c("base_0", x)
+        for i in range(1, 7):
+            x = self._dw(f"base_{i}", x)
+        n = "base_7"
+        b0 = self._c(n + "_b0_2", self._c(n + "_b0_1", self._c(n + "_b0_0", x)))
+        b1 = self._c(n + "_b1_2", self._c(n + "_b1_1", self._c(n + "_b1_0", x)))
+        b2 = self._c(n + "_b2_3", self._c(n + "_b2_2", self._c(n + "_b2_1", self._c(n + "_b2_0", x))))
+        f0 = torch.relu(self._c(n + "_linear", torch.cat([b0, b1, b2], 1)) + self._c(n + "_shortcut", x))
+        f1 = self._dw("base_10", self._dw("base_9", self._dw("base_8", f0)))
+        f2 = self._dw("base_12", self._dw("base_11", f1))
+        f3 = torch.relu(self.extras_1_pw(torch.relu(self.extras_1_dw(torch.relu(self.extras_0(f2))))))
+        conf, loc = [], []
+        for i, f in enumerate((f0, f1, f2)):
+            c = getattr(self, f"cls_{i}_pw")(torch.relu(getattr(self, f"cls_{i}_dw")(f)))
+            r = getattr(self, f"reg_{i}_pw")(torch.relu(getattr(self, f"reg_{i}_dw")(f)))
+            conf.append(c.permute(0, 2, 3, 1).reshape(c.shape[0], -1, 2))
+            loc.append(r.permute(0, 2, 3, 1).reshape(r.shape[0], -1, 4))
+        conf.append(self.cls_3(f3).permute(0, 2, 3, 1).reshape(x.shape[0], -1, 2))
+        loc.append(self.reg_3(f3).permute(0, 2, 3, 1).reshape(x.shape[0], -1, 4))
+        conf, loc = torch.cat(conf, 1), torch.cat(loc, 1)
+        scores = torch.softmax(conf, dim=2)
+        centre = loc[..., :2] * 0.1 * self.priors[..., 2:] + self.priors[..., :2]
+        size = torch.exp(loc[..., 2:] * 0.2) * self.priors[..., 2:]
+        boxes = torch.cat([centre - size / 2, centre + size / 2], dim=2)
+        return torch.cat([scores.reshape(x.shape[0], -1), boxes.reshape(x.shape[0], -1)], 1)
+
+
 CASES = [
+    ("ultraface320", UltraFaceRFB320, 1e-5, (240, 320)),
     ("arcfaceresnet100", ArcFaceR100, 2e-5, 112),
     ("resnet18", lambda: torchvision.models.resnet18(weights=None), 1e-5, 224),
     ("resnet34", lambda: torchvision.models.resnet34(weights=None), 1e-5, 224),
@@ -114,19 +202,23 @@ CASES = [
 
 @pytest.mark.parametrize("name,ctor,eps,size", CASES, ids=[c[0] for c in CASES])
 def test_pack_matches_torchvision(oracle_lib, name, ctor, eps, size):
-    kw = {"bias_std": 0.1} if name == "squeezenet1_1" else {}      # the one model whose convolutions carry biases
+    kw = {"bias_std": 0.1} if name in ("squeezenet1_1", "ultraface320") else {}      # the models whose convolutions carry biases
     g = packer.MODELS[name](seed=1234, **kw)
     model = ctor().eval()
     # DenseNet: only conv0 and every conv1 are followed by a batch-norm; conv2 and the transition convs are not
     folded = (lambda n: n.endswith("conv0") or n.endswith("conv1")) if name == "densenet121" else (lambda n: True)
     pack = _load_into_torch(model, g, eps, folded)
-    x = np.random.default_rng(5).standard_normal((3, size, size), dtype=np.float32)
+    hw = size if isinstance(size, tuple) else (size, size)
+    x = np.random.default_rng(5).standard_normal((3,) + hw, dtype=np.float32)
     with torch.no_grad():
         ref = model(torch.from_numpy(x)[None])[0].numpy()
     got = og.run(pack, x)
     scale = np.abs(ref).max()
     assert np.abs(got - ref).max() <= 2e-4 * scale
-    assert int(got.argmax()) == int(ref.argmax())
+    if name == "ultraface320":       # a detector: the face / background decision of every prior, not one arg-max
+        assert got.size == 4420 * 6 and ((got[:8840:2] > 0.5) == (ref[:8840:2] > 0.5)).mean() > 0.999
+    else:
+        assert int(got.argmax()) == int(ref.argmax())
 
 
 def test_mnist_pack_matches_torch(oracle_lib):
