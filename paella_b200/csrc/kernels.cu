@@ -501,6 +501,244 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
     PB_NOTIFY_END();
 }
 
+// ---- 3x3 windows over tensors that fill the GPU many times over -------------------------------------------
+// window3_strip_kernel loads every input row three times (once per output row it belongs to) and converts
+// it to fp32 each time: about 300 instructions per output vector of 8 bf16 channels, which is what bounds
+// it (28 % of the copy bandwidth for the depthwise case; 70 % of the issue slots busy).  window3_tile_kernel
+// below lets a thread own TWO channels (one 32-bit word of bf16) of a strip of output columns and walk down
+// the output rows: each input row is read and converted ONCE and feeds the (up to) three output rows it
+// belongs to, whose accumulators stay in registers, as do the 18 filter values and the 2 biases of the
+// thread's channels.  Max pooling compares the bf16 pairs themselves (a maximum needs no wider type);
+// ReLU / ReLU6 clamp the rounded bf16 pair (rounding is monotonic and 0 and 6 are bf16 values, so clamping
+// after rounding equals rounding after clamping).  Taps outside the tensor contribute the neutral element
+// (0 for sums and products, -inf for max), which leaves every partial result as it is: the additions per
+// output happen in the order of dwconv_kernel / pool_kernel (filter rows, then columns), so the results
+// are theirs bit for bit (finite filter values assumed).  bf16 only.
+constexpr int kRollStrip1 = 4, kRollStrip2 = 2;
+__device__ __forceinline__ f2_t pair_of(uint32_t u) { return f2_pack(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u)); }
+__device__ __forceinline__ uint32_t bits_of(__nv_bfloat162 h) { return *reinterpret_cast<const uint32_t*>(&h); }
+__device__ __forceinline__ __nv_bfloat162 bf2_of(uint32_t u) { return *reinterpret_cast<const __nv_bfloat162*>(&u); }
+
+// What a thread keeps per (output, channel pair): fp32 pairs for sums, the bf16 pair itself for a maximum.
+template <int kMode> struct RollAcc { typedef f2_t type; };
+template <> struct RollAcc<kWinMax> { typedef uint32_t type; };
+template <int kMode> __device__ __forceinline__ typename RollAcc<kMode>::type roll_neutral() { return f2_pack(0.f, 0.f); }
+template <> __device__ __forceinline__ uint32_t roll_neutral<kWinMax>() { return 0xff80ff80u; }       // (-inf, -inf)
+template <int kMode> __device__ __forceinline__ typename RollAcc<kMode>::type roll_value(uint32_t raw) { return pair_of(raw); }
+template <> __device__ __forceinline__ uint32_t roll_value<kWinMax>(uint32_t raw) { return raw; }
+__device__ __forceinline__ f2_t roll_op(f2_t acc, f2_t x, f2_t w, bool dw) { return dw ? f2_fma(x, w, acc) : f2_add(acc, x); }
+__device__ __forceinline__ uint32_t roll_op(uint32_t acc, uint32_t x, f2_t, bool) { return bits_of(__hmax2(bf2_of(acc), bf2_of(x))); }
+
+// One finished output (two channels) -> bf16 pair.  kAct: 0 none, 1 ReLU, 2 ReLU6 (depthwise only).  div / inv: the
+// average pool's divisor and its reciprocal.
+template <int kMode, int kAct>
+__device__ __forceinline__ uint32_t roll_finish(f2_t acc, float b0, float b1, float div, float inv) {
+    float v0, v1;
+    f2_unpack(acc, v0, v1);
+    if (kMode == kWinDw) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v0 + b0, v1 + b1);
+        if (kAct >= 1) h = __hmax2(h, bf2_of(0u));
+        if (kAct == 2) h = __hmin2(h, bf2_of(0x40c040c0u));          // (6, 6)
+        return bits_of(h);
+    }
+    // correctly rounded v / div without the division sequence (see window3_strip_kernel)
+    const float q0 = v0 * inv, q1 = v1 * inv;
+    const float r0 = fmaf(-div, q0, v0), r1 = fmaf(-div, q1, v1);
+    v0 = fabsf(q0) <= 3.0e38f ? fmaf(r0, inv, q0) : q0;
+    v1 = fabsf(q1) <= 3.0e38f ? fmaf(r1, inv, q1) : q1;
+    return bits_of(__floats2bfloat162_rn(v0, v1));
+}
+template <int kMode, int kAct>
+__device__ __forceinline__ uint32_t roll_finish(uint32_t acc, float, float, float, float) { return acc; }
+
+// ---- 3x3 windows over large tensors, staged through shared memory ---------------------------------------
+// Reading the rows with 4-byte global loads spends a third of the instructions on addresses (every load needs
+// its own 64-bit address; measured on a first version that did so).  Here a block of 8 warps owns a tile of kTileRows x (8 * strip) outputs of ONE slab of
+// 64 channels.  It first copies the tile's input window into shared memory with 16-byte cp.async (zero-filled
+// outside the tensor; 78 KB in flight per block), then every warp walks down its strip of output columns with
+// lane l holding channels 2l, 2l+1 of the slab: all its shared-memory loads are at compile-time offsets from
+// one pointer that advances once per three rows, and consecutive lanes read consecutive words (no bank
+// conflict).  The results are the bits of every other 3x3 kernel here.
+constexpr int kTileSlab = 64;                       // channels per block
+#ifndef PB_TILE_ROWS1
+#define PB_TILE_ROWS1 13
+#endif
+#ifndef PB_TILE_ROWS2
+#define PB_TILE_ROWS2 6
+#endif
+#ifndef PB_TILE_BLOCKS
+#define PB_TILE_BLOCKS 3
+#endif
+constexpr int kTileRows1 = PB_TILE_ROWS1, kTileRows2 = PB_TILE_ROWS2;      // output rows per block at stride 1 / 2
+
+template <int kStride> struct TileGeom {
+    static constexpr int kStrip = kStride == 1 ? kRollStrip1 : kRollStrip2;
+    static constexpr int kRows = kStride == 1 ? kTileRows1 : kTileRows2;
+    static constexpr int kOutCols = 8 * kStrip;
+    static constexpr int kInCols = (kOutCols - 1) * kStride + 3;
+    static constexpr int kInRows = (kRows - 1) * kStride + 3;
+    static constexpr int kSmemBytes = kInRows * kInCols * kTileSlab * 2;
+};
+
+template <int kMode, int kStride>
+__global__ void __launch_bounds__(256, PB_TILE_BLOCKS) window3_tile_kernel(OpArgs a, uint32_t job_id, FinishedBlockNotifier* nf) {
+    PB_NOTIFY_START();
+    typedef __nv_bfloat16 T;
+    typedef TileGeom<kStride> G;
+    typedef typename RollAcc<kMode>::type Acc;
+    constexpr int kStrip = G::kStrip, kCols = (kStrip - 1) * kStride + 3;
+    constexpr bool kDw = kMode == kWinDw;
+    extern __shared__ __align__(16) unsigned char s_tile[];
+
+    const int slabs = (a.Cs + kTileSlab - 1) / kTileSlab;
+    const int col_tiles = (a.Q + G::kOutCols - 1) / G::kOutCols;
+    int b = blockIdx.x;
+    const int slab = b % slabs; b /= slabs;
+    const int q_tile = (b % col_tiles) * G::kOutCols;
+    const int p_tile = (b / col_tiles) * G::kRows;
+    const int ih0 = p_tile * kStride - a.pad_h, iw0 = q_tile * kStride - a.pad_w;
+    const int ch0 = slab * kTileSlab;
+
+    // ---- fill: pixel (r, c) of the window is 8 vectors of 8 channels.  A thread keeps its eighth of the pixel and
+    // moves 32 pixels on per turn (the window is at least 32 pixels wide: at most one row wrap per turn). ----
+    {
+        static_assert(G::kInCols >= 32, "one row wrap per turn of the fill");
+        const T* __restrict__ x = x_img<T>(a);
+        const int ch = ch0 + (threadIdx.x & 7) * 8;
+        const bool ch_ok = ch < a.Cs;
+        int pix = threadIdx.x >> 3;
+        int r = pix / G::kInCols, c = pix - r * G::kInCols;
+        uint32_t dst = (uint32_t)__cvta_generic_to_shared(s_tile) + threadIdx.x * 16u;
+        for (; pix < G::kInRows * G::kInCols; pix += 32, dst += 32u * 128u) {
+            const int ih = ih0 + r, iw = iw0 + c;
+            const bool ok = ch_ok && (unsigned)ih < (unsigned)a.H && (unsigned)iw < (unsigned)a.W;
+            if (kMode == kWinMax && !ok) {
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0xff80ff80u) : "memory");
+            } else {
+                const T* src = ok ? x + (size_t)(ih * a.W + iw) * a.Cs + ch : x;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16u : 0u) : "memory");
+            }
+            c += 32;
+            if (c >= G::kInCols) { c -= G::kInCols; ++r; }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+    }
+
+    // ---- walk: warp = strip of output columns, lane = channel pair ----
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c0 = ch0 + lane * 2;
+    const int q0 = q_tile + warp * kStrip;
+    if (c0 < a.Cs && q0 < a.Q) {
+        const Acc neutral = roll_neutral<kMode>();
+        f2_t w[3][3];
+        float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int s2 = 0; s2 < 3; ++s2) w[r][s2] = f2_pack(0.f, 0.f);
+        if (kDw) {
+            const T* wp = static_cast<const T*>(a.w) + c0;
+#pragma unroll
+            for (int r = 0; r < 3; ++r)
+#pragma unroll
+                for (int s2 = 0; s2 < 3; ++s2) w[r][s2] = pair_of(__ldg(reinterpret_cast<const uint32_t*>(wp + (r * 3 + s2) * a.Cs)));
+            if (a.bias) { b0 = c0 < a.K ? a.bias[c0] : 0.f; b1 = c0 + 1 < a.K ? a.bias[c0 + 1] : 0.f; }
+        }
+        const int nt = min(kStrip, a.Q - q0);
+        const int c_lim = kDw ? a.K : a.C;
+        const uint32_t keep = c0 + 1 < c_lim ? 0xffffffffu : (c0 < c_lim ? 0x0000ffffu : 0u);
+        const int p_end = min(p_tile + G::kRows, a.P);
+        const bool count_pad = (a.flags & 1) != 0;
+        const float inv9 = 1.f / 9.f;
+        T* __restrict__ y = y_img<T>(a) + a.out_c_off + c0;
+        // word (r, col) of this thread: s_row[r * kRowWords + col * 32]
+        constexpr int kRowWords = G::kInCols * (kTileSlab / 2);
+        const uint32_t* s_row = reinterpret_cast<const uint32_t*>(s_tile) + (warp * kStrip * kStride) * (kTileSlab / 2) + lane;
+
+        auto load_row = [&](int r, Acc (&xv)[kCols]) {
+#pragma unroll
+            for (int col = 0; col < kCols; ++col) xv[col] = roll_value<kMode>(s_row[r * kRowWords + col * (kTileSlab / 2)]);
+        };
+        auto row_into = [&](Acc (&acc)[kStrip], const Acc (&xv)[kCols], int r) {
+#pragma unroll
+            for (int t = 0; t < kStrip; ++t)
+#pragma unroll
+                for (int s2 = 0; s2 < 3; ++s2) acc[t] = roll_op(acc[t], xv[t * kStride + s2], w[r][s2], kDw);
+        };
+        const bool full = nt == kStrip && keep == 0xffffffffu;      // every output of the strip and both channels exist
+        // one output row of the strip; ACT and FULL are literals so that the loop body carries no test of them
+#define PB_TILE_STORE_ROW(ACT, FULL)                                                                                             \
+    do {                                                                                                                         \
+        _Pragma("unroll") for (int t = 0; t < kStrip; ++t) {                                                                     \
+            if (!(FULL) && t >= nt) break;                                                                                       \
+            if (kMode == kWinAvg && !count_pad) {                                                                                \
+                const int cols_in = max(min((q0 + t) * kStride - a.pad_w + 3, a.W) - max((q0 + t) * kStride - a.pad_w, 0), 0);   \
+                const int cnt = rows_in * cols_in;                                                                               \
+                if (cnt != 9) { div = (float)(cnt > 0 ? cnt : 1); inv = 1.f / div; }                                             \
+                else { div = 9.f; inv = inv9; }                                                                                  \
+            }                                                                                                                    \
+            const uint32_t o = roll_finish<kMode, ACT>(acc[t], b0, b1, div, inv);                                                \
+            *reinterpret_cast<uint32_t*>(yrow + (size_t)t * a.Ks) = (FULL) ? o : (o & keep);                                     \
+        }                                                                                                                        \
+    } while (0)
+        auto close_row = [&](Acc (&acc)[kStrip], int p) {
+            if (p >= p_tile && p < p_end) {
+                int rows_in = 3;
+                float div = 9.f, inv = inv9;
+                if (kMode == kWinAvg && !count_pad) rows_in = min(p * kStride - a.pad_h + 3, a.H) - max(p * kStride - a.pad_h, 0);
+                T* yrow = y + ((size_t)p * a.Q + q0) * a.Ks;
+                const int act = kDw ? a.act : 0;
+                if (full) {
+                    if (act == 2) PB_TILE_STORE_ROW(2, true);
+                    else if (act == 1) PB_TILE_STORE_ROW(1, true);
+                    else PB_TILE_STORE_ROW(0, true);
+                } else {
+                    if (act == 2) PB_TILE_STORE_ROW(2, false);
+                    else if (act == 1) PB_TILE_STORE_ROW(1, false);
+                    else PB_TILE_STORE_ROW(0, false);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < kStrip; ++t) acc[t] = neutral;
+        };
+#undef PB_TILE_STORE_ROW
+
+        if (kStride == 1) {
+            // window row r opens output row p_tile + r (filter row 0), continues p_tile + r - 1, closes p_tile + r - 2
+            Acc accA[kStrip], accB[kStrip], accC[kStrip];
+#pragma unroll
+            for (int t = 0; t < kStrip; ++t) accA[t] = accB[t] = accC[t] = neutral;
+            static_assert(kStride != 1 || G::kInRows % 3 == 0, "the stride-1 walk takes three window rows per turn");
+#pragma unroll 1
+            for (int r = 0; r < G::kInRows; r += 3) {
+                Acc xv[kCols];
+                load_row(r, xv);     row_into(accB, xv, 2); row_into(accC, xv, 1); row_into(accA, xv, 0); close_row(accB, p_tile + r - 2);
+                load_row(r + 1, xv); row_into(accC, xv, 2); row_into(accA, xv, 1); row_into(accB, xv, 0); close_row(accC, p_tile + r - 1);
+                load_row(r + 2, xv); row_into(accA, xv, 2); row_into(accB, xv, 1); row_into(accC, xv, 0); close_row(accA, p_tile + r);
+            }
+        } else {
+            // window row r: even r closes output row p_tile + r/2 - 1 (filter row 2) and opens p_tile + r/2 (row 0);
+            // odd r is filter row 1 of p_tile + (r - 1)/2
+            Acc acc[kStrip];
+#pragma unroll
+            for (int t = 0; t < kStrip; ++t) acc[t] = neutral;
+#pragma unroll 1
+            for (int r = 0; r + 1 < G::kInRows; r += 2) {
+                Acc xv[kCols];
+                load_row(r, xv);     row_into(acc, xv, 2); close_row(acc, p_tile + r / 2 - 1); row_into(acc, xv, 0);
+                load_row(r + 1, xv); row_into(acc, xv, 1);
+            }
+            Acc xv[kCols];
+            load_row(G::kInRows - 1, xv);
+            row_into(acc, xv, 2);
+            close_row(acc, p_tile + (G::kInRows - 1) / 2 - 1);
+        }
+    }
+    PB_NOTIFY_END();
+}
+
 // ---- global average pool: [HW][Cs] -> [Cs] ---------------------------------------
 // Block = 32 channel vectors x 8 pixel groups; shared-memory reduction over the groups.
 template <typename T>
@@ -893,6 +1131,28 @@ static size_t strip_threads(const pb_op_params* p, int strip) {
     return (size_t)p->P * ((p->Q + strip - 1) / strip) * (p->Cs / vec_n(p->dtype));
 }
 
+// Blocks of window3_tile_kernel for one image, or 0 when the layer keeps the strip kernels: bf16, a 3x3 window of stride 1
+// or 2, and at least two full waves of blocks (two blocks per SM).  PB_WINDOW_TILE=0 switches it off;
+// PB_WINDOW_TILE_MIN_BLOCKS sets another threshold (tests use 1).  Read at every call: this runs when a launch is built
+// (graph capture, direct operator calls), never on the replay path.
+static uint32_t tile_blocks(const pb_op_params* p) {
+    if (p->dtype != 1 || (p->Cs & 7) || (p->Ks & 1) || (p->out_c_off & 1) || strip_of(p) == 0) return 0;
+    const char* e = getenv("PB_WINDOW_TILE");
+    if (e && e[0] == '0') return 0;
+    size_t least = (size_t)148 * 2 * 2;
+    if (const char* m = getenv("PB_WINDOW_TILE_MIN_BLOCKS")) least = (size_t)strtoull(m, nullptr, 10);
+    const int rows = p->stride_h == 1 ? TileGeom<1>::kRows : TileGeom<2>::kRows;
+    const int cols = p->stride_h == 1 ? TileGeom<1>::kOutCols : TileGeom<2>::kOutCols;
+    const size_t n = (size_t)((p->Cs + kTileSlab - 1) / kTileSlab) * ((p->Q + cols - 1) / cols) * ((p->P + rows - 1) / rows);
+    return n * (size_t)batch_of(p) >= least ? (uint32_t)n : 0;
+}
+static const void* tile_fn(int kind, int stride) {
+#define PB_TILE(M) (stride == 1 ? (const void*)window3_tile_kernel<M, 1> : (const void*)window3_tile_kernel<M, 2>)
+    return kind == PB_STAGE_DWCONV ? PB_TILE(kWinDw) : kind == PB_STAGE_MAXPOOL ? PB_TILE(kWinMax) : PB_TILE(kWinAvg);
+#undef PB_TILE
+}
+static uint32_t tile_smem(int stride) { return stride == 1 ? TileGeom<1>::kSmemBytes : TileGeom<2>::kSmemBytes; }
+
 template <int kMode>
 static const void* window3_fn(bool f32, int stride, int strip) {
 #define PB_W3(T) (stride == 1 ? (strip == 1 ? (const void*)window3_strip_kernel<T, kMode, 1, 1> : (const void*)window3_strip_kernel<T, kMode, 1, kStripWide1>) \
@@ -925,7 +1185,9 @@ static int info_one_image(int kind, const pb_op_params* p, pb_launch_info* out) 
             }
             out->num_blocks = blocks_for((size_t)p->H * p->W);
             out->regs_per_thread = f32 ? regs_of(input_transform_kernel<float>) : regs_of(input_transform_kernel<__nv_bfloat16>);
-            out->bytes = in_elems * 4 + in_elems * es;
+            // the output is counted as laid out, Ks channels per pixel: the zero padding up to the vector width is part
+            // of the format the convolutions read
+            out->bytes = in_elems * 4 + (size_t)p->H * p->W * p->Ks * es;
             break;
         case PB_STAGE_CONV_SIMT:
             out->num_blocks = blocks_for((size_t)p->P * p->Q * p->K);
@@ -942,6 +1204,11 @@ static int info_one_image(int kind, const pb_op_params* p, pb_launch_info* out) 
                 out->regs_per_thread = regs_of(window3_fn(kind, f32, p->stride_h, strip));
                 out->smem_per_block = strip > 1 ? (uint32_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2) : 0;
             }
+            if (const uint32_t nblk = tile_blocks(p)) {
+                out->num_blocks = nblk;
+                out->regs_per_thread = regs_of(tile_fn(kind, p->stride_h));
+                out->smem_per_block = tile_smem(p->stride_h);
+            }
             out->flops = 2ull * out_elems * p->R * p->S;
             out->bytes = es * (in_elems + (size_t)p->K * p->R * p->S + out_elems) + 4ull * p->K;
             break;
@@ -955,6 +1222,11 @@ static int info_one_image(int kind, const pb_op_params* p, pb_launch_info* out) 
             if (const int strip = strip_of(p)) {
                 out->num_blocks = blocks_for(strip_threads(p, strip));
                 out->regs_per_thread = regs_of(window3_fn(kind, f32, p->stride_h, strip));
+            }
+            if (const uint32_t nblk = tile_blocks(p)) {
+                out->num_blocks = nblk;
+                out->regs_per_thread = regs_of(tile_fn(kind, p->stride_h));
+                out->smem_per_block = tile_smem(p->stride_h);
             }
             out->bytes = es * (in_elems + out_elems);
             break;
@@ -1091,6 +1363,13 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
         case PB_STAGE_DWCONV:
             PB_REQUIRE(a.groups == a.C && a.K == a.C, "dwconv: needs groups == C == K");
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "dwconv: output slice must be vector aligned");
+            if (tile_blocks(p)) {
+                const void* fn = tile_fn(kind, p->stride_h);
+                PB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem(p->stride_h)));
+                t_launch_smem = tile_smem(p->stride_h);
+                launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))fn, grid, block, st, pdl, a, job_id, nf);
+                break;
+            }
             if (const int strip = strip_of(p)) {
                 t_launch_smem = strip > 1 ? (size_t)window3_smem_bytes(p->Cs, f32 ? 4 : 2) : 0;
                 launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
@@ -1100,6 +1379,13 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
             break;
         case PB_STAGE_MAXPOOL:
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "pool: output slice must be vector aligned");
+            if (tile_blocks(p)) {
+                const void* fn = tile_fn(kind, p->stride_h);
+                PB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem(p->stride_h)));
+                t_launch_smem = tile_smem(p->stride_h);
+                launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))fn, grid, block, st, pdl, a, job_id, nf);
+                break;
+            }
             if (const int strip = strip_of(p)) {
                 launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
                 break;
@@ -1108,6 +1394,13 @@ int simple_op_launch(int kind, const pb_op_params* p, cudaStream_t st, uint32_t 
             break;
         case PB_STAGE_AVGPOOL:
             PB_REQUIRE((a.Ks % N) == 0 && (a.out_c_off % N) == 0, "pool: output slice must be vector aligned");
+            if (tile_blocks(p)) {
+                const void* fn = tile_fn(kind, p->stride_h);
+                PB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem(p->stride_h)));
+                t_launch_smem = tile_smem(p->stride_h);
+                launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))fn, grid, block, st, pdl, a, job_id, nf);
+                break;
+            }
             if (const int strip = strip_of(p)) {
                 launch_k((void (*)(OpArgs, uint32_t, FinishedBlockNotifier*))window3_fn(kind, f32, p->stride_h, strip), grid, block, st, pdl, a, job_id, nf);
                 break;

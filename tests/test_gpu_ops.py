@@ -428,3 +428,61 @@ def test_pools_large_tensor_use_strips(dtype, s, pad, hw, include_pad):
         else:
             _assert_close(got, ref, dtype)
         assert (full[:8] == 3.0).all() and (full[8 + c:] == 3.0).all()     # channels outside the slice untouched
+
+
+ROLL_CASES = [
+    # C, H, W, stride, pad: ragged strips and row chunks, fewer rows than one chunk, channel counts off the vector width
+    (64, 70, 70, 1, 1), (20, 33, 41, 1, 1), (128, 15, 130, 1, 0), (64, 71, 69, 2, 1), (24, 37, 35, 2, 0), (8, 5, 300, 1, 1), (16, 100, 6, 2, 1),
+]
+
+
+@pytest.mark.parametrize("case", ROLL_CASES)
+def test_tiled_window_kernel_equals_the_strip_kernels_bit_for_bit(case, monkeypatch):
+    """The 3x3 kernel for large tensors (window staged in shared memory, a thread walks down the output rows, each
+    input row read and converted once) against the kernels it replaces, same launch with PB_WINDOW_TILE=0: depthwise convolution with bias and
+    ReLU6, max pool, average pool with and without padding counted, into a channel slice.  Bit-identical, and within
+    the usual tolerance of the oracle."""
+    import torch
+    L = capi.load()
+    C_, H, W, st, pad = case
+    P, Q = (H + 2 * pad - 3) // st + 1, (W + 2 * pad - 3) // st + 1
+    x = og.round_bf16(RNG.standard_normal((C_, H, W), dtype=np.float32))
+    w = og.round_bf16(RNG.standard_normal((C_, 1, 3, 3), dtype=np.float32) * np.float32(0.4))
+    b = RNG.standard_normal(C_, dtype=np.float32) * np.float32(0.1)
+    xd, cs = gu.to_device_cl(x, 1)
+    bd = torch.from_numpy(b).cuda()
+    runs = [("dw", capi.STAGE_DWCONV, 0, og.conv2d(x, w, b, (st, st), (pad, pad), C_, 2)),
+            ("max", capi.STAGE_MAXPOOL, 0, og.maxpool(x, (3, 3), (st, st), (pad, pad))),
+            ("avg", capi.STAGE_AVGPOOL, 1, og.avgpool(x, (3, 3), (st, st), (pad, pad), True)),
+            ("avg_nopad", capi.STAGE_AVGPOOL, 0, og.avgpool(x, (3, 3), (st, st), (pad, pad), False))]
+    for name, kind, flags, ref in runs:
+        outs = {}
+        for variant in ("tile", "0"):
+            monkeypatch.setenv("PB_WINDOW_TILE", "1" if variant == "tile" else "0")
+            monkeypatch.setenv("PB_WINDOW_TILE_MIN_BLOCKS", "1")
+            yd, ks = gu.empty_cl(P, Q, C_ + 16, 1, fill=3.0)
+            prm = _params(1, (C_, H, W), C_, P, Q, ks, 3, 3, st, st, pad, pad, groups=C_ if kind == capi.STAGE_DWCONV else 1,
+                          act=2 if kind == capi.STAGE_DWCONV else 0, flags=flags, out_c_off=8, Cs=cs)
+            prm.x, prm.y = xd.data_ptr(), yd.data_ptr()
+            if kind == capi.STAGE_DWCONV:
+                wd = gu.pack_weights(kind, prm, w)
+                prm.w, prm.bias = wd.data_ptr(), bd.data_ptr()
+            li = capi.LaunchInfo()
+            capi.check(L.pb_op_info(kind, C.byref(prm), C.byref(li)), "pb_op_info")
+            strip = 4 if st == 1 else 2
+            if variant == "tile":
+                assert li.num_blocks == -(-cs // 64) * -(-Q // (8 * strip)) * -(-P // (13 if st == 1 else 6)), name
+            capi.check(L.pb_op_launch(kind, C.byref(prm), None, 0, None), name)
+            gu.sync()
+            assert gu.error_flag() == 0
+            outs[variant] = gu.from_device_cl(yd, C_ + 16)
+        outs["1"] = outs["tile"]
+        np.testing.assert_array_equal(outs["1"], outs["0"], err_msg=name)
+        got = outs["1"][8:8 + C_]
+        if kind == capi.STAGE_MAXPOOL:
+            np.testing.assert_array_equal(got, ref)
+        else:
+            _assert_close(got, ref, 1)
+        # channels outside the slice are untouched (a channel count off the vector width zero-fills up to it, as the
+        # kernels it replaces do)
+        assert (outs["1"][:8] == 3.0).all() and (outs["1"][8 + -(-C_ // 8) * 8:] == 3.0).all()
