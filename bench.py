@@ -239,7 +239,7 @@ def roofline_leg(L, capi, models_dir, iters=20, only="", batch=1):
     achieved = conv["flops"] / (conv["us"] * 1e-6) / 1e12 if conv["launches"] else 0.0
     total_us = sum(d["us"] for d in per_kind.values())
     # DRAM bytes per launch of this kernel at batch 1, from the ncu capture summarised in
-    # profiles/conv_umma_kernels__inception_v3_layers.md (mean over the Mixed_* layers), scaled by the batch for the
+    # profiles/conv_umma_tma_kernel__inception_v3_layers.md (mean over the Mixed_* layers), scaled by the batch for the
     # activation part is not attempted: reported for batch 1 only
     traffic = 818185 if (not only and batch == 1) else None
     kern = ("conv_umma_persist_kernel (tcgen05 implicit GEMM, TMA im2col, several tiles per CTA, two TMEM accumulators)" if persist
@@ -566,7 +566,7 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.batch <= 0:
-        args.batch = {"mix": 12000, "mnist": 20000, "fig11": 6000, "fig12": 6000}.get(args.workload, 1500)
+        args.batch = {"mix": 12000, "mnist": 20000, "fig11": 8000, "fig12": 8000}.get(args.workload, 1500)
     paper = PAPER_MIXES.get(args.workload)
     if args.concurrency <= 0:
         args.concurrency = paper["concurrency"] if paper else 192
@@ -761,7 +761,7 @@ def main():
         # above it brackets the knee).  Every point is a full K-step run timed like the others. ----
         def sweep(resident, cap_rps, tag):
             best = None
-            for frac in (1.05, 1.0, 0.95, 0.9, 0.8, 0.7, 0.5):
+            for frac in (1.05, 1.0, 0.95, 0.9, 0.85, 0.8, 0.7, 0.5):
                 offered = frac * cap_rps
                 x = leg(f"poisson_{tag}_{frac}", resident, 1e6 * n_gpus * args.replicas_per_gpu / offered, args.steps, seed=7)
                 sweep_pts.append(dict(point(x, offered), inputs=tag, fraction_of_closed_loop=frac))

@@ -555,7 +555,7 @@ __device__ __forceinline__ uint32_t roll_finish(uint32_t acc, float, float, floa
 // Reading the rows with 4-byte global loads spends a third of the instructions on addresses (every load needs
 // its own 64-bit address; measured on a first version that did so).  Here a block of 8 warps owns a tile of kTileRows x (8 * strip) outputs of ONE slab of
 // 64 channels.  It first copies the tile's input window into shared memory with 16-byte cp.async (zero-filled
-// outside the tensor; 78 KB in flight per block), then every warp walks down its strip of output columns with
+// outside the tensor; 65 KB in flight per block, three blocks per SM), then every warp walks down its strip of output columns with
 // lane l holding channels 2l, 2l+1 of the slab: all its shared-memory loads are at compile-time offsets from
 // one pointer that advances once per three rows, and consecutive lanes read consecutive words (no bank
 // conflict).  The results are the bits of every other 3x3 kernel here.

@@ -383,14 +383,20 @@ def test_input_patch_matrix(dtype, geom):
 # ---- tensors large enough for the strip / wide kernels (chosen by the library from the tensor's size) ----
 def _strip_blocks(P, Q, cs, dtype, stride):
     strip = 4 if stride == 1 else 2          # output pixels per thread of the strip kernel
+    if dtype == 1:
+        # bf16: the shared-memory tile kernel takes over once its blocks fill the GPU twice (two blocks per SM)
+        tiles = -(-cs // 64) * -(-Q // (8 * strip)) * -(-P // (13 if stride == 1 else 6))
+        if tiles >= 148 * 2 * 2:
+            return tiles
     return -(-(P * (-(-Q // strip)) * (cs // gu.vec(dtype))) // 256)
 
 
 @pytest.mark.parametrize("dtype", [0, 1])
 @pytest.mark.parametrize("case", [(64, 402, 398, 1), (64, 803, 797, 2)])
 def test_dwconv_large_tensor_uses_strips(case, dtype):
-    """Depthwise 3x3 on a tensor whose strips (4 pixels at stride 1, 2 at stride 2) fill the GPU: the strip kernel must run (block count)
-    and agree with the oracle like the one-pixel kernel does, ragged last strip and borders included."""
+    """Depthwise 3x3 on a tensor whose strips (4 pixels at stride 1, 2 at stride 2) fill the GPU: the strip kernel (or, in bf16
+    on the larger case, the tile kernel) must run (block count) and agree with the oracle like the one-pixel kernel does,
+    ragged last strip and borders included."""
     L = capi.load()
     C_, H, W, st = case
     P, Q = (H + 2 - 3) // st + 1, (W + 2 - 3) // st + 1
