@@ -238,10 +238,16 @@ def roofline_leg(L, capi, models_dir, iters=20, only="", batch=1):
     conv = per_kind.get("conv_umma", {"launches": 0, "us": 1.0, "flops": 0, "bytes": 0})
     achieved = conv["flops"] / (conv["us"] * 1e-6) / 1e12 if conv["launches"] else 0.0
     total_us = sum(d["us"] for d in per_kind.values())
-    # DRAM bytes per launch of this kernel at batch 1, from the ncu capture summarised in
-    # profiles/conv_umma_tma_kernel__inception_v3_layers.md (mean over the Mixed_* layers), scaled by the batch for the
-    # activation part is not attempted: reported for batch 1 only
-    traffic = 818185 if (not only and batch == 1) else None
+    # DRAM bytes per launch, from the ncu captures summarised in profiles/conv_umma_tma_kernel__inception_v3_layers.md:
+    # 1 image per launch: the mean over the Mixed_* layers (818 185 B against 856 300 B algorithmic); 8 images per
+    # launch: the captured layer's ratio of DRAM traffic to algorithmic bytes (3.91 MB / 4.73 MB: the output stays in
+    # L2), scaled to this leg's mean algorithmic bytes per launch.  Other batches: no capture, null.
+    alg_per_launch = conv["bytes"] / max(conv["launches"], 1)
+    traffic = None
+    if not only and batch == 1:
+        traffic = 818185
+    elif not only and batch == 8:
+        traffic = int(alg_per_launch * 3.912704 / 4.7333)
     kern = ("conv_umma_persist_kernel (tcgen05 implicit GEMM, TMA im2col, several tiles per CTA, two TMEM accumulators)" if persist
             else "conv_umma_tma_kernel (tcgen05 implicit GEMM, TMA im2col, one tile per CTA)")
     roof = {"bound": "tensor", "kernel": f"{kern}: every Inception-v3 conv layer launched alone, {batch} image(s) per launch as served, L2 flushed",

@@ -19,8 +19,7 @@ BIN = os.path.join(os.path.dirname(capi.LIB_PATH), "bin")
 _SERVERS = [0]
 
 
-@pytest.fixture()
-def server(models_dir):
+def _start_server(models_dir):
     _SERVERS[0] += 1
     name = f"pbsrv{os.getpid()}n{_SERVERS[0]}"      # a fresh name per server: a killed server leaves its rings in /dev/shm
     env = dict(os.environ, LLIS_MODELS_DIR=models_dir, CUDA_DEVICE_MAX_CONNECTIONS="32")
@@ -31,7 +30,10 @@ def server(models_dir):
         assert p.poll() is None, p.stderr.read()
         assert time.time() < deadline, "llis_server did not come up"
         time.sleep(0.05)
-    yield name, p
+    return name, p
+
+
+def _stop_server(name, p):
     if p.poll() is None:
         p.terminate()
         p.wait(10)
@@ -41,6 +43,54 @@ def server(models_dir):
                 os.unlink(os.path.join("/dev/shm", f))
             except OSError:
                 pass
+
+
+@pytest.fixture()
+def server(models_dir):
+    name, p = _start_server(models_dir)
+    yield name, p
+    _stop_server(name, p)
+
+
+def test_a_launch_that_fails_is_answered_and_the_server_lives_on(tmp_path):
+    """The models directory holds the MNIST pack only.  A ResNet-18 request cannot be initialised (its pack is
+    missing): the client's wait() must return for it at once instead of blocking for ever, the server must stay up,
+    and MNIST requests sent before and after it are served correctly."""
+    packer.mnist_cnn(seed=1234).save(str(tmp_path / packer.pack_file_name("mnist")))
+    name, proc = _start_server(str(tmp_path))
+    try:
+        L = capi.load()
+        client = C.c_void_p()
+        capi.check(L.pb_client_connect(name.encode(), C.byref(client)), "pb_client_connect")
+        inst = {}
+        for plugin in ("tvm_mnist", "tvm_resnet18"):
+            j, ib, ob = C.c_uint32(), C.c_size_t(), C.c_size_t()
+            capi.check(L.pb_client_register_job(client, capi.plugin_path(plugin).encode(), C.byref(j), C.byref(ib), C.byref(ob)), "register_job")
+            i, pin, pout = C.c_uint64(), C.c_void_p(), C.c_void_p()
+            capi.check(L.pb_client_create_instance(client, j.value, C.byref(i), C.byref(pin), C.byref(pout)), "create_instance")
+            inst[plugin] = (i.value, pin.value, pout.value, ob.value)
+        x = np.random.default_rng(3).random((1, 28, 28), dtype=np.float32)
+        ref = og.run(og.Pack(packer.mnist_cnn(seed=1234).to_bytes()), x)
+        C.memmove(inst["tvm_mnist"][1], x.ctypes.data, x.nbytes)
+        got = C.c_uint64()
+        for plugin in ("tvm_mnist", "tvm_resnet18", "tvm_resnet18", "tvm_mnist"):
+            if plugin == "tvm_mnist":
+                C.memset(inst[plugin][2], 0, inst[plugin][3])
+            capi.check(L.pb_client_launch(client, inst[plugin][0]), "launch")
+            deadline = time.time() + 30
+            rc = 0
+            while rc != 1 and time.time() < deadline:
+                assert proc.poll() is None, proc.stderr.read()
+                rc = L.pb_client_wait(client, 100, C.byref(got))
+            assert rc == 1 and got.value == inst[plugin][0], f"no answer for the {plugin} request"
+            if plugin == "tvm_mnist":
+                y = np.frombuffer((C.c_char * inst[plugin][3]).from_address(inst[plugin][2]), np.float32).copy()
+                assert float(np.abs(y - ref).max()) <= 1e-5 * float(np.abs(ref).max())
+        capi.check(L.pb_client_kill_server(client), "kill_server")
+        assert proc.wait(30) == 0
+        L.pb_client_close(client)
+    finally:
+        _stop_server(name, proc)
 
 
 def test_requests_through_a_server_process(server):
