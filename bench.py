@@ -247,7 +247,7 @@ def roofline_leg(L, capi, models_dir, iters=20, only="", batch=1):
     if not only and batch == 1:
         traffic = 818185
     elif not only and batch == 8:
-        traffic = int(alg_per_launch * 3.912704 / 4.7333)
+        traffic = int(alg_per_launch * 3.912704 / 4.73472)
     kern = ("conv_umma_persist_kernel (tcgen05 implicit GEMM, TMA im2col, several tiles per CTA, two TMEM accumulators)" if persist
             else "conv_umma_tma_kernel (tcgen05 implicit GEMM, TMA im2col, one tile per CTA)")
     roof = {"bound": "tensor", "kernel": f"{kern}: every Inception-v3 conv layer launched alone, {batch} image(s) per launch as served, L2 flushed",
