@@ -849,13 +849,96 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
 // than a dozen tiles, so running the branches side by side in one launch is what fills the SMs.
 // Block b belongs to the sub-problem i with first_block[i] <= b < first_block[i + 1]; the table with
 // each sub-problem's tensor maps and arguments lives in device memory, written once per instance.
+// A 3x3 pooling layer of the same dependence depth can ride along as one more entry (stages == kSubPool): its blocks
+// run pool_sub_block() instead of a convolution tile.  Why it was tried: under serving load every launch of a request's
+// chain waits about 45 us for SM resources behind the other requests' CTAs, whatever its own size, so the 13 pooling
+// launches of an Inception-v3 request cost 20 % of the throughput although they are 6 % of a lone request's time.
+// What came of it: see PB_FUSE_POOLS where the launches are planned (off by default).
+struct PoolSubArgs {
+    const __nv_bfloat16* x;
+    __nv_bfloat16* y;
+    int C, H, W, Cs, P, Q, Ks, out_c_off;
+    int sh, sw, ph, pw;
+    int is_max, count_pad, batch, reserved;
+};
 struct alignas(128) SubConv {
     CUtensorMap tmap_w;
     CUtensorMap tmap_x;
-    ConvArgs a;
+    union {
+        ConvArgs a;
+        PoolSubArgs pool;
+    };
     uint32_t first_block, gx, gy, stages;
 };
+static_assert(sizeof(PoolSubArgs) <= sizeof(ConvArgs), "a pooling entry fits where a convolution's arguments are");
 constexpr int kMaxSubConvs = 8;
+constexpr uint32_t kSubPool = 0xffffffffu;
+constexpr int kPoolVecsPerThread = 2;                 // output vectors (8 channels) per thread of a pooling block
+
+// One block's share of a 3x3 pooling layer: thread t takes output vectors base + t and base + 192 + t.  All nine
+// loads of a window are issued before the first use (addresses clamped into the tensor, taps outside dropped
+// afterwards).  Arithmetic and its order are those of pool_kernel / window3_strip_kernel (rows, then columns, fp32
+// sums from +0, IEEE division; fmaxf from -inf), so the bits are theirs.
+__device__ __forceinline__ void pool_sub_block(const PoolSubArgs& a, uint32_t local_block) {
+    const int cv = a.Cs >> 3;
+    const long long total = (long long)a.batch * a.P * a.Q * cv;
+    const long long base = (long long)local_block * (kThreadsTma * kPoolVecsPerThread) + threadIdx.x;
+#pragma unroll 1
+    for (int u = 0; u < kPoolVecsPerThread; ++u) {
+        const long long idx = base + (long long)u * kThreadsTma;
+        if (idx >= total) break;
+        const int c0 = (int)(idx % cv) * 8;
+        long long pix = idx / cv;
+        const int q = (int)(pix % a.Q);
+        pix /= a.Q;
+        const int p = (int)(pix % a.P), img = (int)(pix / a.P);
+        const __nv_bfloat16* x = a.x + (size_t)img * a.H * a.W * a.Cs + c0;
+        uint4 raw[3][3];
+        uint32_t ok = 0;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int ih = p * a.sh + r - a.ph;
+            const bool row_ok = ih >= 0 && ih < a.H;
+            const __nv_bfloat16* xrow = x + (size_t)min(max(ih, 0), a.H - 1) * a.W * a.Cs;
+#pragma unroll
+            for (int s2 = 0; s2 < 3; ++s2) {
+                const int iw = q * a.sw + s2 - a.pw;
+                if (row_ok && iw >= 0 && iw < a.W) ok |= 1u << (r * 3 + s2);
+                raw[r][s2] = *reinterpret_cast<const uint4*>(xrow + (size_t)min(max(iw, 0), a.W - 1) * a.Cs);
+            }
+        }
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = a.is_max ? -INFINITY : 0.f;
+        int cnt = 0;
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int s2 = 0; s2 < 3; ++s2) {
+                if (!((ok >> (r * 3 + s2)) & 1u)) continue;
+                const uint32_t w[4] = {raw[r][s2].x, raw[r][s2].y, raw[r][s2].z, raw[r][s2].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+                    acc[2 * j] = a.is_max ? fmaxf(acc[2 * j], lo) : acc[2 * j] + lo;
+                    acc[2 * j + 1] = a.is_max ? fmaxf(acc[2 * j + 1], hi) : acc[2 * j + 1] + hi;
+                }
+                ++cnt;
+            }
+        const float div = a.count_pad ? 9.f : (float)(cnt > 0 ? cnt : 1);
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v0 = a.is_max ? acc[2 * j] : acc[2 * j] / div, v1 = a.is_max ? acc[2 * j + 1] : acc[2 * j + 1] / div;
+            if (c0 + 2 * j >= a.C) v0 = 0.f;
+            if (c0 + 2 * j + 1 >= a.C) v1 = 0.f;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+            o[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        __nv_bfloat16* y = a.y + (((size_t)img * a.P + p) * a.Q + q) * a.Ks + a.out_c_off + c0;
+        *reinterpret_cast<uint4*>(y) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
 
 __global__ void __launch_bounds__(kThreadsTma, 3)
 conv_umma_multi_kernel(const SubConv* __restrict__ table, int n_sub, uint32_t job_id, FinishedBlockNotifier* nf) {
@@ -882,6 +965,13 @@ conv_umma_multi_kernel(const SubConv* __restrict__ table, int n_sub, uint32_t jo
         reinterpret_cast<uint32_t*>(&s_args)[threadIdx.x] = reinterpret_cast<const uint32_t*>(&sc->a)[threadIdx.x];
     __syncthreads();
     const uint32_t local = blockIdx.x - sc->first_block;
+    if (sc->stages == kSubPool) {        // a pooling layer riding along: no tensor memory, no pipeline
+        griddep_wait();
+        griddep_launch();
+        pool_sub_block(*reinterpret_cast<const PoolSubArgs*>(&s_args), local);
+        if (nf) nf->end(job_id);
+        return;
+    }
     const uint32_t gx = sc->gx, gy = sc->gy;
     const uint32_t bx = local % gx, rest = local / gx;
     const uint32_t by = rest % gy, bz = rest / gy;
@@ -1639,6 +1729,7 @@ struct ConvUmmaMulti {
     unsigned total_blocks = 0;      // tiles of all sub-problems (= CTAs of the one-tile-per-CTA kernel)
     uint32_t smem = 0;
     uint32_t tmem_cols = 0;
+    bool has_pool = false;          // pooling layers ride along (one-tile kernel only)
     // persistent kernel
     bool persist = false;
     unsigned grid = 0;
@@ -1653,14 +1744,42 @@ uint32_t conv_umma_persist_grid(uint32_t total_tiles) {
     return g < 1 ? 1 : g;
 }
 
-int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, int n,
-                           ConvUmmaMulti** out) {
-    PB_REQUIRE(out && plans && xmaps && params && n >= 1 && n <= kMaxSubConvs, "conv_umma_multi_create: 1..%d convolutions", kMaxSubConvs);
+// A 3x3 max / average pooling layer (bf16, vector-aligned slice) can ride along in a grouped launch.
+bool conv_umma_pool_fusable(int kind, const pb_op_params* p) {
+    return (kind == PB_STAGE_MAXPOOL || kind == PB_STAGE_AVGPOOL) && p->dtype == 1 && p->R == 3 && p->S == 3 && p->Cs % 8 == 0 &&
+           p->Ks % 8 == 0 && p->out_c_off % 8 == 0 && !(p->flags & 2) && p->H >= 1 && p->W >= 1;
+}
+uint32_t conv_umma_pool_blocks(const pb_op_params* p) {
+    const uint64_t vecs = (uint64_t)batch_of(p) * p->P * p->Q * (p->Cs / 8);
+    return (uint32_t)ceil_div<uint64_t>(vecs, (uint64_t)kThreadsTma * kPoolVecsPerThread);
+}
+
+int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, const int* kinds,
+                           int n, ConvUmmaMulti** out) {
+    PB_REQUIRE(out && plans && xmaps && params && n >= 1 && n <= kMaxSubConvs, "conv_umma_multi_create: 1..%d entries", kMaxSubConvs);
     PB_REQUIRE(use_tma_a(), "conv_umma_multi_create: needs the TMA operand path");
     std::vector<SubConv> table((size_t)n);
+    memset(table.data(), 0, sizeof(SubConv) * (size_t)n);
     ConvUmmaMulti* m = new ConvUmmaMulti();
     m->n = n;
     for (int i = 0; i < n; ++i) {
+        if (kinds && kinds[i] != PB_STAGE_CONV_UMMA) {
+            const pb_op_params* p = params[i];
+            if (!p || !conv_umma_pool_fusable(kinds[i], p)) { delete m; set_error("conv_umma_multi_create: entry %d cannot ride along", i); return PB_ERR_INVALID; }
+            SubConv& sc = table[(size_t)i];
+            PoolSubArgs& a = sc.pool;
+            a.x = static_cast<const __nv_bfloat16*>(p->x);
+            a.y = static_cast<__nv_bfloat16*>(p->y);
+            a.C = p->C; a.H = p->H; a.W = p->W; a.Cs = p->Cs; a.P = p->P; a.Q = p->Q; a.Ks = p->Ks; a.out_c_off = p->out_c_off;
+            a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w;
+            a.is_max = kinds[i] == PB_STAGE_MAXPOOL; a.count_pad = p->flags & 1; a.batch = batch_of(p);
+            sc.first_block = m->total_blocks;
+            sc.gx = sc.gy = 1;
+            sc.stages = kSubPool;
+            m->total_blocks += conv_umma_pool_blocks(p);
+            m->has_pool = true;
+            continue;
+        }
         PB_REQUIRE(plans[i] && xmaps[i] && params[i], "conv_umma_multi_create: NULL entry %d", i);
         Geometry g = geometry(params[i]);
         if (g.splits > 1 && (params[i]->scratch == nullptr || params[i]->scratch_bytes < g.scratch_bytes)) drop_split(&g);
@@ -1678,11 +1797,12 @@ int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap*
         m->tmem_cols = std::max(m->tmem_cols, g.tmem_cols);
         m->stage_bytes = std::max(m->stage_bytes, (uint32_t)kATileBytes + g.b_stage_bytes);
     }
+    if (m->stage_bytes == 0) { delete m; set_error("conv_umma_multi_create: no convolution among the entries"); return PB_ERR_INVALID; }
     // persistent kernel: one pipeline for every sub-problem (stages of the widest), two accumulators
     m->stages = (int)std::min<uint32_t>(kMaxStages, (kSmemBudgetPersist - 1024u) / m->stage_bytes);
     m->persist_smem = (uint32_t)m->stages * m->stage_bytes + 1024u;
     m->grid = conv_umma_persist_grid(m->total_blocks);
-    m->persist = persist_enabled() && m->stages >= 2 && 2u * m->tmem_cols <= 512u;
+    m->persist = persist_enabled() && m->stages >= 2 && 2u * m->tmem_cols <= 512u && !m->has_pool;
     cudaError_t e = cudaMalloc((void**)&m->table_dev, sizeof(SubConv) * (size_t)n);
     if (e == cudaSuccess) e = cudaMemcpy(m->table_dev, table.data(), sizeof(SubConv) * (size_t)n, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) { conv_umma_multi_destroy(m); return cuda_fail(e, "conv_umma_multi_create", __FILE__, __LINE__); }
@@ -1761,7 +1881,7 @@ int conv_umma_launch(const pb_op_params* p, cudaStream_t st, uint32_t job_id, vo
             const ConvUmmaPlan* plans[1] = {plan};
             const ConvUmmaXMap* xms[1] = {xm};
             const pb_op_params* pp[1] = {p};
-            rc = conv_umma_multi_create(plans, xms, pp, 1, &mu);
+            rc = conv_umma_multi_create(plans, xms, pp, nullptr, 1, &mu);
         }
         if (rc == PB_OK && !mu->persist) { set_error("conv_umma: this shape does not fit the persistent kernel"); rc = PB_ERR_INVALID; }
         if (rc == PB_OK) rc = conv_umma_multi_launch(mu, st, job_id, notifier, false);
@@ -1792,7 +1912,7 @@ int conv_umma_time(const pb_op_params* p, int mode, int iters, size_t flush_byte
         const ConvUmmaPlan* plans[1] = {plan};
         const ConvUmmaXMap* xms[1] = {xm};
         const pb_op_params* pp[1] = {p};
-        rc = conv_umma_multi_create(plans, xms, pp, 1, &mu);
+        rc = conv_umma_multi_create(plans, xms, pp, nullptr, 1, &mu);
         if (rc == PB_OK && !mu->persist) { set_error("pb_conv_umma_time: the persistent kernel is off or does not fit this shape"); rc = PB_ERR_INVALID; }
     }
     cudaError_t e = cudaSuccess;

@@ -64,8 +64,12 @@ bool conv_umma_persist_enabled();
 uint32_t conv_umma_persist_grid(uint32_t total_tiles);
 // Footprint of a persistent launch over `total_tiles` tiles whose widest accumulator has `max_tmem_cols` columns.
 void conv_umma_persist_footprint(uint32_t total_tiles, uint32_t max_tmem_cols, pb_launch_info* out);
-int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, int n,
-                           ConvUmmaMulti** out);
+// kinds[i] (NULL = all convolutions): PB_STAGE_CONV_UMMA, or PB_STAGE_MAXPOOL / PB_STAGE_AVGPOOL for a 3x3 pooling layer that rides
+// along (conv_umma_pool_fusable; its plan and map entries are NULL).  At least one entry is a convolution.
+int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap* const* xmaps, const pb_op_params* const* params, const int* kinds,
+                           int n, ConvUmmaMulti** out);
+bool conv_umma_pool_fusable(int kind, const pb_op_params* p);
+uint32_t conv_umma_pool_blocks(const pb_op_params* p);
 void conv_umma_multi_destroy(ConvUmmaMulti* m);
 void conv_umma_multi_info(const ConvUmmaMulti* m, pb_launch_info* out);
 int conv_umma_multi_launch(const ConvUmmaMulti* m, cudaStream_t st, uint32_t job_id, void* notifier, bool pdl);

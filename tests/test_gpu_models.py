@@ -307,6 +307,43 @@ def test_stage_groups_replayed_as_graphs_give_the_same_bits(models_dir, model, p
     m.close()
 
 
+@pytest.mark.parametrize("model", ["inception_v3", "googlenet"])
+def test_pooling_layers_ride_along_in_the_grouped_launches(models_dir, monkeypatch, model):
+    """The 3x3 pooling branch of an Inception block shares the grouped launch of the convolutions of its depth
+    (never the last launch of a group, whose block count the group declares).  Same arithmetic as the pooling
+    kernels: the stage graphs give the bits of the kernel-by-kernel run and of a load with PB_FUSE_POOLS=0, for one
+    request and for a gang of three."""
+    path = os.path.join(models_dir, packer.pack_file_name(model))
+    pools = (capi.STAGE_MAXPOOL, capi.STAGE_AVGPOOL)
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("PB_FUSE_POOLS", flag)
+        m = Model(path, 1)
+        kinds = m.kinds()
+        riding = 0
+        first, count = C.c_int(), C.c_int()
+        for g in range(m.L.pb_model_num_groups(m.m)):
+            capi.check(m.L.pb_model_group_stages(m.m, g, C.byref(first), C.byref(count)), "group stages")
+            order, launch = (C.c_int32 * count.value)(), (C.c_int32 * count.value)()
+            assert m.L.pb_model_group_plan(m.m, g, order, launch, count.value) == count.value
+            members = {}
+            for s_idx, l_idx in zip(order, launch):
+                members.setdefault(l_idx, []).append(kinds[s_idx])
+            for l_idx, ks in members.items():
+                if len(ks) > 1:
+                    assert ks[0] == capi.STAGE_CONV_UMMA and all(k == capi.STAGE_CONV_UMMA or k in pools for k in ks)
+                    n_pool = sum(1 for k in ks if k in pools)
+                    riding += n_pool
+                    assert n_pool == 0 or l_idx != launch[-1]
+        assert (riding >= 8) if flag == "1" else (riding == 0)
+        x = make_input(model)
+        y = m.run(x)
+        np.testing.assert_array_equal(m.run_groups(x), y)
+        outs[flag] = y
+        m.close()
+    np.testing.assert_array_equal(outs["1"], outs["0"])
+
+
 def test_persistent_convolution_kernel_in_the_stage_graphs(tmp_path, monkeypatch):
     """PB_CONV_PERSIST=1 when the model is loaded: every tensor-core launch of the stage graphs runs the persistent kernel
     (a CTA walks three tiles, two accumulators in tensor memory).  Same arithmetic per output element, so with the
