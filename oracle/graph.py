@@ -226,10 +226,19 @@ def run(pack: Pack, x: np.ndarray, emulate_bf16: bool = False, keep_all: bool = 
             w = rb(W[woff: woff + cout * cin].reshape(cout, cin))
             b = np.ascontiguousarray(W[boff: boff + cout])
             bufs[out][:] = dense(xin, w, b, act).reshape(oc, oh, ow)
-        elif typ == OP_MAXPOOL:
-            maxpool(xin, (r, s), (sh, sw), (ph, pw), bufs[out], ooff, ceil_mode=bool(flags & 4))
-        elif typ == OP_AVGPOOL:
-            avgpool(xin, (r, s), (sh, sw), (ph, pw), bool(flags & 1), bufs[out], ooff)
+        elif typ in (OP_MAXPOOL, OP_AVGPOOL):
+            if typ == OP_MAXPOOL:
+                maxpool(xin, (r, s), (sh, sw), (ph, pw), bufs[out], ooff, ceil_mode=bool(flags & 4))
+            else:
+                avgpool(xin, (r, s), (sh, sw), (ph, pw), bool(flags & 1), bufs[out], ooff)
+            if flags & 8 or act:     # pooled value + per-channel bias, then the activation (fp32, in that order)
+                sl = bufs[out][ooff: ooff + cin]
+                if flags & 8:
+                    sl += W[boff: boff + cin].reshape(-1, 1, 1)
+                if act == 1:
+                    np.maximum(sl, np.float32(0), out=sl)
+                elif act == 2:
+                    np.clip(sl, np.float32(0), np.float32(6), out=sl)
         elif typ == OP_GAP:
             bufs[out][:] = gap(xin).reshape(oc, 1, 1)
         elif typ == OP_ADD:

@@ -1747,7 +1747,7 @@ uint32_t conv_umma_persist_grid(uint32_t total_tiles) {
 // A 3x3 max / average pooling layer (bf16, vector-aligned slice) can ride along in a grouped launch.
 bool conv_umma_pool_fusable(int kind, const pb_op_params* p) {
     return (kind == PB_STAGE_MAXPOOL || kind == PB_STAGE_AVGPOOL) && p->dtype == 1 && p->R == 3 && p->S == 3 && p->Cs % 8 == 0 &&
-           p->Ks % 8 == 0 && p->out_c_off % 8 == 0 && !(p->flags & 2) && p->H >= 1 && p->W >= 1;
+           p->Ks % 8 == 0 && p->out_c_off % 8 == 0 && !(p->flags & 2) && p->H >= 1 && p->W >= 1 && p->bias == nullptr && p->act == 0;
 }
 uint32_t conv_umma_pool_blocks(const pb_op_params* p) {
     const uint64_t vecs = (uint64_t)batch_of(p) * p->P * p->Q * (p->Cs / 8);

@@ -848,8 +848,15 @@ int pb_model_load(const char* pack_path, int device, int precision, pb_model** o
                 PB_FAIL_LOAD(upload(m, W + b_off, (size_t)p.K * 4, (void**)&st.bias_dev));
                 break;
             }
-            case OP_MAXPOOL: st.kind = PB_STAGE_MAXPOOL; p.K = tx.C; break;
-            case OP_AVGPOOL: st.kind = PB_STAGE_AVGPOOL; p.K = tx.C; break;
+            case OP_MAXPOOL:
+            case OP_AVGPOOL:
+                st.kind = o.type == OP_MAXPOOL ? PB_STAGE_MAXPOOL : PB_STAGE_AVGPOOL;
+                p.K = tx.C;
+                if (o.flags & 8) {      // a per-channel bias is added to the pooled value (then p.act applies)
+                    if (b_off + (uint64_t)tx.C > n_floats) { pb::set_error("%s: pooling op %u: bias outside the weights", pack_path, i); PB_FAIL_LOAD(PB_ERR_IO); }
+                    PB_FAIL_LOAD(upload(m, W + b_off, (size_t)tx.C * 4, (void**)&st.bias_dev));
+                }
+                break;
             case OP_GAP: st.kind = PB_STAGE_GAP; p.K = tx.C; break;
             case OP_ADD: st.kind = PB_STAGE_ADD; break;
             case OP_AFFINE: {

@@ -260,7 +260,11 @@ __global__ void __launch_bounds__(256, 6) pool_kernel(OpArgs a, uint32_t job_id,
         Vec<T> o;
         const float div = (a.flags & 1) ? (float)(a.R * a.S) : (float)(cnt > 0 ? cnt : 1);
 #pragma unroll
-        for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.C) ? (kMax ? acc[j] : acc[j] / div) : 0.f;
+        for (int j = 0; j < N; ++j) {
+            float v = kMax ? acc[j] : acc[j] / div;
+            if (a.bias && c0 + j < a.C) v += a.bias[c0 + j];      // the tail of a convolution that ran before the pooling
+            o.v[j] = (c0 + j < a.C) ? act_fn(v, a.act) : 0.f;
+        }
         o.store(y_img<T>(a) + (size_t)pix * a.Ks + a.out_c_off + c0);
     }
     PB_NOTIFY_END();
@@ -473,7 +477,10 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
                 }
             } else if (kMode == kWinMax) {
 #pragma unroll
-                for (int j = 0; j < N; ++j) o.v[j] = (c0 + j < a.C) ? v[j] : 0.f;
+                for (int j = 0; j < N; ++j) {
+                    const float pv = (a.bias && c0 + j < a.C) ? v[j] + a.bias[c0 + j] : v[j];
+                    o.v[j] = (c0 + j < a.C) ? act_fn(pv, a.act) : 0.f;
+                }
             } else {
                 float div = 9.f;
                 if (!(a.flags & 1)) {
@@ -491,8 +498,9 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
                 for (int j = 0; j < N; ++j) {
                     const float qv = v[j] * inv;
                     const float rv = fmaf(-div, qv, v[j]);
-                    const float out = fabsf(qv) <= 3.0e38f ? fmaf(rv, inv, qv) : qv;
-                    o.v[j] = (c0 + j < a.C) ? out : 0.f;
+                    float out = fabsf(qv) <= 3.0e38f ? fmaf(rv, inv, qv) : qv;
+                    if (a.bias && c0 + j < a.C) out += a.bias[c0 + j];
+                    o.v[j] = (c0 + j < a.C) ? act_fn(out, a.act) : 0.f;
                 }
             }
             o.store(yrow + (size_t)t * a.Ks);
@@ -1136,6 +1144,7 @@ static size_t strip_threads(const pb_op_params* p, int strip) {
 // PB_WINDOW_TILE_MIN_BLOCKS sets another threshold (tests use 1).  Read at every call: this runs when a launch is built
 // (graph capture, direct operator calls), never on the replay path.
 static uint32_t tile_blocks(const pb_op_params* p) {
+    if (p->groups <= 1 && (p->bias != nullptr || p->act != 0)) return 0;      // pooling with a bias / activation tail: strip kernels
     if (p->dtype != 1 || (p->Cs & 7) || (p->Ks & 1) || (p->out_c_off & 1) || strip_of(p) == 0) return 0;
     const char* e = getenv("PB_WINDOW_TILE");
     if (e && e[0] == '0') return 0;
@@ -1228,7 +1237,7 @@ static int info_one_image(int kind, const pb_op_params* p, pb_launch_info* out) 
                 out->regs_per_thread = regs_of(tile_fn(kind, p->stride_h));
                 out->smem_per_block = tile_smem(p->stride_h);
             }
-            out->bytes = es * (in_elems + out_elems);
+            out->bytes = es * (in_elems + out_elems) + (p->bias ? 4ull * p->K : 0);
             break;
         case PB_STAGE_GAP:
             out->num_blocks = (uint32_t)pb::ceil_div(p->Cs / N, 32);

@@ -39,6 +39,7 @@ OP_CONV, OP_DENSE, OP_MAXPOOL, OP_AVGPOOL, OP_GAP, OP_ADD, OP_SOFTMAX, OP_AFFINE
 ACT_NONE, ACT_RELU, ACT_RELU6, ACT_PRELU = 0, 1, 2, 3   # PReLU: the conv's bias block is [bias | per-channel slope]
 FLAG_COUNT_INCLUDE_PAD = 1
 FLAG_CEIL_MODE = 4          # informational: the output tensor's extent already says it
+FLAG_POOL_BIAS = 8          # pooling: a per-channel bias (b_off) is added to the pooled value, then `act` applies
 
 OP_FIELDS = ("type", "in0", "in1", "out", "rsv0", "out_c_off", "cin", "cout", "r", "s",
              "stride_h", "stride_w", "pad_h", "pad_w", "groups", "act", "flags", "rsv1",
@@ -184,7 +185,7 @@ class Graph:
         self.output = out
         return out
 
-    def _pool(self, typ, x, k, stride, pad, out, out_c_off, flags, name):
+    def _pool(self, typ, x, k, stride, pad, out, out_c_off, flags, name, act=ACT_NONE, bias=False):
         c, h, w = self.shape(x)
         r, s = _pair(k)
         sh, sw = _pair(stride)
@@ -195,17 +196,33 @@ class Graph:
             out = self.tensor(c, p, q)
         else:
             assert self.shape(out)[1:] == (p, q), (name, self.shape(out), p, q)
+        b_off = 0
+        if bias:
+            flags |= FLAG_POOL_BIAS
+            b_off = self._push(self._bias(c))
         self.ops.append(Op(typ, x, out, out_c_off=out_c_off, cin=c, cout=c, r=r, s=s,
-                           stride_h=sh, stride_w=sw, pad_h=ph, pad_w=pw, flags=flags, name=name))
+                           stride_h=sh, stride_w=sw, pad_h=ph, pad_w=pw, act=act, flags=flags, b_off=b_off, name=name))
         self.output = out
         return out
 
     def maxpool(self, x, k, stride, pad=0, out=None, out_c_off=0, name="", ceil_mode=False):
         return self._pool(OP_MAXPOOL, x, k, stride, pad, out, out_c_off, FLAG_CEIL_MODE if ceil_mode else 0, name)
 
-    def avgpool(self, x, k, stride, pad=0, count_include_pad=True, out=None, out_c_off=0, name=""):
+    def avgpool(self, x, k, stride, pad=0, count_include_pad=True, out=None, out_c_off=0, name="", act=ACT_NONE, bias=False):
+        """Average pooling; with `bias` / `act` the pooled value gets a per-channel bias and an activation (the tail of a
+        convolution + batch-norm + ReLU whose linear part ran BEFORE the pooling, see pooled_pointwise)."""
         return self._pool(OP_AVGPOOL, x, k, stride, pad, out, out_c_off,
-                          FLAG_COUNT_INCLUDE_PAD if count_include_pad else 0, name)
+                          FLAG_COUNT_INCLUDE_PAD if count_include_pad else 0, name, act, bias)
+
+    def pooled_pointwise(self, x, cout, bn_eps, name, out=None, out_c_off=0):
+        """relu(bn(conv1x1(avgpool3x3(x)))) - the pooling branch of an Inception block - computed as
+        relu(avgpool3x3(conv1x1(x)) + bias): a 1x1 convolution and an average pooling that counts its zero padding are
+        both linear and commute, and pooling AFTER the convolution moves cout instead of cin channels (4 to 10 times
+        fewer in Inception-v3).  The operators keep the names `<name>.conv` and `<name>.avgpool`."""
+        saved, self.bias_std = self.bias_std, 0.0
+        y = self.conv(x, cout, 1, 1, 0, act=ACT_NONE, bn_eps=bn_eps, name=name + ".conv")      # linear part only: no bias
+        self.bias_std = saved
+        return self.avgpool(y, 3, 1, 1, True, out=out, out_c_off=out_c_off, name=name + ".avgpool", act=ACT_RELU, bias=True)
 
     def gap(self, x, name=""):
         c, h, w = self.shape(x)
@@ -415,7 +432,8 @@ def mobilenet_v2(seed=1234, precision=1, num_classes=1000, **kw) -> Graph:
 
 def inception_v3(seed=1234, precision=1, num_classes=1000, size=299, **kw) -> Graph:
     """Inception-v3 (A/B/C/D/E blocks), no auxiliary head, batch-norm (eps 1e-3) folded.
-    Every branch writes its channel slice of the block's output tensor directly."""
+    Every branch writes its channel slice of the block's output tensor directly.  The pooling branch of the A, C and E
+    blocks (average pool 3x3 -> 1x1 convolution -> batch-norm -> ReLU) runs its convolution first (pooled_pointwise)."""
     eps = 1e-3
     g = Graph("inception_v3", (3, size, size), seed, precision, **kw)
 
@@ -439,8 +457,7 @@ def inception_v3(seed=1234, precision=1, num_classes=1000, size=299, **kw) -> Gr
         y = bc(x, 64, 1, name=n + ".branch3x3dbl_1")
         y = bc(y, 96, 3, 1, 1, n + ".branch3x3dbl_2")
         bc(y, 96, 3, 1, 1, n + ".branch3x3dbl_3", out=out, off=128)
-        y = g.avgpool(x, 3, 1, 1, True, name=n + ".avgpool")
-        bc(y, pool_features, 1, name=n + ".branch_pool", out=out, off=224)
+        g.pooled_pointwise(x, pool_features, eps, n + ".branch_pool", out=out, out_c_off=224)
         return out
 
     def block_b(x, n):
@@ -466,8 +483,7 @@ def inception_v3(seed=1234, precision=1, num_classes=1000, size=299, **kw) -> Gr
         y = bc(y, c7, (1, 7), 1, (0, 3), n + ".branch7x7dbl_3")
         y = bc(y, c7, (7, 1), 1, (3, 0), n + ".branch7x7dbl_4")
         bc(y, 192, (1, 7), 1, (0, 3), n + ".branch7x7dbl_5", out=out, off=384)
-        y = g.avgpool(x, 3, 1, 1, True, name=n + ".avgpool")
-        bc(y, 192, 1, name=n + ".branch_pool", out=out, off=576)
+        g.pooled_pointwise(x, 192, eps, n + ".branch_pool", out=out, out_c_off=576)
         return out
 
     def block_d(x, n):
@@ -494,8 +510,7 @@ def inception_v3(seed=1234, precision=1, num_classes=1000, size=299, **kw) -> Gr
         y = bc(y, 384, 3, 1, 1, n + ".branch3x3dbl_2")
         bc(y, 384, (1, 3), 1, (0, 1), n + ".branch3x3dbl_3a", out=out, off=1088)
         bc(y, 384, (3, 1), 1, (1, 0), n + ".branch3x3dbl_3b", out=out, off=1472)
-        y = g.avgpool(x, 3, 1, 1, True, name=n + ".avgpool")
-        bc(y, 192, 1, name=n + ".branch_pool", out=out, off=1856)
+        g.pooled_pointwise(x, 192, eps, n + ".branch_pool", out=out, out_c_off=1856)
         return out
 
     x = block_a(x, 32, "Mixed_5b")

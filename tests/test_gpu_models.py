@@ -335,7 +335,9 @@ def test_pooling_layers_ride_along_in_the_grouped_launches(models_dir, monkeypat
                     n_pool = sum(1 for k in ks if k in pools)
                     riding += n_pool
                     assert n_pool == 0 or l_idx != launch[-1]
-        assert (riding >= 8) if flag == "1" else (riding == 0)
+        # GoogLeNet: the max pool of every Inception module; Inception-v3: the max pools of its two reduction blocks (its
+        # average pools carry the bias + ReLU tail of the convolution that runs before them and keep their own launch)
+        assert (riding >= (2 if model == "inception_v3" else 8)) if flag == "1" else (riding == 0)
         x = make_input(model)
         y = m.run(x)
         np.testing.assert_array_equal(m.run_groups(x), y)

@@ -274,6 +274,37 @@ def test_pools(dtype, k, s, p, hw, c):
 
 
 @pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("k,s,p,hw,c,act", [(3, 1, 1, 17, 192, 1), (3, 1, 1, 35, 64, 1), (3, 2, 0, 9, 24, 2), (2, 2, 0, 12, 16, 0)])
+def test_pools_with_a_bias_and_activation_tail(dtype, k, s, p, hw, c, act):
+    """Pooling followed by a per-channel bias and an activation in the same kernel (the tail of a 1x1 convolution +
+    batch-norm + ReLU that ran before an average pooling): act(pool(x) + bias), fp32, in that order."""
+    import torch
+    L = capi.load()
+    x = RNG.standard_normal((c, hw, hw), dtype=np.float32)
+    b = RNG.standard_normal(c, dtype=np.float32) * np.float32(0.3)
+    if dtype == 1:
+        x = og.round_bf16(x)
+    P = (hw + 2 * p - k) // s + 1
+    bd = torch.from_numpy(b).cuda()
+
+    def tail(v):
+        v = v + b.reshape(-1, 1, 1)
+        return np.maximum(v, 0) if act == 1 else (np.clip(v, 0, 6) if act == 2 else v)
+
+    for kind, ref in ((capi.STAGE_MAXPOOL, tail(og.maxpool(x, (k, k), (s, s), (p, p)))),
+                      (capi.STAGE_AVGPOOL, tail(og.avgpool(x, (k, k), (s, s), (p, p), True)))):
+        xd, cs = gu.to_device_cl(x, dtype)
+        yd, ks = gu.empty_cl(P, P, c + 16, dtype, fill=3.0)
+        prm = _params(dtype, (c, hw, hw), c, P, P, ks, k, k, s, s, p, p, act=act, flags=1, out_c_off=8, Cs=cs)
+        prm.x, prm.y, prm.bias = xd.data_ptr(), yd.data_ptr(), bd.data_ptr()
+        capi.check(L.pb_op_launch(kind, C.byref(prm), None, 0, None), "pool")
+        gu.sync()
+        got = gu.from_device_cl(yd, c + 16)
+        _assert_close(got[8:8 + c], ref.astype(np.float32), dtype)
+        assert (got[:8] == 3.0).all() and (got[8 + c:] == 3.0).all()
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
 def test_gap_dense_add_softmax(dtype):
     import torch
     L = capi.load()
