@@ -385,7 +385,8 @@ def test_input_layout_conversion(dtype):
 
 
 @pytest.mark.parametrize("dtype", [0, 1])
-@pytest.mark.parametrize("geom", [(3, 31, 29, 3, 3, 2, 0), (3, 30, 30, 7, 7, 2, 3), (1, 12, 12, 5, 5, 1, 2)])
+@pytest.mark.parametrize("geom", [(3, 31, 29, 3, 3, 2, 0), (3, 30, 30, 7, 7, 2, 3), (1, 12, 12, 5, 5, 1, 2), (3, 70, 75, 3, 3, 2, 0), (3, 64, 50, 7, 7, 2, 3),
+                                  (4, 41, 67, 3, 3, 1, 1), (3, 33, 33, 9, 9, 1, 4)])
 def test_input_patch_matrix(dtype, geom):
     """Stage 0 in its patch-matrix form: row (p, q) holds the stem convolution's receptive field,
     k = (r*S + s)*C + c, zeros outside the image and beyond R*S*C."""
@@ -415,9 +416,9 @@ def test_input_patch_matrix(dtype, geom):
 def _strip_blocks(P, Q, cs, dtype, stride):
     strip = 4 if stride == 1 else 2          # output pixels per thread of the strip kernel
     if dtype == 1:
-        # bf16: the shared-memory tile kernel takes over once its blocks fill the GPU twice (two blocks per SM)
+        # bf16: the shared-memory tile kernel takes over from 100 blocks on
         tiles = -(-cs // 64) * -(-Q // (8 * strip)) * -(-P // (13 if stride == 1 else 6))
-        if tiles >= 148 * 2 * 2:
+        if tiles >= 100:
             return tiles
     return -(-(P * (-(-Q // strip)) * (cs // gu.vec(dtype))) // 256)
 
