@@ -250,3 +250,27 @@ def test_algorithmic_work_matches_published_counts():
     assert abs(packer.inception_v3().macs() / 1e9 - 5.713) < 0.003
     assert abs(packer.resnet50().macs() / 1e9 - 4.089) < 0.003
     assert abs(packer.mobilenet_v2().macs() / 1e9 - 0.3006) < 0.001
+
+
+def test_pooling_branch_with_its_convolution_first_equals_the_original_order(oracle_lib):
+    """packer.pooled_pointwise writes relu(bn(conv1x1(avgpool3x3(x)))) as relu(avgpool3x3(conv1x1(x)) + bias).  With the
+    same weights and a non-zero bias both orders give the same tensor (fp32, 1e-5 of its range), borders included:
+    the average pooling counts its zero padding, so it is linear and commutes with the 1x1 convolution."""
+    eps = 1e-3
+    a = packer.Graph("a", (24, 9, 11), seed=7, precision=0, bias_std=0.3)
+    a.pooled_pointwise(a.input, 16, eps, "branch_pool")
+    b = packer.Graph("b", (24, 9, 11), seed=7, precision=0, bias_std=0.3)
+    y = b.avgpool(b.input, 3, 1, 1, True, name="avgpool")
+    b.conv(y, 16, 1, 1, 0, bn_eps=eps, name="branch_pool.conv")
+    # same seed, same order of draws: convolution weights first, then the bias
+    pa, pb_ = og.Pack(a.to_bytes()), og.Pack(b.to_bytes())
+    wa = pa.weights[pa.ops[0][18]: pa.ops[0][18] + 16 * 24]
+    wb = pb_.weights[pb_.ops[1][18]: pb_.ops[1][18] + 16 * 24]
+    np.testing.assert_array_equal(wa, wb)
+    np.testing.assert_array_equal(pa.weights[pa.ops[1][20]: pa.ops[1][20] + 16], pb_.weights[pb_.ops[1][20]: pb_.ops[1][20] + 16])
+    assert np.abs(pa.weights[pa.ops[1][20]: pa.ops[1][20] + 16]).max() > 0.05
+    x = np.random.default_rng(3).standard_normal((24, 9, 11), dtype=np.float32)
+    ya, yb = og.run(pa, x), og.run(pb_, x)
+    assert ya.shape == yb.shape == (16 * 9 * 11,)
+    assert float(np.abs(ya - yb).max()) <= 1e-5 * float(np.abs(yb).max())
+    assert (ya == 0).mean() > 0.1 and (ya > 0).mean() > 0.1        # the ReLU is at work
