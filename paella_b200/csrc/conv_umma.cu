@@ -1321,15 +1321,24 @@ bool use_tma_a() {
 // Widest output-channel tile of the TMA kernel.  A tile of N channels re-reads operand A once per tile,
 // so wide tiles cut the bytes an SM pulls; they also take 2 x 48 KB of pipeline and 256 TMEM columns
 // (two CTAs per SM instead of three) and halve the CTAs of a launch.  Measured (GPU us per request, 1 / 32 /
-// 64 requests in flight): Inception-v3 696 / 46.0 / 43.4 at 128 against 750 / 46.3 / 40.3 at 256; ResNet-50
-// 583 / 39.0 / 34.9 against 737 / 43.1 / 37.5: 128 is the default, PB_CONV_MAX_BN=256 selects the wide tile.
-int max_bn() {
-    static const int v = [] {
+// 64 requests in flight, one image per launch): Inception-v3 696 / 46.0 / 43.4 at 128 against 750 / 46.3 / 40.3 at
+// 256; ResNet-50 583 / 39.0 / 34.9 against 737 / 43.1 / 37.5; with 8 images per launch (gangs) and 96 requests in
+// flight 256 gives +3.7 % requests/s.  So the width follows the launch: 128 for a lone image, 256 for launches of at
+// least PB_CONV_WIDE_MIN_BATCH images (default 2: under Poisson arrivals near capacity, where gangs average 3-4
+// requests, the mix met its latency bound at 290k offered requests/s with 2 and not with 4; 0 = never wide).
+// PB_CONV_MAX_BN=128 / 256 fixes the width for every launch.
+int bn_limit(const pb_op_params* p) {
+    static const int fixed = [] {
         const char* e = getenv("PB_CONV_MAX_BN");
-        const int n = e ? atoi(e) : 128;
-        return n >= 256 ? 256 : 128;
+        return e ? (atoi(e) >= 256 ? 256 : 128) : 0;
     }();
-    return v;
+    static const int wide_from = [] {
+        const char* e = getenv("PB_CONV_WIDE_MIN_BATCH");
+        return e ? atoi(e) : 2;
+    }();
+    if (!use_tma_a()) return 128;
+    if (fixed) return fixed;
+    return (wide_from > 0 && (p->batch > 1 ? p->batch : 1) >= wide_from) ? 256 : 128;
 }
 
 // PB_CONV_PERSIST=1: model launches run the persistent kernel (a CTA walks several tiles).  Off by default.
@@ -1384,14 +1393,15 @@ struct Geometry {
     uint32_t tmem_cols, b_stage_bytes, smem_bytes, idesc;
 };
 
-Geometry geometry(const pb_op_params* p) {
+Geometry geometry(const pb_op_params* p, int bn_max = 0) {
     Geometry g;
+    if (bn_max <= 0) bn_max = bn_limit(p);
     g.cpt = ceil_div(p->Cs, kBK);
     g.Cp = g.cpt * kBK;
     g.nkb = p->R * p->S * g.cpt;
     g.Kdim_pad = g.nkb * kBK;
     g.Kp16 = round_up(p->K, 16);
-    g.n_tiles = ceil_div(g.Kp16, use_tma_a() ? max_bn() : 128);
+    g.n_tiles = ceil_div(g.Kp16, bn_max);
     g.BN = round_up(ceil_div(g.Kp16, g.n_tiles), 16);
     g.Kout_pad = g.n_tiles * g.BN;
     g.m_tiles = ceil_div(batch_of(p) * p->P * p->Q, kBM);
@@ -1465,9 +1475,12 @@ cudaError_t raise_smem_limits() {
 }  // namespace
 
 struct ConvUmmaPlan {
-    CUtensorMap tmap;
+    CUtensorMap tmap;        // weights [Kout_pad][Kdim_pad], boxes of g.BN rows (the width a launch of one image uses)
+    CUtensorMap tmap_wide;   // the same weights in boxes of BN_wide rows (launches of a gang)
     Geometry g;
+    int BN_wide;             // = g.BN when the layer has one column tile either way
     int device;
+    const CUtensorMap* map_for(int BN) const { return BN == g.BN ? &tmap : (BN == BN_wide ? &tmap_wide : nullptr); }
 };
 
 #ifdef PB_CONV_STATS
@@ -1535,7 +1548,9 @@ int conv_umma_info(const pb_op_params* p, pb_launch_info* out) {
 
 int64_t conv_umma_pack_weights(const pb_op_params* p, const float* w, void* dst) {
     if (!conv_umma_supported(p)) { set_error("conv_umma: unsupported convolution"); return PB_ERR_INVALID; }
-    const Geometry g = geometry(p);
+    pb_op_params one = *p;      // the layout does not depend on how many images a launch will carry
+    one.batch = 1;
+    const Geometry g = geometry(&one);
     const size_t n = (size_t)g.Kout_pad * g.Kdim_pad;
     if (dst) {
         memset(dst, 0, n * 2);
@@ -1631,10 +1646,21 @@ void conv_umma_xmap_destroy(ConvUmmaXMap* m) { delete m; }
 int conv_umma_plan_create(const pb_op_params* p, const void* w_dev, ConvUmmaPlan** out) {
     PB_REQUIRE(conv_umma_supported(p), "conv_umma: unsupported convolution");
     ConvUmmaPlan* plan = new ConvUmmaPlan();
-    plan->g = geometry(p);
+    pb_op_params one = *p;
+    one.batch = 1;
+    plan->g = geometry(&one);
     cudaGetDevice(&plan->device);
     int rc = make_tmap(plan->g, w_dev, &plan->tmap);
     if (rc != PB_OK) { delete plan; return rc; }
+    // The weights were packed for plan->g (rows padded to its column tiles); a wider tiling needs at most as many rows.
+    const Geometry gw = geometry(&one, 256);
+    plan->BN_wide = gw.BN;
+    plan->tmap_wide = plan->tmap;
+    if (gw.BN != plan->g.BN) {
+        if (gw.Kout_pad > plan->g.Kout_pad) { delete plan; set_error("conv_umma: wide tiling needs more weight rows than were packed"); return PB_ERR_INVALID; }
+        rc = make_tmap(gw, w_dev, &plan->tmap_wide);
+        if (rc != PB_OK) { delete plan; return rc; }
+    }
     // The shared-memory limit is a per-device function attribute: raise it once on every device used.
     static std::once_flag once[16];
     static cudaError_t attr_errs[16] = {};
@@ -1709,7 +1735,9 @@ int conv_umma_launch_planned(const ConvUmmaPlan* plan, const ConvUmmaXMap* xmap,
             if (rc != PB_OK) return rc;
             xmap = &local;
         }
-        const cudaError_t e = launch_pdl(conv_umma_tma_kernel, grid, g.smem_bytes, st, pdl, plan->tmap, xmap->map, a, g.stages, job_id, nf);
+        const CUtensorMap* wmap = plan->map_for(g.BN);
+        PB_REQUIRE(wmap != nullptr, "conv_umma: no weight map for a tile of %d channels", g.BN);
+        const cudaError_t e = launch_pdl(conv_umma_tma_kernel, grid, g.smem_bytes, st, pdl, *wmap, xmap->map, a, g.stages, job_id, nf);
         if (e != cudaSuccess) return cuda_fail(e, "launch of conv_umma_tma_kernel", __FILE__, __LINE__);
         return PB_OK;
     } else {
@@ -1784,7 +1812,9 @@ int conv_umma_multi_create(const ConvUmmaPlan* const* plans, const ConvUmmaXMap*
         Geometry g = geometry(params[i]);
         if (g.splits > 1 && (params[i]->scratch == nullptr || params[i]->scratch_bytes < g.scratch_bytes)) drop_split(&g);
         SubConv& sc = table[(size_t)i];
-        sc.tmap_w = plans[i]->tmap;
+        const CUtensorMap* wmap = plans[i]->map_for(g.BN);
+        if (!wmap) { delete m; set_error("conv_umma_multi_create: no weight map for a tile of %d channels", g.BN); return PB_ERR_INVALID; }
+        sc.tmap_w = *wmap;
         sc.tmap_x = xmaps[i]->map;
         const int rc = fill_args(plans[i], g, params[i], nullptr, &sc.a);
         if (rc != PB_OK) { delete m; return rc; }
