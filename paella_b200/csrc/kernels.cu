@@ -593,25 +593,25 @@ __global__ void __launch_bounds__(256, 2) window3_strip_kernel(OpArgs a, uint32_
 // (0 for sums and products, -inf for max), which leaves every partial result as it is: the additions per
 // output happen in the order of dwconv_kernel / pool_kernel (filter rows, then columns), so the results
 // are theirs bit for bit (finite filter values assumed).  bf16 only.
-constexpr int kRollStrip1 = 4, kRollStrip2 = 2;
+constexpr int kTileStrip1 = 4, kTileStrip2 = 2;
 __device__ __forceinline__ f2_t pair_of(uint32_t u) { return f2_pack(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u)); }
 __device__ __forceinline__ uint32_t bits_of(__nv_bfloat162 h) { return *reinterpret_cast<const uint32_t*>(&h); }
 __device__ __forceinline__ __nv_bfloat162 bf2_of(uint32_t u) { return *reinterpret_cast<const __nv_bfloat162*>(&u); }
 
 // What a thread keeps per (output, channel pair): fp32 pairs for sums, the bf16 pair itself for a maximum.
-template <int kMode> struct RollAcc { typedef f2_t type; };
-template <> struct RollAcc<kWinMax> { typedef uint32_t type; };
-template <int kMode> __device__ __forceinline__ typename RollAcc<kMode>::type roll_neutral() { return f2_pack(0.f, 0.f); }
-template <> __device__ __forceinline__ uint32_t roll_neutral<kWinMax>() { return 0xff80ff80u; }       // (-inf, -inf)
-template <int kMode> __device__ __forceinline__ typename RollAcc<kMode>::type roll_value(uint32_t raw) { return pair_of(raw); }
-template <> __device__ __forceinline__ uint32_t roll_value<kWinMax>(uint32_t raw) { return raw; }
-__device__ __forceinline__ f2_t roll_op(f2_t acc, f2_t x, f2_t w, bool dw) { return dw ? f2_fma(x, w, acc) : f2_add(acc, x); }
-__device__ __forceinline__ uint32_t roll_op(uint32_t acc, uint32_t x, f2_t, bool) { return bits_of(__hmax2(bf2_of(acc), bf2_of(x))); }
+template <int kMode> struct WinAcc { typedef f2_t type; };
+template <> struct WinAcc<kWinMax> { typedef uint32_t type; };
+template <int kMode> __device__ __forceinline__ typename WinAcc<kMode>::type win_neutral() { return f2_pack(0.f, 0.f); }
+template <> __device__ __forceinline__ uint32_t win_neutral<kWinMax>() { return 0xff80ff80u; }       // (-inf, -inf)
+template <int kMode> __device__ __forceinline__ typename WinAcc<kMode>::type win_value(uint32_t raw) { return pair_of(raw); }
+template <> __device__ __forceinline__ uint32_t win_value<kWinMax>(uint32_t raw) { return raw; }
+__device__ __forceinline__ f2_t win_step(f2_t acc, f2_t x, f2_t w, bool dw) { return dw ? f2_fma(x, w, acc) : f2_add(acc, x); }
+__device__ __forceinline__ uint32_t win_step(uint32_t acc, uint32_t x, f2_t, bool) { return bits_of(__hmax2(bf2_of(acc), bf2_of(x))); }
 
 // One finished output (two channels) -> bf16 pair.  kAct: 0 none, 1 ReLU, 2 ReLU6 (depthwise only).  div / inv: the
 // average pool's divisor and its reciprocal.
 template <int kMode, int kAct>
-__device__ __forceinline__ uint32_t roll_finish(f2_t acc, float b0, float b1, float div, float inv) {
+__device__ __forceinline__ uint32_t win_finish(f2_t acc, float b0, float b1, float div, float inv) {
     float v0, v1;
     f2_unpack(acc, v0, v1);
     if (kMode == kWinDw) {
@@ -628,7 +628,7 @@ __device__ __forceinline__ uint32_t roll_finish(f2_t acc, float b0, float b1, fl
     return bits_of(__floats2bfloat162_rn(v0, v1));
 }
 template <int kMode, int kAct>
-__device__ __forceinline__ uint32_t roll_finish(uint32_t acc, float, float, float, float) { return acc; }
+__device__ __forceinline__ uint32_t win_finish(uint32_t acc, float, float, float, float) { return acc; }
 
 // ---- 3x3 windows over large tensors, staged through shared memory ---------------------------------------
 // Reading the rows with 4-byte global loads spends a third of the instructions on addresses (every load needs
@@ -651,7 +651,7 @@ constexpr int kTileSlab = 64;                       // channels per block
 constexpr int kTileRows1 = PB_TILE_ROWS1, kTileRows2 = PB_TILE_ROWS2;      // output rows per block at stride 1 / 2
 
 template <int kStride> struct TileGeom {
-    static constexpr int kStrip = kStride == 1 ? kRollStrip1 : kRollStrip2;
+    static constexpr int kStrip = kStride == 1 ? kTileStrip1 : kTileStrip2;
     static constexpr int kRows = kStride == 1 ? kTileRows1 : kTileRows2;
     static constexpr int kOutCols = 8 * kStrip;
     static constexpr int kInCols = (kOutCols - 1) * kStride + 3;
@@ -664,7 +664,7 @@ __global__ void __launch_bounds__(256, PB_TILE_BLOCKS) window3_tile_kernel(OpArg
     PB_NOTIFY_START();
     typedef __nv_bfloat16 T;
     typedef TileGeom<kStride> G;
-    typedef typename RollAcc<kMode>::type Acc;
+    typedef typename WinAcc<kMode>::type Acc;
     constexpr int kStrip = G::kStrip, kCols = (kStrip - 1) * kStride + 3;
     constexpr bool kDw = kMode == kWinDw;
     extern __shared__ __align__(16) unsigned char s_tile[];
@@ -710,7 +710,7 @@ __global__ void __launch_bounds__(256, PB_TILE_BLOCKS) window3_tile_kernel(OpArg
     const int c0 = ch0 + lane * 2;
     const int q0 = q_tile + warp * kStrip;
     if (c0 < a.Cs && q0 < a.Q) {
-        const Acc neutral = roll_neutral<kMode>();
+        const Acc neutral = win_neutral<kMode>();
         f2_t w[3][3];
         float b0 = 0.f, b1 = 0.f;
 #pragma unroll
@@ -738,13 +738,13 @@ __global__ void __launch_bounds__(256, PB_TILE_BLOCKS) window3_tile_kernel(OpArg
 
         auto load_row = [&](int r, Acc (&xv)[kCols]) {
 #pragma unroll
-            for (int col = 0; col < kCols; ++col) xv[col] = roll_value<kMode>(s_row[r * kRowWords + col * (kTileSlab / 2)]);
+            for (int col = 0; col < kCols; ++col) xv[col] = win_value<kMode>(s_row[r * kRowWords + col * (kTileSlab / 2)]);
         };
         auto row_into = [&](Acc (&acc)[kStrip], const Acc (&xv)[kCols], int r) {
 #pragma unroll
             for (int t = 0; t < kStrip; ++t)
 #pragma unroll
-                for (int s2 = 0; s2 < 3; ++s2) acc[t] = roll_op(acc[t], xv[t * kStride + s2], w[r][s2], kDw);
+                for (int s2 = 0; s2 < 3; ++s2) acc[t] = win_step(acc[t], xv[t * kStride + s2], w[r][s2], kDw);
         };
         const bool full = nt == kStrip && keep == 0xffffffffu;      // every output of the strip and both channels exist
         // one output row of the strip; ACT and FULL are literals so that the loop body carries no test of them
@@ -758,7 +758,7 @@ __global__ void __launch_bounds__(256, PB_TILE_BLOCKS) window3_tile_kernel(OpArg
                 if (cnt != 9) { div = (float)(cnt > 0 ? cnt : 1); inv = 1.f / div; }                                             \
                 else { div = 9.f; inv = inv9; }                                                                                  \
             }                                                                                                                    \
-            const uint32_t o = roll_finish<kMode, ACT>(acc[t], b0, b1, div, inv);                                                \
+            const uint32_t o = win_finish<kMode, ACT>(acc[t], b0, b1, div, inv);                                                \
             *reinterpret_cast<uint32_t*>(yrow + (size_t)t * a.Ks) = (FULL) ? o : (o & keep);                                     \
         }                                                                                                                        \
     } while (0)

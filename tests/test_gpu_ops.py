@@ -468,13 +468,13 @@ def test_pools_large_tensor_use_strips(dtype, s, pad, hw, include_pad):
         assert (full[:8] == 3.0).all() and (full[8 + c:] == 3.0).all()     # channels outside the slice untouched
 
 
-ROLL_CASES = [
+TILE_CASES = [
     # C, H, W, stride, pad: ragged strips and row chunks, fewer rows than one chunk, channel counts off the vector width
     (64, 70, 70, 1, 1), (20, 33, 41, 1, 1), (128, 15, 130, 1, 0), (64, 71, 69, 2, 1), (24, 37, 35, 2, 0), (8, 5, 300, 1, 1), (16, 100, 6, 2, 1),
 ]
 
 
-@pytest.mark.parametrize("case", ROLL_CASES)
+@pytest.mark.parametrize("case", TILE_CASES)
 def test_tiled_window_kernel_equals_the_strip_kernels_bit_for_bit(case, monkeypatch):
     """The 3x3 kernel for large tensors (window staged in shared memory, a thread walks down the output rows, each
     input row read and converted once) against the kernels it replaces, same launch with PB_WINDOW_TILE=0: depthwise convolution with bias and
