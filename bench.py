@@ -772,7 +772,7 @@ def main():
         # above it brackets the knee).  Every point is a full K-step run timed like the others. ----
         def sweep(resident, cap_rps, tag):
             best = None
-            for frac in (1.05, 1.0, 0.95, 0.9, 0.85, 0.8, 0.7, 0.5):
+            for frac in (1.05, 1.0, 0.975, 0.95, 0.925, 0.9, 0.85, 0.8, 0.7, 0.5):
                 offered = frac * cap_rps
                 x = leg(f"poisson_{tag}_{frac}", resident, 1e6 * n_gpus * args.replicas_per_gpu / offered, args.steps, seed=7)
                 sweep_pts.append(dict(point(x, offered), inputs=tag, fraction_of_closed_loop=frac))
