@@ -48,6 +48,51 @@ def test_conv2d_matches_torch(oracle_lib, case, act):
     np.testing.assert_allclose(got, ref.numpy(), rtol=1e-4, atol=1e-4)
 
 
+DILATED_CASES = [
+    # C, H, W, K, R, S, sh, sw, ph, pw, groups, (dil_h, dil_w): the receptive-field block of the face detector and odd ones
+    (16, 30, 40, 16, 3, 3, 1, 1, 2, 2, 1, (2, 2)), (16, 30, 40, 16, 3, 3, 1, 1, 3, 3, 1, (3, 3)), (16, 30, 40, 16, 3, 3, 1, 1, 5, 5, 1, (5, 5)),
+    (6, 19, 23, 8, 3, 3, 2, 2, 2, 1, 1, (2, 1)), (8, 14, 14, 8, 3, 3, 1, 1, 0, 0, 2, (2, 3)), (3, 9, 9, 4, 2, 2, 1, 1, 0, 0, 1, (4, 4)),
+]
+
+
+@pytest.mark.parametrize("case", DILATED_CASES)
+def test_dilated_conv2d_matches_torch(oracle_lib, case):
+    C, H, W, K, R, S, sh, sw, ph, pw, g, dil = case
+    x = RNG.standard_normal((C, H, W), dtype=np.float32)
+    w = RNG.standard_normal((K, C // g, R, S), dtype=np.float32)
+    b = RNG.standard_normal(K, dtype=np.float32)
+    ref = torch.relu(F.conv2d(_t(x)[None], _t(w), _t(b), (sh, sw), (ph, pw), dil, g)[0]).numpy()
+    got = og.conv2d(x, w, b, (sh, sw), (ph, pw), g, 1, dilation=dil)
+    assert got.shape == ref.shape
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-4)
+
+
+def test_detection_head_matches_its_formula(oracle_lib):
+    """orc_detect against the published post-processing written with torch tensors: softmax over the two class logits,
+    centre = l[:2] * 0.1 * prior_wh + prior_centre, size = exp(l[2:] * 0.2) * prior_wh, corners = centre -+ size / 2;
+    priors and head in (row, column, anchor) order, the head's channels (anchor, class) then (anchor, coordinate)."""
+    A, H, W, first, n_total = 3, 5, 7, 11, 200
+    head = RNG.standard_normal((6 * A, H, W), dtype=np.float32)
+    priors = RNG.random((H * W * A, 4), dtype=np.float32)
+    out = np.full(n_total * 6, -7.0, np.float32)
+    og.detect(head, A, priors, 0.1, 0.2, first, n_total, out)
+    t = _t(head)
+    conf = t[:2 * A].permute(1, 2, 0).reshape(-1, 2)
+    loc = t[2 * A:].permute(1, 2, 0).reshape(-1, 4)
+    pr = _t(priors)
+    scores = torch.softmax(conf, dim=1).numpy()
+    centre = loc[:, :2] * 0.1 * pr[:, 2:] + pr[:, :2]
+    size = torch.exp(loc[:, 2:] * 0.2) * pr[:, 2:]
+    boxes = torch.cat([centre - size / 2, centre + size / 2], dim=1).numpy()
+    n = H * W * A
+    np.testing.assert_allclose(out[first * 2:(first + n) * 2].reshape(n, 2), scores, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(out[n_total * 2 + first * 4: n_total * 2 + (first + n) * 4].reshape(n, 4), boxes, rtol=1e-5, atol=1e-6)
+    untouched = np.ones(n_total * 6, bool)
+    untouched[first * 2:(first + n) * 2] = False
+    untouched[n_total * 2 + first * 4: n_total * 2 + (first + n) * 4] = False
+    assert (out[untouched] == -7.0).all()
+
+
 def test_conv2d_writes_channel_slice(oracle_lib):
     x = RNG.standard_normal((4, 9, 9), dtype=np.float32)
     w = RNG.standard_normal((6, 4, 3, 3), dtype=np.float32)
