@@ -37,6 +37,11 @@ class SmResources {
                left_.blocks >= nb && left_.tmem_cols >= (int)d.tmem_cols_per_block * nb;
     }
     bool is_full() const { return left_.regs <= 0 || left_.smem <= 0 || left_.threads <= 0 || left_.blocks <= 0; }
+    // Nothing is acquired: no kernel stage is in flight.
+    bool idle() const {
+        return left_.regs == max_.regs && left_.smem == max_.smem && left_.threads == max_.threads && left_.blocks == max_.blocks &&
+               left_.tmem_cols == max_.tmem_cols;
+    }
     const SmTotals& left() const { return left_; }
     const SmTotals& total() const { return max_; }
     double occupancy() const;

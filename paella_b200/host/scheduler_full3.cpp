@@ -246,7 +246,10 @@ class SchedulerFull3 final : public Scheduler {
             if (!is_mem && free_notifiers_.empty()) break;      // cannot happen while every kernel reports each block once
             bool unfit = false;
             if (!is_mem && !gpu_resources_.job_fits(job)) {
-                if (num_outstanding_kernels_ >= (int)max_num_outstanding_kernels_) break;
+                // A stage larger than the whole GPU (a gang's, or with no over-subscription allowed) never fits: with
+                // nothing in flight waiting cannot help, so it goes as an over-subscribed stage (the reference would
+                // wait for ever, scheduler_full3.cpp:380-392).
+                if (num_outstanding_kernels_ >= (int)max_num_outstanding_kernels_ && !gpu_resources_.idle()) break;
                 ++num_outstanding_kernels_;
                 job->set_unfit();
                 unfit = true;

@@ -224,3 +224,25 @@ def test_stage_watchdog_gives_up_a_stage_that_never_ends():
     assert all(s.done[100 + i] == 0 for i in range(12))
     assert stuck_id not in [e[0] for e in s.log if e[7] >= 100]
     s.close()
+
+
+def test_a_tight_occupancy_gate_makes_waiting_requests_leave_as_a_gang():
+    """The GPU of this test holds one and a half stages of TWO at a time.  With no over-subscribed stage allowed, the
+    first request is dispatched alone; three more arrive one after the other while it runs, do not fit, wait in the
+    queue - and when the first request is through they leave together as ONE gang.  With a wide-open gate (64
+    over-subscribed stages) the same arrivals are dispatched one by one the moment they arrive.  This is the mechanism
+    behind the benchmark's gate of 18 stages: under load, requests meet in the queue."""
+    TWO = [dict(mem=False, blocks=100), dict(mem=False, blocks=100)]
+    tight = (150 * 256 * 32, 148 * 233472, 150 * 256, 148 * 32)      # registers, shared memory, threads, block slots
+    for extra, want in ((0, [1, 3]), (64, [1, 1, 1, 1])):
+        s = Sim([TWO], streams=16, extra=extra, totals=tight, gang=4, cap=8)
+        s.submit(0, 1)
+        s.run(until=0.5)                       # dispatched; its first stage is in flight (block records come later)
+        assert [e[6] for e in s.log if e[2] == 0] == [1]
+        for k, t in ((2, 3.0), (3, 6.0), (4, 9.0)):
+            s.submit(0, k)
+            s.run(until=t)
+        s.run()
+        assert len(s.done) == 4 and all(v == 0 for v in s.done.values())
+        assert sorted(e[6] for e in s.log if e[2] == 0) == want, (extra, s.log)
+        s.close()
